@@ -1,0 +1,220 @@
+"""CPU oracle for the contrastive-loss path.  TEST INFRASTRUCTURE ONLY.
+
+Nothing in the shipped package imports this module: it is the checker used by
+``tests/``, by ``__graft_entry__.smoke()`` and by the CPU-baseline leg of
+``bench.py``.  The product path is the CUDA library and fails without it.
+
+Two independent statements of the same mathematics live here:
+
+* ``clip_dense`` / ``lit_dense`` - the dense PyTorch formulation
+  ``0.5 * (CE(x y^T / T, diag) + CE(y x^T / T, diag))`` (LiT: one direction)
+  differentiated by autograd.  This is the parity reference.
+* ``clip_closed_form`` / ``lit_closed_form`` - a numpy restatement of the
+  reference's tile algorithm without tiles: fixed-max exponentials, row and
+  column sums, loss from the diagonal, and the explicit gradient formulas
+  (reference clip_loss.py:56, 59-64, 115-124, 206-211, 235-236, 252-254;
+  lit_loss.py:59, 62, 113-120, 199-203, 227).
+
+Pinning: the reference ships no tests or golden vectors.  The closed form is
+pinned against the reference's own Triton kernels run on CPU through Triton's
+interpreter (``tests/golden/make_golden.py`` writes ``tests/golden/*.npz``),
+and against the dense formulation, in ``tests/test_oracle.py``.
+"""
+from __future__ import annotations
+
+import math
+
+import numpy as np
+import torch
+import torch.nn.functional as F
+
+LOG2E = 1.4426950408889634
+
+
+# --------------------------------------------------------------------------- #
+# dense formulation (autograd)
+# --------------------------------------------------------------------------- #
+def _prep(t: torch.Tensor, dtype: torch.dtype, requires_grad: bool) -> torch.Tensor:
+    return t.detach().to("cpu").to(dtype).clone().requires_grad_(requires_grad)
+
+
+def grad_multiplier(batch: int, temperature: float, stable: bool) -> float:
+    """Stable variants keep the loss and multiply every gradient by sqrt(B*T).
+
+    Reference clip_loss.py:299 uses sqrt(B/T)/B where the plain variant uses
+    1/(B*T) (clip_loss.py:182, 235); the ratio is sqrt(B*T).
+    """
+    return math.sqrt(batch * temperature) if stable else 1.0
+
+
+def clip_dense(image, text, temperature=0.07, normalized_inputs=False, stable=False,
+               grad_output=1.0, dtype=torch.float64):
+    """Dense CLIP loss and gradients w.r.t. the module inputs.
+
+    Mirrors MemoryEfficientCLIPLoss.forward (clip_loss.py:265-273): optional
+    F.normalize(dim=1) on both inputs, then the symmetric cross entropy.
+    Returns (loss, d_image, d_text) as CPU tensors of ``dtype``.
+    """
+    x = _prep(image, dtype, True)
+    y = _prep(text, dtype, True)
+    xn, yn = (x, y) if normalized_inputs else (F.normalize(x, dim=1), F.normalize(y, dim=1))
+    logits = xn @ yn.t() / temperature
+    labels = torch.arange(x.shape[0])
+    loss = 0.5 * (F.cross_entropy(logits, labels) + F.cross_entropy(logits.t(), labels))
+    mult = grad_multiplier(x.shape[0], temperature, stable) * grad_output
+    gx, gy = torch.autograd.grad(loss, (x, y))
+    return loss.detach(), gx * mult, gy * mult
+
+
+def lit_dense(text, image, temperature=0.07, normalized_inputs=False, stable=False,
+              grad_output=1.0, dtype=torch.float64):
+    """Dense LiT loss (text -> image direction only), gradient for text only.
+
+    Mirrors MemoryEfficientLiTLoss.forward(text_features, image_features)
+    (lit_loss.py:256-263); the image tower is frozen (lit_loss.py:247).
+    """
+    x = _prep(text, dtype, True)
+    y = _prep(image, dtype, False)
+    xn, yn = (x, y) if normalized_inputs else (F.normalize(x, dim=1), F.normalize(y, dim=1))
+    logits = xn @ yn.t() / temperature
+    loss = F.cross_entropy(logits, torch.arange(x.shape[0]))
+    mult = grad_multiplier(x.shape[0], temperature, stable) * grad_output
+    (gx,) = torch.autograd.grad(loss, (x,))
+    return loss.detach(), gx * mult
+
+
+# --------------------------------------------------------------------------- #
+# closed form: the reference's algorithm without the tiling
+# --------------------------------------------------------------------------- #
+def sum_exp(xn: np.ndarray, yn: np.ndarray, temperature: float):
+    """E = exp2(k*S - k), k = log2(e)/T; row sums r and column sums c.
+
+    Reference clip_loss.py:53-60 (forward tile) with the padding columns left
+    out, i.e. what the reference computes when B is a multiple of 128.
+    """
+    k = LOG2E / temperature
+    e = np.exp2(xn @ yn.T * k - k)
+    return e, e.sum(axis=1), e.sum(axis=0)
+
+
+def clip_closed_form(xn, yn, temperature=0.07, stable=False, grad_output=1.0):
+    """Loss and gradients w.r.t. *normalised* inputs, numpy float64.
+
+    loss: clip_loss.py:206-211.  G: clip_loss.py:121-124.  Gradient init and
+    accumulation: clip_loss.py:235-236, 148-156.  grad_output: :252-254.
+    """
+    xn = np.asarray(xn, dtype=np.float64)
+    yn = np.asarray(yn, dtype=np.float64)
+    b = xn.shape[0]
+    k = LOG2E / temperature
+    e, r, c = sum_exp(xn, yn, temperature)
+    sv = np.einsum("bi,bi->b", xn, yn) * k - k
+    loss = -(np.log(np.exp2(sv) / r) + np.log(np.exp2(sv) / c)).mean() / 2.0
+    scale = math.sqrt(b / temperature) / b if stable else 1.0 / (temperature * b)
+    g = (e / r[:, None] + e / c[None, :]) * (scale / 2.0)
+    dx = (g @ yn - yn * scale) * grad_output
+    dy = (g.T @ xn - xn * scale) * grad_output
+    return {"loss": loss, "row_sum": r, "col_sum": c, "dx": dx, "dy": dy}
+
+
+def lit_closed_form(xn, yn, temperature=0.07, stable=False, grad_output=1.0):
+    """LiT: X = text, Y = image; row sums only (lit_loss.py:59-62, 118-120, 199-203, 227)."""
+    xn = np.asarray(xn, dtype=np.float64)
+    yn = np.asarray(yn, dtype=np.float64)
+    b = xn.shape[0]
+    k = LOG2E / temperature
+    e, r, _ = sum_exp(xn, yn, temperature)
+    sv = np.einsum("bi,bi->b", xn, yn) * k - k
+    loss = -np.log(np.exp2(sv) / r).mean()
+    scale = math.sqrt(b / temperature) / b if stable else 1.0 / (temperature * b)
+    g = e / r[:, None] * scale
+    dx = (g @ yn - yn * scale) * grad_output
+    return {"loss": loss, "row_sum": r, "dx": dx}
+
+
+def normalize_np(x: np.ndarray, eps: float = 1e-12):
+    """F.normalize(dim=1): x / max(||x||, eps).  Returns (x_hat, 1/max(||x||, eps))."""
+    x = np.asarray(x, dtype=np.float64)
+    inv = 1.0 / np.maximum(np.sqrt((x * x).sum(axis=1)), eps)
+    return x * inv[:, None], inv
+
+
+def normalize_jacobian_np(x_hat: np.ndarray, inv_norm: np.ndarray, g_hat: np.ndarray):
+    """Backward of F.normalize: dx = (g - x_hat * (x_hat . g)) / ||x||."""
+    dot = (x_hat * g_hat).sum(axis=1, keepdims=True)
+    return (g_hat - x_hat * dot) * inv_norm[:, None]
+
+
+# --------------------------------------------------------------------------- #
+# streaming form for batches whose B x B matrix does not fit in host memory
+# --------------------------------------------------------------------------- #
+def clip_streaming(xn: torch.Tensor, yn: torch.Tensor, temperature: float, sample_rows,
+                   block: int = 4096, lit: bool = False, dtype=torch.float32):
+    """Row-blocked evaluation: exact r, c, loss, and exact gradient rows for
+    ``sample_rows`` of d_x and d_y.  O(block * B) memory.  Same formulas as the
+    closed form above; used for the ring-distributed configurations.
+    """
+    xn = xn.to(dtype)
+    yn = yn.to(dtype)
+    b = xn.shape[0]
+    k = LOG2E / temperature
+    r = torch.zeros(b, dtype=torch.float64)
+    c = torch.zeros(b, dtype=torch.float64)
+    for i0 in range(0, b, block):
+        e = torch.exp2((xn[i0:i0 + block] @ yn.t()) * k - k).double()
+        r[i0:i0 + block] = e.sum(dim=1)
+        c += e.sum(dim=0)
+    sv = ((xn.double() * yn.double()).sum(dim=1) * k - k) * math.log(2.0)
+    if lit:
+        loss = (torch.log(r) - sv).mean()
+    else:
+        loss = 0.5 * (torch.log(r) + torch.log(c) - 2 * sv).mean()
+    scale = 1.0 / (temperature * b)
+    rows = torch.as_tensor(sample_rows, dtype=torch.long)
+    # d_x rows: G[rows, :] @ yn - yn[rows] * scale
+    e = torch.exp2((xn[rows] @ yn.t()) * k - k).double()
+    if lit:
+        g = e / r[rows, None] * scale
+    else:
+        g = (e / r[rows, None] + e / c[None, :]) * (scale / 2)
+    dx_rows = g @ yn.double() - yn[rows].double() * scale
+    out = {"loss": loss, "row_sum": r, "col_sum": c, "rows": rows, "dx_rows": dx_rows}
+    if not lit:
+        et = torch.exp2((yn[rows] @ xn.t()) * k - k).double()      # E^T rows: [s, B]
+        gt = (et / r[None, :] + et / c[rows, None]) * (scale / 2)
+        out["dy_rows"] = gt @ xn.double() - xn[rows].double() * scale
+    return out
+
+
+# --------------------------------------------------------------------------- #
+# tolerances (loss 1e-3 relative; gradients 1e-2 max-relative, cosine >= 0.9999)
+# --------------------------------------------------------------------------- #
+LOSS_RTOL = 1e-3
+GRAD_MAX_REL = 1e-2
+GRAD_COS_MIN = 0.9999
+
+
+def loss_rel_err(got, ref) -> float:
+    got = float(got)
+    ref = float(ref)
+    return abs(got - ref) / max(abs(ref), 1e-30)
+
+
+def grad_errors(got, ref):
+    """(max|got-ref| / max|ref|, cosine similarity) over the whole tensor."""
+    g = torch.as_tensor(np.asarray(got.detach().cpu().double()) if isinstance(got, torch.Tensor) else got,
+                        dtype=torch.float64).flatten()
+    r = torch.as_tensor(np.asarray(ref.detach().cpu().double()) if isinstance(ref, torch.Tensor) else ref,
+                        dtype=torch.float64).flatten()
+    max_rel = float((g - r).abs().max() / r.abs().max().clamp_min(1e-300))
+    cos = float(torch.dot(g, r) / (g.norm() * r.norm()).clamp_min(1e-300))
+    return max_rel, cos
+
+
+def assert_parity(loss, loss_ref, grads, grads_ref, what=""):
+    le = loss_rel_err(loss, loss_ref)
+    assert le <= LOSS_RTOL, f"{what}: loss rel err {le:.3e} > {LOSS_RTOL}"
+    for name, (g, r) in zip(("grad0", "grad1"), zip(grads, grads_ref)):
+        mr, cs = grad_errors(g, r)
+        assert mr <= GRAD_MAX_REL, f"{what}: {name} max-rel {mr:.3e} > {GRAD_MAX_REL}"
+        assert cs >= GRAD_COS_MIN, f"{what}: {name} cosine {cs:.6f} < {GRAD_COS_MIN}"
