@@ -1,0 +1,158 @@
+/*
+ * meclip.h - C ABI of libmeclip_sm100.so: the CLIP / LiT contrastive-loss path
+ * (forward sums + loss, recompute backward, L2-normalise and its Jacobian) as
+ * hand-written sm_100a kernels.
+ *
+ * Conventions
+ *  - Plain C types only.  Every pointer is a DEVICE pointer unless it says host.
+ *  - The library never allocates or frees device memory: the caller owns every
+ *    buffer, including the workspace (size from meclip_grad_workspace_bytes).
+ *  - Every call is asynchronous on `stream` (a cudaStream_t passed as void*),
+ *    holds no thread-local state and may be made from any host thread (PyTorch
+ *    runs backward on its autograd thread).
+ *  - Return value: MECLIP_OK or an error code; meclip_last_error() gives text.
+ *    Nothing here calls exit/abort or throws.
+ *  - Matrices are row-major with a leading dimension in ELEMENTS (ld >= D).
+ *    Operand matrices of the tile kernels are bf16; D must be a multiple of 8
+ *    and base pointers / row pitches 16-byte aligned (TMA requirements).
+ *  - `status` is a device int the kernels set non-zero when a bounded wait inside
+ *    a kernel ran out (MECLIP_ETIMEOUT); read it with meclip_read_status().
+ *
+ * Reference = b0nce/MemoryEfficientCLIP (clip_loss.py, lit_loss.py).
+ */
+#ifndef MECLIP_H
+#define MECLIP_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum meclip_status {
+    MECLIP_OK = 0,
+    MECLIP_EINVAL = 1,       /* null / misaligned pointer, bad size, bad enum */
+    MECLIP_ENOSPC = 2,       /* workspace too small */
+    MECLIP_ECUDA = 3,        /* a CUDA runtime / driver call failed */
+    MECLIP_ETIMEOUT = 4,     /* a bounded in-kernel wait expired (from status word) */
+    MECLIP_EUNSUPPORTED = 5  /* not an sm_100 device, or driver lacks TMA entry point */
+};
+
+enum meclip_kind { MECLIP_CLIP = 0, MECLIP_LIT = 1 };
+enum meclip_dtype { MECLIP_BF16 = 0, MECLIP_F32 = 1 };
+
+/* How a gradient output buffer is written. */
+enum meclip_out_mode {
+    MECLIP_STORE_BF16 = 0,  /* out = value, bf16 */
+    MECLIP_STORE_F32 = 1,   /* out = value, fp32 */
+    MECLIP_ACCUM_F32 = 2    /* out += value, fp32 (ring steps, caller zeroes first) */
+};
+
+int meclip_version(void);
+const char* meclip_status_string(int code);
+/* Copies the calling thread's process-wide last error text (host buffer). */
+int meclip_last_error(char* buf, size_t buf_len);
+/* Synchronises `stream`, copies *status to the host and maps non-zero to MECLIP_ETIMEOUT. */
+int meclip_read_status(const int* status, void* stream);
+
+/*
+ * x_hat = x / max(||x||_2, 1e-12) per row, written as bf16, plus inv_norm[i] =
+ * 1/max(||x_i||, 1e-12).  With normalize == 0 only the dtype conversion to bf16
+ * is done (inv_norm may be NULL).  Replaces F.normalize(dim=1) at
+ * clip_loss.py:266-268 / lit_loss.py:257-259 and the fp32 -> bf16 staging.
+ */
+int meclip_normalize_fwd(const void* x, int x_dtype, int64_t rows, int64_t d, int64_t ldx, int normalize,
+                         void* x_hat_bf16, int64_t ldh, float* inv_norm, void* stream);
+
+/*
+ * Jacobian of the row normalisation: dx = (g - x_hat * (x_hat . g)) * inv_norm.
+ * Replaces the autograd node PyTorch records for F.normalize
+ * (clip_loss.py:266-268).  g is fp32 or bf16; dx takes dx_dtype.
+ */
+int meclip_normalize_bwd(const void* g, int g_dtype, int64_t ldg, const void* x_hat_bf16, int64_t ldh,
+                         const float* inv_norm, int64_t rows, int64_t d, void* dx, int dx_dtype, int64_t lddx,
+                         void* stream);
+
+/*
+ * Forward tile pass over one rows x cols block of the similarity matrix
+ * S = X Y^T (X: rows x d, Y: cols x d, both bf16, L2-normalised):
+ *   E_ij = exp(S_ij/T - 1/T);  row_sum[i] += sum_j E_ij;  col_sum[j] += sum_i E_ij
+ *   diag_s[i] = S_ij for the column j with row_off + i == col_off + j, if in range.
+ * The sums ACCUMULATE (fp32 atomics): zero them before the first block.
+ * col_sum may be NULL (LiT).  Out-of-range rows/columns of edge tiles are
+ * masked, so any rows/cols >= 1 is exact.  row_off / col_off are the global
+ * indices of X row 0 and Y row 0 (0 on one GPU; shard offsets in the ring).
+ * Replaces clip_sum_exp_kernel (clip_loss.py:9-64), lit_sum_exp_kernel
+ * (lit_loss.py:9-62) and the diagonal einsum (clip_loss.py:206).
+ */
+int meclip_sum_exp(int kind, const void* x_bf16, const void* y_bf16, int64_t rows, int64_t cols, int64_t d,
+                   int64_t ldx, int64_t ldy, float temperature, int64_t row_off, int64_t col_off, float* row_sum,
+                   float* col_sum, float* diag_s, int* status, void* stream);
+
+/*
+ * loss_out (+)= scale * sum_i [ w*(log row_sum[i] + log col_sum[i]) - (diag_s[i] - 1)/T ],
+ * w = 1/2 and both logs for CLIP; w = 1 and only the row log for LiT.
+ * scale = 1/B gives the mean.  Deterministic single-block reduction.
+ * Replaces the loss epilogue at clip_loss.py:206-211 / lit_loss.py:199-203.
+ */
+int meclip_loss_finalize(int kind, const float* row_sum, const float* col_sum, const float* diag_s, int64_t n,
+                         float temperature, float scale, int accumulate, float* loss_out, void* stream);
+
+/* Workspace for meclip_grad on a rows x cols block (bytes; 256-byte aligned base expected). */
+size_t meclip_grad_workspace_bytes(int64_t rows, int64_t cols, int64_t d);
+
+/*
+ * Backward over one rows x cols block.  Recomputes E from X, Y and the saved
+ * sums, forms the coefficient matrix
+ *   CLIP: G_ij = g * (E_ij/row_sum[i] + E_ij/col_sum[j]) / 2,   LiT: G_ij = g * E_ij/row_sum[i]
+ *   G_ii -= g   (the "-Y/(B T)" initialisation of clip_loss.py:235-236 folded in)
+ * with g = grad_scale * (*grad_out), panel by panel in bf16, and contracts it:
+ *   dX (rows x d) = G Y,     dY (cols x d) = G^T X   (dY NULL for LiT).
+ * grad_scale is 1/(B*T) (clip_loss.py:182) or 1/sqrt(B*T) for the Stable
+ * variants (clip_loss.py:299); B is the GLOBAL batch.  grad_out is a device
+ * scalar (no host sync, unlike clip_loss.py:252).  Deterministic: no atomics.
+ * Replaces clip_grad_kernel (clip_loss.py:67-156), lit_grad_kernel
+ * (lit_loss.py:65-148) and the gradient glue at clip_loss.py:235-254.
+ */
+int meclip_grad(int kind, const void* x_bf16, const void* y_bf16, int64_t rows, int64_t cols, int64_t d, int64_t ldx,
+                int64_t ldy, float temperature, int64_t row_off, int64_t col_off, const float* row_sum,
+                const float* col_sum, const float* grad_out, float grad_scale, void* dx, int dx_mode, int64_t lddx,
+                void* dy, int dy_mode, int64_t lddy, void* workspace, size_t workspace_bytes, int* status,
+                void* stream);
+
+/*
+ * One-call forward for a whole batch on one GPU: zeroes the sums, runs
+ * meclip_sum_exp with offsets 0 and meclip_loss_finalize with scale 1/B.
+ * Mirrors MemoryEfficient{CLIP,LiT}LossNormed.forward (clip_loss.py:160-213,
+ * lit_loss.py:152-205): X = first argument of apply(), Y = second.
+ * row_sum, col_sum (NULL for LiT), diag_s: B floats each, kept for backward.
+ */
+int meclip_loss_forward(int kind, const void* x_bf16, const void* y_bf16, int64_t batch, int64_t d, int64_t ldx,
+                        int64_t ldy, float temperature, float* row_sum, float* col_sum, float* diag_s, float* loss_out,
+                        int* status, void* stream);
+
+/*
+ * One-call backward for a whole batch on one GPU (offsets 0, square block).
+ * Mirrors MemoryEfficient{CLIP,LiT}LossNormed.backward (clip_loss.py:215-256,
+ * lit_loss.py:207-247); grad_scale selects plain or Stable scaling.
+ */
+int meclip_loss_backward(int kind, const void* x_bf16, const void* y_bf16, int64_t batch, int64_t d, int64_t ldx,
+                         int64_t ldy, float temperature, const float* row_sum, const float* col_sum,
+                         const float* grad_out, float grad_scale, void* dx, int dx_mode, int64_t lddx, void* dy,
+                         int dy_mode, int64_t lddy, void* workspace, size_t workspace_bytes, int* status, void* stream);
+
+/*
+ * Test hook: C (m x n, fp32, ldc) = A * B^T-style contraction through the same
+ * tcgen05 mainloop the loss kernels use.  a_mn_major == 0: A is m x k row-major
+ * (K contiguous); 1: A is stored k x m row-major (M contiguous).  Same for B
+ * with n.  Has no counterpart in the reference; used by the GPU unit tests.
+ */
+int meclip_debug_gemm(const void* a_bf16, int64_t lda, int a_mn_major, const void* b_bf16, int64_t ldb, int b_mn_major,
+                      int64_t m, int64_t n, int64_t k, int tile_n, float* c, int64_t ldc, const float* c_in,
+                      int* status, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MECLIP_H */

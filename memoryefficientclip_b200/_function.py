@@ -1,0 +1,71 @@
+"""The one autograd node behind all eight public classes.
+
+forward:  [normalise | convert to bf16] -> tile pass for the sums -> loss
+backward: coefficient panels + two contractions -> [normalise Jacobian]
+Saved for backward: the bf16 operands, the fp32 row/column sums and, when the node
+normalises, the inverse norms - O(B*D) like the reference (clip_loss.py:199).
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _lib, ops
+
+
+class ContrastiveLossFn(torch.autograd.Function):
+    """apply(x, y, temperature, kind, stable, normalize) -> 0-dim fp32 loss."""
+
+    @staticmethod
+    def run_forward(ctx, x, y, temperature, kind, stable, normalize):
+        assert x.is_cuda and y.is_cuda                      # reference clip_loss.py:166
+        assert x.shape == y.shape                           # reference clip_loss.py:167
+        ops._check_matrix(x, "first input")
+        ops._check_matrix(y, "second input")
+        assert x.device == y.device
+        if normalize:
+            x_hat, inv_x = ops.normalize_fwd(x, True)
+            y_hat, inv_y = ops.normalize_fwd(y, True)
+        else:
+            x_hat, inv_x = ops.as_operand(x), None
+            y_hat, inv_y = ops.as_operand(y), None
+        loss, row_sum, col_sum, _diag = ops.loss_forward(kind, x_hat, y_hat, temperature)
+        saved = [x_hat, y_hat, row_sum]
+        if col_sum is not None:
+            saved.append(col_sum)
+        if normalize:
+            saved += [inv_x, inv_y]
+        ctx.save_for_backward(*saved)
+        ctx.meclip = (float(temperature), kind, bool(stable), bool(normalize), x.dtype, y.dtype)
+        return loss
+
+    @staticmethod
+    def run_backward(ctx, grad_output):
+        temperature, kind, stable, normalize, x_dtype, y_dtype = ctx.meclip
+        saved = list(ctx.saved_tensors)
+        x_hat, y_hat, row_sum = saved[:3]
+        rest = saved[3:]
+        col_sum = rest.pop(0) if kind == _lib.CLIP else None
+        inv_x, inv_y = (rest if normalize else (None, None))
+        batch = x_hat.shape[0]
+        # grad_output stays on the device: no host sync (the reference compares it to 1.0 on the host)
+        go = grad_output.detach().to(device=x_hat.device, dtype=torch.float32).reshape(1).contiguous()
+        scale = ops.grad_scale(batch, temperature, stable)
+        want_dy = kind == _lib.CLIP
+        # with the fused Jacobian the contraction output stays fp32 until the Jacobian rounds once
+        dx_t = torch.float32 if normalize else x_dtype
+        dy_t = torch.float32 if normalize else y_dtype
+        dx, dy = ops.loss_backward(kind, x_hat, y_hat, temperature, row_sum, col_sum, go, scale, dx_t, dy_t)
+        if normalize:
+            dx = ops.normalize_bwd(dx, x_hat, inv_x, x_dtype)
+            if want_dy:
+                dy = ops.normalize_bwd(dy, y_hat, inv_y, y_dtype)
+        return dx, (dy if want_dy else None)
+
+    @staticmethod
+    def forward(ctx, x, y, temperature, kind, stable, normalize):
+        return ContrastiveLossFn.run_forward(ctx, x, y, temperature, kind, stable, normalize)
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        dx, dy = ContrastiveLossFn.run_backward(ctx, grad_output)
+        return dx, dy, None, None, None, None

@@ -1,0 +1,86 @@
+"""ctypes binding of libmeclip_sm100.so (the C ABI in include/meclip.h).
+
+There is no fallback: if the shared library is missing this module raises, and
+every operation of the package fails with it.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import threading
+from ctypes import c_char_p, c_float, c_int, c_int64, c_size_t, c_void_p
+
+PKG_DIR = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(PKG_DIR, "libmeclip_sm100.so")
+
+OK, EINVAL, ENOSPC, ECUDA, ETIMEOUT, EUNSUPPORTED = range(6)
+CLIP, LIT = 0, 1
+BF16, F32 = 0, 1
+STORE_BF16, STORE_F32, ACCUM_F32 = 0, 1, 2
+
+# name -> (restype, argtypes); mirrors include/meclip.h declaration by declaration
+SIGNATURES = {
+    "meclip_version": (c_int, []),
+    "meclip_status_string": (c_char_p, [c_int]),
+    "meclip_last_error": (c_int, [c_char_p, c_size_t]),
+    "meclip_read_status": (c_int, [c_void_p, c_void_p]),
+    "meclip_normalize_fwd": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_int, c_void_p, c_int64, c_void_p,
+                                     c_void_p]),
+    "meclip_normalize_bwd": (c_int, [c_void_p, c_int, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int64,
+                                     c_void_p, c_int, c_int64, c_void_p]),
+    "meclip_sum_exp": (c_int, [c_int, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64, c_float,
+                               c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "meclip_loss_finalize": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_int64, c_float, c_float, c_int,
+                                     c_void_p, c_void_p]),
+    "meclip_grad_workspace_bytes": (c_size_t, [c_int64, c_int64, c_int64]),
+    "meclip_grad": (c_int, [c_int, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64, c_float, c_int64,
+                            c_int64, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_int, c_int64, c_void_p,
+                            c_int, c_int64, c_void_p, c_size_t, c_void_p, c_void_p]),
+    "meclip_loss_forward": (c_int, [c_int, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_float,
+                                    c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "meclip_loss_backward": (c_int, [c_int, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_float,
+                                     c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_int, c_int64, c_void_p,
+                                     c_int, c_int64, c_void_p, c_size_t, c_void_p, c_void_p]),
+    "meclip_debug_gemm": (c_int, [c_void_p, c_int64, c_int, c_void_p, c_int64, c_int, c_int64, c_int64, c_int64,
+                                  c_int, c_void_p, c_int64, c_void_p, c_void_p, c_void_p]),
+}
+
+_lock = threading.Lock()
+_lib = None
+
+
+class MeclipError(RuntimeError):
+    def __init__(self, code: int, message: str):
+        super().__init__(f"libmeclip_sm100 error {code}: {message}")
+        self.code = code
+
+
+def load() -> ctypes.CDLL:
+    """Load the library once; raise if it has not been built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    with _lock:
+        if _lib is None:
+            if not os.path.exists(LIB_PATH):
+                raise RuntimeError(
+                    f"{LIB_PATH} is missing. The CUDA extension is the only implementation of this package; build it "
+                    "with `python -m memoryefficientclip_b200.build` (needs nvcc with sm_100a support).")
+            lib = ctypes.CDLL(LIB_PATH)
+            for name, (res, args) in SIGNATURES.items():
+                fn = getattr(lib, name)     # AttributeError if the symbol is not exported
+                fn.restype = res
+                fn.argtypes = args
+            _lib = lib
+    return _lib
+
+
+def last_error() -> str:
+    buf = ctypes.create_string_buffer(1024)
+    load().meclip_last_error(buf, len(buf))
+    return buf.value.decode("utf-8", "replace")
+
+
+def check(code: int) -> None:
+    if code != OK:
+        raise MeclipError(code, last_error() or load().meclip_status_string(code).decode())

@@ -1,0 +1,608 @@
+// libmeclip_sm100.so: host launchers and the C ABI declared in include/meclip.h.
+// Device code: umma_gemm.cuh (tcgen05 tile kernels) and the row kernels below.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <cmath>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <string>
+
+#include "../../include/meclip.h"
+#include "umma_gemm.cuh"
+
+namespace meclip {
+
+// ------------------------------------------------------------------------------------
+// error bookkeeping
+// ------------------------------------------------------------------------------------
+static std::mutex g_err_mutex;
+static std::string g_last_error;
+
+static int fail(int code, const char* fmt, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof(buf), fmt, ap);
+    va_end(ap);
+    std::lock_guard<std::mutex> lock(g_err_mutex);
+    g_last_error = buf;
+    return code;
+}
+
+#define MECLIP_CUDA(expr)                                                                         \
+    do {                                                                                          \
+        cudaError_t e__ = (expr);                                                                 \
+        if (e__ != cudaSuccess) return fail(MECLIP_ECUDA, "%s: %s", #expr, cudaGetErrorString(e__)); \
+    } while (0)
+
+static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+static inline size_t round_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+// ------------------------------------------------------------------------------------
+// row kernels: one warp per row, 16-byte vector accesses (HBM-bound passes)
+// ------------------------------------------------------------------------------------
+__device__ __forceinline__ void load8(const float* p, float (&v)[8]) {
+    const float4 a = *reinterpret_cast<const float4*>(p);
+    const float4 b = *reinterpret_cast<const float4*>(p + 4);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+__device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&v)[8]) {
+    const uint4 u = *reinterpret_cast<const uint4*>(p);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 f = __bfloat1622float2(h[i]);
+        v[2 * i] = f.x;
+        v[2 * i + 1] = f.y;
+    }
+}
+__device__ __forceinline__ void store8(float* p, const float (&v)[8]) {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+    *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
+}
+__device__ __forceinline__ void store8(__nv_bfloat16* p, const float (&v)[8]) {
+    uint4 u;
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+    *reinterpret_cast<uint4*>(p) = u;
+}
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o >= 1; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+static constexpr int ROW_KERNEL_THREADS = 256;
+
+// x_hat = x / max(||x||, 1e-12) as bf16 (+ inv_norm); normalize == 0: dtype conversion only.
+template <typename TIn>
+__global__ void __launch_bounds__(ROW_KERNEL_THREADS)
+normalize_fwd_kernel(const TIn* __restrict__ x, long long ldx, long long rows, int d, int normalize,
+                     __nv_bfloat16* __restrict__ out, long long ldh, float* __restrict__ inv_norm) {
+    const long long row = (long long)blockIdx.x * (ROW_KERNEL_THREADS / 32) + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (row >= rows) return;
+    const TIn* xr = x + row * ldx;
+    float inv = 1.f;
+    if (normalize) {
+        float ss = 0.f;
+        for (int c = lane * 8; c < d; c += 256) {
+            float v[8];
+            load8(xr + c, v);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) ss = fmaf(v[i], v[i], ss);
+        }
+        ss = warp_sum(ss);
+        inv = 1.f / fmaxf(sqrtf(ss), 1e-12f);
+        if (lane == 0 && inv_norm != nullptr) inv_norm[row] = inv;
+    }
+    __nv_bfloat16* orow = out + row * ldh;
+    for (int c = lane * 8; c < d; c += 256) {
+        float v[8];
+        load8(xr + c, v);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] *= inv;
+        store8(orow + c, v);
+    }
+}
+
+// dx = (g - x_hat (x_hat . g)) * inv_norm
+template <typename TG, typename TOut>
+__global__ void __launch_bounds__(ROW_KERNEL_THREADS)
+normalize_bwd_kernel(const TG* __restrict__ g, long long ldg, const __nv_bfloat16* __restrict__ xh, long long ldh,
+                     const float* __restrict__ inv_norm, long long rows, int d, TOut* __restrict__ dx,
+                     long long lddx) {
+    const long long row = (long long)blockIdx.x * (ROW_KERNEL_THREADS / 32) + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (row >= rows) return;
+    const TG* gr = g + row * ldg;
+    const __nv_bfloat16* hr = xh + row * ldh;
+    float dot = 0.f;
+    for (int c = lane * 8; c < d; c += 256) {
+        float gv[8], hv[8];
+        load8(gr + c, gv);
+        load8(hr + c, hv);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) dot = fmaf(gv[i], hv[i], dot);
+    }
+    dot = warp_sum(dot);
+    const float inv = inv_norm[row];
+    TOut* orow = dx + row * lddx;
+    for (int c = lane * 8; c < d; c += 256) {
+        float gv[8], hv[8];
+        load8(gr + c, gv);
+        load8(hr + c, hv);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) gv[i] = (gv[i] - hv[i] * dot) * inv;
+        store8(orow + c, gv);
+    }
+}
+
+// loss (+)= scale * sum_i [ w (log r_i + log c_i) - (s_ii - 1)/T ]: one block, fixed order.
+__global__ void __launch_bounds__(1024)
+loss_finalize_kernel(const float* __restrict__ r, const float* __restrict__ c, const float* __restrict__ diag,
+                     long long n, float inv_t, float scale, int accumulate, float* __restrict__ loss) {
+    __shared__ double part[1024];
+    double acc = 0.0;
+    for (long long i = threadIdx.x; i < n; i += 1024) {
+        double t = log((double)r[i]);
+        if (c != nullptr) t = 0.5 * (t + log((double)c[i]));
+        acc += t - ((double)diag[i] - 1.0) * (double)inv_t;
+    }
+    part[threadIdx.x] = acc;
+    __syncthreads();
+    for (int s = 512; s >= 1; s >>= 1) {
+        if ((int)threadIdx.x < s) part[threadIdx.x] += part[threadIdx.x + s];
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) {
+        const float v = (float)(part[0] * (double)scale);
+        *loss = accumulate ? *loss + v : v;
+    }
+}
+
+// ------------------------------------------------------------------------------------
+// TMA descriptors
+// ------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+    static EncodeTiledFn fn = []() -> EncodeTiledFn {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess) return nullptr;
+        if (q != cudaDriverEntryPointSuccess) return nullptr;
+        return reinterpret_cast<EncodeTiledFn>(p);
+    }();
+    return fn;
+}
+
+// bf16 matrix, row-major: `outer` rows of `inner` contiguous elements, pitch ld elements.
+// Box = box_inner (64 elements = 128 bytes, swizzled) x box_outer rows.
+static int make_tmap(CUtensorMap* tm, const void* base, long long inner, long long outer, long long ld, int box_inner,
+                     int box_outer) {
+    EncodeTiledFn enc = get_encode_fn();
+    if (enc == nullptr) return fail(MECLIP_EUNSUPPORTED, "cuTensorMapEncodeTiled not available from this driver");
+    cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)outer};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {(cuuint32_t)box_inner, (cuuint32_t)box_outer};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        return fail(MECLIP_ECUDA, "cuTensorMapEncodeTiled failed (%d) inner=%lld outer=%lld ld=%lld box=%dx%d", (int)r,
+                    inner, outer, ld, box_inner, box_outer);
+    return MECLIP_OK;
+}
+
+static int sm_count() {
+    static int cached[64] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    if (cached[dev] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        cached[dev] = n;
+    }
+    return cached[dev];
+}
+
+static int check_device() {
+    static int verdict[64] = {0};   // 0 unknown, 1 ok, -1 unsupported
+    int dev = 0;
+    MECLIP_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return fail(MECLIP_EUNSUPPORTED, "device index %d out of range", dev);
+    if (verdict[dev] == 0) {
+        int major = 0;
+        MECLIP_CUDA(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev));
+        verdict[dev] = (major == 10) ? 1 : -1;
+    }
+    if (verdict[dev] < 0) return fail(MECLIP_EUNSUPPORTED, "device %d is not sm_100: these kernels are sm_100a only", dev);
+    return MECLIP_OK;
+}
+
+// Tile width for an N extent: least padding first, then the wider tile.
+static int pick_bn(long long n) {
+    const int cand[4] = {256, 192, 128, 64};
+    int best = 64;
+    long long best_pad = -1;
+    for (int i = 0; i < 4; ++i) {
+        const long long tiles = (n + cand[i] - 1) / cand[i];
+        const long long pad = tiles * cand[i] - n;
+        if (best_pad < 0 || pad < best_pad) { best_pad = pad; best = cand[i]; }
+    }
+    return best;
+}
+
+// ------------------------------------------------------------------------------------
+// GEMM launcher
+// ------------------------------------------------------------------------------------
+struct Operand {
+    const void* ptr;
+    long long ld;      // elements
+    bool mn_major;     // false: [extent rows][K contiguous]; true: [K rows][extent contiguous]
+};
+
+template <int EPI, bool A_MN, bool B_MN>
+static int launch_gemm_t(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, cudaStream_t stream) {
+    auto kern = umma_gemm_kernel<EPI, A_MN, B_MN>;
+    MECLIP_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GEMM_SMEM_BYTES));
+    const int tiles = p.num_m_tiles * p.num_n_tiles;
+    const int grid = tiles < sm_count() ? tiles : sm_count();
+    kern<<<grid, GEMM_THREADS, GEMM_SMEM_BYTES, stream>>>(ta, tb, p);
+    MECLIP_CUDA(cudaGetLastError());
+    return MECLIP_OK;
+}
+
+static int launch_gemm(int epi, const Operand& a, const Operand& b, long long m, long long n, long long k, int bn,
+                       GemmParams p, cudaStream_t stream) {
+    if (m < 1 || n < 1 || k < 1) return fail(MECLIP_EINVAL, "gemm extents must be >= 1 (m=%lld n=%lld k=%lld)", m, n, k);
+    if (m > 0x7fffffffLL || n > 0x7fffffffLL || k > 0x7fffffffLL) return fail(MECLIP_EINVAL, "gemm extent exceeds 2^31");
+    if (bn < 32 || bn > MAX_BN || bn % 32 != 0 || (b.mn_major && bn % 64 != 0))
+        return fail(MECLIP_EINVAL, "tile width %d not supported", bn);
+    if (!aligned16(a.ptr) || !aligned16(b.ptr) || a.ld % 8 != 0 || b.ld % 8 != 0)
+        return fail(MECLIP_EINVAL, "operands must be 16-byte aligned with pitches that are multiples of 8 elements");
+    CUtensorMap ta, tb;
+    int rc;
+    if (a.mn_major) rc = make_tmap(&ta, a.ptr, m, k, a.ld, 64, BK);
+    else            rc = make_tmap(&ta, a.ptr, k, m, a.ld, BK, BM);
+    if (rc) return rc;
+    if (b.mn_major) rc = make_tmap(&tb, b.ptr, n, k, b.ld, 64, BK);
+    else            rc = make_tmap(&tb, b.ptr, k, n, b.ld, BK, bn);
+    if (rc) return rc;
+    p.m = (int)m; p.n = (int)n; p.k = (int)k; p.bn = bn;
+    p.num_m_tiles = (int)((m + BM - 1) / BM);
+    p.num_n_tiles = (int)((n + bn - 1) / bn);
+    p.k_steps = (int)((k + BK - 1) / BK);
+    p.group_m = 16;
+    p.idesc = umma_idesc_bf16(BM, bn, a.mn_major ? 1 : 0, b.mn_major ? 1 : 0);
+    if ((long long)p.num_m_tiles * p.num_n_tiles > 0x7fffffffLL) return fail(MECLIP_EINVAL, "too many tiles");
+#define MECLIP_DISPATCH(E)                                                                          \
+    if (epi == E) {                                                                                 \
+        if (!a.mn_major && !b.mn_major) return launch_gemm_t<E, false, false>(ta, tb, p, stream);   \
+        if (!a.mn_major && b.mn_major) return launch_gemm_t<E, false, true>(ta, tb, p, stream);     \
+        if (a.mn_major && b.mn_major) return launch_gemm_t<E, true, true>(ta, tb, p, stream);       \
+        return launch_gemm_t<E, true, false>(ta, tb, p, stream);                                    \
+    }
+    if (epi == EPI_SUMS) return launch_gemm_t<EPI_SUMS, false, false>(ta, tb, p, stream);
+    if (epi == EPI_COEF) return launch_gemm_t<EPI_COEF, false, false>(ta, tb, p, stream);
+    MECLIP_DISPATCH(EPI_OUT)
+#undef MECLIP_DISPATCH
+    return fail(MECLIP_EINVAL, "unknown epilogue %d", epi);
+}
+
+// ------------------------------------------------------------------------------------
+// backward blocking
+// ------------------------------------------------------------------------------------
+static constexpr long long ROW_BLOCK = 32768;                  // rows of G formed per block
+static constexpr long long PANEL_BYTES = 512ll << 20;          // bf16 coefficient panel budget
+
+struct GradPlan {
+    long long row_block, panel_w, ldg;
+    long long n_row_blocks, n_panels;
+    size_t g_bytes, dx_bytes, dy_bytes;
+};
+
+static GradPlan plan_grad(long long rows, long long cols, long long d) {
+    GradPlan g;
+    g.row_block = rows < ROW_BLOCK ? rows : ROW_BLOCK;
+    long long w = PANEL_BYTES / (g.row_block * 2) / 256 * 256;
+    if (w < 256) w = 256;
+    if (w > 32768) w = 32768;
+    if (w > cols) w = cols;
+    g.panel_w = w;
+    g.ldg = (long long)round_up((size_t)w, 64);
+    g.n_row_blocks = (rows + g.row_block - 1) / g.row_block;
+    g.n_panels = (cols + w - 1) / w;
+    g.g_bytes = round_up((size_t)g.row_block * g.ldg * 2, 256);
+    g.dx_bytes = g.n_panels > 1 ? round_up((size_t)g.row_block * d * 4, 256) : 0;
+    g.dy_bytes = g.n_row_blocks > 1 ? round_up((size_t)cols * d * 4, 256) : 0;
+    return g;
+}
+
+static int check_out_mode(int mode) { return mode == MECLIP_STORE_BF16 || mode == MECLIP_STORE_F32 || mode == MECLIP_ACCUM_F32; }
+
+}  // namespace meclip
+
+using namespace meclip;
+
+// ------------------------------------------------------------------------------------
+// C ABI
+// ------------------------------------------------------------------------------------
+extern "C" {
+
+int meclip_version(void) { return 100; }
+
+const char* meclip_status_string(int code) {
+    switch (code) {
+        case MECLIP_OK: return "ok";
+        case MECLIP_EINVAL: return "invalid argument";
+        case MECLIP_ENOSPC: return "workspace too small";
+        case MECLIP_ECUDA: return "CUDA error";
+        case MECLIP_ETIMEOUT: return "bounded wait inside a kernel expired";
+        case MECLIP_EUNSUPPORTED: return "unsupported device or driver";
+        default: return "unknown status";
+    }
+}
+
+int meclip_last_error(char* buf, size_t buf_len) {
+    if (buf == nullptr || buf_len == 0) return MECLIP_EINVAL;
+    std::lock_guard<std::mutex> lock(g_err_mutex);
+    std::strncpy(buf, g_last_error.c_str(), buf_len - 1);
+    buf[buf_len - 1] = '\0';
+    return MECLIP_OK;
+}
+
+int meclip_read_status(const int* status, void* stream) {
+    if (status == nullptr) return fail(MECLIP_EINVAL, "status pointer is null");
+    int host = 0;
+    MECLIP_CUDA(cudaMemcpyAsync(&host, status, sizeof(int), cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+    MECLIP_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
+    if (host != 0) return fail(MECLIP_ETIMEOUT, "a kernel gave up waiting on a barrier (status word %d)", host);
+    return MECLIP_OK;
+}
+
+int meclip_normalize_fwd(const void* x, int x_dtype, int64_t rows, int64_t d, int64_t ldx, int normalize,
+                         void* x_hat_bf16, int64_t ldh, float* inv_norm, void* stream) {
+    if (x == nullptr || x_hat_bf16 == nullptr) return fail(MECLIP_EINVAL, "normalize_fwd: null pointer");
+    if (rows < 1 || d < 8 || d % 8 != 0 || ldx < d || ldh < d) return fail(MECLIP_EINVAL, "normalize_fwd: need rows >= 1, d a multiple of 8, ld >= d");
+    if (!aligned16(x) || !aligned16(x_hat_bf16) || ldx % 8 != 0 || ldh % 8 != 0)
+        return fail(MECLIP_EINVAL, "normalize_fwd: pointers must be 16-byte aligned and pitches multiples of 8");
+    if (normalize && inv_norm == nullptr) return fail(MECLIP_EINVAL, "normalize_fwd: inv_norm is null");
+    const int wpb = ROW_KERNEL_THREADS / 32;
+    const unsigned grid = (unsigned)((rows + wpb - 1) / wpb);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (x_dtype == MECLIP_F32)
+        normalize_fwd_kernel<float><<<grid, ROW_KERNEL_THREADS, 0, s>>>((const float*)x, ldx, rows, (int)d, normalize, (__nv_bfloat16*)x_hat_bf16, ldh, inv_norm);
+    else if (x_dtype == MECLIP_BF16)
+        normalize_fwd_kernel<__nv_bfloat16><<<grid, ROW_KERNEL_THREADS, 0, s>>>((const __nv_bfloat16*)x, ldx, rows, (int)d, normalize, (__nv_bfloat16*)x_hat_bf16, ldh, inv_norm);
+    else
+        return fail(MECLIP_EINVAL, "normalize_fwd: bad dtype %d", x_dtype);
+    MECLIP_CUDA(cudaGetLastError());
+    return MECLIP_OK;
+}
+
+int meclip_normalize_bwd(const void* g, int g_dtype, int64_t ldg, const void* x_hat_bf16, int64_t ldh,
+                         const float* inv_norm, int64_t rows, int64_t d, void* dx, int dx_dtype, int64_t lddx,
+                         void* stream) {
+    if (g == nullptr || x_hat_bf16 == nullptr || inv_norm == nullptr || dx == nullptr)
+        return fail(MECLIP_EINVAL, "normalize_bwd: null pointer");
+    if (rows < 1 || d < 8 || d % 8 != 0 || ldg < d || ldh < d || lddx < d)
+        return fail(MECLIP_EINVAL, "normalize_bwd: need rows >= 1, d a multiple of 8, ld >= d");
+    if (!aligned16(g) || !aligned16(x_hat_bf16) || !aligned16(dx) || ldg % 8 != 0 || ldh % 8 != 0 || lddx % 8 != 0)
+        return fail(MECLIP_EINVAL, "normalize_bwd: pointers must be 16-byte aligned and pitches multiples of 8");
+    const int wpb = ROW_KERNEL_THREADS / 32;
+    const unsigned grid = (unsigned)((rows + wpb - 1) / wpb);
+    cudaStream_t s = (cudaStream_t)stream;
+    const __nv_bfloat16* xh = (const __nv_bfloat16*)x_hat_bf16;
+    if (g_dtype == MECLIP_F32 && dx_dtype == MECLIP_F32)
+        normalize_bwd_kernel<float, float><<<grid, ROW_KERNEL_THREADS, 0, s>>>((const float*)g, ldg, xh, ldh, inv_norm, rows, (int)d, (float*)dx, lddx);
+    else if (g_dtype == MECLIP_F32 && dx_dtype == MECLIP_BF16)
+        normalize_bwd_kernel<float, __nv_bfloat16><<<grid, ROW_KERNEL_THREADS, 0, s>>>((const float*)g, ldg, xh, ldh, inv_norm, rows, (int)d, (__nv_bfloat16*)dx, lddx);
+    else if (g_dtype == MECLIP_BF16 && dx_dtype == MECLIP_F32)
+        normalize_bwd_kernel<__nv_bfloat16, float><<<grid, ROW_KERNEL_THREADS, 0, s>>>((const __nv_bfloat16*)g, ldg, xh, ldh, inv_norm, rows, (int)d, (float*)dx, lddx);
+    else if (g_dtype == MECLIP_BF16 && dx_dtype == MECLIP_BF16)
+        normalize_bwd_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, ROW_KERNEL_THREADS, 0, s>>>((const __nv_bfloat16*)g, ldg, xh, ldh, inv_norm, rows, (int)d, (__nv_bfloat16*)dx, lddx);
+    else
+        return fail(MECLIP_EINVAL, "normalize_bwd: bad dtype");
+    MECLIP_CUDA(cudaGetLastError());
+    return MECLIP_OK;
+}
+
+int meclip_sum_exp(int kind, const void* x_bf16, const void* y_bf16, int64_t rows, int64_t cols, int64_t d,
+                   int64_t ldx, int64_t ldy, float temperature, int64_t row_off, int64_t col_off, float* row_sum,
+                   float* col_sum, float* diag_s, int* status, void* stream) {
+    if (kind != MECLIP_CLIP && kind != MECLIP_LIT) return fail(MECLIP_EINVAL, "sum_exp: bad kind %d", kind);
+    if (x_bf16 == nullptr || y_bf16 == nullptr || row_sum == nullptr || diag_s == nullptr)
+        return fail(MECLIP_EINVAL, "sum_exp: null pointer");
+    if (kind == MECLIP_CLIP && col_sum == nullptr) return fail(MECLIP_EINVAL, "sum_exp: CLIP needs col_sum");
+    if (rows < 1 || cols < 1 || d < 8 || d % 8 != 0 || ldx < d || ldy < d)
+        return fail(MECLIP_EINVAL, "sum_exp: need rows, cols >= 1, d a multiple of 8 (got %lld), ld >= d", (long long)d);
+    if (!(temperature > 0.f)) return fail(MECLIP_EINVAL, "sum_exp: temperature must be positive");
+    int rc = check_device();
+    if (rc) return rc;
+    GemmParams p;
+    std::memset(&p, 0, sizeof(p));
+    p.k2 = 1.4426950408889634f / temperature;
+    p.diag_shift = (long long)row_off - (long long)col_off;
+    p.row_sum = row_sum;
+    p.col_sum = (kind == MECLIP_CLIP) ? col_sum : nullptr;
+    p.diag = diag_s;
+    p.status = status;
+    Operand a{x_bf16, ldx, false}, b{y_bf16, ldy, false};
+    return launch_gemm(EPI_SUMS, a, b, rows, cols, d, pick_bn(cols), p, (cudaStream_t)stream);
+}
+
+int meclip_loss_finalize(int kind, const float* row_sum, const float* col_sum, const float* diag_s, int64_t n,
+                         float temperature, float scale, int accumulate, float* loss_out, void* stream) {
+    if (kind != MECLIP_CLIP && kind != MECLIP_LIT) return fail(MECLIP_EINVAL, "loss_finalize: bad kind %d", kind);
+    if (row_sum == nullptr || diag_s == nullptr || loss_out == nullptr || n < 1 || !(temperature > 0.f))
+        return fail(MECLIP_EINVAL, "loss_finalize: bad argument");
+    if (kind == MECLIP_CLIP && col_sum == nullptr) return fail(MECLIP_EINVAL, "loss_finalize: CLIP needs col_sum");
+    loss_finalize_kernel<<<1, 1024, 0, (cudaStream_t)stream>>>(row_sum, kind == MECLIP_CLIP ? col_sum : nullptr, diag_s, n,
+                                                               1.f / temperature, scale, accumulate, loss_out);
+    MECLIP_CUDA(cudaGetLastError());
+    return MECLIP_OK;
+}
+
+size_t meclip_grad_workspace_bytes(int64_t rows, int64_t cols, int64_t d) {
+    if (rows < 1 || cols < 1 || d < 1) return 0;
+    const GradPlan g = plan_grad(rows, cols, d);
+    return g.g_bytes + g.dx_bytes + g.dy_bytes + 256;
+}
+
+int meclip_grad(int kind, const void* x_bf16, const void* y_bf16, int64_t rows, int64_t cols, int64_t d, int64_t ldx,
+                int64_t ldy, float temperature, int64_t row_off, int64_t col_off, const float* row_sum,
+                const float* col_sum, const float* grad_out, float grad_scale, void* dx, int dx_mode, int64_t lddx,
+                void* dy, int dy_mode, int64_t lddy, void* workspace, size_t workspace_bytes, int* status,
+                void* stream) {
+    if (kind != MECLIP_CLIP && kind != MECLIP_LIT) return fail(MECLIP_EINVAL, "grad: bad kind %d", kind);
+    if (x_bf16 == nullptr || y_bf16 == nullptr || row_sum == nullptr || dx == nullptr || workspace == nullptr)
+        return fail(MECLIP_EINVAL, "grad: null pointer");
+    if (kind == MECLIP_CLIP && (col_sum == nullptr || dy == nullptr)) return fail(MECLIP_EINVAL, "grad: CLIP needs col_sum and dy");
+    if (rows < 1 || cols < 1 || d < 8 || d % 8 != 0 || ldx < d || ldy < d || lddx < d || (dy != nullptr && lddy < d))
+        return fail(MECLIP_EINVAL, "grad: need rows, cols >= 1, d a multiple of 8, ld >= d");
+    if (!check_out_mode(dx_mode) || (dy != nullptr && !check_out_mode(dy_mode))) return fail(MECLIP_EINVAL, "grad: bad output mode");
+    if (!aligned16(dx) || lddx % 8 != 0 || (dy != nullptr && (!aligned16(dy) || lddy % 8 != 0)))
+        return fail(MECLIP_EINVAL, "grad: outputs must be 16-byte aligned with pitches multiples of 8");
+    if ((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0) return fail(MECLIP_EINVAL, "grad: workspace must be 256-byte aligned");
+    if (!(temperature > 0.f)) return fail(MECLIP_EINVAL, "grad: temperature must be positive");
+    int rc = check_device();
+    if (rc) return rc;
+    const GradPlan plan = plan_grad(rows, cols, d);
+    if (workspace_bytes < plan.g_bytes + plan.dx_bytes + plan.dy_bytes)
+        return fail(MECLIP_ENOSPC, "grad: workspace %zu < %zu bytes", workspace_bytes, plan.g_bytes + plan.dx_bytes + plan.dy_bytes);
+    cudaStream_t s = (cudaStream_t)stream;
+    const bool clip = (kind == MECLIP_CLIP);
+    uint8_t* ws = reinterpret_cast<uint8_t*>(workspace);
+    __nv_bfloat16* gpanel = reinterpret_cast<__nv_bfloat16*>(ws);
+    float* dx_scratch = reinterpret_cast<float*>(ws + plan.g_bytes);
+    float* dy_scratch = reinterpret_cast<float*>(ws + plan.g_bytes + plan.dx_bytes);
+    const __nv_bfloat16* X = reinterpret_cast<const __nv_bfloat16*>(x_bf16);
+    const __nv_bfloat16* Y = reinterpret_cast<const __nv_bfloat16*>(y_bf16);
+    const int bn_d = pick_bn(d);
+    const size_t dx_elt = dx_mode == MECLIP_STORE_BF16 ? 2 : 4;
+    const size_t dy_elt = dy_mode == MECLIP_STORE_BF16 ? 2 : 4;
+
+    for (long long rb = 0; rb < plan.n_row_blocks; ++rb) {
+        const long long r0 = rb * plan.row_block;
+        const long long nr = (rows - r0) < plan.row_block ? (rows - r0) : plan.row_block;
+        for (long long cp = 0; cp < plan.n_panels; ++cp) {
+            const long long c0 = cp * plan.panel_w;
+            const long long nc = (cols - c0) < plan.panel_w ? (cols - c0) : plan.panel_w;
+            // (1) coefficient panel G [nr x nc] = epi(X[r0:] Y[c0:]^T)
+            {
+                GemmParams p;
+                std::memset(&p, 0, sizeof(p));
+                p.k2 = 1.4426950408889634f / temperature;
+                p.diag_shift = ((long long)row_off + r0) - ((long long)col_off + c0);
+                p.r = row_sum + r0;
+                p.c = clip ? col_sum + c0 : nullptr;
+                p.grad_out = grad_out;
+                p.coef = clip ? 0.5f * grad_scale : grad_scale;
+                p.dcoef = grad_scale;
+                p.g = gpanel;
+                p.ldg = plan.ldg;
+                p.status = status;
+                Operand a{X + r0 * ldx, ldx, false}, b{Y + c0 * ldy, ldy, false};
+                rc = launch_gemm(EPI_COEF, a, b, nr, nc, d, pick_bn(nc), p, s);
+                if (rc) return rc;
+            }
+            // (2) dX[r0:] (+)= G Y[c0:]          M = nr, N = d, K = nc; A = G (K contiguous), B = Y (N contiguous)
+            {
+                GemmParams p;
+                std::memset(&p, 0, sizeof(p));
+                p.status = status;
+                uint8_t* user = reinterpret_cast<uint8_t*>(dx) + (size_t)r0 * lddx * dx_elt;
+                if (dx_mode == MECLIP_ACCUM_F32) {
+                    p.acc_in = reinterpret_cast<const float*>(user); p.ld_acc = lddx;
+                    p.out = user; p.ld_out = lddx; p.out_bf16 = 0;
+                } else if (plan.n_panels == 1) {
+                    p.out = user; p.ld_out = lddx; p.out_bf16 = (dx_mode == MECLIP_STORE_BF16);
+                } else {
+                    if (cp > 0) { p.acc_in = dx_scratch; p.ld_acc = d; }
+                    if (cp == plan.n_panels - 1) { p.out = user; p.ld_out = lddx; p.out_bf16 = (dx_mode == MECLIP_STORE_BF16); }
+                    else { p.out = dx_scratch; p.ld_out = d; p.out_bf16 = 0; }
+                }
+                Operand a{gpanel, plan.ldg, false}, b{Y + c0 * ldy, ldy, true};
+                rc = launch_gemm(EPI_OUT, a, b, nr, d, nc, bn_d, p, s);
+                if (rc) return rc;
+            }
+            // (3) dY[c0:] (+)= G^T X[r0:]        M = nc, N = d, K = nr; A = G^T (M contiguous), B = X (N contiguous)
+            if (clip) {
+                GemmParams p;
+                std::memset(&p, 0, sizeof(p));
+                p.status = status;
+                uint8_t* user = reinterpret_cast<uint8_t*>(dy) + (size_t)c0 * lddy * dy_elt;
+                float* scratch = dy_scratch + (size_t)c0 * d;
+                if (dy_mode == MECLIP_ACCUM_F32) {
+                    p.acc_in = reinterpret_cast<const float*>(user); p.ld_acc = lddy;
+                    p.out = user; p.ld_out = lddy; p.out_bf16 = 0;
+                } else if (plan.n_row_blocks == 1) {
+                    p.out = user; p.ld_out = lddy; p.out_bf16 = (dy_mode == MECLIP_STORE_BF16);
+                } else {
+                    if (rb > 0) { p.acc_in = scratch; p.ld_acc = d; }
+                    if (rb == plan.n_row_blocks - 1) { p.out = user; p.ld_out = lddy; p.out_bf16 = (dy_mode == MECLIP_STORE_BF16); }
+                    else { p.out = scratch; p.ld_out = d; p.out_bf16 = 0; }
+                }
+                Operand a{gpanel, plan.ldg, true}, b{X + r0 * ldx, ldx, true};
+                rc = launch_gemm(EPI_OUT, a, b, nc, d, nr, bn_d, p, s);
+                if (rc) return rc;
+            }
+        }
+    }
+    return MECLIP_OK;
+}
+
+int meclip_loss_forward(int kind, const void* x_bf16, const void* y_bf16, int64_t batch, int64_t d, int64_t ldx,
+                        int64_t ldy, float temperature, float* row_sum, float* col_sum, float* diag_s, float* loss_out,
+                        int* status, void* stream) {
+    if (batch < 1 || row_sum == nullptr || diag_s == nullptr || loss_out == nullptr)
+        return fail(MECLIP_EINVAL, "loss_forward: bad argument");
+    cudaStream_t s = (cudaStream_t)stream;
+    MECLIP_CUDA(cudaMemsetAsync(row_sum, 0, (size_t)batch * sizeof(float), s));
+    if (kind == MECLIP_CLIP && col_sum != nullptr) MECLIP_CUDA(cudaMemsetAsync(col_sum, 0, (size_t)batch * sizeof(float), s));
+    MECLIP_CUDA(cudaMemsetAsync(diag_s, 0, (size_t)batch * sizeof(float), s));
+    int rc = meclip_sum_exp(kind, x_bf16, y_bf16, batch, batch, d, ldx, ldy, temperature, 0, 0, row_sum, col_sum, diag_s,
+                            status, stream);
+    if (rc) return rc;
+    return meclip_loss_finalize(kind, row_sum, col_sum, diag_s, batch, temperature, 1.0f / (float)batch, 0, loss_out,
+                                stream);
+}
+
+int meclip_loss_backward(int kind, const void* x_bf16, const void* y_bf16, int64_t batch, int64_t d, int64_t ldx,
+                         int64_t ldy, float temperature, const float* row_sum, const float* col_sum,
+                         const float* grad_out, float grad_scale, void* dx, int dx_mode, int64_t lddx, void* dy,
+                         int dy_mode, int64_t lddy, void* workspace, size_t workspace_bytes, int* status, void* stream) {
+    return meclip_grad(kind, x_bf16, y_bf16, batch, batch, d, ldx, ldy, temperature, 0, 0, row_sum, col_sum, grad_out,
+                       grad_scale, dx, dx_mode, lddx, dy, dy_mode, lddy, workspace, workspace_bytes, status, stream);
+}
+
+int meclip_debug_gemm(const void* a_bf16, int64_t lda, int a_mn_major, const void* b_bf16, int64_t ldb, int b_mn_major,
+                      int64_t m, int64_t n, int64_t k, int tile_n, float* c, int64_t ldc, const float* c_in,
+                      int* status, void* stream) {
+    if (a_bf16 == nullptr || b_bf16 == nullptr || c == nullptr) return fail(MECLIP_EINVAL, "debug_gemm: null pointer");
+    if (!aligned16(c) || ldc % 4 != 0 || n % 8 != 0) return fail(MECLIP_EINVAL, "debug_gemm: c must be 16-byte aligned, n a multiple of 8");
+    int rc = check_device();
+    if (rc) return rc;
+    GemmParams p;
+    std::memset(&p, 0, sizeof(p));
+    p.out = c;
+    p.ld_out = ldc;
+    p.out_bf16 = 0;
+    p.acc_in = c_in;
+    p.ld_acc = ldc;
+    p.status = status;
+    Operand a{a_bf16, lda, a_mn_major != 0}, b{b_bf16, ldb, b_mn_major != 0};
+    return launch_gemm(EPI_OUT, a, b, m, n, k, tile_n > 0 ? tile_n : pick_bn(n), p, (cudaStream_t)stream);
+}
+
+}  // extern "C"

@@ -1,0 +1,415 @@
+// Persistent, warp-specialised tcgen05 GEMM mainloop shared by every tile kernel
+// of the loss path, with three epilogues:
+//
+//   EPI_SUMS  S = X Y^T tile -> E = exp2(k S - k) -> row sums, column sums, diagonal
+//   EPI_COEF  S tile -> E -> G = E (g/r_i + g/c_j) - [i==j] g -> bf16 panel in global memory
+//   EPI_OUT   plain contraction -> (+ fp32 partial) -> fp32 / bf16 store
+//
+// One CTA per SM, 192 threads:
+//   warp 0      TMA producer (one lane): global -> 128B-swizzled shared tiles, 4 stages
+//   warp 1      TMEM allocator + MMA issuer (one lane): tcgen05.mma 128 x BN x 16, bf16 -> fp32
+//   warps 2-5   epilogue: tcgen05.ld of the finished accumulator while the MMA warp
+//               already fills the other accumulator (2 x 256 TMEM columns)
+// A and B operands may each be K-major (K contiguous in global memory) or MN-major
+// (M / N contiguous), so G, G^T, X and Y are all consumed from their one row-major copy.
+#pragma once
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include "sm100_ptx.cuh"
+
+namespace meclip {
+
+static constexpr int BM = 128;            // tile rows  (UMMA M)
+static constexpr int BK = 64;             // K per stage: 64 bf16 = one 128-byte swizzle row
+static constexpr int MAX_BN = 256;        // tile columns (UMMA N), runtime value <= this
+static constexpr int STAGES = 4;
+static constexpr int A_STAGE_BYTES = BM * BK * 2;        // 16 KiB
+static constexpr int B_STAGE_BYTES = MAX_BN * BK * 2;    // 32 KiB
+static constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+static constexpr int TMEM_COLS = 512;     // two accumulators of up to 256 columns
+static constexpr int GEMM_THREADS = 192;
+static constexpr int EPI_THREADS = 128;
+
+enum { EPI_SUMS = 0, EPI_COEF = 1, EPI_OUT = 2 };
+
+struct GemmParams {
+    int m, n, k;              // valid extents of the problem
+    int bn;                   // tile width (multiple of 32; multiple of 64 when B is MN-major)
+    int num_m_tiles, num_n_tiles, k_steps;
+    int group_m;              // rasterisation: m-tiles per group swept along n
+    uint32_t idesc;
+    // EPI_SUMS / EPI_COEF
+    float k2;                 // log2(e) / T
+    long long diag_shift;     // (row_off - col_off): row i meets column i + diag_shift
+    float* row_sum;           // SUMS: accumulated with atomics
+    float* col_sum;           // SUMS: may be null (LiT)
+    float* diag;              // SUMS: S_ii per row, written where the diagonal crosses the block
+    const float* r;           // COEF: saved row sums
+    const float* c;           // COEF: saved column sums or null (LiT)
+    const float* grad_out;    // COEF: device scalar
+    float coef;               // COEF: grad_scale * (0.5 for CLIP, 1 for LiT)
+    float dcoef;              // COEF: grad_scale (subtracted on the diagonal)
+    __nv_bfloat16* g;         // COEF: output panel, row-major [m x n]
+    long long ldg;
+    // EPI_OUT
+    void* out;
+    long long ld_out;
+    int out_bf16;
+    const float* acc_in;      // optional fp32 partial added before the store
+    long long ld_acc;
+    int* status;
+};
+
+struct SharedTail {
+    unsigned long long full_bar[STAGES];
+    unsigned long long empty_bar[STAGES];
+    unsigned long long tmem_full_bar[2];
+    unsigned long long tmem_empty_bar[2];
+    uint32_t tmem_base;
+    int abort_flag;
+    float colpart[4][MAX_BN];   // per-epilogue-warp column partial sums
+    float icol[MAX_BN];         // g / c_j for the tile's columns
+};
+
+static constexpr size_t GEMM_SMEM_BYTES = (size_t)STAGES * STAGE_BYTES + 1024 + sizeof(SharedTail);
+
+// Sum over the warp of v[lane'] for each of 32 slots: lane L returns the total of slot L.
+// 31 shuffles instead of 32 x 5.
+template <int HALF>
+__device__ __forceinline__ void transpose_reduce_step(float (&v)[32], int lane) {
+    const bool up = (lane & HALF) != 0;
+#pragma unroll
+    for (int i = 0; i < HALF; ++i) {
+        const float send = up ? v[i] : v[i + HALF];
+        const float keep = up ? v[i + HALF] : v[i];
+        v[i] = keep + __shfl_xor_sync(0xffffffffu, send, HALF);
+    }
+}
+__device__ __forceinline__ float warp_transpose_reduce32(float (&v)[32], int lane) {
+    transpose_reduce_step<16>(v, lane);
+    transpose_reduce_step<8>(v, lane);
+    transpose_reduce_step<4>(v, lane);
+    transpose_reduce_step<2>(v, lane);
+    transpose_reduce_step<1>(v, lane);
+    return v[0];
+}
+
+__device__ __forceinline__ void tile_coords(const GemmParams& p, int tile, int& mt, int& nt) {
+    const int per_group = p.group_m * p.num_n_tiles;
+    const int grp = tile / per_group;
+    const int first_m = grp * p.group_m;
+    const int rows_in_group = min(p.group_m, p.num_m_tiles - first_m);
+    const int local = tile - grp * per_group;
+    mt = first_m + local % rows_in_group;
+    nt = local / rows_in_group;
+}
+
+template <int EPI, bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                 const __grid_constant__ GemmParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw_addr = smem_u32(smem_raw);
+    const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
+    uint8_t* smem = smem_raw + pad;
+    const uint32_t smem_base = raw_addr + pad;
+    SharedTail* tail = reinterpret_cast<SharedTail*>(smem + (size_t)STAGES * STAGE_BYTES);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int num_tiles = p.num_m_tiles * p.num_n_tiles;
+    volatile int* abort_flag = &tail->abort_flag;
+
+    if (threadIdx.x == 0) {
+        tail->abort_flag = 0;
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(smem_u32(&tail->full_bar[s]), 1);
+            mbar_init(smem_u32(&tail->empty_bar[s]), 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(smem_u32(&tail->tmem_full_bar[a]), 1);
+            mbar_init(smem_u32(&tail->tmem_empty_bar[a]), EPI_THREADS);
+        }
+        fence_barrier_init();
+        tma_prefetch_desc(&tmap_a);
+        tma_prefetch_desc(&tmap_b);
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(&tail->tmem_base), TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tail->tmem_base;
+
+    if (warp == 0) {
+        // ------------------------------ TMA producer ------------------------------
+        if (lane == 0) {
+            const uint32_t stage_tx = (uint32_t)A_STAGE_BYTES + (uint32_t)p.bn * BK * 2;
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+                int mt, nt;
+                tile_coords(p, tile, mt, nt);
+                const int m0 = mt * BM, n0 = nt * p.bn;
+                for (int ks = 0; ks < p.k_steps; ++ks) {
+                    if (!mbar_wait(smem_u32(&tail->empty_bar[stage]), phase ^ 1u, abort_flag)) { ok = false; break; }
+                    const uint32_t full = smem_u32(&tail->full_bar[stage]);
+                    mbar_expect_tx(full, stage_tx);
+                    const uint32_t sa = smem_base + (uint32_t)stage * STAGE_BYTES;
+                    const uint32_t sb = sa + A_STAGE_BYTES;
+                    const int k0 = ks * BK;
+                    if (A_MN) {   // global [K rows][M contiguous]: 64-wide column chunks of BK rows
+                        tma_load_2d(sa, &tmap_a, full, m0, k0);
+                        tma_load_2d(sa + BK * 128, &tmap_a, full, m0 + 64, k0);
+                    } else {      // global [M rows][K contiguous]
+                        tma_load_2d(sa, &tmap_a, full, k0, m0);
+                    }
+                    if (B_MN) {
+                        for (int c = 0; c < p.bn / 64; ++c) tma_load_2d(sb + c * (BK * 128), &tmap_b, full, n0 + c * 64, k0);
+                    } else {
+                        tma_load_2d(sb, &tmap_b, full, k0, n0);
+                    }
+                    if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // ------------------------------ MMA issuer --------------------------------
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            int acc = 0;
+            uint32_t acc_phase = 0;
+            bool ok = true;
+            // K-major: 8-row groups 1024 B apart (SBO), 32 B per K=16 step inside the swizzle row.
+            // MN-major: 64-element chunks BK*128 B apart (LBO), 8-row K groups 1024 B apart (SBO),
+            //           a K=16 step is 16 rows = 2048 B.
+            constexpr uint32_t A_LBO = A_MN ? BK * 128 : 16, A_KSTEP = A_MN ? 2048 : 32;
+            constexpr uint32_t B_LBO = B_MN ? BK * 128 : 16, B_KSTEP = B_MN ? 2048 : 32;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+                if (!mbar_wait(smem_u32(&tail->tmem_empty_bar[acc]), acc_phase ^ 1u, abort_flag)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t tmem_d = tmem_base + (uint32_t)acc * MAX_BN;
+                for (int ks = 0; ks < p.k_steps; ++ks) {
+                    if (!mbar_wait(smem_u32(&tail->full_bar[stage]), phase, abort_flag)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t sa = smem_base + (uint32_t)stage * STAGE_BYTES;
+                    const uint32_t sb = sa + A_STAGE_BYTES;
+#pragma unroll
+                    for (int kk = 0; kk < BK / 16; ++kk) {
+                        const uint64_t ad = umma_smem_desc(sa + kk * A_KSTEP, A_LBO, 1024);
+                        const uint64_t bd = umma_smem_desc(sb + kk * B_KSTEP, B_LBO, 1024);
+                        umma_bf16(tmem_d, ad, bd, p.idesc, (ks | kk) != 0 ? 1u : 0u);
+                    }
+                    umma_commit(smem_u32(&tail->empty_bar[stage]));   // frees the stage when these MMAs retire
+                    if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                }
+                if (!ok) break;
+                umma_commit(smem_u32(&tail->tmem_full_bar[acc]));     // accumulator complete
+                acc ^= 1;
+                if (acc == 0) acc_phase ^= 1u;
+            }
+        }
+        __syncwarp();
+    } else {
+        // ------------------------------ epilogue -----------------------------------
+        const int q = warp & 3;                 // TMEM lane quadrant this warp can read
+        const int et = threadIdx.x - 64;        // 0..127 within the epilogue group
+        const int row_in_tile = q * 32 + lane;
+        int acc = 0;
+        uint32_t acc_phase = 0;
+        bool ok = true;
+        float gscale = 1.f;
+        if (EPI == EPI_COEF) gscale = p.grad_out ? __ldg(p.grad_out) : 1.f;
+        const int chunks = p.bn / 32;
+        for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+            int mt, nt;
+            tile_coords(p, tile, mt, nt);
+            const int m0 = mt * BM, n0 = nt * p.bn;
+            const int grow = m0 + row_in_tile;
+            const bool rvalid = grow < p.m;
+            const bool full_tile = (m0 + BM <= p.m) && (n0 + p.bn <= p.n);
+            // column (tile-local) on which this row meets the diagonal; may be out of range
+            const long long jd_ll = (long long)grow + p.diag_shift - n0;
+            const int jd = (jd_ll >= 0 && jd_ll < p.bn && n0 + jd_ll < p.n && rvalid) ? (int)jd_ll : -1;
+
+            float inv_r = 0.f;
+            if (EPI == EPI_COEF) {
+                named_bar_sync(1, EPI_THREADS);            // previous tile's readers of icol are done
+                for (int j = et; j < p.bn; j += EPI_THREADS) {
+                    float v = 0.f;
+                    if (p.c != nullptr && n0 + j < p.n) v = p.coef * gscale / __ldg(p.c + n0 + j);
+                    tail->icol[j] = v;
+                }
+                if (rvalid) inv_r = p.coef * gscale / __ldg(p.r + grow);
+                named_bar_sync(1, EPI_THREADS);
+            }
+
+            // The four warps wait on the same phase and then agree on the verdict, so that they
+            // always leave the tile loop (and its named barriers) together.
+            ok = mbar_wait(smem_u32(&tail->tmem_full_bar[acc]), acc_phase, abort_flag, false);
+            ok = named_bar_and(2, EPI_THREADS, ok);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)acc * MAX_BN;
+
+            if (EPI == EPI_SUMS) {
+                float ra0 = 0.f, ra1 = 0.f, ra2 = 0.f, ra3 = 0.f;
+                float sdiag = 0.f;
+                for (int ch = 0; ch < chunks; ++ch) {
+                    uint32_t v[32];
+                    tmem_ld32(taddr + ch * 32, v);
+                    tmem_ld_wait();
+                    float e[32];
+                    const int jdc = (jd >= 0 && (jd >> 5) == ch) ? (jd & 31) : -1;
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) {
+                        const float sv = __uint_as_float(v[c]);
+                        e[c] = ex2_approx(fmaf(sv, p.k2, -p.k2));
+                        sdiag = (c == jdc) ? sv : sdiag;
+                    }
+                    if (!full_tile) {
+#pragma unroll
+                        for (int c = 0; c < 32; ++c)
+                            if (!rvalid || n0 + ch * 32 + c >= p.n) e[c] = 0.f;
+                    }
+#pragma unroll
+                    for (int c = 0; c < 32; c += 4) { ra0 += e[c]; ra1 += e[c + 1]; ra2 += e[c + 2]; ra3 += e[c + 3]; }
+                    if (p.col_sum != nullptr) {
+                        const float cs = warp_transpose_reduce32(e, lane);
+                        tail->colpart[q][ch * 32 + lane] = cs;
+                    }
+                }
+                tc_fence_before();
+                mbar_arrive(smem_u32(&tail->tmem_empty_bar[acc]));
+                if (rvalid) atomicAdd(p.row_sum + grow, (ra0 + ra1) + (ra2 + ra3));
+                if (jd >= 0) p.diag[grow] = sdiag;
+                if (p.col_sum != nullptr) {
+                    named_bar_sync(1, EPI_THREADS);
+                    for (int j = et; j < p.bn; j += EPI_THREADS)
+                        if (n0 + j < p.n)
+                            atomicAdd(p.col_sum + n0 + j, (tail->colpart[0][j] + tail->colpart[1][j]) +
+                                                              (tail->colpart[2][j] + tail->colpart[3][j]));
+                    named_bar_sync(1, EPI_THREADS);
+                }
+            } else if (EPI == EPI_COEF) {
+                const float dsub = p.dcoef * gscale;
+                __nv_bfloat16* grow_ptr = p.g + (long long)grow * p.ldg + n0;
+                for (int ch = 0; ch < chunks; ++ch) {
+                    uint32_t v[32];
+                    tmem_ld32(taddr + ch * 32, v);
+                    tmem_ld_wait();
+                    float gv[32];
+                    const int jdc = (jd >= 0 && (jd >> 5) == ch) ? (jd & 31) : -1;
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) {
+                        const float e = ex2_approx(fmaf(__uint_as_float(v[c]), p.k2, -p.k2));
+                        gv[c] = fmaf(e, inv_r + tail->icol[ch * 32 + c], (c == jdc) ? -dsub : 0.f);
+                    }
+                    if (rvalid) {
+#pragma unroll
+                        for (int c = 0; c < 32; c += 8) {
+                            if (n0 + ch * 32 + c < p.n) {   // n is a multiple of 8: whole group valid or not
+                                __nv_bfloat162 b0 = __floats2bfloat162_rn(gv[c], gv[c + 1]);
+                                __nv_bfloat162 b1 = __floats2bfloat162_rn(gv[c + 2], gv[c + 3]);
+                                __nv_bfloat162 b2 = __floats2bfloat162_rn(gv[c + 4], gv[c + 5]);
+                                __nv_bfloat162 b3 = __floats2bfloat162_rn(gv[c + 6], gv[c + 7]);
+                                uint4 pk;
+                                pk.x = *reinterpret_cast<uint32_t*>(&b0);
+                                pk.y = *reinterpret_cast<uint32_t*>(&b1);
+                                pk.z = *reinterpret_cast<uint32_t*>(&b2);
+                                pk.w = *reinterpret_cast<uint32_t*>(&b3);
+                                *reinterpret_cast<uint4*>(grow_ptr + ch * 32 + c) = pk;
+                            }
+                        }
+                    }
+                }
+                tc_fence_before();
+                mbar_arrive(smem_u32(&tail->tmem_empty_bar[acc]));
+            } else {   // EPI_OUT
+                for (int ch = 0; ch < chunks; ++ch) {
+                    uint32_t v[32];
+                    tmem_ld32(taddr + ch * 32, v);
+                    tmem_ld_wait();
+                    if (rvalid) {
+                        const int col0 = n0 + ch * 32;
+                        if (p.acc_in != nullptr) {
+                            const float* ap = p.acc_in + (long long)grow * p.ld_acc + col0;
+#pragma unroll
+                            for (int c = 0; c < 32; c += 4) {
+                                if (col0 + c < p.n) {
+                                    const float4 a = *reinterpret_cast<const float4*>(ap + c);
+                                    v[c] = __float_as_uint(__uint_as_float(v[c]) + a.x);
+                                    v[c + 1] = __float_as_uint(__uint_as_float(v[c + 1]) + a.y);
+                                    v[c + 2] = __float_as_uint(__uint_as_float(v[c + 2]) + a.z);
+                                    v[c + 3] = __float_as_uint(__uint_as_float(v[c + 3]) + a.w);
+                                }
+                            }
+                        }
+                        if (p.out_bf16) {
+                            __nv_bfloat16* op = reinterpret_cast<__nv_bfloat16*>(p.out) + (long long)grow * p.ld_out + col0;
+#pragma unroll
+                            for (int c = 0; c < 32; c += 8) {
+                                if (col0 + c < p.n) {
+                                    __nv_bfloat162 b0 = __floats2bfloat162_rn(__uint_as_float(v[c]), __uint_as_float(v[c + 1]));
+                                    __nv_bfloat162 b1 = __floats2bfloat162_rn(__uint_as_float(v[c + 2]), __uint_as_float(v[c + 3]));
+                                    __nv_bfloat162 b2 = __floats2bfloat162_rn(__uint_as_float(v[c + 4]), __uint_as_float(v[c + 5]));
+                                    __nv_bfloat162 b3 = __floats2bfloat162_rn(__uint_as_float(v[c + 6]), __uint_as_float(v[c + 7]));
+                                    uint4 pk;
+                                    pk.x = *reinterpret_cast<uint32_t*>(&b0);
+                                    pk.y = *reinterpret_cast<uint32_t*>(&b1);
+                                    pk.z = *reinterpret_cast<uint32_t*>(&b2);
+                                    pk.w = *reinterpret_cast<uint32_t*>(&b3);
+                                    *reinterpret_cast<uint4*>(op + c) = pk;
+                                }
+                            }
+                        } else {
+                            float* op = reinterpret_cast<float*>(p.out) + (long long)grow * p.ld_out + col0;
+#pragma unroll
+                            for (int c = 0; c < 32; c += 4) {
+                                if (col0 + c < p.n) {
+                                    float4 o;
+                                    o.x = __uint_as_float(v[c]);
+                                    o.y = __uint_as_float(v[c + 1]);
+                                    o.z = __uint_as_float(v[c + 2]);
+                                    o.w = __uint_as_float(v[c + 3]);
+                                    *reinterpret_cast<float4*>(op + c) = o;
+                                }
+                            }
+                        }
+                    }
+                }
+                tc_fence_before();
+                mbar_arrive(smem_u32(&tail->tmem_empty_bar[acc]));
+            }
+            acc ^= 1;
+            if (acc == 0) acc_phase ^= 1u;
+        }
+    }
+
+    // ------------------------------ teardown ---------------------------------------
+    tc_fence_before();
+    __syncthreads();
+    if (tail->abort_flag) {
+        if (threadIdx.x == 0) {
+            if (p.status != nullptr) atomicExch(p.status, 1);
+            // give tile copies that may still be in flight time to land before the CTA's
+            // shared memory is handed to another CTA
+            const unsigned long long t0 = global_ns();
+            while (global_ns() - t0 < 2000000ull) { __nanosleep(1000); }
+        }
+        __syncthreads();
+    }
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
+}  // namespace meclip

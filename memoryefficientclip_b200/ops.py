@@ -1,0 +1,161 @@
+"""Torch-tensor front end of the C ABI: every function here launches CUDA kernels from
+libmeclip_sm100.so on the current stream of the tensors' device.  Torch is used for
+device memory and streams only; no arithmetic of the loss path happens in torch.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from . import _lib
+
+_DT = {torch.bfloat16: _lib.BF16, torch.float32: _lib.F32}
+
+
+def _ptr(t):
+    return None if t is None else t.data_ptr()
+
+
+def _stream(t: torch.Tensor):
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def _check_matrix(t: torch.Tensor, name: str):
+    assert t.is_cuda, f"{name} must be a CUDA tensor"
+    assert t.dim() == 2, f"{name} must be 2-D [batch, features]"
+    assert t.dtype in _DT, f"{name}: dtype {t.dtype} not supported (float32 or bfloat16)"
+    assert t.shape[1] % 8 == 0 and t.shape[1] >= 8, \
+        f"{name}: feature dimension {t.shape[1]} must be a multiple of 8 (16-byte rows for the TMA tile loads)"
+
+
+def new_status(device) -> torch.Tensor:
+    return torch.zeros(1, dtype=torch.int32, device=device)
+
+
+def read_status(status: torch.Tensor) -> None:
+    """Synchronise and raise if a kernel recorded an expired wait."""
+    with torch.cuda.device(status.device):
+        _lib.check(_lib.load().meclip_read_status(status.data_ptr(), _stream(status)))
+
+
+def normalize_fwd(x: torch.Tensor, normalize: bool = True):
+    """Returns (x_hat bf16 [rows, d], inv_norm fp32 [rows] or None)."""
+    _check_matrix(x, "x")
+    x = x if x.stride(1) == 1 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 else x.contiguous()
+    rows, d = x.shape
+    out = torch.empty(rows, d, dtype=torch.bfloat16, device=x.device)
+    inv = torch.empty(rows, dtype=torch.float32, device=x.device) if normalize else None
+    with torch.cuda.device(x.device):
+        _lib.check(_lib.load().meclip_normalize_fwd(x.data_ptr(), _DT[x.dtype], rows, d, x.stride(0), int(normalize),
+                                                    out.data_ptr(), d, _ptr(inv), _stream(x)))
+    return out, inv
+
+
+def normalize_bwd(g: torch.Tensor, x_hat: torch.Tensor, inv_norm: torch.Tensor, out_dtype) -> torch.Tensor:
+    rows, d = g.shape
+    dx = torch.empty(rows, d, dtype=out_dtype, device=g.device)
+    with torch.cuda.device(g.device):
+        _lib.check(_lib.load().meclip_normalize_bwd(g.data_ptr(), _DT[g.dtype], g.stride(0), x_hat.data_ptr(),
+                                                    x_hat.stride(0), inv_norm.data_ptr(), rows, d, dx.data_ptr(),
+                                                    _DT[out_dtype], d, _stream(g)))
+    return dx
+
+
+def as_operand(x: torch.Tensor) -> torch.Tensor:
+    """bf16, unit-stride rows, 16-byte aligned: what the tile kernels read."""
+    _check_matrix(x, "operand")
+    if x.dtype == torch.bfloat16 and x.stride(1) == 1 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0:
+        return x
+    if x.dtype == torch.bfloat16:
+        return x.contiguous()
+    return normalize_fwd(x, normalize=False)[0]
+
+
+def sum_exp(kind, x_hat, y_hat, temperature, row_sum, col_sum, diag_s, row_off=0, col_off=0, status=None):
+    rows, d = x_hat.shape
+    cols = y_hat.shape[0]
+    with torch.cuda.device(x_hat.device):
+        _lib.check(_lib.load().meclip_sum_exp(kind, x_hat.data_ptr(), y_hat.data_ptr(), rows, cols, d, x_hat.stride(0),
+                                              y_hat.stride(0), float(temperature), row_off, col_off, row_sum.data_ptr(),
+                                              _ptr(col_sum), diag_s.data_ptr(), _ptr(status), _stream(x_hat)))
+
+
+def loss_finalize(kind, row_sum, col_sum, diag_s, temperature, scale, loss_out, accumulate=False):
+    with torch.cuda.device(row_sum.device):
+        _lib.check(_lib.load().meclip_loss_finalize(kind, row_sum.data_ptr(), _ptr(col_sum), diag_s.data_ptr(),
+                                                    row_sum.numel(), float(temperature), float(scale), int(accumulate),
+                                                    loss_out.data_ptr(), _stream(row_sum)))
+
+
+def loss_forward(kind, x_hat, y_hat, temperature, status=None):
+    """Returns (loss 0-dim fp32, row_sum, col_sum or None, diag_s)."""
+    b, d = x_hat.shape
+    assert y_hat.shape == x_hat.shape
+    dev = x_hat.device
+    row_sum = torch.empty(b, dtype=torch.float32, device=dev)
+    col_sum = torch.empty(b, dtype=torch.float32, device=dev) if kind == _lib.CLIP else None
+    diag_s = torch.empty(b, dtype=torch.float32, device=dev)
+    loss = torch.empty((), dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        _lib.check(_lib.load().meclip_loss_forward(kind, x_hat.data_ptr(), y_hat.data_ptr(), b, d, x_hat.stride(0),
+                                                   y_hat.stride(0), float(temperature), row_sum.data_ptr(),
+                                                   _ptr(col_sum), diag_s.data_ptr(), loss.data_ptr(), _ptr(status),
+                                                   _stream(x_hat)))
+    return loss, row_sum, col_sum, diag_s
+
+
+_MODE = {torch.bfloat16: _lib.STORE_BF16, torch.float32: _lib.STORE_F32}
+
+
+def grad_workspace(rows, cols, d, device) -> torch.Tensor:
+    n = _lib.load().meclip_grad_workspace_bytes(rows, cols, d)
+    return torch.empty(n, dtype=torch.uint8, device=device)
+
+
+def grad_block(kind, x_hat, y_hat, temperature, row_sum, col_sum, grad_out, grad_scale, dx, dx_mode, dy, dy_mode,
+               row_off=0, col_off=0, workspace=None, status=None):
+    """One rows x cols block of the backward (see meclip_grad in include/meclip.h)."""
+    rows, d = x_hat.shape
+    cols = y_hat.shape[0]
+    if workspace is None:
+        workspace = grad_workspace(rows, cols, d, x_hat.device)
+    with torch.cuda.device(x_hat.device):
+        _lib.check(_lib.load().meclip_grad(kind, x_hat.data_ptr(), y_hat.data_ptr(), rows, cols, d, x_hat.stride(0),
+                                           y_hat.stride(0), float(temperature), row_off, col_off, row_sum.data_ptr(),
+                                           _ptr(col_sum), _ptr(grad_out), float(grad_scale), dx.data_ptr(), dx_mode,
+                                           dx.stride(0), _ptr(dy), dy_mode, dy.stride(0) if dy is not None else 0,
+                                           workspace.data_ptr(), workspace.numel(), _ptr(status), _stream(x_hat)))
+
+
+def loss_backward(kind, x_hat, y_hat, temperature, row_sum, col_sum, grad_out, grad_scale, dx_dtype, dy_dtype,
+                  status=None):
+    """Whole-batch backward on one GPU.  Returns (dx, dy or None) w.r.t. the normalised operands."""
+    b, d = x_hat.shape
+    dev = x_hat.device
+    dx = torch.empty(b, d, dtype=dx_dtype, device=dev)
+    dy = torch.empty(b, d, dtype=dy_dtype, device=dev) if kind == _lib.CLIP else None
+    ws = grad_workspace(b, b, d, dev)
+    with torch.cuda.device(dev):
+        _lib.check(_lib.load().meclip_loss_backward(kind, x_hat.data_ptr(), y_hat.data_ptr(), b, d, x_hat.stride(0),
+                                                    y_hat.stride(0), float(temperature), row_sum.data_ptr(),
+                                                    _ptr(col_sum), _ptr(grad_out), float(grad_scale), dx.data_ptr(),
+                                                    _MODE[dx_dtype], d, _ptr(dy),
+                                                    _MODE[dy_dtype] if dy is not None else 0, d, ws.data_ptr(),
+                                                    ws.numel(), _ptr(status), _stream(x_hat)))
+    return dx, dy
+
+
+def grad_scale(batch: int, temperature: float, stable: bool) -> float:
+    """1/(B T) (reference clip_loss.py:182, 235) or, for the Stable variants,
+    sqrt(B/T)/B = 1/sqrt(B T) (clip_loss.py:299, 352)."""
+    return 1.0 / math.sqrt(batch * temperature) if stable else 1.0 / (batch * temperature)
+
+
+def debug_gemm(a, b, a_mn_major, b_mn_major, m, n, k, tile_n=0, c_in=None, status=None) -> torch.Tensor:
+    c = torch.empty(m, n, dtype=torch.float32, device=a.device) if c_in is None else c_in.clone()
+    with torch.cuda.device(a.device):
+        _lib.check(_lib.load().meclip_debug_gemm(a.data_ptr(), a.stride(0), int(a_mn_major), b.data_ptr(), b.stride(0),
+                                                 int(b_mn_major), m, n, k, tile_n, c.data_ptr(), c.stride(0),
+                                                 _ptr(c_in) and c.data_ptr(), _ptr(status), _stream(a)))
+    return c

@@ -1,0 +1,57 @@
+"""The tcgen05 mainloop alone: every operand layout against torch fp32 matmul."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _run(m, n, k, a_mn, b_mn, tile_n=0, accumulate=False, seed=0):
+    from memoryefficientclip_b200 import ops
+    g = torch.Generator().manual_seed(seed)
+    a = torch.randn(m, k, generator=g).bfloat16().cuda()
+    b = torch.randn(n, k, generator=g).bfloat16().cuda()
+    a_store = a.t().contiguous() if a_mn else a
+    b_store = b.t().contiguous() if b_mn else b
+    c_in = torch.randn(m, n, generator=g).cuda() if accumulate else None
+    status = ops.new_status(a.device)
+    c = ops.debug_gemm(a_store, b_store, a_mn, b_mn, m, n, k, tile_n, c_in, status)
+    ops.read_status(status)
+    ref = a.double() @ b.double().t()
+    if accumulate:
+        ref = ref + c_in.double()
+    err = (c.double() - ref).abs().max().item()
+    tol = 1e-3 * max(1.0, k ** 0.5)
+    assert err < tol, f"m={m} n={n} k={k} a_mn={a_mn} b_mn={b_mn} tile_n={tile_n}: max err {err} (tol {tol})"
+
+
+LAYOUTS = [(False, False), (False, True), (True, True), (True, False)]
+
+
+@pytest.mark.parametrize("a_mn,b_mn", LAYOUTS)
+def test_single_tile(a_mn, b_mn):
+    _run(128, 256, 64, a_mn, b_mn, 256)
+
+
+@pytest.mark.parametrize("a_mn,b_mn", LAYOUTS)
+def test_multi_k_multi_tile(a_mn, b_mn):
+    _run(512, 768, 320, a_mn, b_mn, 256)
+    _run(384, 384, 512, a_mn, b_mn, 192)
+    _run(256, 128, 192, a_mn, b_mn, 64)
+
+
+@pytest.mark.parametrize("a_mn,b_mn", LAYOUTS)
+def test_ragged_edges(a_mn, b_mn):
+    # m, n, k not multiples of the tile: TMA zero-fills, the epilogue masks
+    _run(200, 200, 136, a_mn, b_mn, 128)
+    _run(72, 1152, 200, a_mn, b_mn, 192)
+
+
+@pytest.mark.parametrize("a_mn,b_mn", LAYOUTS)
+def test_accumulate_input(a_mn, b_mn):
+    _run(256, 512, 256, a_mn, b_mn, 256, accumulate=True)
+
+
+def test_more_tiles_than_sms():
+    # 40 x 9 = 360 tiles on 148 persistent CTAs, long K: pipeline wrap-around and TMEM double buffering
+    _run(5120, 1152, 2048, False, True, 128)
+    _run(2048, 4096, 1152, False, False, 256)

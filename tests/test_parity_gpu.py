@@ -1,0 +1,153 @@
+"""CUDA path vs. the CPU oracle on the same seeded inputs (through the public modules,
+i.e. through the C ABI).  Tolerances: loss 1e-3 relative; gradients 1e-2 max-relative
+and cosine >= 0.9999 (oracle.dense.LOSS_RTOL / GRAD_MAX_REL / GRAD_COS_MIN).
+"""
+import glob
+import os
+
+import numpy as np
+import pytest
+import torch
+import torch.nn.functional as F
+
+from oracle import dense
+
+pytestmark = pytest.mark.gpu
+
+GOLDEN = sorted(glob.glob(os.path.join(os.path.dirname(__file__), "golden", "*.npz")))
+
+
+def _mods():
+    import memoryefficientclip_b200 as m
+    return m
+
+
+def _inputs(b, d, seed=0, normalized=True, dtype=torch.float32):
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(b, d, generator=g)
+    y = torch.randn(b, d, generator=g)
+    if normalized:
+        x, y = F.normalize(x, dim=1), F.normalize(y, dim=1)
+    return x.to(dtype), y.to(dtype)
+
+
+def _run_clip(x, y, t, normalized_inputs, stable=False, grad_output=None):
+    m = _mods()
+    mod = (m.StableMemoryEfficientCLIPLoss if stable else m.MemoryEfficientCLIPLoss)(t, normalized_inputs)
+    xg = x.cuda().requires_grad_(True)
+    yg = y.cuda().requires_grad_(True)
+    loss = mod(xg, yg)
+    if grad_output is None:
+        loss.backward()
+    else:
+        loss.backward(torch.tensor(grad_output, device="cuda"))
+    torch.cuda.synchronize()
+    assert loss.dtype == torch.float32 and loss.dim() == 0
+    assert xg.grad.dtype == x.dtype and yg.grad.dtype == y.dtype
+    return loss.item(), xg.grad.float().cpu(), yg.grad.float().cpu()
+
+
+def _run_lit(txt, img, t, normalized_inputs, stable=False):
+    m = _mods()
+    mod = (m.StableMemoryEfficientLiTLoss if stable else m.MemoryEfficientLiTLoss)(t, normalized_inputs)
+    xg = txt.cuda().requires_grad_(True)
+    yg = img.cuda().requires_grad_(True)
+    loss = mod(xg, yg)
+    loss.backward()
+    torch.cuda.synchronize()
+    assert yg.grad is None            # image tower frozen (reference lit_loss.py:247)
+    return loss.item(), xg.grad.float().cpu()
+
+
+@pytest.mark.parametrize("path", GOLDEN, ids=[os.path.basename(p)[:-4] for p in GOLDEN])
+def test_against_reference_golden_vectors(path):
+    """fp32 inputs of the golden cases; outputs of the reference's own kernels."""
+    g = np.load(path)
+    kind = str(g["kind"])
+    t, stable, go = float(g["temperature"]), bool(g["stable"]), float(g["grad_output"])
+    x, y = torch.from_numpy(g["x"]), torch.from_numpy(g["y"])
+    if kind == "clip":
+        loss, dx, dy = _run_clip(x, y, t, True, stable, None if go == 1.0 else go)
+        dense.assert_parity(loss, g["loss"], (dx, dy), (g["dx"], g["dy"]), path)
+    else:
+        loss, dx = _run_lit(x, y, t, True, stable)
+        dense.assert_parity(loss, g["loss"], (dx,), (g["dx"],), path)
+
+
+@pytest.mark.parametrize("b,d,dtype", [(128, 64, torch.float32), (256, 64, torch.bfloat16), (192, 96, torch.bfloat16),
+                                       (200, 48, torch.float32), (1024, 512, torch.bfloat16),
+                                       (520, 1152, torch.bfloat16), (8, 16, torch.float32)])
+def test_clip_normalized_inputs(b, d, dtype):
+    x, y = _inputs(b, d, 0, True, dtype)
+    loss, dx, dy = _run_clip(x, y, 0.07, True)
+    rl, rx, ry = dense.clip_dense(x, y, 0.07, True)
+    dense.assert_parity(loss, rl, (dx, dy), (rx, ry), f"clip b={b} d={d} {dtype}")
+
+
+@pytest.mark.parametrize("b,d,dtype,t", [(256, 64, torch.float32, 0.07), (384, 128, torch.bfloat16, 0.03),
+                                         (200, 72, torch.float32, 1.0)])
+def test_clip_unnormalized_inputs_fused_normalize(b, d, dtype, t):
+    x, y = _inputs(b, d, 1, False, dtype)
+    loss, dx, dy = _run_clip(x, y, t, False)
+    rl, rx, ry = dense.clip_dense(x, y, t, False)
+    dense.assert_parity(loss, rl, (dx, dy), (rx, ry), f"clip raw b={b} d={d} {dtype}")
+
+
+def test_clip_stable_and_grad_output():
+    x, y = _inputs(256, 128, 2, True, torch.float32)
+    loss, dx, dy = _run_clip(x, y, 0.07, True, stable=True, grad_output=0.25)
+    rl, rx, ry = dense.clip_dense(x, y, 0.07, True, stable=True, grad_output=0.25)
+    dense.assert_parity(loss, rl, (dx, dy), (rx, ry), "stable clip")
+
+
+@pytest.mark.parametrize("b,d,dtype,norm", [(128, 64, torch.float32, True), (320, 96, torch.bfloat16, False),
+                                            (1024, 256, torch.bfloat16, False)])
+def test_lit(b, d, dtype, norm):
+    g = torch.Generator().manual_seed(4)
+    img = F.normalize(torch.randn(b, d, generator=g), dim=1)
+    txt = F.normalize(img + torch.randn(b, d, generator=g), dim=1)
+    img, txt = img.to(dtype), txt.to(dtype)
+    loss, dx = _run_lit(txt, img, 0.07, norm)
+    rl, rx = dense.lit_dense(txt, img, 0.07, norm)
+    dense.assert_parity(loss, rl, (dx,), (rx,), f"lit b={b} d={d}")
+    loss, dx = _run_lit(txt, img, 0.07, norm, stable=True)
+    rl, rx = dense.lit_dense(txt, img, 0.07, norm, stable=True)
+    dense.assert_parity(loss, rl, (dx,), (rx,), f"stable lit b={b} d={d}")
+
+
+def test_normed_function_apply_signature():
+    """XxxNormed.apply(x, y, temperature) as in the reference (clip_loss.py:271, lit_loss.py:261)."""
+    m = _mods()
+    x, y = _inputs(128, 64, 5, True)
+    xg, yg = x.cuda().requires_grad_(True), y.cuda().requires_grad_(True)
+    loss = m.MemoryEfficientCLIPLossNormed.apply(xg, yg, 0.07)
+    loss.backward()
+    rl, rx, ry = dense.clip_dense(x, y, 0.07, True)
+    dense.assert_parity(loss.item(), rl, (xg.grad.cpu(), yg.grad.cpu()), (rx, ry), "normed apply")
+    xg.grad = None
+    loss = m.MemoryEfficientLiTLossNormed.apply(xg, yg, 0.07)
+    loss.backward()
+    rl, rx = dense.lit_dense(x, y, 0.07, True)
+    dense.assert_parity(loss.item(), rl, (xg.grad.cpu(),), (rx,), "lit normed apply")
+
+
+def test_backward_is_deterministic():
+    """Same saved sums -> bit-identical gradients: the backward has no atomics."""
+    from memoryefficientclip_b200 import _lib, ops
+    x, y = _inputs(512, 256, 6, True, torch.bfloat16)
+    xg, yg = x.cuda(), y.cuda()
+    go = torch.ones(1, device="cuda")
+    _loss, r, c, _diag = ops.loss_forward(_lib.CLIP, xg, yg, 0.07)
+    scale = ops.grad_scale(512, 0.07, False)
+    a = ops.loss_backward(_lib.CLIP, xg, yg, 0.07, r, c, go, scale, torch.float32, torch.float32)
+    b = ops.loss_backward(_lib.CLIP, xg, yg, 0.07, r, c, go, scale, torch.float32, torch.float32)
+    assert torch.equal(a[0], b[0]) and torch.equal(a[1], b[1])
+
+
+def test_medium_batch_multi_panel_properties():
+    """B=4096, D=512 fp32 un-normalised inputs (the CPU-runnable benchmark configuration)."""
+    from memoryefficientclip_b200 import synth
+    img, txt = synth.make("clip_b4096_d512_f32")
+    loss, dx, dy = _run_clip(img, txt, 0.07, False)
+    rl, rx, ry = dense.clip_dense(img, txt, 0.07, False, dtype=torch.float32)
+    dense.assert_parity(loss, rl, (dx, dy), (rx, ry), "clip_b4096_d512_f32")
