@@ -56,6 +56,20 @@ int meclip_last_error(char* buf, size_t buf_len);
 /* Synchronises `stream`, copies *status to the host and maps non-zero to MECLIP_ETIMEOUT. */
 int meclip_read_status(const int* status, void* stream);
 
+/* Number of kernels this library has launched in this process (all threads). */
+long long meclip_launch_count(void);
+
+/*
+ * Per-kernel timing with CUDA events on the launch stream.  Between begin and end
+ * every launch is bracketed by an event pair; end synchronises on them and sums
+ * milliseconds, launches and useful FLOPs per tag: 0 sums pass, 1 coefficient
+ * panel, 2 dX contraction, 3 dY contraction, 4 row kernels (normalise, loss).
+ * Meant for benchmarks; the events serialise nothing but add launch overhead.
+ * Has no counterpart in the reference.
+ */
+int meclip_profile_begin(void);
+int meclip_profile_end(double* ms_by_tag, long long* launches_by_tag, double* flops_by_tag, int n_tags);
+
 /*
  * x_hat = x / max(||x||_2, 1e-12) per row, written as bf16, plus inv_norm[i] =
  * 1/max(||x_i||, 1e-12).  With normalize == 0 only the dtype conversion to bf16

@@ -8,7 +8,9 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
+#include <atomic>
 #include <mutex>
+#include <vector>
 #include <string>
 
 #include "../../include/meclip.h"
@@ -38,6 +40,37 @@ static int fail(int code, const char* fmt, ...) {
         cudaError_t e__ = (expr);                                                                 \
         if (e__ != cudaSuccess) return fail(MECLIP_ECUDA, "%s: %s", #expr, cudaGetErrorString(e__)); \
     } while (0)
+
+// ------------------------------------------------------------------------------------
+// launch counter and optional per-kernel CUDA-event timing
+// ------------------------------------------------------------------------------------
+static std::atomic<long long> g_launches{0};
+enum { TAG_SUMS = 0, TAG_COEF = 1, TAG_DX = 2, TAG_DY = 3, TAG_ROW = 4, TAG_COUNT = 5 };
+struct ProfileRecord { int tag; cudaEvent_t start, stop; double flops; };
+static std::mutex g_prof_mutex;
+static bool g_prof_on = false;
+static std::vector<ProfileRecord> g_prof;
+static thread_local int t_tag = TAG_ROW;
+
+struct ScopedTiming {   // brackets one launch with events on its stream while profiling is on
+    cudaStream_t s; bool on; ProfileRecord rec;
+    ScopedTiming(cudaStream_t stream, int tag, double flops) : s(stream), on(false) {
+        g_launches.fetch_add(1, std::memory_order_relaxed);
+        std::lock_guard<std::mutex> lock(g_prof_mutex);
+        if (!g_prof_on) return;
+        rec.tag = tag; rec.flops = flops;
+        if (cudaEventCreate(&rec.start) != cudaSuccess) return;
+        if (cudaEventCreate(&rec.stop) != cudaSuccess) { cudaEventDestroy(rec.start); return; }
+        cudaEventRecord(rec.start, s);
+        on = true;
+    }
+    ~ScopedTiming() {
+        if (!on) return;
+        cudaEventRecord(rec.stop, s);
+        std::lock_guard<std::mutex> lock(g_prof_mutex);
+        g_prof.push_back(rec);
+    }
+};
 
 static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 static inline size_t round_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
@@ -215,10 +248,14 @@ static int sm_count() {
     return cached[dev];
 }
 
+// Also binds the runtime's primary context to the calling thread: the tensor-map encoder is a
+// driver-API entry point and fails with "invalid context" on a thread that has made no runtime
+// call yet (PyTorch's autograd thread on its first backward).
 static int check_device() {
     static int verdict[64] = {0};   // 0 unknown, 1 ok, -1 unsupported
     int dev = 0;
     MECLIP_CUDA(cudaGetDevice(&dev));
+    MECLIP_CUDA(cudaSetDevice(dev));
     if (dev < 0 || dev >= 64) return fail(MECLIP_EUNSUPPORTED, "device index %d out of range", dev);
     if (verdict[dev] == 0) {
         int major = 0;
@@ -257,6 +294,7 @@ static int launch_gemm_t(const CUtensorMap& ta, const CUtensorMap& tb, const Gem
     MECLIP_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GEMM_SMEM_BYTES));
     const int tiles = p.num_m_tiles * p.num_n_tiles;
     const int grid = tiles < sm_count() ? tiles : sm_count();
+    ScopedTiming timing(stream, t_tag, 2.0 * p.m * p.n * p.k);
     kern<<<grid, GEMM_THREADS, GEMM_SMEM_BYTES, stream>>>(ta, tb, p);
     MECLIP_CUDA(cudaGetLastError());
     return MECLIP_OK;
@@ -370,6 +408,42 @@ int meclip_read_status(const int* status, void* stream) {
     return MECLIP_OK;
 }
 
+long long meclip_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+int meclip_profile_begin(void) {
+    std::lock_guard<std::mutex> lock(g_prof_mutex);
+    for (auto& r : g_prof) { cudaEventDestroy(r.start); cudaEventDestroy(r.stop); }
+    g_prof.clear();
+    g_prof_on = true;
+    return MECLIP_OK;
+}
+
+int meclip_profile_end(double* ms_by_tag, long long* launches_by_tag, double* flops_by_tag, int n_tags) {
+    std::lock_guard<std::mutex> lock(g_prof_mutex);
+    g_prof_on = false;
+    for (int i = 0; i < n_tags; ++i) {
+        if (ms_by_tag) ms_by_tag[i] = 0.0;
+        if (launches_by_tag) launches_by_tag[i] = 0;
+        if (flops_by_tag) flops_by_tag[i] = 0.0;
+    }
+    int rc = MECLIP_OK;
+    for (auto& r : g_prof) {
+        float ms = 0.f;
+        if (cudaEventSynchronize(r.stop) != cudaSuccess || cudaEventElapsedTime(&ms, r.start, r.stop) != cudaSuccess)
+            rc = MECLIP_ECUDA;
+        if (r.tag >= 0 && r.tag < n_tags) {
+            if (ms_by_tag) ms_by_tag[r.tag] += ms;
+            if (launches_by_tag) launches_by_tag[r.tag] += 1;
+            if (flops_by_tag) flops_by_tag[r.tag] += r.flops;
+        }
+        cudaEventDestroy(r.start);
+        cudaEventDestroy(r.stop);
+    }
+    g_prof.clear();
+    if (rc) return fail(rc, "profile_end: reading an event failed");
+    return MECLIP_OK;
+}
+
 int meclip_normalize_fwd(const void* x, int x_dtype, int64_t rows, int64_t d, int64_t ldx, int normalize,
                          void* x_hat_bf16, int64_t ldh, float* inv_norm, void* stream) {
     if (x == nullptr || x_hat_bf16 == nullptr) return fail(MECLIP_EINVAL, "normalize_fwd: null pointer");
@@ -380,6 +454,7 @@ int meclip_normalize_fwd(const void* x, int x_dtype, int64_t rows, int64_t d, in
     const int wpb = ROW_KERNEL_THREADS / 32;
     const unsigned grid = (unsigned)((rows + wpb - 1) / wpb);
     cudaStream_t s = (cudaStream_t)stream;
+    ScopedTiming timing(s, TAG_ROW, 0.0);
     if (x_dtype == MECLIP_F32)
         normalize_fwd_kernel<float><<<grid, ROW_KERNEL_THREADS, 0, s>>>((const float*)x, ldx, rows, (int)d, normalize, (__nv_bfloat16*)x_hat_bf16, ldh, inv_norm);
     else if (x_dtype == MECLIP_BF16)
@@ -402,6 +477,7 @@ int meclip_normalize_bwd(const void* g, int g_dtype, int64_t ldg, const void* x_
     const int wpb = ROW_KERNEL_THREADS / 32;
     const unsigned grid = (unsigned)((rows + wpb - 1) / wpb);
     cudaStream_t s = (cudaStream_t)stream;
+    ScopedTiming timing(s, TAG_ROW, 0.0);
     const __nv_bfloat16* xh = (const __nv_bfloat16*)x_hat_bf16;
     if (g_dtype == MECLIP_F32 && dx_dtype == MECLIP_F32)
         normalize_bwd_kernel<float, float><<<grid, ROW_KERNEL_THREADS, 0, s>>>((const float*)g, ldg, xh, ldh, inv_norm, rows, (int)d, (float*)dx, lddx);
@@ -438,6 +514,7 @@ int meclip_sum_exp(int kind, const void* x_bf16, const void* y_bf16, int64_t row
     p.diag = diag_s;
     p.status = status;
     Operand a{x_bf16, ldx, false}, b{y_bf16, ldy, false};
+    t_tag = TAG_SUMS;
     return launch_gemm(EPI_SUMS, a, b, rows, cols, d, pick_bn(cols), p, (cudaStream_t)stream);
 }
 
@@ -447,6 +524,7 @@ int meclip_loss_finalize(int kind, const float* row_sum, const float* col_sum, c
     if (row_sum == nullptr || diag_s == nullptr || loss_out == nullptr || n < 1 || !(temperature > 0.f))
         return fail(MECLIP_EINVAL, "loss_finalize: bad argument");
     if (kind == MECLIP_CLIP && col_sum == nullptr) return fail(MECLIP_EINVAL, "loss_finalize: CLIP needs col_sum");
+    ScopedTiming timing((cudaStream_t)stream, TAG_ROW, 0.0);
     loss_finalize_kernel<<<1, 1024, 0, (cudaStream_t)stream>>>(row_sum, kind == MECLIP_CLIP ? col_sum : nullptr, diag_s, n,
                                                                1.f / temperature, scale, accumulate, loss_out);
     MECLIP_CUDA(cudaGetLastError());
@@ -513,6 +591,7 @@ int meclip_grad(int kind, const void* x_bf16, const void* y_bf16, int64_t rows, 
                 p.ldg = plan.ldg;
                 p.status = status;
                 Operand a{X + r0 * ldx, ldx, false}, b{Y + c0 * ldy, ldy, false};
+                t_tag = TAG_COEF;
                 rc = launch_gemm(EPI_COEF, a, b, nr, nc, d, pick_bn(nc), p, s);
                 if (rc) return rc;
             }
@@ -533,6 +612,7 @@ int meclip_grad(int kind, const void* x_bf16, const void* y_bf16, int64_t rows, 
                     else { p.out = dx_scratch; p.ld_out = d; p.out_bf16 = 0; }
                 }
                 Operand a{gpanel, plan.ldg, false}, b{Y + c0 * ldy, ldy, true};
+                t_tag = TAG_DX;
                 rc = launch_gemm(EPI_OUT, a, b, nr, d, nc, bn_d, p, s);
                 if (rc) return rc;
             }
@@ -554,6 +634,7 @@ int meclip_grad(int kind, const void* x_bf16, const void* y_bf16, int64_t rows, 
                     else { p.out = scratch; p.ld_out = d; p.out_bf16 = 0; }
                 }
                 Operand a{gpanel, plan.ldg, true}, b{X + r0 * ldx, ldx, true};
+                t_tag = TAG_DY;
                 rc = launch_gemm(EPI_OUT, a, b, nc, d, nr, bn_d, p, s);
                 if (rc) return rc;
             }
@@ -602,6 +683,7 @@ int meclip_debug_gemm(const void* a_bf16, int64_t lda, int a_mn_major, const voi
     p.ld_acc = ldc;
     p.status = status;
     Operand a{a_bf16, lda, a_mn_major != 0}, b{b_bf16, ldb, b_mn_major != 0};
+    t_tag = TAG_DX;
     return launch_gemm(EPI_OUT, a, b, m, n, k, tile_n > 0 ? tile_n : pick_bn(n), p, (cudaStream_t)stream);
 }
 

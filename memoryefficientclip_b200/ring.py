@@ -1,0 +1,237 @@
+"""Ring-distributed CLIP / LiT loss for one NVLink box: one process per GPU.
+
+Rank r keeps its B/N image rows (first argument) for the whole step.  The N text
+shards (second argument) rotate around the ring: at step s rank r works on shard
+(r + s) mod N while it already sends that shard to rank r-1 and receives the next
+one from rank r+1 (NCCL send/recv on the process group's stream, waited on only
+after the tile kernels of the step have been queued, so the transfer runs under the
+MMAs).  A shard always lands in local HBM before a kernel reads it.
+
+forward   row sums finish locally; per-shard column partial sums [N, b] are
+          reduce-scattered so that each rank ends with the column sums of its own
+          shard; the loss is the all-reduced sum of the local terms.
+backward  column sums are all-gathered (B floats); d(first) accumulates locally in
+          fp32 over the N steps; the d(second) partial of each visiting shard is
+          written to a [N, b, D] fp32 table and reduce-scattered at the end.
+
+The reference has no distributed code; the result is defined as the single-process
+loss on the concatenated global batch (rank-major row order).
+"""
+from __future__ import annotations
+
+from typing import List, Optional
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+
+from . import _lib, ops
+
+
+def shard_at(rank: int, step: int, world: int) -> int:
+    """Index of the text shard rank `rank` holds at ring step `step`."""
+    return (rank + step) % world
+
+
+def ring_neighbours(rank: int, world: int):
+    """(destination of this rank's sends, source of its receives)."""
+    return (rank - 1) % world, (rank + 1) % world
+
+
+class CudaBlockOps:
+    """Block primitives on the sm_100a kernels (the only product implementation)."""
+
+    def prepare(self, x, normalize):
+        if normalize:
+            return ops.normalize_fwd(x, True)
+        return ops.as_operand(x), None
+
+    def sum_exp(self, kind, x_hat, y_hat, t, row_sum, col_sum, diag, row_off, col_off):
+        ops.sum_exp(kind, x_hat, y_hat, t, row_sum, col_sum, diag, row_off, col_off)
+
+    def local_loss_sum(self, kind, row_sum, col_sum, diag, t, scale):
+        out = torch.empty((), dtype=torch.float32, device=row_sum.device)
+        ops.loss_finalize(kind, row_sum, col_sum, diag, t, scale, out)
+        return out
+
+    def grad(self, kind, x_hat, y_hat, t, row_sum, col_sum, go, scale, dx_acc, dy_out, row_off, col_off, workspace):
+        ops.grad_block(kind, x_hat, y_hat, t, row_sum, col_sum, go, scale, dx_acc, _lib.ACCUM_F32, dy_out,
+                       _lib.STORE_F32, row_off, col_off, workspace)
+
+    def workspace(self, rows, cols, d, device):
+        return ops.grad_workspace(rows, cols, d, device)
+
+    def reduce_scatter(self, out, table, group):
+        dist.reduce_scatter_tensor(out.view(-1), table.view(-1), op=dist.ReduceOp.SUM, group=group)
+
+    def all_gather(self, table, part, group):
+        dist.all_gather_into_tensor(table.view(-1), part.contiguous().view(-1), group=group)
+
+    def finish_grad(self, g_f32, x_hat, inv_norm, out_dtype):
+        if inv_norm is not None:
+            return ops.normalize_bwd(g_f32, x_hat, inv_norm, out_dtype)
+        if out_dtype == torch.float32:
+            return g_f32
+        return ops.normalize_fwd(g_f32, False)[0]
+
+
+def _rotate(cur: torch.Tensor, nxt: torch.Tensor, group, rank: int, world: int):
+    """Start sending `cur` to rank-1 and receiving `nxt` from rank+1; returns the requests."""
+    dst, src = ring_neighbours(rank, world)
+    dst_g = dist.get_global_rank(group, dst) if group is not None else dst
+    src_g = dist.get_global_rank(group, src) if group is not None else src
+    p2p = [dist.P2POp(dist.isend, cur, dst_g, group), dist.P2POp(dist.irecv, nxt, src_g, group)]
+    return dist.batch_isend_irecv(p2p)
+
+
+def ring_forward(block, kind, x_hat, y_hat, temperature, group, rank, world):
+    """Returns (loss, row_sum [b], col_sum_own [b] or None, diag [b])."""
+    b, d = x_hat.shape
+    dev = x_hat.device
+    clip = kind == _lib.CLIP
+    row_sum = torch.zeros(b, dtype=torch.float32, device=dev)
+    diag = torch.zeros(b, dtype=torch.float32, device=dev)
+    col_part = torch.zeros(world, b, dtype=torch.float32, device=dev) if clip else None
+    bufs = [y_hat, torch.empty_like(y_hat)] if world > 1 else [y_hat]
+    if world > 2:
+        bufs.append(torch.empty_like(y_hat))      # never receive into the caller's own shard
+    cur = 0
+    for step in range(world):
+        shard = shard_at(rank, step, world)
+        reqs = []
+        if step + 1 < world:
+            nxt = 1 + (step % 2) if world > 2 else 1
+            reqs = _rotate(bufs[cur], bufs[nxt], group, rank, world)
+        block.sum_exp(kind, x_hat, bufs[cur], temperature, row_sum, col_part[shard] if clip else None, diag,
+                      rank * b, shard * b)
+        for r in reqs:
+            r.wait()
+        if step + 1 < world:
+            cur = nxt
+    col_sum = None
+    if clip:
+        if world > 1:
+            col_sum = torch.empty(b, dtype=torch.float32, device=dev)
+            block.reduce_scatter(col_sum, col_part, group)
+        else:
+            col_sum = col_part[0]
+    loss = block.local_loss_sum(kind, row_sum, col_sum, diag, temperature, 1.0 / (b * world))
+    if world > 1:
+        dist.all_reduce(loss, op=dist.ReduceOp.SUM, group=group)
+    return loss, row_sum, col_sum, diag
+
+
+def ring_backward(block, kind, x_hat, y_hat, temperature, row_sum, col_sum, grad_out, grad_scale, group, rank, world):
+    """Returns (dx fp32 [b, D], dy_own fp32 [b, D] or None) w.r.t. the normalised operands."""
+    b, d = x_hat.shape
+    dev = x_hat.device
+    clip = kind == _lib.CLIP
+    col_all = None
+    if clip:
+        if world > 1:
+            col_all = torch.empty(world, b, dtype=torch.float32, device=dev)
+            block.all_gather(col_all, col_sum, group)
+        else:
+            col_all = col_sum.view(1, b)
+    dx = torch.zeros(b, d, dtype=torch.float32, device=dev)
+    dy_table = torch.empty(world, b, d, dtype=torch.float32, device=dev) if clip else None
+    workspace = block.workspace(b, b, d, dev)
+    bufs = [y_hat, torch.empty_like(y_hat)] if world > 1 else [y_hat]
+    if world > 2:
+        bufs.append(torch.empty_like(y_hat))
+    cur = 0
+    for step in range(world):
+        shard = shard_at(rank, step, world)
+        reqs = []
+        if step + 1 < world:
+            nxt = 1 + (step % 2) if world > 2 else 1
+            reqs = _rotate(bufs[cur], bufs[nxt], group, rank, world)
+        block.grad(kind, x_hat, bufs[cur], temperature, row_sum, col_all[shard] if clip else None, grad_out,
+                   grad_scale, dx, dy_table[shard] if clip else None, rank * b, shard * b, workspace)
+        for r in reqs:
+            r.wait()
+        if step + 1 < world:
+            cur = nxt
+    dy = None
+    if clip:
+        if world > 1:
+            dy = torch.empty(b, d, dtype=torch.float32, device=dev)
+            block.reduce_scatter(dy, dy_table, group)
+        else:
+            dy = dy_table[0]
+    return dx, dy
+
+
+class RingContrastiveLossFn(torch.autograd.Function):
+    """apply(x_local, y_local, temperature, kind, stable, normalize, group, block_ops) -> global loss."""
+
+    @staticmethod
+    def forward(ctx, x, y, temperature, kind, stable, normalize, group, block):
+        assert x.shape == y.shape and x.dim() == 2
+        world = dist.get_world_size(group) if dist.is_initialized() else 1
+        rank = dist.get_rank(group) if dist.is_initialized() else 0
+        block = block or CudaBlockOps()
+        x_hat, inv_x = block.prepare(x, normalize)
+        y_hat, inv_y = block.prepare(y, normalize)
+        loss, row_sum, col_sum, _diag = ring_forward(block, kind, x_hat, y_hat, temperature, group, rank, world)
+        saved = [x_hat, y_hat, row_sum]
+        if col_sum is not None:
+            saved.append(col_sum)
+        if normalize:
+            saved += [inv_x, inv_y]
+        ctx.save_for_backward(*saved)
+        ctx.ring = (float(temperature), kind, bool(stable), bool(normalize), x.dtype, y.dtype, group, rank, world, block)
+        return loss
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        temperature, kind, stable, normalize, x_dtype, y_dtype, group, rank, world, block = ctx.ring
+        saved = list(ctx.saved_tensors)
+        x_hat, y_hat, row_sum = saved[:3]
+        rest = saved[3:]
+        col_sum = rest.pop(0) if kind == _lib.CLIP else None
+        inv_x, inv_y = rest if normalize else (None, None)
+        b = x_hat.shape[0]
+        go = grad_output.detach().to(device=x_hat.device, dtype=torch.float32).reshape(1).contiguous()
+        scale = ops.grad_scale(b * world, temperature, stable)
+        dx, dy = ring_backward(block, kind, x_hat, y_hat, temperature, row_sum, col_sum, go, scale, group, rank, world)
+        dx = block.finish_grad(dx, x_hat, inv_x, x_dtype)
+        if dy is not None:
+            dy = block.finish_grad(dy, y_hat, inv_y, y_dtype)
+        return dx, dy, None, None, None, None, None, None
+
+
+class _RingLoss(nn.Module):
+    _kind = _lib.CLIP
+    _stable = False
+
+    def __init__(self, temperature=0.07, normalized_inputs=False, process_group=None, block_ops=None):
+        super().__init__()
+        self.temperature = temperature
+        self.normalized_inputs = normalized_inputs
+        self.process_group = process_group
+        self.block_ops = block_ops
+
+    def forward(self, first_local, second_local):
+        return RingContrastiveLossFn.apply(first_local, second_local, self.temperature, self._kind, self._stable,
+                                           not self.normalized_inputs, self.process_group, self.block_ops)
+
+
+class RingMemoryEfficientCLIPLoss(_RingLoss):
+    """forward(image_features_local, text_features_local): CLIP loss of the global batch."""
+    _kind = _lib.CLIP
+
+
+class RingStableMemoryEfficientCLIPLoss(_RingLoss):
+    _kind = _lib.CLIP
+    _stable = True
+
+
+class RingMemoryEfficientLiTLoss(_RingLoss):
+    """forward(text_features_local, image_features_local): text rows stay, image shards rotate."""
+    _kind = _lib.LIT
+
+
+class RingStableMemoryEfficientLiTLoss(_RingLoss):
+    _kind = _lib.LIT
+    _stable = True
