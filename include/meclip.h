@@ -136,6 +136,32 @@ int meclip_grad(int kind, const void* x_bf16, const void* y_bf16, int64_t rows, 
                 void* stream);
 
 /*
+ * meclip_grad for callers that have no device memory to give: the coefficient panel
+ * goes to a 32 MiB scratch array that is part of the library image, so this entry
+ * point takes no workspace and never calls cudaMalloc / cudaFree or any other
+ * allocating routine.  It is meant for hosts that bind the loss as a fixed
+ * (inputs, outputs) plugin with no hook for scratch buffers, and for processes whose
+ * device memory is already handed out in full to another allocator, where a fresh
+ * allocation would fail or stall the device.
+ *   - Limit: rows <= 4096 and cols <= 4096 (any d).  Larger blocks return
+ *     MECLIP_ENOSPC; use meclip_grad with a workspace for those.
+ *   - The 32 MiB stay allocated on every GPU that loads the library, until exit.
+ *   - The first call on each device looks up the scratch address (a one-time host-side
+ *     set-up with that device current); make that first call before any stream capture.
+ *   - All calls on a device share the one array and it keeps the previous call's
+ *     contents.  Nothing needs clearing (each call overwrites what it later reads),
+ *     but two calls that overlap on the GPU - different streams, or different host
+ *     threads on different streams - race on it: keep them on one stream or order
+ *     them with events.
+ * Arguments and results are those of meclip_grad without workspace/workspace_bytes.
+ * This entry point has no counterpart in the reference.
+ */
+int meclip_grad_static(int kind, const void* x_bf16, const void* y_bf16, int64_t rows, int64_t cols, int64_t d,
+                       int64_t ldx, int64_t ldy, float temperature, int64_t row_off, int64_t col_off,
+                       const float* row_sum, const float* col_sum, const float* grad_out, float grad_scale, void* dx,
+                       int dx_mode, int64_t lddx, void* dy, int dy_mode, int64_t lddy, int* status, void* stream);
+
+/*
  * One-call forward for a whole batch on one GPU: zeroes the sums, runs
  * meclip_sum_exp with offsets 0 and meclip_loss_finalize with scale 1/B.
  * Mirrors MemoryEfficient{CLIP,LiT}LossNormed.forward (clip_loss.py:160-213,

@@ -39,6 +39,9 @@ SIGNATURES = {
     "meclip_grad": (c_int, [c_int, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64, c_float, c_int64,
                             c_int64, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_int, c_int64, c_void_p,
                             c_int, c_int64, c_void_p, c_size_t, c_void_p, c_void_p]),
+    "meclip_grad_static": (c_int, [c_int, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64, c_float,
+                                   c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_int, c_int64,
+                                   c_void_p, c_int, c_int64, c_void_p, c_void_p]),
     "meclip_loss_forward": (c_int, [c_int, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_float,
                                     c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "meclip_loss_backward": (c_int, [c_int, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_float,

@@ -667,6 +667,58 @@ int meclip_loss_backward(int kind, const void* x_bf16, const void* y_bf16, int64
                        grad_scale, dx, dx_mode, lddx, dy, dy_mode, lddy, workspace, workspace_bytes, status, stream);
 }
 
+// ------------------------------------------------------------------------------------
+// backward without a caller-provided workspace
+// ------------------------------------------------------------------------------------
+// The coefficient panel of meclip_grad_static lives here instead of in caller memory.
+// 4096 x 4096 bf16 = 32 MiB, resident on every GPU that loads this library until the
+// process exits.  In host code the name below is only a handle for the symbol, not a
+// device address: static_scratch_ptr() asks the runtime for the real address once per device.
+static constexpr long long STATIC_MAX_ROWS = 4096;
+static constexpr long long STATIC_MAX_COLS = 4096;
+static constexpr size_t STATIC_SCRATCH_BYTES = (size_t)STATIC_MAX_ROWS * STATIC_MAX_COLS * 2;
+static __device__ __align__(256) unsigned char g_static_scratch[STATIC_SCRATCH_BYTES];
+
+static std::mutex g_scratch_mutex;
+static void* g_scratch_ptr[64] = {nullptr};
+
+static int static_scratch_ptr(void** out) {
+    int dev = 0;
+    MECLIP_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return fail(MECLIP_EUNSUPPORTED, "device index %d out of range", dev);
+    std::lock_guard<std::mutex> lock(g_scratch_mutex);
+    if (g_scratch_ptr[dev] == nullptr) {
+        void* ptr = nullptr;
+        MECLIP_CUDA(cudaSetDevice(dev));   // the symbol is looked up in the current device's copy of the module
+        MECLIP_CUDA(cudaGetSymbolAddress(&ptr, g_static_scratch));
+        if (ptr == nullptr || (reinterpret_cast<uintptr_t>(ptr) & 255u) != 0)
+            return fail(MECLIP_ECUDA, "static scratch: bad symbol address %p", ptr);
+        g_scratch_ptr[dev] = ptr;
+    }
+    *out = g_scratch_ptr[dev];
+    return MECLIP_OK;
+}
+
+int meclip_grad_static(int kind, const void* x_bf16, const void* y_bf16, int64_t rows, int64_t cols, int64_t d,
+                       int64_t ldx, int64_t ldy, float temperature, int64_t row_off, int64_t col_off,
+                       const float* row_sum, const float* col_sum, const float* grad_out, float grad_scale, void* dx,
+                       int dx_mode, int64_t lddx, void* dy, int dy_mode, int64_t lddy, int* status, void* stream) {
+    if (rows < 1 || cols < 1) return fail(MECLIP_EINVAL, "grad_static: rows and cols must be >= 1");
+    if (rows > STATIC_MAX_ROWS || cols > STATIC_MAX_COLS)
+        return fail(MECLIP_ENOSPC,
+                    "grad_static: block %lld x %lld exceeds the built-in scratch (at most %lld x %lld); "
+                    "use meclip_grad with a caller workspace",
+                    (long long)rows, (long long)cols, STATIC_MAX_ROWS, STATIC_MAX_COLS);
+    void* scratch = nullptr;
+    int rc = static_scratch_ptr(&scratch);
+    if (rc) return rc;
+    // Nothing in the scratch has to start at zero: every panel element that is read was written
+    // by this call first, and the tile loads are bounded to the rows x cols that were written.
+    return meclip_grad(kind, x_bf16, y_bf16, rows, cols, d, ldx, ldy, temperature, row_off, col_off, row_sum, col_sum,
+                       grad_out, grad_scale, dx, dx_mode, lddx, dy, dy_mode, lddy, scratch, STATIC_SCRATCH_BYTES,
+                       status, stream);
+}
+
 int meclip_debug_gemm(const void* a_bf16, int64_t lda, int a_mn_major, const void* b_bf16, int64_t ldb, int b_mn_major,
                       int64_t m, int64_t n, int64_t k, int tile_n, float* c, int64_t ldc, const float* c_in,
                       int* status, void* stream) {

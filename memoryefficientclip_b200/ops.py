@@ -128,6 +128,22 @@ def grad_block(kind, x_hat, y_hat, temperature, row_sum, col_sum, grad_out, grad
                                            workspace.data_ptr(), workspace.numel(), _ptr(status), _stream(x_hat)))
 
 
+def grad_block_static(kind, x_hat, y_hat, temperature, row_sum, col_sum, grad_out, grad_scale, dx, dx_mode, dy, dy_mode,
+                      row_off=0, col_off=0, status=None):
+    """grad_block on the library's built-in 32 MiB scratch (meclip_grad_static): no workspace
+    argument and no allocation inside the call, for blocks of at most 4096 x 4096.  Calls share
+    the scratch, so keep them on one stream."""
+    rows, d = x_hat.shape
+    cols = y_hat.shape[0]
+    with torch.cuda.device(x_hat.device):
+        _lib.check(_lib.load().meclip_grad_static(kind, x_hat.data_ptr(), y_hat.data_ptr(), rows, cols, d,
+                                                  x_hat.stride(0), y_hat.stride(0), float(temperature), row_off,
+                                                  col_off, row_sum.data_ptr(), _ptr(col_sum), _ptr(grad_out),
+                                                  float(grad_scale), dx.data_ptr(), dx_mode, dx.stride(0), _ptr(dy),
+                                                  dy_mode, dy.stride(0) if dy is not None else 0, _ptr(status),
+                                                  _stream(x_hat)))
+
+
 def loss_backward(kind, x_hat, y_hat, temperature, row_sum, col_sum, grad_out, grad_scale, dx_dtype, dy_dtype,
                   status=None):
     """Whole-batch backward on one GPU.  Returns (dx, dy or None) w.r.t. the normalised operands."""
