@@ -183,8 +183,9 @@ loss_finalize_kernel(const float* __restrict__ r, const float* __restrict__ c, c
     __shared__ double part[1024];
     double acc = 0.0;
     for (long long i = threadIdx.x; i < n; i += 1024) {
-        double t = log((double)r[i]);
-        if (c != nullptr) t = 0.5 * (t + log((double)c[i]));
+        // fp32 logarithms (fp64 transcendentals are slow on this part), fp64 accumulation
+        double t = (double)logf(r[i]);
+        if (c != nullptr) t = 0.5 * (t + (double)logf(c[i]));
         acc += t - ((double)diag[i] - 1.0) * (double)inv_t;
     }
     part[threadIdx.x] = acc;

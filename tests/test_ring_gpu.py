@@ -1,0 +1,92 @@
+"""The ring-distributed loss on real GPUs (NCCL), one process per GPU, against the dense
+oracle on the concatenated batch.  Skipped on a box with a single GPU."""
+import os
+import socket
+import tempfile
+
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+from oracle import dense
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, kind, b_global, d, dtype_name, normalize, outdir):
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        from memoryefficientclip_b200 import ring
+        dtype = getattr(torch, dtype_name)
+        g = torch.Generator().manual_seed(0)
+        x = torch.randn(b_global, d, generator=g)
+        y = torch.randn(b_global, d, generator=g)
+        if not normalize:
+            x, y = torch.nn.functional.normalize(x, dim=1), torch.nn.functional.normalize(y, dim=1)
+        x, y = x.to(dtype), y.to(dtype)
+        b = b_global // world
+        xl = x[rank * b:(rank + 1) * b].cuda().requires_grad_(True)
+        yl = y[rank * b:(rank + 1) * b].cuda().requires_grad_(True)
+        cls = ring.RingMemoryEfficientCLIPLoss if kind == "clip" else ring.RingMemoryEfficientLiTLoss
+        loss = cls(0.07, not normalize)(xl, yl)
+        loss.backward()
+        torch.cuda.synchronize()
+        torch.save({"loss": loss.item(), "dx": xl.grad.float().cpu(),
+                    "dy": None if yl.grad is None else yl.grad.float().cpu()}, os.path.join(outdir, f"r{rank}.pt"))
+    finally:
+        dist.destroy_process_group()
+
+
+def _run(world, kind, b_global, d, dtype_name, normalize):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    with tempfile.TemporaryDirectory() as outdir:
+        mp.spawn(_worker, args=(world, _free_port(), kind, b_global, d, dtype_name, normalize, outdir), nprocs=world,
+                 join=True)
+        res = [torch.load(os.path.join(outdir, f"r{r}.pt")) for r in range(world)]
+    dtype = getattr(torch, dtype_name)
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(b_global, d, generator=g)
+    y = torch.randn(b_global, d, generator=g)
+    if not normalize:
+        x, y = torch.nn.functional.normalize(x, dim=1), torch.nn.functional.normalize(y, dim=1)
+    x, y = x.to(dtype), y.to(dtype)
+    if kind == "clip":
+        loss, gx, gy = dense.clip_dense(x, y, 0.07, not normalize)
+    else:
+        loss, gx = dense.lit_dense(x, y, 0.07, not normalize)
+        gy = None
+    dx = torch.cat([r["dx"] for r in res])
+    for r in res:
+        assert dense.loss_rel_err(r["loss"], loss) <= dense.LOSS_RTOL
+    if gy is not None:
+        dy = torch.cat([r["dy"] for r in res])
+        dense.assert_parity(res[0]["loss"], loss, (dx, dy), (gx, gy), f"ring{world} {kind}")
+    else:
+        assert all(r["dy"] is None for r in res)
+        dense.assert_parity(res[0]["loss"], loss, (dx,), (gx,), f"ring{world} {kind}")
+
+
+@pytest.mark.parametrize("kind,b,d,dtype,normalize", [("clip", 1024, 128, "bfloat16", False),
+                                                      ("clip", 768, 64, "float32", True),
+                                                      ("lit", 512, 256, "bfloat16", True)])
+def test_ring_two_gpus(kind, b, d, dtype, normalize):
+    _run(2, kind, b, d, dtype, normalize)
+
+
+def test_ring_four_gpus():
+    _run(4, "clip", 2048, 128, "bfloat16", False)
+
+
+def test_ring_eight_gpus():
+    _run(8, "clip", 4096, 64, "bfloat16", True)
