@@ -8,8 +8,11 @@
  *  - The library never allocates or frees device memory: the caller owns every
  *    buffer, including the workspace (size from meclip_grad_workspace_bytes).
  *  - Every call is asynchronous on `stream` (a cudaStream_t passed as void*),
- *    holds no thread-local state and may be made from any host thread (PyTorch
- *    runs backward on its autograd thread).
+ *    and may be made from any host thread (PyTorch runs backward on its autograd
+ *    thread); calls from several threads are serialised where they share state.
+ *    meclip_grad may also use two library-owned side streams, forked from and
+ *    joined back into `stream`, so that independent kernels of one backward overlap
+ *    (set MECLIP_SERIAL=1 to keep everything on `stream`).
  *  - Return value: MECLIP_OK or an error code; meclip_last_error() gives text.
  *    Nothing here calls exit/abort or throws.
  *  - Matrices are row-major with a leading dimension in ELEMENTS (ld >= D).
@@ -137,22 +140,22 @@ int meclip_grad(int kind, const void* x_bf16, const void* y_bf16, int64_t rows, 
 
 /*
  * meclip_grad for callers that have no device memory to give: the coefficient panel
- * goes to a 32 MiB scratch array that is part of the library image, so this entry
- * point takes no workspace and never calls cudaMalloc / cudaFree or any other
- * allocating routine.  It is meant for hosts that bind the loss as a fixed
+ * goes to a 32 MiB (+ 4 KiB of tile counters) scratch array that is part of the
+ * library image, so this entry point takes no workspace, never calls cudaMalloc /
+ * cudaFree or any other allocating routine, and keeps all its launches on `stream`.  It is meant for hosts that bind the loss as a fixed
  * (inputs, outputs) plugin with no hook for scratch buffers, and for processes whose
  * device memory is already handed out in full to another allocator, where a fresh
  * allocation would fail or stall the device.
  *   - Limit: rows <= 4096 and cols <= 4096 (any d).  Larger blocks return
  *     MECLIP_ENOSPC; use meclip_grad with a workspace for those.
- *   - The 32 MiB stay allocated on every GPU that loads the library, until exit.
+ *   - The scratch stays allocated on every GPU that loads the library, until exit.
  *   - The first call on each device looks up the scratch address (a one-time host-side
  *     set-up with that device current); make that first call before any stream capture.
  *   - All calls on a device share the one array and it keeps the previous call's
- *     contents.  Nothing needs clearing (each call overwrites what it later reads),
- *     but two calls that overlap on the GPU - different streams, or different host
- *     threads on different streams - race on it: keep them on one stream or order
- *     them with events.
+ *     contents.  The call clears the tile counters, the only part that must start at
+ *     zero; the panel is overwritten before it is read.  Two calls that overlap on
+ *     the GPU - different streams, or different host threads on different streams -
+ *     race on it: keep them on one stream or order them with events.
  * Arguments and results are those of meclip_grad without workspace/workspace_bytes.
  * This entry point has no counterpart in the reference.
  */

@@ -7,6 +7,7 @@
 #include <cmath>
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <atomic>
 #include <mutex>
@@ -176,6 +177,41 @@ normalize_bwd_kernel(const TG* __restrict__ g, long long ldg, const __nv_bfloat1
     }
 }
 
+// out[c][r] = in[r][c] for a bf16 matrix: 64 x 64 tiles through shared memory, 16-byte global accesses.
+// The contractions read X^T / Y^T as K-major B operands (K-major tiles feed the tensor cores
+// measurably faster than MN-major ones when A is the transposed panel).
+__global__ void __launch_bounds__(256)
+transpose_bf16_kernel(const __nv_bfloat16* __restrict__ in, long long ld_in, long long rows, int cols,
+                      __nv_bfloat16* __restrict__ out, long long ld_out) {
+    __shared__ __nv_bfloat16 tile[64][64 + 8];
+    const long long r0 = (long long)blockIdx.x * 64;
+    const int c0 = blockIdx.y * 64;
+    const int t = threadIdx.x;
+    const int cc = (t & 7) * 8;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const int rr = (t >> 3) + h * 32;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (r0 + rr < rows && c0 + cc < cols) v = *reinterpret_cast<const uint4*>(in + (r0 + rr) * ld_in + c0 + cc);
+        const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(&v);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) tile[cc + i][rr] = e[i];
+    }
+    __syncthreads();
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const int oc = (t >> 3) + h * 32;     // output row = input column
+        const int orr = (t & 7) * 8;          // 8 consecutive output columns = input rows
+        if (c0 + oc < cols && r0 + orr < rows) {   // rows is padded to a multiple of 8 in ld_out, stores stay in the pitch
+            uint4 v;
+            __nv_bfloat16* e = reinterpret_cast<__nv_bfloat16*>(&v);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) e[i] = tile[oc][orr + i];
+            *reinterpret_cast<uint4*>(out + (long long)(c0 + oc) * ld_out + r0 + orr) = v;
+        }
+    }
+}
+
 // loss (+)= scale * sum_i [ w (log r_i + log c_i) - (s_ii - 1)/T ]: one block, fixed order.
 __global__ void __launch_bounds__(1024)
 loss_finalize_kernel(const float* __restrict__ r, const float* __restrict__ c, const float* __restrict__ diag,
@@ -237,6 +273,32 @@ static int make_tmap(CUtensorMap* tm, const void* base, long long inner, long lo
     return MECLIP_OK;
 }
 
+// Coefficient panel in its column-blocked layout: chunk c (64 columns) is a contiguous
+// [rows_alloc x 64] bf16 slab.  Tensor map dims {64, rows, chunks}; box {64, box_rows, 1}.
+static int make_tmap_blocked(CUtensorMap* tm, const void* base, long long rows, long long chunks, long long rows_alloc,
+                             int box_rows, long long chunks_alloc) {
+    EncodeTiledFn enc = get_encode_fn();
+    if (enc == nullptr) return fail(MECLIP_EUNSUPPORTED, "cuTensorMapEncodeTiled not available from this driver");
+    cuuint64_t dims[3] = {64, (cuuint64_t)rows, (cuuint64_t)chunks};
+    // MECLIP_PANEL_ROWMAJOR=1 (experiments): same 3-D view over a plain row-major panel whose pitch
+    // is chunks_alloc * 64 elements; chunk c then starts 128 bytes after chunk c-1 inside a row.
+    static const bool rowmajor = []() {
+        const char* v = std::getenv("MECLIP_PANEL_ROWMAJOR");
+        return v != nullptr && v[0] == '1';
+    }();
+    cuuint64_t strides[2] = {128, (cuuint64_t)rows_alloc * 128};
+    if (rowmajor) { strides[0] = (cuuint64_t)chunks_alloc * 128; strides[1] = 128; }
+    cuuint32_t box[3] = {64, (cuuint32_t)box_rows, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = enc(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        return fail(MECLIP_ECUDA, "cuTensorMapEncodeTiled (blocked panel) failed (%d) rows=%lld chunks=%lld alloc=%lld box=%d",
+                    (int)r, rows, chunks, rows_alloc, box_rows);
+    return MECLIP_OK;
+}
+
 static int sm_count() {
     static int cached[64] = {0};
     int dev = 0;
@@ -287,36 +349,55 @@ struct Operand {
     const void* ptr;
     long long ld;      // elements
     bool mn_major;     // false: [extent rows][K contiguous]; true: [K rows][extent contiguous]
+    // > 0: the operand is a coefficient panel in column-blocked layout with this many allocated rows
+    // per 64-column chunk (ld then holds the allocated chunk count); only for the A operand
+    long long blocked_rows_alloc = 0;
 };
 
 template <int EPI, bool A_MN, bool B_MN>
-static int launch_gemm_t(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, cudaStream_t stream) {
+static int launch_gemm_t(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmParams& p,
+                         size_t smem_bytes, cudaStream_t stream) {
     auto kern = umma_gemm_kernel<EPI, A_MN, B_MN>;
-    MECLIP_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GEMM_SMEM_BYTES));
+    MECLIP_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_LIMIT));
     const int tiles = p.num_m_tiles * p.num_n_tiles;
     const int grid = tiles < sm_count() ? tiles : sm_count();
     ScopedTiming timing(stream, t_tag, 2.0 * p.m * p.n * p.k);
-    kern<<<grid, GEMM_THREADS, GEMM_SMEM_BYTES, stream>>>(ta, tb, p);
+    kern<<<grid, GEMM_THREADS, smem_bytes, stream>>>(ta, tb, tc, p);
     MECLIP_CUDA(cudaGetLastError());
     return MECLIP_OK;
 }
 
+// `panel` (EPI_COEF only): the bf16 output panel [m x n], column-blocked with panel_rows_alloc rows
+// per chunk, written by TMA stores.
 static int launch_gemm(int epi, const Operand& a, const Operand& b, long long m, long long n, long long k, int bn,
-                       GemmParams p, cudaStream_t stream) {
+                       GemmParams p, cudaStream_t stream, void* panel = nullptr, long long panel_rows_alloc = 0,
+                       long long panel_chunks_alloc = 0) {
     if (m < 1 || n < 1 || k < 1) return fail(MECLIP_EINVAL, "gemm extents must be >= 1 (m=%lld n=%lld k=%lld)", m, n, k);
     if (m > 0x7fffffffLL || n > 0x7fffffffLL || k > 0x7fffffffLL) return fail(MECLIP_EINVAL, "gemm extent exceeds 2^31");
-    if (bn < 32 || bn > MAX_BN || bn % 32 != 0 || (b.mn_major && bn % 64 != 0))
+    if (bn < 32 || bn > MAX_BN || bn % 32 != 0 || ((b.mn_major || epi == EPI_COEF) && bn % 64 != 0))
         return fail(MECLIP_EINVAL, "tile width %d not supported", bn);
-    if (!aligned16(a.ptr) || !aligned16(b.ptr) || a.ld % 8 != 0 || b.ld % 8 != 0)
+    if (!aligned16(a.ptr) || !aligned16(b.ptr) || (a.blocked_rows_alloc == 0 && a.ld % 8 != 0) || b.ld % 8 != 0)
         return fail(MECLIP_EINVAL, "operands must be 16-byte aligned with pitches that are multiples of 8 elements");
-    CUtensorMap ta, tb;
+    CUtensorMap ta, tb, tc;
     int rc;
-    if (a.mn_major) rc = make_tmap(&ta, a.ptr, m, k, a.ld, 64, BK);
-    else            rc = make_tmap(&ta, a.ptr, k, m, a.ld, BK, BM);
+    if (a.blocked_rows_alloc > 0) {
+        // panel of G [rows x cols]: as A = G (K-major) rows = m, cols = k; as A = G^T (MN-major) rows = k, cols = m
+        if (a.mn_major) rc = make_tmap_blocked(&ta, a.ptr, k, (m + 63) / 64, a.blocked_rows_alloc, BK, a.ld);
+        else            rc = make_tmap_blocked(&ta, a.ptr, m, (k + 63) / 64, a.blocked_rows_alloc, BM, a.ld);
+        p.a_blocked = 1;
+    } else if (a.mn_major) rc = make_tmap(&ta, a.ptr, m, k, a.ld, 64, BK);
+    else                   rc = make_tmap(&ta, a.ptr, k, m, a.ld, BK, BM);
     if (rc) return rc;
     if (b.mn_major) rc = make_tmap(&tb, b.ptr, n, k, b.ld, 64, BK);
     else            rc = make_tmap(&tb, b.ptr, k, n, b.ld, BK, bn);
     if (rc) return rc;
+    if (epi == EPI_COEF) {
+        if (panel == nullptr || !aligned16(panel) || panel_rows_alloc < m) return fail(MECLIP_EINVAL, "coefficient panel misaligned");
+        rc = make_tmap_blocked(&tc, panel, m, (n + 63) / 64, panel_rows_alloc, 32, panel_chunks_alloc);   // one warp's 32 rows x 64 columns per store
+        if (rc) return rc;
+    } else {
+        tc = ta;
+    }
     p.m = (int)m; p.n = (int)n; p.k = (int)k; p.bn = bn;
     p.num_m_tiles = (int)((m + BM - 1) / BM);
     p.num_n_tiles = (int)((n + bn - 1) / bn);
@@ -324,15 +405,26 @@ static int launch_gemm(int epi, const Operand& a, const Operand& b, long long m,
     p.group_m = 16;
     p.idesc = umma_idesc_bf16(BM, bn, a.mn_major ? 1 : 0, b.mn_major ? 1 : 0);
     if ((long long)p.num_m_tiles * p.num_n_tiles > 0x7fffffffLL) return fail(MECLIP_EINVAL, "too many tiles");
-#define MECLIP_DISPATCH(E)                                                                          \
-    if (epi == E) {                                                                                 \
-        if (!a.mn_major && !b.mn_major) return launch_gemm_t<E, false, false>(ta, tb, p, stream);   \
-        if (!a.mn_major && b.mn_major) return launch_gemm_t<E, false, true>(ta, tb, p, stream);     \
-        if (a.mn_major && b.mn_major) return launch_gemm_t<E, true, true>(ta, tb, p, stream);       \
-        return launch_gemm_t<E, true, false>(ta, tb, p, stream);                                    \
+    // shared memory: [<= 1023 B alignment slack][stages][tail]; as many stages as fit, at least 2
+    p.stage_bytes = A_STAGE_BYTES + bn * BK * 2;
+    int stages = (SMEM_LIMIT - 1024 - tail_bytes(epi)) / p.stage_bytes;
+    if (stages > MAX_STAGES) stages = MAX_STAGES;
+    static const int env_max_stages = []() { const char* v = std::getenv("MECLIP_MAX_STAGES"); return v ? std::atoi(v) : 0; }();
+    static const bool env_static = []() { const char* v = std::getenv("MECLIP_STATIC_SCHED"); return v && v[0] == '1'; }();
+    if (env_max_stages >= 2 && stages > env_max_stages) stages = env_max_stages;
+    if (env_static) p.tile_counter = nullptr;
+    if (stages < 2) return fail(MECLIP_EINVAL, "tile does not fit shared memory");
+    p.num_stages = stages;
+    const size_t smem_bytes = 1024 + (size_t)stages * p.stage_bytes + tail_bytes(epi);
+#define MECLIP_DISPATCH(E)                                                                                        \
+    if (epi == E) {                                                                                               \
+        if (!a.mn_major && !b.mn_major) return launch_gemm_t<E, false, false>(ta, tb, tc, p, smem_bytes, stream); \
+        if (!a.mn_major && b.mn_major) return launch_gemm_t<E, false, true>(ta, tb, tc, p, smem_bytes, stream);   \
+        if (a.mn_major && b.mn_major) return launch_gemm_t<E, true, true>(ta, tb, tc, p, smem_bytes, stream);     \
+        return launch_gemm_t<E, true, false>(ta, tb, tc, p, smem_bytes, stream);                                  \
     }
-    if (epi == EPI_SUMS) return launch_gemm_t<EPI_SUMS, false, false>(ta, tb, p, stream);
-    if (epi == EPI_COEF) return launch_gemm_t<EPI_COEF, false, false>(ta, tb, p, stream);
+    if (epi == EPI_SUMS) return launch_gemm_t<EPI_SUMS, false, false>(ta, tb, tc, p, smem_bytes, stream);
+    if (epi == EPI_COEF) return launch_gemm_t<EPI_COEF, false, false>(ta, tb, tc, p, smem_bytes, stream);
     MECLIP_DISPATCH(EPI_OUT)
 #undef MECLIP_DISPATCH
     return fail(MECLIP_EINVAL, "unknown epilogue %d", epi);
@@ -346,11 +438,15 @@ static constexpr long long PANEL_BYTES = 512ll << 20;          // bf16 coefficie
 
 struct GradPlan {
     long long row_block, panel_w, ldg;
-    long long n_row_blocks, n_panels;
-    size_t g_bytes, dx_bytes, dy_bytes;
+    long long n_row_blocks, n_panels, n_blocks;
+    int g_buffers;                       // 2 when there is more than one block: panel t+1 is formed while t is contracted
+    size_t g_bytes, dx_bytes, dy_bytes, counter_bytes;
+    long long ld_xt, ld_yt;              // pitches of the transposed operand copies X^T [d x rows], Y^T [d x cols]
+    size_t xt_bytes, yt_bytes;
+    size_t total() const { return g_bytes * g_buffers + dx_bytes + dy_bytes + counter_bytes + xt_bytes + yt_bytes; }
 };
 
-static GradPlan plan_grad(long long rows, long long cols, long long d) {
+static GradPlan plan_grad(long long rows, long long cols, long long d, bool transposed_copies = true) {
     GradPlan g;
     g.row_block = rows < ROW_BLOCK ? rows : ROW_BLOCK;
     long long w = PANEL_BYTES / (g.row_block * 2) / 256 * 256;
@@ -361,10 +457,63 @@ static GradPlan plan_grad(long long rows, long long cols, long long d) {
     g.ldg = (long long)round_up((size_t)w, 64);
     g.n_row_blocks = (rows + g.row_block - 1) / g.row_block;
     g.n_panels = (cols + w - 1) / w;
+    g.n_blocks = g.n_row_blocks * g.n_panels;
+    g.g_buffers = g.n_blocks > 1 ? 2 : 1;
     g.g_bytes = round_up((size_t)g.row_block * g.ldg * 2, 256);
     g.dx_bytes = g.n_panels > 1 ? round_up((size_t)g.row_block * d * 4, 256) : 0;
     g.dy_bytes = g.n_row_blocks > 1 ? round_up((size_t)cols * d * 4, 256) : 0;
+    g.counter_bytes = round_up((size_t)g.n_blocks * 3 * sizeof(unsigned int), 256);   // one tile counter per launch
+    g.ld_xt = (long long)round_up((size_t)rows, 8);
+    g.ld_yt = (long long)round_up((size_t)cols, 8);
+    g.xt_bytes = transposed_copies ? round_up((size_t)d * g.ld_xt * 2, 256) : 0;
+    g.yt_bytes = transposed_copies ? round_up((size_t)d * g.ld_yt * 2, 256) : 0;
     return g;
+}
+
+// ------------------------------------------------------------------------------------
+// side streams: the two contractions of a block and the next block's coefficient pass
+// run next to each other, so the tail of one kernel is filled by the next
+// ------------------------------------------------------------------------------------
+struct SideStreams {
+    bool ready = false;
+    cudaStream_t sx = nullptr, sy = nullptr;
+    cudaEvent_t coef[2] = {nullptr, nullptr}, dx[2] = {nullptr, nullptr}, dy[2] = {nullptr, nullptr};
+    cudaEvent_t join_x = nullptr, join_y = nullptr;
+    std::mutex mutex;       // one meclip_grad enqueue at a time per device: the events are shared
+};
+static SideStreams g_side[64];
+static std::mutex g_side_init_mutex;
+
+static int get_side_streams(SideStreams** out) {
+    int dev = 0;
+    MECLIP_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return fail(MECLIP_EUNSUPPORTED, "device index %d out of range", dev);
+    SideStreams& ss = g_side[dev];
+    std::lock_guard<std::mutex> lock(g_side_init_mutex);
+    if (!ss.ready) {
+        MECLIP_CUDA(cudaStreamCreateWithFlags(&ss.sx, cudaStreamNonBlocking));
+        MECLIP_CUDA(cudaStreamCreateWithFlags(&ss.sy, cudaStreamNonBlocking));
+        cudaEvent_t* evs[8] = {&ss.coef[0], &ss.coef[1], &ss.dx[0], &ss.dx[1], &ss.dy[0], &ss.dy[1], &ss.join_x, &ss.join_y};
+        for (auto e : evs) MECLIP_CUDA(cudaEventCreateWithFlags(e, cudaEventDisableTiming));
+        ss.ready = true;
+    }
+    *out = &ss;
+    return MECLIP_OK;
+}
+
+static bool transposes_allowed() {
+    static const bool off = []() { const char* v = std::getenv("MECLIP_NO_TRANSPOSE"); return v && v[0] == '1'; }();
+    return !off;
+}
+
+static bool overlap_allowed() {
+    static const bool env_serial = []() {
+        const char* v = std::getenv("MECLIP_SERIAL");
+        return v != nullptr && v[0] != '\0' && v[0] != '0';
+    }();
+    if (env_serial) return false;
+    std::lock_guard<std::mutex> lock(g_prof_mutex);
+    return !g_prof_on;      // per-kernel timing wants kernels that do not share the GPU
 }
 
 static int check_out_mode(int mode) { return mode == MECLIP_STORE_BF16 || mode == MECLIP_STORE_F32 || mode == MECLIP_ACCUM_F32; }
@@ -534,15 +683,20 @@ int meclip_loss_finalize(int kind, const float* row_sum, const float* col_sum, c
 
 size_t meclip_grad_workspace_bytes(int64_t rows, int64_t cols, int64_t d) {
     if (rows < 1 || cols < 1 || d < 1) return 0;
-    const GradPlan g = plan_grad(rows, cols, d);
-    return g.g_bytes + g.dx_bytes + g.dy_bytes + 256;
+    return plan_grad(rows, cols, d, true).total() + 256;
 }
 
-int meclip_grad(int kind, const void* x_bf16, const void* y_bf16, int64_t rows, int64_t cols, int64_t d, int64_t ldx,
-                int64_t ldy, float temperature, int64_t row_off, int64_t col_off, const float* row_sum,
-                const float* col_sum, const float* grad_out, float grad_scale, void* dx, int dx_mode, int64_t lddx,
-                void* dy, int dy_mode, int64_t lddy, void* workspace, size_t workspace_bytes, int* status,
-                void* stream) {
+}  // extern "C"
+
+namespace meclip {
+
+// The backward over one rows x cols block.  overlap == false keeps every launch on the caller's
+// stream and creates no stream or event.
+static int grad_impl(int kind, const void* x_bf16, const void* y_bf16, int64_t rows, int64_t cols, int64_t d, int64_t ldx,
+                     int64_t ldy, float temperature, int64_t row_off, int64_t col_off, const float* row_sum,
+                     const float* col_sum, const float* grad_out, float grad_scale, void* dx, int dx_mode, int64_t lddx,
+                     void* dy, int dy_mode, int64_t lddy, void* workspace, size_t workspace_bytes, int* status,
+                     cudaStream_t s0, bool overlap, bool transposed_copies) {
     if (kind != MECLIP_CLIP && kind != MECLIP_LIT) return fail(MECLIP_EINVAL, "grad: bad kind %d", kind);
     if (x_bf16 == nullptr || y_bf16 == nullptr || row_sum == nullptr || dx == nullptr || workspace == nullptr)
         return fail(MECLIP_EINVAL, "grad: null pointer");
@@ -556,28 +710,64 @@ int meclip_grad(int kind, const void* x_bf16, const void* y_bf16, int64_t rows, 
     if (!(temperature > 0.f)) return fail(MECLIP_EINVAL, "grad: temperature must be positive");
     int rc = check_device();
     if (rc) return rc;
-    const GradPlan plan = plan_grad(rows, cols, d);
-    if (workspace_bytes < plan.g_bytes + plan.dx_bytes + plan.dy_bytes)
-        return fail(MECLIP_ENOSPC, "grad: workspace %zu < %zu bytes", workspace_bytes, plan.g_bytes + plan.dx_bytes + plan.dy_bytes);
-    cudaStream_t s = (cudaStream_t)stream;
+    const GradPlan plan = plan_grad(rows, cols, d, transposed_copies);
+    if (workspace_bytes < plan.total())
+        return fail(MECLIP_ENOSPC, "grad: workspace %zu < %zu bytes", workspace_bytes, plan.total());
     const bool clip = (kind == MECLIP_CLIP);
     uint8_t* ws = reinterpret_cast<uint8_t*>(workspace);
-    __nv_bfloat16* gpanel = reinterpret_cast<__nv_bfloat16*>(ws);
-    float* dx_scratch = reinterpret_cast<float*>(ws + plan.g_bytes);
-    float* dy_scratch = reinterpret_cast<float*>(ws + plan.g_bytes + plan.dx_bytes);
+    __nv_bfloat16* gpanel[2] = {reinterpret_cast<__nv_bfloat16*>(ws),
+                                reinterpret_cast<__nv_bfloat16*>(ws + (plan.g_buffers > 1 ? plan.g_bytes : 0))};
+    uint8_t* after_g = ws + plan.g_bytes * plan.g_buffers;
+    float* dx_scratch = reinterpret_cast<float*>(after_g);
+    float* dy_scratch = reinterpret_cast<float*>(after_g + plan.dx_bytes);
+    unsigned int* counters = reinterpret_cast<unsigned int*>(after_g + plan.dx_bytes + plan.dy_bytes);
+    __nv_bfloat16* xt = reinterpret_cast<__nv_bfloat16*>(after_g + plan.dx_bytes + plan.dy_bytes + plan.counter_bytes);
+    __nv_bfloat16* yt = reinterpret_cast<__nv_bfloat16*>(after_g + plan.dx_bytes + plan.dy_bytes + plan.counter_bytes + plan.xt_bytes);
     const __nv_bfloat16* X = reinterpret_cast<const __nv_bfloat16*>(x_bf16);
     const __nv_bfloat16* Y = reinterpret_cast<const __nv_bfloat16*>(y_bf16);
     const int bn_d = pick_bn(d);
     const size_t dx_elt = dx_mode == MECLIP_STORE_BF16 ? 2 : 4;
     const size_t dy_elt = dy_mode == MECLIP_STORE_BF16 ? 2 : 4;
 
+    SideStreams* side = nullptr;
+    std::unique_lock<std::mutex> side_lock;
+    cudaStream_t sx = s0, sy = s0;
+    if (overlap) {
+        rc = get_side_streams(&side);
+        if (rc) return rc;
+        side_lock = std::unique_lock<std::mutex>(side->mutex);
+        sx = side->sx;
+        sy = side->sy;
+    }
+    // the tile counters are the only part of the workspace that has to start at zero
+    MECLIP_CUDA(cudaMemsetAsync(counters, 0, plan.counter_bytes, s0));
+    if (transposed_copies) {
+        {
+            ScopedTiming timing(s0, TAG_ROW, 0.0);
+            dim3 grid((unsigned)((cols + 63) / 64), (unsigned)((d + 63) / 64));
+            transpose_bf16_kernel<<<grid, 256, 0, s0>>>(Y, ldy, cols, (int)d, yt, plan.ld_yt);
+        }
+        if (clip) {
+            ScopedTiming timing(s0, TAG_ROW, 0.0);
+            dim3 grid((unsigned)((rows + 63) / 64), (unsigned)((d + 63) / 64));
+            transpose_bf16_kernel<<<grid, 256, 0, s0>>>(X, ldx, rows, (int)d, xt, plan.ld_xt);
+        }
+        MECLIP_CUDA(cudaGetLastError());
+    }
+
+    long long t = 0;
     for (long long rb = 0; rb < plan.n_row_blocks; ++rb) {
         const long long r0 = rb * plan.row_block;
         const long long nr = (rows - r0) < plan.row_block ? (rows - r0) : plan.row_block;
-        for (long long cp = 0; cp < plan.n_panels; ++cp) {
+        for (long long cp = 0; cp < plan.n_panels; ++cp, ++t) {
             const long long c0 = cp * plan.panel_w;
             const long long nc = (cols - c0) < plan.panel_w ? (cols - c0) : plan.panel_w;
-            // (1) coefficient panel G [nr x nc] = epi(X[r0:] Y[c0:]^T)
+            const int gb = (int)(t & 1) & (plan.g_buffers - 1);
+            // (1) coefficient panel G [nr x nc] = epi(X[r0:] Y[c0:]^T), once its buffer is free again
+            if (overlap && t >= 2) {
+                MECLIP_CUDA(cudaStreamWaitEvent(s0, side->dx[gb], 0));
+                if (clip) MECLIP_CUDA(cudaStreamWaitEvent(s0, side->dy[gb], 0));
+            }
             {
                 GemmParams p;
                 std::memset(&p, 0, sizeof(p));
@@ -588,40 +778,25 @@ int meclip_grad(int kind, const void* x_bf16, const void* y_bf16, int64_t rows, 
                 p.grad_out = grad_out;
                 p.coef = clip ? 0.5f * grad_scale : grad_scale;
                 p.dcoef = grad_scale;
-                p.g = gpanel;
-                p.ldg = plan.ldg;
+                p.tile_counter = counters + 3 * t;
                 p.status = status;
                 Operand a{X + r0 * ldx, ldx, false}, b{Y + c0 * ldy, ldy, false};
                 t_tag = TAG_COEF;
-                rc = launch_gemm(EPI_COEF, a, b, nr, nc, d, pick_bn(nc), p, s);
+                rc = launch_gemm(EPI_COEF, a, b, nr, nc, d, pick_bn(nc), p, s0, gpanel[gb], plan.row_block, plan.ldg / 64);
                 if (rc) return rc;
             }
-            // (2) dX[r0:] (+)= G Y[c0:]          M = nr, N = d, K = nc; A = G (K contiguous), B = Y (N contiguous)
-            {
-                GemmParams p;
-                std::memset(&p, 0, sizeof(p));
-                p.status = status;
-                uint8_t* user = reinterpret_cast<uint8_t*>(dx) + (size_t)r0 * lddx * dx_elt;
-                if (dx_mode == MECLIP_ACCUM_F32) {
-                    p.acc_in = reinterpret_cast<const float*>(user); p.ld_acc = lddx;
-                    p.out = user; p.ld_out = lddx; p.out_bf16 = 0;
-                } else if (plan.n_panels == 1) {
-                    p.out = user; p.ld_out = lddx; p.out_bf16 = (dx_mode == MECLIP_STORE_BF16);
-                } else {
-                    if (cp > 0) { p.acc_in = dx_scratch; p.ld_acc = d; }
-                    if (cp == plan.n_panels - 1) { p.out = user; p.ld_out = lddx; p.out_bf16 = (dx_mode == MECLIP_STORE_BF16); }
-                    else { p.out = dx_scratch; p.ld_out = d; p.out_bf16 = 0; }
-                }
-                Operand a{gpanel, plan.ldg, false}, b{Y + c0 * ldy, ldy, true};
-                t_tag = TAG_DX;
-                rc = launch_gemm(EPI_OUT, a, b, nr, d, nc, bn_d, p, s);
-                if (rc) return rc;
+            if (overlap) {
+                MECLIP_CUDA(cudaEventRecord(side->coef[gb], s0));
+                MECLIP_CUDA(cudaStreamWaitEvent(sx, side->coef[gb], 0));
+                if (clip) MECLIP_CUDA(cudaStreamWaitEvent(sy, side->coef[gb], 0));
             }
             // (3) dY[c0:] (+)= G^T X[r0:]        M = nc, N = d, K = nr; A = G^T (M contiguous), B = X (N contiguous)
+            //     issued before dX: its tiles are the long ones (K = nr)
             if (clip) {
                 GemmParams p;
                 std::memset(&p, 0, sizeof(p));
                 p.status = status;
+                p.tile_counter = counters + 3 * t + 2;
                 uint8_t* user = reinterpret_cast<uint8_t*>(dy) + (size_t)c0 * lddy * dy_elt;
                 float* scratch = dy_scratch + (size_t)c0 * d;
                 if (dy_mode == MECLIP_ACCUM_F32) {
@@ -634,14 +809,62 @@ int meclip_grad(int kind, const void* x_bf16, const void* y_bf16, int64_t rows, 
                     if (rb == plan.n_row_blocks - 1) { p.out = user; p.ld_out = lddy; p.out_bf16 = (dy_mode == MECLIP_STORE_BF16); }
                     else { p.out = scratch; p.ld_out = d; p.out_bf16 = 0; }
                 }
-                Operand a{gpanel, plan.ldg, true}, b{X + r0 * ldx, ldx, true};
+                Operand a{gpanel[gb], plan.ldg / 64, true, plan.row_block}, b{X + r0 * ldx, ldx, true};
+                if (transposed_copies) b = Operand{xt + r0, plan.ld_xt, false};   // [d][K = rows] K-major
                 t_tag = TAG_DY;
-                rc = launch_gemm(EPI_OUT, a, b, nc, d, nr, bn_d, p, s);
+                rc = launch_gemm(EPI_OUT, a, b, nc, d, nr, bn_d, p, sy);
                 if (rc) return rc;
+                if (overlap) MECLIP_CUDA(cudaEventRecord(side->dy[gb], sy));
+            }
+            // (2) dX[r0:] (+)= G Y[c0:]          M = nr, N = d, K = nc; A = G (K contiguous), B = Y (N contiguous)
+            {
+                GemmParams p;
+                std::memset(&p, 0, sizeof(p));
+                p.status = status;
+                p.tile_counter = counters + 3 * t + 1;
+                uint8_t* user = reinterpret_cast<uint8_t*>(dx) + (size_t)r0 * lddx * dx_elt;
+                if (dx_mode == MECLIP_ACCUM_F32) {
+                    p.acc_in = reinterpret_cast<const float*>(user); p.ld_acc = lddx;
+                    p.out = user; p.ld_out = lddx; p.out_bf16 = 0;
+                } else if (plan.n_panels == 1) {
+                    p.out = user; p.ld_out = lddx; p.out_bf16 = (dx_mode == MECLIP_STORE_BF16);
+                } else {
+                    if (cp > 0) { p.acc_in = dx_scratch; p.ld_acc = d; }
+                    if (cp == plan.n_panels - 1) { p.out = user; p.ld_out = lddx; p.out_bf16 = (dx_mode == MECLIP_STORE_BF16); }
+                    else { p.out = dx_scratch; p.ld_out = d; p.out_bf16 = 0; }
+                }
+                Operand a{gpanel[gb], plan.ldg / 64, false, plan.row_block}, b{Y + c0 * ldy, ldy, true};
+                if (transposed_copies) b = Operand{yt + c0, plan.ld_yt, false};   // [d][K = cols] K-major
+                t_tag = TAG_DX;
+                rc = launch_gemm(EPI_OUT, a, b, nr, d, nc, bn_d, p, sx);
+                if (rc) return rc;
+                if (overlap) MECLIP_CUDA(cudaEventRecord(side->dx[gb], sx));
             }
         }
     }
+    if (overlap) {   // join: everything the side streams did is ordered before the caller's next work
+        MECLIP_CUDA(cudaEventRecord(side->join_x, sx));
+        MECLIP_CUDA(cudaStreamWaitEvent(s0, side->join_x, 0));
+        if (clip) {
+            MECLIP_CUDA(cudaEventRecord(side->join_y, sy));
+            MECLIP_CUDA(cudaStreamWaitEvent(s0, side->join_y, 0));
+        }
+    }
     return MECLIP_OK;
+}
+
+}  // namespace meclip
+
+extern "C" {
+
+int meclip_grad(int kind, const void* x_bf16, const void* y_bf16, int64_t rows, int64_t cols, int64_t d, int64_t ldx,
+                int64_t ldy, float temperature, int64_t row_off, int64_t col_off, const float* row_sum,
+                const float* col_sum, const float* grad_out, float grad_scale, void* dx, int dx_mode, int64_t lddx,
+                void* dy, int dy_mode, int64_t lddy, void* workspace, size_t workspace_bytes, int* status,
+                void* stream) {
+    return grad_impl(kind, x_bf16, y_bf16, rows, cols, d, ldx, ldy, temperature, row_off, col_off, row_sum, col_sum,
+                     grad_out, grad_scale, dx, dx_mode, lddx, dy, dy_mode, lddy, workspace, workspace_bytes, status,
+                     (cudaStream_t)stream, overlap_allowed(), transposes_allowed());
 }
 
 int meclip_loss_forward(int kind, const void* x_bf16, const void* y_bf16, int64_t batch, int64_t d, int64_t ldx,
@@ -672,12 +895,12 @@ int meclip_loss_backward(int kind, const void* x_bf16, const void* y_bf16, int64
 // backward without a caller-provided workspace
 // ------------------------------------------------------------------------------------
 // The coefficient panel of meclip_grad_static lives here instead of in caller memory.
-// 4096 x 4096 bf16 = 32 MiB, resident on every GPU that loads this library until the
+// 4096 x 4096 bf16 = 32 MiB (+ 4 KiB for tile counters), resident on every GPU that loads this library until the
 // process exits.  In host code the name below is only a handle for the symbol, not a
 // device address: static_scratch_ptr() asks the runtime for the real address once per device.
 static constexpr long long STATIC_MAX_ROWS = 4096;
 static constexpr long long STATIC_MAX_COLS = 4096;
-static constexpr size_t STATIC_SCRATCH_BYTES = (size_t)STATIC_MAX_ROWS * STATIC_MAX_COLS * 2;
+static constexpr size_t STATIC_SCRATCH_BYTES = (size_t)STATIC_MAX_ROWS * STATIC_MAX_COLS * 2 + 4096;  // panel + tile counters
 static __device__ __align__(256) unsigned char g_static_scratch[STATIC_SCRATCH_BYTES];
 
 static std::mutex g_scratch_mutex;
@@ -713,11 +936,14 @@ int meclip_grad_static(int kind, const void* x_bf16, const void* y_bf16, int64_t
     void* scratch = nullptr;
     int rc = static_scratch_ptr(&scratch);
     if (rc) return rc;
-    // Nothing in the scratch has to start at zero: every panel element that is read was written
-    // by this call first, and the tile loads are bounded to the rows x cols that were written.
-    return meclip_grad(kind, x_bf16, y_bf16, rows, cols, d, ldx, ldy, temperature, row_off, col_off, row_sum, col_sum,
-                       grad_out, grad_scale, dx, dx_mode, lddx, dy, dy_mode, lddy, scratch, STATIC_SCRATCH_BYTES,
-                       status, stream);
+    // The scratch keeps the previous call's contents.  The panel needs no clearing: every element
+    // that is read was written by this call first and the tile loads are bounded to the rows x cols
+    // written.  The tile counters behind it must start at zero and are cleared on the stream first.
+    // All launches stay on the caller's stream; no stream, event or memory is created, and the
+    // contractions read X and Y as they are (no transposed copies, which would need more scratch).
+    return grad_impl(kind, x_bf16, y_bf16, rows, cols, d, ldx, ldy, temperature, row_off, col_off, row_sum, col_sum,
+                     grad_out, grad_scale, dx, dx_mode, lddx, dy, dy_mode, lddy, scratch, STATIC_SCRATCH_BYTES,
+                     status, (cudaStream_t)stream, false, false);
 }
 
 int meclip_debug_gemm(const void* a_bf16, int64_t lda, int a_mn_major, const void* b_bf16, int64_t ldb, int b_mn_major,

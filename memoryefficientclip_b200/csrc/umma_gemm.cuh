@@ -2,14 +2,19 @@
 // of the loss path, with three epilogues:
 //
 //   EPI_SUMS  S = X Y^T tile -> E = exp2(k S - k) -> row sums, column sums, diagonal
-//   EPI_COEF  S tile -> E -> G = E (g/r_i + g/c_j) - [i==j] g -> bf16 panel in global memory
+//   EPI_COEF  S tile -> E -> G = E (g/r_i + g/c_j) - [i==j] g -> bf16 panel, TMA-stored in a
+//             column-blocked layout [64-column chunk][row][64] so that every later tile load of
+//             the panel (as G or as G^T) is one contiguous run of memory
 //   EPI_OUT   plain contraction -> (+ fp32 partial) -> fp32 / bf16 store
 //
 // One CTA per SM, 192 threads:
-//   warp 0      TMA producer (one lane): global -> 128B-swizzled shared tiles, 4 stages
+//   warp 0      tile scheduler + TMA producer (one lane): global -> 128B-swizzled shared tiles
 //   warp 1      TMEM allocator + MMA issuer (one lane): tcgen05.mma 128 x BN x 16, bf16 -> fp32
 //   warps 2-5   epilogue: tcgen05.ld of the finished accumulator while the MMA warp
 //               already fills the other accumulator (2 x 256 TMEM columns)
+// Tiles are handed out dynamically (one atomic per tile on a caller-zeroed counter) when a
+// counter is given, so that kernels sharing the GPU with each other balance themselves;
+// without a counter the tiles are dealt round-robin.
 // A and B operands may each be K-major (K contiguous in global memory) or MN-major
 // (M / N contiguous), so G, G^T, X and Y are all consumed from their one row-major copy.
 #pragma once
@@ -24,13 +29,14 @@ namespace meclip {
 static constexpr int BM = 128;            // tile rows  (UMMA M)
 static constexpr int BK = 64;             // K per stage: 64 bf16 = one 128-byte swizzle row
 static constexpr int MAX_BN = 256;        // tile columns (UMMA N), runtime value <= this
-static constexpr int STAGES = 4;
+static constexpr int MAX_STAGES = 8;
+static constexpr int SCHED_DEPTH = 4;     // tile ids in flight between the scheduler and the consumers
 static constexpr int A_STAGE_BYTES = BM * BK * 2;        // 16 KiB
-static constexpr int B_STAGE_BYTES = MAX_BN * BK * 2;    // 32 KiB
-static constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
 static constexpr int TMEM_COLS = 512;     // two accumulators of up to 256 columns
 static constexpr int GEMM_THREADS = 192;
 static constexpr int EPI_THREADS = 128;
+static constexpr int SMEM_LIMIT = 232448; // 227 KiB: most dynamic shared memory one CTA can have
+static constexpr int STORE_BUF_BYTES = 32 * 128;   // one warp's 32 rows x 64 bf16 staging tile
 
 enum { EPI_SUMS = 0, EPI_COEF = 1, EPI_OUT = 2 };
 
@@ -39,7 +45,11 @@ struct GemmParams {
     int bn;                   // tile width (multiple of 32; multiple of 64 when B is MN-major)
     int num_m_tiles, num_n_tiles, k_steps;
     int group_m;              // rasterisation: m-tiles per group swept along n
+    int num_stages;           // operand ring depth, from the shared memory left over
+    int stage_bytes;          // A_STAGE_BYTES + bn * 128
     uint32_t idesc;
+    unsigned int* tile_counter;   // zeroed by the caller; null = static round-robin
+    int a_blocked;            // A is the coefficient panel in its column-blocked layout (3-D tensor map)
     // EPI_SUMS / EPI_COEF
     float k2;                 // log2(e) / T
     long long diag_shift;     // (row_off - col_off): row i meets column i + diag_shift
@@ -51,8 +61,6 @@ struct GemmParams {
     const float* grad_out;    // COEF: device scalar
     float coef;               // COEF: grad_scale * (0.5 for CLIP, 1 for LiT)
     float dcoef;              // COEF: grad_scale (subtracted on the diagonal)
-    __nv_bfloat16* g;         // COEF: output panel, row-major [m x n]
-    long long ldg;
     // EPI_OUT
     void* out;
     long long ld_out;
@@ -62,21 +70,29 @@ struct GemmParams {
     int* status;
 };
 
+// Everything in shared memory that is not an operand stage.  `scratch` is a union by use:
+// SUMS keeps per-warp column partials there (4 x 256 floats), COEF its TMA-store staging
+// tiles (4 warps x 2 buffers x 4 KiB, 1024-byte aligned for the 128-byte swizzle).
 struct SharedTail {
-    unsigned long long full_bar[STAGES];
-    unsigned long long empty_bar[STAGES];
+    uint8_t scratch[4 * 2 * STORE_BUF_BYTES];   // placed on a 1024-byte boundary by the kernel
+    float icol[MAX_BN];         // COEF: g / c_j for the tile's columns
+    unsigned long long full_bar[MAX_STAGES];
+    unsigned long long empty_bar[MAX_STAGES];
     unsigned long long tmem_full_bar[2];
     unsigned long long tmem_empty_bar[2];
+    unsigned long long sched_full_bar[SCHED_DEPTH];
+    unsigned long long sched_empty_bar[SCHED_DEPTH];
+    int sched_tile[SCHED_DEPTH];
     uint32_t tmem_base;
     int abort_flag;
-    float colpart[4][MAX_BN];   // per-epilogue-warp column partial sums
-    float icol[MAX_BN];         // g / c_j for the tile's columns
 };
 
-static constexpr size_t GEMM_SMEM_BYTES = (size_t)STAGES * STAGE_BYTES + 1024 + sizeof(SharedTail);
+__host__ __device__ constexpr int tail_bytes(int epi) {
+    // the scratch union is the first member; kernels that do not need all of it start the tail later
+    return (int)sizeof(SharedTail) - (epi == EPI_COEF ? 0 : epi == EPI_SUMS ? 4 * 2 * STORE_BUF_BYTES - 4 * MAX_BN * 4
+                                                                            : 4 * 2 * STORE_BUF_BYTES);
+}
 
-// Sum over the warp of v[lane'] for each of 32 slots: lane L returns the total of slot L.
-// 31 shuffles instead of 32 x 5.
 template <int HALF>
 __device__ __forceinline__ void transpose_reduce_step(float (&v)[32], int lane) {
     const bool up = (lane & HALF) != 0;
@@ -87,6 +103,8 @@ __device__ __forceinline__ void transpose_reduce_step(float (&v)[32], int lane) 
         v[i] = keep + __shfl_xor_sync(0xffffffffu, send, HALF);
     }
 }
+// Sum over the warp of v[slot] for each of 32 slots: lane L returns the total of slot L.
+// 31 shuffles instead of 32 x 5.
 __device__ __forceinline__ float warp_transpose_reduce32(float (&v)[32], int lane) {
     transpose_reduce_step<16>(v, lane);
     transpose_reduce_step<8>(v, lane);
@@ -106,25 +124,35 @@ __device__ __forceinline__ void tile_coords(const GemmParams& p, int tile, int& 
     nt = local / rows_in_group;
 }
 
+__device__ __forceinline__ uint32_t pack_bf16x2(float a, float b) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&h);
+}
+
 template <int EPI, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                 const __grid_constant__ GemmParams p) {
+                 const __grid_constant__ CUtensorMap tmap_c, const __grid_constant__ GemmParams p) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw_addr = smem_u32(smem_raw);
     const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
     uint8_t* smem = smem_raw + pad;
     const uint32_t smem_base = raw_addr + pad;
-    SharedTail* tail = reinterpret_cast<SharedTail*>(smem + (size_t)STAGES * STAGE_BYTES);
+    // The tail sits behind the stages; its unused leading part of `scratch` overlaps the last stage
+    // region on purpose for SUMS / OUT (they never touch those bytes), see tail_bytes().
+    const uint32_t stages_bytes = (uint32_t)p.num_stages * (uint32_t)p.stage_bytes;
+    const uint32_t tail_off = ((stages_bytes + 1023u) & ~1023u) + (uint32_t)tail_bytes(EPI) - (uint32_t)sizeof(SharedTail);
+    SharedTail* tail = reinterpret_cast<SharedTail*>(smem + (int)tail_off);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const int num_tiles = p.num_m_tiles * p.num_n_tiles;
+    const int num_stages = p.num_stages;
     volatile int* abort_flag = &tail->abort_flag;
 
     if (threadIdx.x == 0) {
         tail->abort_flag = 0;
-        for (int s = 0; s < STAGES; ++s) {
+        for (int s = 0; s < num_stages; ++s) {
             mbar_init(smem_u32(&tail->full_bar[s]), 1);
             mbar_init(smem_u32(&tail->empty_bar[s]), 1);
         }
@@ -132,9 +160,14 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             mbar_init(smem_u32(&tail->tmem_full_bar[a]), 1);
             mbar_init(smem_u32(&tail->tmem_empty_bar[a]), EPI_THREADS);
         }
+        for (int s = 0; s < SCHED_DEPTH; ++s) {
+            mbar_init(smem_u32(&tail->sched_full_bar[s]), 1);
+            mbar_init(smem_u32(&tail->sched_empty_bar[s]), 1 + EPI_THREADS);
+        }
         fence_barrier_init();
         tma_prefetch_desc(&tmap_a);
         tma_prefetch_desc(&tmap_b);
+        if (EPI == EPI_COEF) tma_prefetch_desc(&tmap_c);
     }
     if (warp == 1) {
         tmem_alloc(smem_u32(&tail->tmem_base), TMEM_COLS);
@@ -146,13 +179,21 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     const uint32_t tmem_base = tail->tmem_base;
 
     if (warp == 0) {
-        // ------------------------------ TMA producer ------------------------------
+        // ------------------- tile scheduler + TMA producer -------------------------
         if (lane == 0) {
             const uint32_t stage_tx = (uint32_t)A_STAGE_BYTES + (uint32_t)p.bn * BK * 2;
-            int stage = 0;
-            uint32_t phase = 0;
+            int stage = 0, slot = 0;
+            uint32_t phase = 0, sphase = 0;
+            int tile = blockIdx.x;                   // first tile is free; later ones come from the counter
             bool ok = true;
-            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+            while (ok) {
+                // publish the tile id (or -1 = no more work) to the MMA and epilogue roles
+                if (!mbar_wait(smem_u32(&tail->sched_empty_bar[slot]), sphase ^ 1u, abort_flag)) break;
+                const int pub = tile < num_tiles ? tile : -1;
+                tail->sched_tile[slot] = pub;
+                mbar_arrive(smem_u32(&tail->sched_full_bar[slot]));
+                if (++slot == SCHED_DEPTH) { slot = 0; sphase ^= 1u; }
+                if (pub < 0) break;
                 int mt, nt;
                 tile_coords(p, tile, mt, nt);
                 const int m0 = mt * BM, n0 = nt * p.bn;
@@ -160,10 +201,18 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                     if (!mbar_wait(smem_u32(&tail->empty_bar[stage]), phase ^ 1u, abort_flag)) { ok = false; break; }
                     const uint32_t full = smem_u32(&tail->full_bar[stage]);
                     mbar_expect_tx(full, stage_tx);
-                    const uint32_t sa = smem_base + (uint32_t)stage * STAGE_BYTES;
+                    const uint32_t sa = smem_base + (uint32_t)stage * (uint32_t)p.stage_bytes;
                     const uint32_t sb = sa + A_STAGE_BYTES;
                     const int k0 = ks * BK;
-                    if (A_MN) {   // global [K rows][M contiguous]: 64-wide column chunks of BK rows
+                    if (p.a_blocked) {
+                        // coefficient panel stored as [64-column chunk][row][64]: every box is one contiguous run
+                        if (A_MN) {   // A = G^T: M runs along the panel's columns, K along its rows
+                            tma_load_3d(sa, &tmap_a, full, 0, k0, m0 >> 6);
+                            tma_load_3d(sa + BK * 128, &tmap_a, full, 0, k0, (m0 >> 6) + 1);
+                        } else {      // A = G: M along rows, K along columns
+                            tma_load_3d(sa, &tmap_a, full, 0, m0, ks);
+                        }
+                    } else if (A_MN) {   // global [K rows][M contiguous]: 64-wide column chunks of BK rows
                         tma_load_2d(sa, &tmap_a, full, m0, k0);
                         tma_load_2d(sa + BK * 128, &tmap_a, full, m0 + 64, k0);
                     } else {      // global [M rows][K contiguous]
@@ -174,16 +223,17 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                     } else {
                         tma_load_2d(sb, &tmap_b, full, k0, n0);
                     }
-                    if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                    if (++stage == num_stages) { stage = 0; phase ^= 1u; }
                 }
+                tile = p.tile_counter != nullptr ? (int)(atomicAdd(p.tile_counter, 1u) + gridDim.x) : tile + (int)gridDim.x;
             }
         }
         __syncwarp();
     } else if (warp == 1) {
         // ------------------------------ MMA issuer --------------------------------
         if (lane == 0) {
-            int stage = 0;
-            uint32_t phase = 0;
+            int stage = 0, slot = 0;
+            uint32_t phase = 0, sphase = 0;
             int acc = 0;
             uint32_t acc_phase = 0;
             bool ok = true;
@@ -192,14 +242,19 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             //           a K=16 step is 16 rows = 2048 B.
             constexpr uint32_t A_LBO = A_MN ? BK * 128 : 16, A_KSTEP = A_MN ? 2048 : 32;
             constexpr uint32_t B_LBO = B_MN ? BK * 128 : 16, B_KSTEP = B_MN ? 2048 : 32;
-            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-                if (!mbar_wait(smem_u32(&tail->tmem_empty_bar[acc]), acc_phase ^ 1u, abort_flag)) { ok = false; break; }
+            while (ok) {
+                if (!mbar_wait(smem_u32(&tail->sched_full_bar[slot]), sphase, abort_flag)) break;
+                const int tile = tail->sched_tile[slot];
+                mbar_arrive(smem_u32(&tail->sched_empty_bar[slot]));
+                if (++slot == SCHED_DEPTH) { slot = 0; sphase ^= 1u; }
+                if (tile < 0) break;
+                if (!mbar_wait(smem_u32(&tail->tmem_empty_bar[acc]), acc_phase ^ 1u, abort_flag)) break;
                 tc_fence_after();
                 const uint32_t tmem_d = tmem_base + (uint32_t)acc * MAX_BN;
                 for (int ks = 0; ks < p.k_steps; ++ks) {
                     if (!mbar_wait(smem_u32(&tail->full_bar[stage]), phase, abort_flag)) { ok = false; break; }
                     tc_fence_after();
-                    const uint32_t sa = smem_base + (uint32_t)stage * STAGE_BYTES;
+                    const uint32_t sa = smem_base + (uint32_t)stage * (uint32_t)p.stage_bytes;
                     const uint32_t sb = sa + A_STAGE_BYTES;
 #pragma unroll
                     for (int kk = 0; kk < BK / 16; ++kk) {
@@ -208,7 +263,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                         umma_bf16(tmem_d, ad, bd, p.idesc, (ks | kk) != 0 ? 1u : 0u);
                     }
                     umma_commit(smem_u32(&tail->empty_bar[stage]));   // frees the stage when these MMAs retire
-                    if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                    if (++stage == num_stages) { stage = 0; phase ^= 1u; }
                 }
                 if (!ok) break;
                 umma_commit(smem_u32(&tail->tmem_full_bar[acc]));     // accumulator complete
@@ -222,20 +277,35 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         const int q = warp & 3;                 // TMEM lane quadrant this warp can read
         const int et = threadIdx.x - 64;        // 0..127 within the epilogue group
         const int row_in_tile = q * 32 + lane;
-        int acc = 0;
-        uint32_t acc_phase = 0;
-        bool ok = true;
+        int acc = 0, slot = 0;
+        uint32_t acc_phase = 0, sphase = 0;
+        int stores_in_flight = 0;               // COEF: lane 0's outstanding TMA-store groups
+        uint32_t store_idx = 0;                 // COEF: running store number; its parity picks the staging tile
         float gscale = 1.f;
         if (EPI == EPI_COEF) gscale = p.grad_out ? __ldg(p.grad_out) : 1.f;
         const int chunks = p.bn / 32;
-        for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+        float (*colpart)[MAX_BN] = reinterpret_cast<float (*)[MAX_BN]>(tail->scratch + sizeof(tail->scratch) - 4 * MAX_BN * 4);
+        uint8_t* store_buf = tail->scratch + (size_t)q * 2 * STORE_BUF_BYTES;
+        while (true) {
+            // The four warps wait on the same barrier phase and then agree on the verdict, so that
+            // they always leave the tile loop (and its named barriers) together.
+            bool ok = mbar_wait(smem_u32(&tail->sched_full_bar[slot]), sphase, abort_flag, false);
+            int tile = -1;
+            if (ok) {
+                tile = tail->sched_tile[slot];
+                mbar_arrive(smem_u32(&tail->sched_empty_bar[slot]));
+            }
+            if (++slot == SCHED_DEPTH) { slot = 0; sphase ^= 1u; }
+            ok = named_bar_and(2, EPI_THREADS, ok);
+            if (!ok || tile < 0) break;
+
             int mt, nt;
             tile_coords(p, tile, mt, nt);
             const int m0 = mt * BM, n0 = nt * p.bn;
             const int grow = m0 + row_in_tile;
             const bool rvalid = grow < p.m;
             const bool full_tile = (m0 + BM <= p.m) && (n0 + p.bn <= p.n);
-            // column (tile-local) on which this row meets the diagonal; may be out of range
+            // column (tile-local) on which this row meets the diagonal, -1 if outside the tile
             const long long jd_ll = (long long)grow + p.diag_shift - n0;
             const int jd = (jd_ll >= 0 && jd_ll < p.bn && n0 + jd_ll < p.n && rvalid) ? (int)jd_ll : -1;
 
@@ -251,8 +321,6 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                 named_bar_sync(1, EPI_THREADS);
             }
 
-            // The four warps wait on the same phase and then agree on the verdict, so that they
-            // always leave the tile loop (and its named barriers) together.
             ok = mbar_wait(smem_u32(&tail->tmem_full_bar[acc]), acc_phase, abort_flag, false);
             ok = named_bar_and(2, EPI_THREADS, ok);
             if (!ok) break;
@@ -283,7 +351,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                     for (int c = 0; c < 32; c += 4) { ra0 += e[c]; ra1 += e[c + 1]; ra2 += e[c + 2]; ra3 += e[c + 3]; }
                     if (p.col_sum != nullptr) {
                         const float cs = warp_transpose_reduce32(e, lane);
-                        tail->colpart[q][ch * 32 + lane] = cs;
+                        colpart[q][ch * 32 + lane] = cs;
                     }
                 }
                 tc_fence_before();
@@ -294,40 +362,57 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                     named_bar_sync(1, EPI_THREADS);
                     for (int j = et; j < p.bn; j += EPI_THREADS)
                         if (n0 + j < p.n)
-                            atomicAdd(p.col_sum + n0 + j, (tail->colpart[0][j] + tail->colpart[1][j]) +
-                                                              (tail->colpart[2][j] + tail->colpart[3][j]));
+                            atomicAdd(p.col_sum + n0 + j, (colpart[0][j] + colpart[1][j]) + (colpart[2][j] + colpart[3][j]));
                     named_bar_sync(1, EPI_THREADS);
                 }
             } else if (EPI == EPI_COEF) {
+                // Each warp turns its 32 rows x 64 columns into a 128-byte-swizzled shared tile and one
+                // lane TMA-stores it (full 128-byte lines; rows and columns outside the panel are clipped
+                // by the tensor map).  Two tiles per warp alternate so a store overlaps the next chunk.
                 const float dsub = p.dcoef * gscale;
-                __nv_bfloat16* grow_ptr = p.g + (long long)grow * p.ldg + n0;
-                for (int ch = 0; ch < chunks; ++ch) {
-                    uint32_t v[32];
-                    tmem_ld32(taddr + ch * 32, v);
-                    tmem_ld_wait();
-                    float gv[32];
-                    const int jdc = (jd >= 0 && (jd >> 5) == ch) ? (jd & 31) : -1;
-#pragma unroll
-                    for (int c = 0; c < 32; ++c) {
-                        const float e = ex2_approx(fmaf(__uint_as_float(v[c]), p.k2, -p.k2));
-                        gv[c] = fmaf(e, inv_r + tail->icol[ch * 32 + c], (c == jdc) ? -dsub : 0.f);
+                for (int ch2 = 0; ch2 < chunks / 2; ++ch2) {
+                    uint8_t* buf = store_buf + (store_idx & 1u) * STORE_BUF_BYTES;
+                    ++store_idx;
+                    if (lane == 0 && stores_in_flight > 1) {     // the store that last read `buf` has drained
+                        asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+                        stores_in_flight = 1;
                     }
-                    if (rvalid) {
+                    __syncwarp();
 #pragma unroll
-                        for (int c = 0; c < 32; c += 8) {
-                            if (n0 + ch * 32 + c < p.n) {   // n is a multiple of 8: whole group valid or not
-                                __nv_bfloat162 b0 = __floats2bfloat162_rn(gv[c], gv[c + 1]);
-                                __nv_bfloat162 b1 = __floats2bfloat162_rn(gv[c + 2], gv[c + 3]);
-                                __nv_bfloat162 b2 = __floats2bfloat162_rn(gv[c + 4], gv[c + 5]);
-                                __nv_bfloat162 b3 = __floats2bfloat162_rn(gv[c + 6], gv[c + 7]);
-                                uint4 pk;
-                                pk.x = *reinterpret_cast<uint32_t*>(&b0);
-                                pk.y = *reinterpret_cast<uint32_t*>(&b1);
-                                pk.z = *reinterpret_cast<uint32_t*>(&b2);
-                                pk.w = *reinterpret_cast<uint32_t*>(&b3);
-                                *reinterpret_cast<uint4*>(grow_ptr + ch * 32 + c) = pk;
-                            }
+                    for (int half = 0; half < 2; ++half) {
+                        const int ch = ch2 * 2 + half;
+                        uint32_t v[32];
+                        tmem_ld32(taddr + ch * 32, v);
+                        tmem_ld_wait();
+                        const int jdc = (jd >= 0 && (jd >> 5) == ch) ? (jd & 31) : -1;
+                        float gv[32];
+#pragma unroll
+                        for (int c = 0; c < 32; ++c) {
+                            const float e = ex2_approx(fmaf(__uint_as_float(v[c]), p.k2, -p.k2));
+                            gv[c] = fmaf(e, inv_r + tail->icol[ch * 32 + c], (c == jdc) ? -dsub : 0.f);
                         }
+                        if (!full_tile) {     // columns past the panel edge share a stored chunk with valid ones: zero them
+#pragma unroll
+                            for (int c = 0; c < 32; ++c)
+                                if (n0 + ch * 32 + c >= p.n) gv[c] = 0.f;
+                        }
+#pragma unroll
+                        for (int pc = 0; pc < 4; ++pc) {         // 16-byte piece index within the 128-byte row
+                            uint4 pk;
+                            pk.x = pack_bf16x2(gv[pc * 8 + 0], gv[pc * 8 + 1]);
+                            pk.y = pack_bf16x2(gv[pc * 8 + 2], gv[pc * 8 + 3]);
+                            pk.z = pack_bf16x2(gv[pc * 8 + 4], gv[pc * 8 + 5]);
+                            pk.w = pack_bf16x2(gv[pc * 8 + 6], gv[pc * 8 + 7]);
+                            const int piece = half * 4 + pc;
+                            *reinterpret_cast<uint4*>(buf + lane * 128 + ((piece ^ (lane & 7)) << 4)) = pk;
+                        }
+                    }
+                    fence_proxy_async();
+                    __syncwarp();
+                    if (lane == 0) {
+                        tma_store_3d(&tmap_c, smem_u32(buf), 0, m0 + q * 32, (n0 >> 6) + ch2);
+                        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                        ++stores_in_flight;
                     }
                 }
                 tc_fence_before();
@@ -357,15 +442,11 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 #pragma unroll
                             for (int c = 0; c < 32; c += 8) {
                                 if (col0 + c < p.n) {
-                                    __nv_bfloat162 b0 = __floats2bfloat162_rn(__uint_as_float(v[c]), __uint_as_float(v[c + 1]));
-                                    __nv_bfloat162 b1 = __floats2bfloat162_rn(__uint_as_float(v[c + 2]), __uint_as_float(v[c + 3]));
-                                    __nv_bfloat162 b2 = __floats2bfloat162_rn(__uint_as_float(v[c + 4]), __uint_as_float(v[c + 5]));
-                                    __nv_bfloat162 b3 = __floats2bfloat162_rn(__uint_as_float(v[c + 6]), __uint_as_float(v[c + 7]));
                                     uint4 pk;
-                                    pk.x = *reinterpret_cast<uint32_t*>(&b0);
-                                    pk.y = *reinterpret_cast<uint32_t*>(&b1);
-                                    pk.z = *reinterpret_cast<uint32_t*>(&b2);
-                                    pk.w = *reinterpret_cast<uint32_t*>(&b3);
+                                    pk.x = pack_bf16x2(__uint_as_float(v[c]), __uint_as_float(v[c + 1]));
+                                    pk.y = pack_bf16x2(__uint_as_float(v[c + 2]), __uint_as_float(v[c + 3]));
+                                    pk.z = pack_bf16x2(__uint_as_float(v[c + 4]), __uint_as_float(v[c + 5]));
+                                    pk.w = pack_bf16x2(__uint_as_float(v[c + 6]), __uint_as_float(v[c + 7]));
                                     *reinterpret_cast<uint4*>(op + c) = pk;
                                 }
                             }
@@ -390,6 +471,9 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             }
             acc ^= 1;
             if (acc == 0) acc_phase ^= 1u;
+        }
+        if (EPI == EPI_COEF && lane == 0 && stores_in_flight > 0) {
+            asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // panel writes done before the CTA ends
         }
     }
 
