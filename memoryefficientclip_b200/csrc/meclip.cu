@@ -16,6 +16,7 @@
 
 #include "../../include/meclip.h"
 #include "umma_gemm.cuh"
+#include "umma_gemm2.cuh"
 
 namespace meclip {
 
@@ -367,6 +368,45 @@ static int launch_gemm_t(const CUtensorMap& ta, const CUtensorMap& tb, const CUt
     return MECLIP_OK;
 }
 
+template <int EPI, bool A_MN>
+static int launch_pair_t(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmParams& p,
+                         size_t smem_bytes, cudaStream_t stream) {
+    auto kern = umma_gemm_pair_kernel<EPI, A_MN>;
+    MECLIP_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_LIMIT));
+    // how many CTA pairs the device can hold at once (an SM without a free neighbour cannot host one)
+    static int max_clusters[64] = {0};
+    int dev = 0;
+    MECLIP_CUDA(cudaGetDevice(&dev));
+    if (dev >= 0 && dev < 64 && max_clusters[dev] == 0) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(2 * sm_count());
+        cfg.blockDim = dim3(GEMM_THREADS);
+        cfg.dynamicSmemBytes = SMEM_LIMIT;
+        cudaLaunchAttribute attr;
+        attr.id = cudaLaunchAttributeClusterDimension;
+        attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
+        cfg.attrs = &attr;
+        cfg.numAttrs = 1;
+        int n = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n <= 0) { cudaGetLastError(); n = sm_count() / 2; }
+        max_clusters[dev] = n;
+    }
+    const int cap = (dev >= 0 && dev < 64) ? max_clusters[dev] : sm_count() / 2;
+    const int tiles = p.num_m_tiles * p.num_n_tiles;
+    const int clusters = tiles < cap ? tiles : cap;
+    ScopedTiming timing(stream, t_tag, 2.0 * p.m * p.n * p.k);
+    kern<<<2 * clusters, GEMM_THREADS, smem_bytes, stream>>>(ta, tb, tc, p);
+    MECLIP_CUDA(cudaGetLastError());
+    return MECLIP_OK;
+}
+
+static bool pair_allowed() {
+    // Off by default: with round-robin tiles the pair kernels measure within +-3 % of the single-CTA
+    // kernels, which balance better when kernels overlap.  MECLIP_PAIR=1 switches them on.
+    static const bool on = []() { const char* v = std::getenv("MECLIP_PAIR"); return v != nullptr && v[0] == '1'; }();
+    return on;
+}
+
 // `panel` (EPI_COEF only): the bf16 output panel [m x n], column-blocked with panel_rows_alloc rows
 // per chunk, written by TMA stores.
 static int launch_gemm(int epi, const Operand& a, const Operand& b, long long m, long long n, long long k, int bn,
@@ -388,8 +428,10 @@ static int launch_gemm(int epi, const Operand& a, const Operand& b, long long m,
     } else if (a.mn_major) rc = make_tmap(&ta, a.ptr, m, k, a.ld, 64, BK);
     else                   rc = make_tmap(&ta, a.ptr, k, m, a.ld, BK, BM);
     if (rc) return rc;
+    // CTA pairs (256 x bn tiles) whenever B is K-major; the single-CTA kernel keeps MN-major B
+    const bool pair = pair_allowed() && !b.mn_major && bn % 64 == 0;
     if (b.mn_major) rc = make_tmap(&tb, b.ptr, n, k, b.ld, 64, BK);
-    else            rc = make_tmap(&tb, b.ptr, k, n, b.ld, BK, bn);
+    else            rc = make_tmap(&tb, b.ptr, k, n, b.ld, BK, pair ? bn / 2 : bn);
     if (rc) return rc;
     if (epi == EPI_COEF) {
         if (panel == nullptr || !aligned16(panel) || panel_rows_alloc < m) return fail(MECLIP_EINVAL, "coefficient panel misaligned");
@@ -414,6 +456,21 @@ static int launch_gemm(int epi, const Operand& a, const Operand& b, long long m,
     if (env_max_stages >= 2 && stages > env_max_stages) stages = env_max_stages;
     if (env_static) p.tile_counter = nullptr;
     if (stages < 2) return fail(MECLIP_EINVAL, "tile does not fit shared memory");
+    if (pair) {
+        p.num_m_tiles = (int)((m + PAIR_BM - 1) / PAIR_BM);
+        p.idesc = umma_idesc_bf16(PAIR_BM, bn, a.mn_major ? 1 : 0, 0);
+        p.stage_bytes = A_STAGE_BYTES + (bn / 2) * BK * 2;
+        stages = (SMEM_LIMIT - 1024 - tail_bytes(epi)) / p.stage_bytes;
+        if (stages > MAX_STAGES) stages = MAX_STAGES;
+        if (env_max_stages >= 2 && stages > env_max_stages) stages = env_max_stages;
+        p.num_stages = stages;
+        const size_t pair_smem = 1024 + (size_t)stages * p.stage_bytes + tail_bytes(epi);
+        if (epi == EPI_SUMS) return launch_pair_t<EPI_SUMS, false>(ta, tb, tc, p, pair_smem, stream);
+        if (epi == EPI_COEF) return launch_pair_t<EPI_COEF, false>(ta, tb, tc, p, pair_smem, stream);
+        if (epi == EPI_OUT) return a.mn_major ? launch_pair_t<EPI_OUT, true>(ta, tb, tc, p, pair_smem, stream)
+                                              : launch_pair_t<EPI_OUT, false>(ta, tb, tc, p, pair_smem, stream);
+        return fail(MECLIP_EINVAL, "unknown epilogue %d", epi);
+    }
     p.num_stages = stages;
     const size_t smem_bytes = 1024 + (size_t)stages * p.stage_bytes + tail_bytes(epi);
 #define MECLIP_DISPATCH(E)                                                                                        \
