@@ -100,12 +100,15 @@ int meclip_normalize_bwd(const void* g, int g_dtype, int64_t ldg, const void* x_
  * col_sum may be NULL (LiT).  Out-of-range rows/columns of edge tiles are
  * masked, so any rows/cols >= 1 is exact.  row_off / col_off are the global
  * indices of X row 0 and Y row 0 (0 on one GPU; shard offsets in the ring).
+ * tile_counter: optional device word that must be ZERO when the kernel starts; with
+ * it the CTAs fetch tiles dynamically (better balance when other kernels, e.g. NCCL
+ * transfers, share the GPU); NULL deals the tiles round-robin.
  * Replaces clip_sum_exp_kernel (clip_loss.py:9-64), lit_sum_exp_kernel
  * (lit_loss.py:9-62) and the diagonal einsum (clip_loss.py:206).
  */
 int meclip_sum_exp(int kind, const void* x_bf16, const void* y_bf16, int64_t rows, int64_t cols, int64_t d,
                    int64_t ldx, int64_t ldy, float temperature, int64_t row_off, int64_t col_off, float* row_sum,
-                   float* col_sum, float* diag_s, int* status, void* stream);
+                   float* col_sum, float* diag_s, unsigned int* tile_counter, int* status, void* stream);
 
 /*
  * loss_out (+)= scale * sum_i [ w*(log row_sum[i] + log col_sum[i]) - (diag_s[i] - 1)/T ],
@@ -170,10 +173,11 @@ int meclip_grad_static(int kind, const void* x_bf16, const void* y_bf16, int64_t
  * Mirrors MemoryEfficient{CLIP,LiT}LossNormed.forward (clip_loss.py:160-213,
  * lit_loss.py:152-205): X = first argument of apply(), Y = second.
  * row_sum, col_sum (NULL for LiT), diag_s: B floats each, kept for backward.
+ * tile_counter: optional device word (cleared by this call), see meclip_sum_exp.
  */
 int meclip_loss_forward(int kind, const void* x_bf16, const void* y_bf16, int64_t batch, int64_t d, int64_t ldx,
                         int64_t ldy, float temperature, float* row_sum, float* col_sum, float* diag_s, float* loss_out,
-                        int* status, void* stream);
+                        unsigned int* tile_counter, int* status, void* stream);
 
 /*
  * One-call backward for a whole batch on one GPU (offsets 0, square block).

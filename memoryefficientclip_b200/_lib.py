@@ -32,7 +32,7 @@ SIGNATURES = {
     "meclip_normalize_bwd": (c_int, [c_void_p, c_int, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int64,
                                      c_void_p, c_int, c_int64, c_void_p]),
     "meclip_sum_exp": (c_int, [c_int, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64, c_float,
-                               c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+                               c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "meclip_loss_finalize": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_int64, c_float, c_float, c_int,
                                      c_void_p, c_void_p]),
     "meclip_grad_workspace_bytes": (c_size_t, [c_int64, c_int64, c_int64]),
@@ -43,7 +43,7 @@ SIGNATURES = {
                                    c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_int, c_int64,
                                    c_void_p, c_int, c_int64, c_void_p, c_void_p]),
     "meclip_loss_forward": (c_int, [c_int, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_float,
-                                    c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+                                    c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "meclip_loss_backward": (c_int, [c_int, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_float,
                                      c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_int, c_int64, c_void_p,
                                      c_int, c_int64, c_void_p, c_size_t, c_void_p, c_void_p]),

@@ -702,7 +702,7 @@ int meclip_normalize_bwd(const void* g, int g_dtype, int64_t ldg, const void* x_
 
 int meclip_sum_exp(int kind, const void* x_bf16, const void* y_bf16, int64_t rows, int64_t cols, int64_t d,
                    int64_t ldx, int64_t ldy, float temperature, int64_t row_off, int64_t col_off, float* row_sum,
-                   float* col_sum, float* diag_s, int* status, void* stream) {
+                   float* col_sum, float* diag_s, unsigned int* tile_counter, int* status, void* stream) {
     if (kind != MECLIP_CLIP && kind != MECLIP_LIT) return fail(MECLIP_EINVAL, "sum_exp: bad kind %d", kind);
     if (x_bf16 == nullptr || y_bf16 == nullptr || row_sum == nullptr || diag_s == nullptr)
         return fail(MECLIP_EINVAL, "sum_exp: null pointer");
@@ -719,6 +719,7 @@ int meclip_sum_exp(int kind, const void* x_bf16, const void* y_bf16, int64_t row
     p.row_sum = row_sum;
     p.col_sum = (kind == MECLIP_CLIP) ? col_sum : nullptr;
     p.diag = diag_s;
+    p.tile_counter = tile_counter;
     p.status = status;
     Operand a{x_bf16, ldx, false}, b{y_bf16, ldy, false};
     t_tag = TAG_SUMS;
@@ -926,15 +927,16 @@ int meclip_grad(int kind, const void* x_bf16, const void* y_bf16, int64_t rows, 
 
 int meclip_loss_forward(int kind, const void* x_bf16, const void* y_bf16, int64_t batch, int64_t d, int64_t ldx,
                         int64_t ldy, float temperature, float* row_sum, float* col_sum, float* diag_s, float* loss_out,
-                        int* status, void* stream) {
+                        unsigned int* tile_counter, int* status, void* stream) {
     if (batch < 1 || row_sum == nullptr || diag_s == nullptr || loss_out == nullptr)
         return fail(MECLIP_EINVAL, "loss_forward: bad argument");
     cudaStream_t s = (cudaStream_t)stream;
     MECLIP_CUDA(cudaMemsetAsync(row_sum, 0, (size_t)batch * sizeof(float), s));
     if (kind == MECLIP_CLIP && col_sum != nullptr) MECLIP_CUDA(cudaMemsetAsync(col_sum, 0, (size_t)batch * sizeof(float), s));
     MECLIP_CUDA(cudaMemsetAsync(diag_s, 0, (size_t)batch * sizeof(float), s));
+    if (tile_counter != nullptr) MECLIP_CUDA(cudaMemsetAsync(tile_counter, 0, sizeof(unsigned int), s));
     int rc = meclip_sum_exp(kind, x_bf16, y_bf16, batch, batch, d, ldx, ldy, temperature, 0, 0, row_sum, col_sum, diag_s,
-                            status, stream);
+                            tile_counter, status, stream);
     if (rc) return rc;
     return meclip_loss_finalize(kind, row_sum, col_sum, diag_s, batch, temperature, 1.0f / (float)batch, 0, loss_out,
                                 stream);

@@ -7,11 +7,11 @@
 //             the panel (as G or as G^T) is one contiguous run of memory
 //   EPI_OUT   plain contraction -> (+ fp32 partial) -> fp32 / bf16 store
 //
-// One CTA per SM, 192 threads:
+// One CTA per SM, 320 threads:
 //   warp 0      tile scheduler + TMA producer (one lane): global -> 128B-swizzled shared tiles
 //   warp 1      TMEM allocator + MMA issuer (one lane): tcgen05.mma 128 x BN x 16, bf16 -> fp32
-//   warps 2-5   epilogue: tcgen05.ld of the finished accumulator while the MMA warp
-//               already fills the other accumulator (2 x 256 TMEM columns)
+//   warps 2-9   epilogue (epilogue.cuh): tcgen05.ld of the finished accumulator while the MMA
+//               warp already fills the other accumulator (2 x 256 TMEM columns)
 // Tiles are handed out dynamically (one atomic per tile on a caller-zeroed counter) when a
 // counter is given, so that kernels sharing the GPU with each other balance themselves;
 // without a counter the tiles are dealt round-robin.
@@ -33,8 +33,8 @@ static constexpr int MAX_STAGES = 8;
 static constexpr int SCHED_DEPTH = 4;     // tile ids in flight between the scheduler and the consumers
 static constexpr int A_STAGE_BYTES = BM * BK * 2;        // 16 KiB
 static constexpr int TMEM_COLS = 512;     // two accumulators of up to 256 columns
-static constexpr int GEMM_THREADS = 192;
-static constexpr int EPI_THREADS = 128;
+static constexpr int GEMM_THREADS = 320;   // producer warp + MMA warp + 8 epilogue warps
+static constexpr int EPI_THREADS = 256;
 static constexpr int SMEM_LIMIT = 232448; // 227 KiB: most dynamic shared memory one CTA can have
 static constexpr int STORE_BUF_BYTES = 32 * 128;   // one warp's 32 rows x 64 bf16 staging tile
 
@@ -71,8 +71,8 @@ struct GemmParams {
 };
 
 // Everything in shared memory that is not an operand stage.  `scratch` is a union by use:
-// SUMS keeps per-warp column partials there (4 x 256 floats), COEF its TMA-store staging
-// tiles (4 warps x 2 buffers x 4 KiB, 1024-byte aligned for the 128-byte swizzle).
+// SUMS keeps per-quadrant column partials there (4 x 256 floats), COEF its TMA-store staging
+// tiles (8 warps x 4 KiB, 1024-byte aligned for the 128-byte swizzle).
 struct SharedTail {
     uint8_t scratch[4 * 2 * STORE_BUF_BYTES];   // placed on a 1024-byte boundary by the kernel
     float icol[MAX_BN];         // COEF: g / c_j for the tile's columns
@@ -128,6 +128,10 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float a, float b) {
     __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
     return *reinterpret_cast<uint32_t*>(&h);
 }
+
+}  // namespace meclip
+#include "epilogue.cuh"
+namespace meclip {
 
 template <int EPI, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
@@ -275,19 +279,12 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     } else {
         // ------------------------------ epilogue -----------------------------------
         const int q = warp & 3;                 // TMEM lane quadrant this warp can read
-        const int et = threadIdx.x - 64;        // 0..127 within the epilogue group
-        const int row_in_tile = q * 32 + lane;
         int acc = 0, slot = 0;
         uint32_t acc_phase = 0, sphase = 0;
-        int stores_in_flight = 0;               // COEF: lane 0's outstanding TMA-store groups
-        uint32_t store_idx = 0;                 // COEF: running store number; its parity picks the staging tile
-        float gscale = 1.f;
-        if (EPI == EPI_COEF) gscale = p.grad_out ? __ldg(p.grad_out) : 1.f;
-        const int chunks = p.bn / 32;
-        float (*colpart)[MAX_BN] = reinterpret_cast<float (*)[MAX_BN]>(tail->scratch + sizeof(tail->scratch) - 4 * MAX_BN * 4);
-        uint8_t* store_buf = tail->scratch + (size_t)q * 2 * STORE_BUF_BYTES;
+        EpiState st;
+        if (EPI == EPI_COEF) st.gscale = p.grad_out ? __ldg(p.grad_out) : 1.f;
         while (true) {
-            // The four warps wait on the same barrier phase and then agree on the verdict, so that
+            // The eight warps wait on the same barrier phase and then agree on the verdict, so that
             // they always leave the tile loop (and its named barriers) together.
             bool ok = mbar_wait(smem_u32(&tail->sched_full_bar[slot]), sphase, abort_flag, false);
             int tile = -1;
@@ -298,183 +295,20 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             if (++slot == SCHED_DEPTH) { slot = 0; sphase ^= 1u; }
             ok = named_bar_and(2, EPI_THREADS, ok);
             if (!ok || tile < 0) break;
-
             int mt, nt;
             tile_coords(p, tile, mt, nt);
-            const int m0 = mt * BM, n0 = nt * p.bn;
-            const int grow = m0 + row_in_tile;
-            const bool rvalid = grow < p.m;
-            const bool full_tile = (m0 + BM <= p.m) && (n0 + p.bn <= p.n);
-            // column (tile-local) on which this row meets the diagonal, -1 if outside the tile
-            const long long jd_ll = (long long)grow + p.diag_shift - n0;
-            const int jd = (jd_ll >= 0 && jd_ll < p.bn && n0 + jd_ll < p.n && rvalid) ? (int)jd_ll : -1;
-
-            float inv_r = 0.f;
-            if (EPI == EPI_COEF) {
-                named_bar_sync(1, EPI_THREADS);            // previous tile's readers of icol are done
-                for (int j = et; j < p.bn; j += EPI_THREADS) {
-                    float v = 0.f;
-                    if (p.c != nullptr && n0 + j < p.n) v = p.coef * gscale / __ldg(p.c + n0 + j);
-                    tail->icol[j] = v;
-                }
-                if (rvalid) inv_r = p.coef * gscale / __ldg(p.r + grow);
-                named_bar_sync(1, EPI_THREADS);
-            }
-
             ok = mbar_wait(smem_u32(&tail->tmem_full_bar[acc]), acc_phase, abort_flag, false);
             ok = named_bar_and(2, EPI_THREADS, ok);
             if (!ok) break;
             tc_fence_after();
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)acc * MAX_BN;
-
-            if (EPI == EPI_SUMS) {
-                float ra0 = 0.f, ra1 = 0.f, ra2 = 0.f, ra3 = 0.f;
-                float sdiag = 0.f;
-                for (int ch = 0; ch < chunks; ++ch) {
-                    uint32_t v[32];
-                    tmem_ld32(taddr + ch * 32, v);
-                    tmem_ld_wait();
-                    float e[32];
-                    const int jdc = (jd >= 0 && (jd >> 5) == ch) ? (jd & 31) : -1;
-#pragma unroll
-                    for (int c = 0; c < 32; ++c) {
-                        const float sv = __uint_as_float(v[c]);
-                        e[c] = ex2_approx(fmaf(sv, p.k2, -p.k2));
-                        sdiag = (c == jdc) ? sv : sdiag;
-                    }
-                    if (!full_tile) {
-#pragma unroll
-                        for (int c = 0; c < 32; ++c)
-                            if (!rvalid || n0 + ch * 32 + c >= p.n) e[c] = 0.f;
-                    }
-#pragma unroll
-                    for (int c = 0; c < 32; c += 4) { ra0 += e[c]; ra1 += e[c + 1]; ra2 += e[c + 2]; ra3 += e[c + 3]; }
-                    if (p.col_sum != nullptr) {
-                        const float cs = warp_transpose_reduce32(e, lane);
-                        colpart[q][ch * 32 + lane] = cs;
-                    }
-                }
-                tc_fence_before();
-                mbar_arrive(smem_u32(&tail->tmem_empty_bar[acc]));
-                if (rvalid) atomicAdd(p.row_sum + grow, (ra0 + ra1) + (ra2 + ra3));
-                if (jd >= 0) p.diag[grow] = sdiag;
-                if (p.col_sum != nullptr) {
-                    named_bar_sync(1, EPI_THREADS);
-                    for (int j = et; j < p.bn; j += EPI_THREADS)
-                        if (n0 + j < p.n)
-                            atomicAdd(p.col_sum + n0 + j, (colpart[0][j] + colpart[1][j]) + (colpart[2][j] + colpart[3][j]));
-                    named_bar_sync(1, EPI_THREADS);
-                }
-            } else if (EPI == EPI_COEF) {
-                // Each warp turns its 32 rows x 64 columns into a 128-byte-swizzled shared tile and one
-                // lane TMA-stores it (full 128-byte lines; rows and columns outside the panel are clipped
-                // by the tensor map).  Two tiles per warp alternate so a store overlaps the next chunk.
-                const float dsub = p.dcoef * gscale;
-                for (int ch2 = 0; ch2 < chunks / 2; ++ch2) {
-                    uint8_t* buf = store_buf + (store_idx & 1u) * STORE_BUF_BYTES;
-                    ++store_idx;
-                    if (lane == 0 && stores_in_flight > 1) {     // the store that last read `buf` has drained
-                        asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
-                        stores_in_flight = 1;
-                    }
-                    __syncwarp();
-#pragma unroll
-                    for (int half = 0; half < 2; ++half) {
-                        const int ch = ch2 * 2 + half;
-                        uint32_t v[32];
-                        tmem_ld32(taddr + ch * 32, v);
-                        tmem_ld_wait();
-                        const int jdc = (jd >= 0 && (jd >> 5) == ch) ? (jd & 31) : -1;
-                        float gv[32];
-#pragma unroll
-                        for (int c = 0; c < 32; ++c) {
-                            const float e = ex2_approx(fmaf(__uint_as_float(v[c]), p.k2, -p.k2));
-                            gv[c] = fmaf(e, inv_r + tail->icol[ch * 32 + c], (c == jdc) ? -dsub : 0.f);
-                        }
-                        if (!full_tile) {     // columns past the panel edge share a stored chunk with valid ones: zero them
-#pragma unroll
-                            for (int c = 0; c < 32; ++c)
-                                if (n0 + ch * 32 + c >= p.n) gv[c] = 0.f;
-                        }
-#pragma unroll
-                        for (int pc = 0; pc < 4; ++pc) {         // 16-byte piece index within the 128-byte row
-                            uint4 pk;
-                            pk.x = pack_bf16x2(gv[pc * 8 + 0], gv[pc * 8 + 1]);
-                            pk.y = pack_bf16x2(gv[pc * 8 + 2], gv[pc * 8 + 3]);
-                            pk.z = pack_bf16x2(gv[pc * 8 + 4], gv[pc * 8 + 5]);
-                            pk.w = pack_bf16x2(gv[pc * 8 + 6], gv[pc * 8 + 7]);
-                            const int piece = half * 4 + pc;
-                            *reinterpret_cast<uint4*>(buf + lane * 128 + ((piece ^ (lane & 7)) << 4)) = pk;
-                        }
-                    }
-                    fence_proxy_async();
-                    __syncwarp();
-                    if (lane == 0) {
-                        tma_store_3d(&tmap_c, smem_u32(buf), 0, m0 + q * 32, (n0 >> 6) + ch2);
-                        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-                        ++stores_in_flight;
-                    }
-                }
-                tc_fence_before();
-                mbar_arrive(smem_u32(&tail->tmem_empty_bar[acc]));
-            } else {   // EPI_OUT
-                for (int ch = 0; ch < chunks; ++ch) {
-                    uint32_t v[32];
-                    tmem_ld32(taddr + ch * 32, v);
-                    tmem_ld_wait();
-                    if (rvalid) {
-                        const int col0 = n0 + ch * 32;
-                        if (p.acc_in != nullptr) {
-                            const float* ap = p.acc_in + (long long)grow * p.ld_acc + col0;
-#pragma unroll
-                            for (int c = 0; c < 32; c += 4) {
-                                if (col0 + c < p.n) {
-                                    const float4 a = *reinterpret_cast<const float4*>(ap + c);
-                                    v[c] = __float_as_uint(__uint_as_float(v[c]) + a.x);
-                                    v[c + 1] = __float_as_uint(__uint_as_float(v[c + 1]) + a.y);
-                                    v[c + 2] = __float_as_uint(__uint_as_float(v[c + 2]) + a.z);
-                                    v[c + 3] = __float_as_uint(__uint_as_float(v[c + 3]) + a.w);
-                                }
-                            }
-                        }
-                        if (p.out_bf16) {
-                            __nv_bfloat16* op = reinterpret_cast<__nv_bfloat16*>(p.out) + (long long)grow * p.ld_out + col0;
-#pragma unroll
-                            for (int c = 0; c < 32; c += 8) {
-                                if (col0 + c < p.n) {
-                                    uint4 pk;
-                                    pk.x = pack_bf16x2(__uint_as_float(v[c]), __uint_as_float(v[c + 1]));
-                                    pk.y = pack_bf16x2(__uint_as_float(v[c + 2]), __uint_as_float(v[c + 3]));
-                                    pk.z = pack_bf16x2(__uint_as_float(v[c + 4]), __uint_as_float(v[c + 5]));
-                                    pk.w = pack_bf16x2(__uint_as_float(v[c + 6]), __uint_as_float(v[c + 7]));
-                                    *reinterpret_cast<uint4*>(op + c) = pk;
-                                }
-                            }
-                        } else {
-                            float* op = reinterpret_cast<float*>(p.out) + (long long)grow * p.ld_out + col0;
-#pragma unroll
-                            for (int c = 0; c < 32; c += 4) {
-                                if (col0 + c < p.n) {
-                                    float4 o;
-                                    o.x = __uint_as_float(v[c]);
-                                    o.y = __uint_as_float(v[c + 1]);
-                                    o.z = __uint_as_float(v[c + 2]);
-                                    o.w = __uint_as_float(v[c + 3]);
-                                    *reinterpret_cast<float4*>(op + c) = o;
-                                }
-                            }
-                        }
-                    }
-                }
-                tc_fence_before();
-                mbar_arrive(smem_u32(&tail->tmem_empty_bar[acc]));
-            }
+            const uint32_t free_bar = smem_u32(&tail->tmem_empty_bar[acc]);
+            epilogue_tile<EPI>(p, &tmap_c, tail, st, taddr, mt * BM, nt * p.bn, warp, lane,
+                               [free_bar]() { mbar_arrive(free_bar); });
             acc ^= 1;
             if (acc == 0) acc_phase ^= 1u;
         }
-        if (EPI == EPI_COEF && lane == 0 && stores_in_flight > 0) {
-            asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // panel writes done before the CTA ends
-        }
+        epilogue_drain<EPI>(st, lane);
     }
 
     // ------------------------------ teardown ---------------------------------------

@@ -3,12 +3,12 @@
 // B rows (BN/2), so every operand byte crosses L2 -> shared memory once per 256 x BN tile instead
 // of once per 128 x BN tile, and a stage is 16 KiB + BN/2 * 128 B (6 stages at BN = 256).
 //
-// Roles per CTA (192 threads, as in umma_gemm.cuh):
+// Roles per CTA (320 threads, as in umma_gemm.cuh):
 //   warp 0  TMA producer for this CTA's halves; the byte count of both CTAs lands on the LEADER's
 //           `full` barrier (rank 0 of the pair)
 //   warp 1  TMEM allocation in both CTAs; the leader's lane 0 issues the MMAs for the pair and
 //           releases stages / publishes accumulators in BOTH CTAs with multicast commits
-//   warps 2-5  epilogue of this CTA's 128 accumulator rows (same three epilogues); the peer's
+//   warps 2-9  epilogue of this CTA's 128 accumulator rows (same three epilogues); the peer's
 //           epilogue warps tell the leader that an accumulator is free with a remote arrive
 // B is K-major here (the backward keeps transposed copies of X and Y); A is K-major or the
 // column-blocked coefficient panel read as G (K-major) or G^T (MN-major).
@@ -51,7 +51,7 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(smem_u32(&tail->tmem_full_bar[a]), 1);
-            mbar_init(smem_u32(&tail->tmem_empty_bar[a]), 8);   // 4 epilogue warps x 2 CTAs (leader only)
+            mbar_init(smem_u32(&tail->tmem_empty_bar[a]), 16);  // 8 epilogue warps x 2 CTAs (leader only)
         }
         fence_barrier_init();
         tma_prefetch_desc(&tmap_a);
@@ -144,194 +144,28 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
     } else {
         // ------------------------------ epilogue -----------------------------------
         const int q = warp & 3;
-        const int et = threadIdx.x - 64;
-        const int row_in_tile = q * 32 + lane;
         int acc = 0;
         uint32_t acc_phase = 0;
-        int stores_in_flight = 0;
-        uint32_t store_idx = 0;
-        float gscale = 1.f;
-        if (EPI == EPI_COEF) gscale = p.grad_out ? __ldg(p.grad_out) : 1.f;
-        const int chunks = p.bn / 32;
-        float (*colpart)[MAX_BN] = reinterpret_cast<float (*)[MAX_BN]>(tail->scratch + sizeof(tail->scratch) - 4 * MAX_BN * 4);
-        uint8_t* store_buf = tail->scratch + (size_t)q * 2 * STORE_BUF_BYTES;
+        EpiState st;
+        if (EPI == EPI_COEF) st.gscale = p.grad_out ? __ldg(p.grad_out) : 1.f;
         for (int tile = cluster_id; tile < num_tiles; tile += num_clusters) {
             int mt, nt;
             tile_coords(p, tile, mt, nt);
-            const int m0 = mt * PAIR_BM + (int)rank * BM, n0 = nt * p.bn;
-            const int grow = m0 + row_in_tile;
-            const bool rvalid = grow < p.m;
-            const bool full_tile = (m0 + BM <= p.m) && (n0 + p.bn <= p.n);
-            const long long jd_ll = (long long)grow + p.diag_shift - n0;
-            const int jd = (jd_ll >= 0 && jd_ll < p.bn && n0 + jd_ll < p.n && rvalid) ? (int)jd_ll : -1;
-
-            float inv_r = 0.f;
-            if (EPI == EPI_COEF) {
-                named_bar_sync(1, EPI_THREADS);
-                for (int j = et; j < p.bn; j += EPI_THREADS) {
-                    float v = 0.f;
-                    if (p.c != nullptr && n0 + j < p.n) v = p.coef * gscale / __ldg(p.c + n0 + j);
-                    tail->icol[j] = v;
-                }
-                if (rvalid) inv_r = p.coef * gscale / __ldg(p.r + grow);
-                named_bar_sync(1, EPI_THREADS);
-            }
-
             bool ok = mbar_wait(smem_u32(&tail->tmem_full_bar[acc]), acc_phase, abort_flag, false);
             ok = named_bar_and(2, EPI_THREADS, ok);
             if (!ok) break;
             tc_fence_after();
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)acc * MAX_BN;
-            const uint32_t free_bar = mapa_u32(smem_u32(&tail->tmem_empty_bar[acc]), 0);
-
-            if (EPI == EPI_SUMS) {
-                float ra0 = 0.f, ra1 = 0.f, ra2 = 0.f, ra3 = 0.f;
-                float sdiag = 0.f;
-                for (int ch = 0; ch < chunks; ++ch) {
-                    uint32_t v[32];
-                    tmem_ld32(taddr + ch * 32, v);
-                    tmem_ld_wait();
-                    float e[32];
-                    const int jdc = (jd >= 0 && (jd >> 5) == ch) ? (jd & 31) : -1;
-#pragma unroll
-                    for (int c = 0; c < 32; ++c) {
-                        const float sv = __uint_as_float(v[c]);
-                        e[c] = ex2_approx(fmaf(sv, p.k2, -p.k2));
-                        sdiag = (c == jdc) ? sv : sdiag;
-                    }
-                    if (!full_tile) {
-#pragma unroll
-                        for (int c = 0; c < 32; ++c)
-                            if (!rvalid || n0 + ch * 32 + c >= p.n) e[c] = 0.f;
-                    }
-#pragma unroll
-                    for (int c = 0; c < 32; c += 4) { ra0 += e[c]; ra1 += e[c + 1]; ra2 += e[c + 2]; ra3 += e[c + 3]; }
-                    if (p.col_sum != nullptr) {
-                        const float cs = warp_transpose_reduce32(e, lane);
-                        colpart[q][ch * 32 + lane] = cs;
-                    }
-                }
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive_cluster(free_bar);
-                if (rvalid) atomicAdd(p.row_sum + grow, (ra0 + ra1) + (ra2 + ra3));
-                if (jd >= 0) p.diag[grow] = sdiag;
-                if (p.col_sum != nullptr) {
-                    named_bar_sync(1, EPI_THREADS);
-                    for (int j = et; j < p.bn; j += EPI_THREADS)
-                        if (n0 + j < p.n)
-                            atomicAdd(p.col_sum + n0 + j, (colpart[0][j] + colpart[1][j]) + (colpart[2][j] + colpart[3][j]));
-                    named_bar_sync(1, EPI_THREADS);
-                }
-            } else if (EPI == EPI_COEF) {
-                const float dsub = p.dcoef * gscale;
-                for (int ch2 = 0; ch2 < chunks / 2; ++ch2) {
-                    uint8_t* buf = store_buf + (store_idx & 1u) * STORE_BUF_BYTES;
-                    ++store_idx;
-                    if (lane == 0 && stores_in_flight > 1) {
-                        asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
-                        stores_in_flight = 1;
-                    }
-                    __syncwarp();
-#pragma unroll
-                    for (int half = 0; half < 2; ++half) {
-                        const int ch = ch2 * 2 + half;
-                        uint32_t v[32];
-                        tmem_ld32(taddr + ch * 32, v);
-                        tmem_ld_wait();
-                        const int jdc = (jd >= 0 && (jd >> 5) == ch) ? (jd & 31) : -1;
-                        float gv[32];
-#pragma unroll
-                        for (int c = 0; c < 32; ++c) {
-                            const float e = ex2_approx(fmaf(__uint_as_float(v[c]), p.k2, -p.k2));
-                            gv[c] = fmaf(e, inv_r + tail->icol[ch * 32 + c], (c == jdc) ? -dsub : 0.f);
-                        }
-                        if (!full_tile) {
-#pragma unroll
-                            for (int c = 0; c < 32; ++c)
-                                if (n0 + ch * 32 + c >= p.n) gv[c] = 0.f;
-                        }
-#pragma unroll
-                        for (int pc = 0; pc < 4; ++pc) {
-                            uint4 pk;
-                            pk.x = pack_bf16x2(gv[pc * 8 + 0], gv[pc * 8 + 1]);
-                            pk.y = pack_bf16x2(gv[pc * 8 + 2], gv[pc * 8 + 3]);
-                            pk.z = pack_bf16x2(gv[pc * 8 + 4], gv[pc * 8 + 5]);
-                            pk.w = pack_bf16x2(gv[pc * 8 + 6], gv[pc * 8 + 7]);
-                            const int piece = half * 4 + pc;
-                            *reinterpret_cast<uint4*>(buf + lane * 128 + ((piece ^ (lane & 7)) << 4)) = pk;
-                        }
-                    }
-                    fence_proxy_async();
-                    __syncwarp();
-                    if (lane == 0) {
-                        tma_store_3d(&tmap_c, smem_u32(buf), 0, m0 + q * 32, (n0 >> 6) + ch2);
-                        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-                        ++stores_in_flight;
-                    }
-                }
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive_cluster(free_bar);
-            } else {   // EPI_OUT
-                for (int ch = 0; ch < chunks; ++ch) {
-                    uint32_t v[32];
-                    tmem_ld32(taddr + ch * 32, v);
-                    tmem_ld_wait();
-                    if (rvalid) {
-                        const int col0 = n0 + ch * 32;
-                        if (p.acc_in != nullptr) {
-                            const float* ap = p.acc_in + (long long)grow * p.ld_acc + col0;
-#pragma unroll
-                            for (int c = 0; c < 32; c += 4) {
-                                if (col0 + c < p.n) {
-                                    const float4 a = *reinterpret_cast<const float4*>(ap + c);
-                                    v[c] = __float_as_uint(__uint_as_float(v[c]) + a.x);
-                                    v[c + 1] = __float_as_uint(__uint_as_float(v[c + 1]) + a.y);
-                                    v[c + 2] = __float_as_uint(__uint_as_float(v[c + 2]) + a.z);
-                                    v[c + 3] = __float_as_uint(__uint_as_float(v[c + 3]) + a.w);
-                                }
-                            }
-                        }
-                        if (p.out_bf16) {
-                            __nv_bfloat16* op = reinterpret_cast<__nv_bfloat16*>(p.out) + (long long)grow * p.ld_out + col0;
-#pragma unroll
-                            for (int c = 0; c < 32; c += 8) {
-                                if (col0 + c < p.n) {
-                                    uint4 pk;
-                                    pk.x = pack_bf16x2(__uint_as_float(v[c]), __uint_as_float(v[c + 1]));
-                                    pk.y = pack_bf16x2(__uint_as_float(v[c + 2]), __uint_as_float(v[c + 3]));
-                                    pk.z = pack_bf16x2(__uint_as_float(v[c + 4]), __uint_as_float(v[c + 5]));
-                                    pk.w = pack_bf16x2(__uint_as_float(v[c + 6]), __uint_as_float(v[c + 7]));
-                                    *reinterpret_cast<uint4*>(op + c) = pk;
-                                }
-                            }
-                        } else {
-                            float* op = reinterpret_cast<float*>(p.out) + (long long)grow * p.ld_out + col0;
-#pragma unroll
-                            for (int c = 0; c < 32; c += 4) {
-                                if (col0 + c < p.n) {
-                                    float4 o;
-                                    o.x = __uint_as_float(v[c]);
-                                    o.y = __uint_as_float(v[c + 1]);
-                                    o.z = __uint_as_float(v[c + 2]);
-                                    o.w = __uint_as_float(v[c + 3]);
-                                    *reinterpret_cast<float4*>(op + c) = o;
-                                }
-                            }
-                        }
-                    }
-                }
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive_cluster(free_bar);
-            }
+            const uint32_t free_bar = mapa_u32(smem_u32(&tail->tmem_empty_bar[acc]), 0);   // the leader's barrier
+            epilogue_tile<EPI>(p, &tmap_c, tail, st, taddr, mt * PAIR_BM + (int)rank * BM, nt * p.bn, warp, lane,
+                               [free_bar, lane]() {
+                                   __syncwarp();
+                                   if (lane == 0) mbar_arrive_cluster(free_bar);
+                               });
             acc ^= 1;
             if (acc == 0) acc_phase ^= 1u;
         }
-        if (EPI == EPI_COEF && lane == 0 && stores_in_flight > 0) {
-            asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
-        }
+        epilogue_drain<EPI>(st, lane);
     }
 
     // ------------------------------ teardown ---------------------------------------

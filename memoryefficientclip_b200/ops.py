@@ -75,10 +75,12 @@ def as_operand(x: torch.Tensor) -> torch.Tensor:
 def sum_exp(kind, x_hat, y_hat, temperature, row_sum, col_sum, diag_s, row_off=0, col_off=0, status=None):
     rows, d = x_hat.shape
     cols = y_hat.shape[0]
+    counter = torch.zeros(1, dtype=torch.int32, device=x_hat.device)     # dynamic tile hand-out
     with torch.cuda.device(x_hat.device):
         _lib.check(_lib.load().meclip_sum_exp(kind, x_hat.data_ptr(), y_hat.data_ptr(), rows, cols, d, x_hat.stride(0),
                                               y_hat.stride(0), float(temperature), row_off, col_off, row_sum.data_ptr(),
-                                              _ptr(col_sum), diag_s.data_ptr(), _ptr(status), _stream(x_hat)))
+                                              _ptr(col_sum), diag_s.data_ptr(), counter.data_ptr(), _ptr(status),
+                                              _stream(x_hat)))
 
 
 def loss_finalize(kind, row_sum, col_sum, diag_s, temperature, scale, loss_out, accumulate=False):
@@ -97,11 +99,12 @@ def loss_forward(kind, x_hat, y_hat, temperature, status=None):
     col_sum = torch.empty(b, dtype=torch.float32, device=dev) if kind == _lib.CLIP else None
     diag_s = torch.empty(b, dtype=torch.float32, device=dev)
     loss = torch.empty((), dtype=torch.float32, device=dev)
+    counter = torch.empty(1, dtype=torch.int32, device=dev)              # cleared by the call
     with torch.cuda.device(dev):
         _lib.check(_lib.load().meclip_loss_forward(kind, x_hat.data_ptr(), y_hat.data_ptr(), b, d, x_hat.stride(0),
                                                    y_hat.stride(0), float(temperature), row_sum.data_ptr(),
-                                                   _ptr(col_sum), diag_s.data_ptr(), loss.data_ptr(), _ptr(status),
-                                                   _stream(x_hat)))
+                                                   _ptr(col_sum), diag_s.data_ptr(), loss.data_ptr(),
+                                                   counter.data_ptr(), _ptr(status), _stream(x_hat)))
     return loss, row_sum, col_sum, diag_s
 
 

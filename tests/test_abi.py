@@ -48,15 +48,15 @@ def test_workspace_query_is_pure_host(lib):
 def test_bad_arguments_return_error_codes(lib):
     from memoryefficientclip_b200 import _lib
     # null pointers
-    assert lib.meclip_sum_exp(0, None, None, 8, 8, 8, 8, 8, 0.07, 0, 0, None, None, None, None, None) == _lib.EINVAL
+    assert lib.meclip_sum_exp(0, None, None, 8, 8, 8, 8, 8, 0.07, 0, 0, None, None, None, None, None, None) == _lib.EINVAL
     assert "null" in _lib.last_error()
     # feature dimension not a multiple of 8
     fake = ctypes.c_void_p(0x1000)
-    assert lib.meclip_sum_exp(0, fake, fake, 8, 8, 12, 12, 12, 0.07, 0, 0, fake, fake, fake, None, None) == _lib.EINVAL
+    assert lib.meclip_sum_exp(0, fake, fake, 8, 8, 12, 12, 12, 0.07, 0, 0, fake, fake, fake, None, None, None) == _lib.EINVAL
     # bad kind
-    assert lib.meclip_sum_exp(7, fake, fake, 8, 8, 8, 8, 8, 0.07, 0, 0, fake, fake, fake, None, None) == _lib.EINVAL
+    assert lib.meclip_sum_exp(7, fake, fake, 8, 8, 8, 8, 8, 0.07, 0, 0, fake, fake, fake, None, None, None) == _lib.EINVAL
     # non-positive temperature
-    assert lib.meclip_sum_exp(0, fake, fake, 8, 8, 8, 8, 8, 0.0, 0, 0, fake, fake, fake, None, None) == _lib.EINVAL
+    assert lib.meclip_sum_exp(0, fake, fake, 8, 8, 8, 8, 8, 0.0, 0, 0, fake, fake, fake, None, None, None) == _lib.EINVAL
     # misaligned normalise input
     odd = ctypes.c_void_p(0x1004)
     assert lib.meclip_normalize_fwd(odd, 1, 4, 8, 8, 1, fake, 8, fake, None) == _lib.EINVAL
