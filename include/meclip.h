@@ -59,6 +59,17 @@ int meclip_last_error(char* buf, size_t buf_len);
 /* Synchronises `stream`, copies *status to the host and maps non-zero to MECLIP_ETIMEOUT. */
 int meclip_read_status(const int* status, void* stream);
 
+/*
+ * Test hook: in-kernel trace.  device_words points to n_words zeroed 64-bit words on the
+ * device; while set, CTA 0 of every tile kernel appends {tag, tile, nanosecond timer}
+ * records from word 2 on (the producer, the MMA issuer and the epilogue each fill their
+ * own third; unused records stay zero).  Tags: 1/2 loads of a tile
+ * begin/end, 10/11/12 MMA tile begin / first operands arrived / last MMA issued,
+ * 20/21/22 epilogue begin / accumulator released / end.  NULL switches it off.
+ * Has no counterpart in the reference.
+ */
+int meclip_debug_set_trace(void* device_words, size_t n_words);
+
 /* Number of kernels this library has launched in this process (all threads). */
 long long meclip_launch_count(void);
 

@@ -24,6 +24,7 @@ SIGNATURES = {
     "meclip_status_string": (c_char_p, [c_int]),
     "meclip_last_error": (c_int, [c_char_p, c_size_t]),
     "meclip_read_status": (c_int, [c_void_p, c_void_p]),
+    "meclip_debug_set_trace": (c_int, [c_void_p, c_size_t]),
     "meclip_launch_count": (ctypes.c_longlong, []),
     "meclip_profile_begin": (c_int, []),
     "meclip_profile_end": (c_int, [c_void_p, c_void_p, c_void_p, c_int]),

@@ -7,10 +7,45 @@
 
 namespace meclip {
 
+static constexpr int COL_SLOTS = MAX_BN / 64;   // 32-column chunks one warp group owns at most (half the tile)
+
 struct EpiState {        // per-thread state that lives across tiles
     int stores_in_flight = 0;   // COEF: lane 0's outstanding TMA-store groups
     float gscale = 1.f;         // COEF: *grad_out
+    // SUMS: column sums of this thread's row, kept in registers over a strip of tiles that share
+    // their columns; reduced across rows (shuffles, shared memory, atomics) once per strip
+    float cacc[COL_SLOTS][32] = {};
+    int strip_n0 = -1;          // first column of the tiles accumulated so far, -1 = nothing pending
 };
+
+// SUMS: add the pending column accumulators of all eight warps into col_sum and clear them.
+// Every epilogue thread must call this at the same point (it uses the epilogue named barrier).
+__device__ __forceinline__ void flush_column_sums(const GemmParams& p, SharedTail* tail, EpiState& st, int warp, int lane) {
+    if (st.strip_n0 < 0) return;
+    const int q = warp & 3;
+    const int wg = (warp - 2) >> 2;
+    const int et = (int)threadIdx.x - 64;
+    const int units = p.bn >> 5;
+    const int u_split = (units + 1) >> 1;
+    const int u_begin = wg == 0 ? 0 : u_split;
+    const int u_end = wg == 0 ? u_split : units;
+    float (*colpart)[MAX_BN] = reinterpret_cast<float (*)[MAX_BN]>(tail->scratch + sizeof(tail->scratch) - 4 * MAX_BN * 4);
+#pragma unroll
+    for (int k = 0; k < COL_SLOTS; ++k) {
+        if (u_begin + k < u_end) {
+            const float cs = warp_transpose_reduce32(st.cacc[k], lane);
+            colpart[q][(u_begin + k) * 32 + lane] = cs;
+        }
+#pragma unroll
+        for (int c = 0; c < 32; ++c) st.cacc[k][c] = 0.f;
+    }
+    named_bar_sync(1, EPI_THREADS);
+    for (int j = et; j < p.bn; j += EPI_THREADS)
+        if (st.strip_n0 + j < p.n)
+            atomicAdd(p.col_sum + st.strip_n0 + j, (colpart[0][j] + colpart[1][j]) + (colpart[2][j] + colpart[3][j]));
+    named_bar_sync(1, EPI_THREADS);
+    st.strip_n0 = -1;
+}
 
 // `release()` is called by every thread once its last tcgen05.ld of the tile has completed; it must
 // tell the MMA issuer that this thread is done with the accumulator.
@@ -34,44 +69,51 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, const CUtenso
     const int u_end = wg == 0 ? u_split : units;
 
     if (EPI == EPI_SUMS) {
-        float (*colpart)[MAX_BN] = reinterpret_cast<float (*)[MAX_BN]>(tail->scratch + sizeof(tail->scratch) - 4 * MAX_BN * 4);
+        const bool want_cols = p.col_sum != nullptr;
+        if (want_cols && st.strip_n0 != n0) {       // the columns change: hand in what was accumulated
+            flush_column_sums(p, tail, st, warp, lane);
+            st.strip_n0 = n0;
+        }
         float ra0 = 0.f, ra1 = 0.f, ra2 = 0.f, ra3 = 0.f;
         float sdiag = 0.f;
-        for (int ch = u_begin; ch < u_end; ++ch) {
-            uint32_t v[32];
-            tmem_ld32(taddr + ch * 32, v);
-            tmem_ld_wait();
-            float e[32];
-            const int jdc = (jd >= 0 && (jd >> 5) == ch) ? (jd & 31) : -1;
+        const bool diag_here = __any_sync(0xffffffffu, jd >= 0);   // warp-uniform: most tiles miss the diagonal
 #pragma unroll
-            for (int c = 0; c < 32; ++c) {
-                const float sv = __uint_as_float(v[c]);
-                e[c] = ex2_approx(fmaf(sv, p.k2, -p.k2));
-                sdiag = (c == jdc) ? sv : sdiag;
-            }
-            if (!full_tile) {
+        for (int k = 0; k < COL_SLOTS; ++k) {
+            const int ch = u_begin + k;
+            if (ch < u_end) {
+                uint32_t v[32];
+                tmem_ld32(taddr + ch * 32, v);
+                tmem_ld_wait();
+                if (diag_here) {
+                    const int jdc = (jd >= 0 && (jd >> 5) == ch) ? (jd & 31) : -1;
 #pragma unroll
-                for (int c = 0; c < 32; ++c)
-                    if (!rvalid || n0 + ch * 32 + c >= p.n) e[c] = 0.f;
-            }
+                    for (int c = 0; c < 32; ++c) sdiag = (c == jdc) ? __uint_as_float(v[c]) : sdiag;
+                }
+                if (full_tile) {
 #pragma unroll
-            for (int c = 0; c < 32; c += 4) { ra0 += e[c]; ra1 += e[c + 1]; ra2 += e[c + 2]; ra3 += e[c + 3]; }
-            if (p.col_sum != nullptr) {
-                const float cs = warp_transpose_reduce32(e, lane);
-                colpart[q][ch * 32 + lane] = cs;
+                    for (int c = 0; c < 32; c += 4) {
+                        const float e0 = ex2_approx(fmaf(__uint_as_float(v[c]), p.k2, -p.k2));
+                        const float e1 = ex2_approx(fmaf(__uint_as_float(v[c + 1]), p.k2, -p.k2));
+                        const float e2 = ex2_approx(fmaf(__uint_as_float(v[c + 2]), p.k2, -p.k2));
+                        const float e3 = ex2_approx(fmaf(__uint_as_float(v[c + 3]), p.k2, -p.k2));
+                        ra0 += e0; ra1 += e1; ra2 += e2; ra3 += e3;
+                        if (want_cols) { st.cacc[k][c] += e0; st.cacc[k][c + 1] += e1; st.cacc[k][c + 2] += e2; st.cacc[k][c + 3] += e3; }
+                    }
+                } else {
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) {
+                        float e = ex2_approx(fmaf(__uint_as_float(v[c]), p.k2, -p.k2));
+                        if (!rvalid || n0 + ch * 32 + c >= p.n) e = 0.f;
+                        ra0 += e;
+                        if (want_cols) st.cacc[k][c] += e;
+                    }
+                }
             }
         }
         tc_fence_before();
         release();
         if (rvalid && u_end > u_begin) atomicAdd(p.row_sum + grow, (ra0 + ra1) + (ra2 + ra3));
         if (jd >= 0 && (jd >> 5) >= u_begin && (jd >> 5) < u_end) p.diag[grow] = sdiag;
-        if (p.col_sum != nullptr) {
-            named_bar_sync(1, EPI_THREADS);
-            for (int j = et; j < p.bn; j += EPI_THREADS)
-                if (n0 + j < p.n)
-                    atomicAdd(p.col_sum + n0 + j, (colpart[0][j] + colpart[1][j]) + (colpart[2][j] + colpart[3][j]));
-            named_bar_sync(1, EPI_THREADS);
-        }
     } else if (EPI == EPI_COEF) {
         // g / c_j for the tile's columns, staged once per tile for all eight warps
         named_bar_sync(1, EPI_THREADS);            // previous tile's readers of icol are done
@@ -86,6 +128,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, const CUtenso
         // TMA-stores it (full 128-byte lines; rows and chunks outside the panel are clipped by the
         // tensor map).
         const float dsub = p.dcoef * st.gscale;
+        const bool diag_here = __any_sync(0xffffffffu, jd >= 0);
         uint8_t* buf = tail->scratch + (size_t)(warp - 2) * STORE_BUF_BYTES;
         for (int u = u_begin; u < u_end; ++u) {
             if (lane == 0 && st.stores_in_flight > 0) {     // the previous store has finished reading `buf`
@@ -99,12 +142,19 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, const CUtenso
                 uint32_t v[32];
                 tmem_ld32(taddr + ch * 32, v);
                 tmem_ld_wait();
-                const int jdc = (jd >= 0 && (jd >> 5) == ch) ? (jd & 31) : -1;
                 float gv[32];
 #pragma unroll
-                for (int c = 0; c < 32; ++c) {
-                    const float e = ex2_approx(fmaf(__uint_as_float(v[c]), p.k2, -p.k2));
-                    gv[c] = fmaf(e, inv_r + tail->icol[ch * 32 + c], (c == jdc) ? -dsub : 0.f);
+                for (int c = 0; c < 32; c += 4) {
+                    const float4 ic = *reinterpret_cast<const float4*>(&tail->icol[ch * 32 + c]);   // broadcast read
+                    gv[c] = ex2_approx(fmaf(__uint_as_float(v[c]), p.k2, -p.k2)) * (inv_r + ic.x);
+                    gv[c + 1] = ex2_approx(fmaf(__uint_as_float(v[c + 1]), p.k2, -p.k2)) * (inv_r + ic.y);
+                    gv[c + 2] = ex2_approx(fmaf(__uint_as_float(v[c + 2]), p.k2, -p.k2)) * (inv_r + ic.z);
+                    gv[c + 3] = ex2_approx(fmaf(__uint_as_float(v[c + 3]), p.k2, -p.k2)) * (inv_r + ic.w);
+                }
+                if (diag_here) {      // warp-uniform: only tiles that cross the diagonal pay for the correction
+                    const int jdc = (jd >= 0 && (jd >> 5) == ch) ? (jd & 31) : -1;
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) gv[c] -= (c == jdc) ? dsub : 0.f;
                 }
                 if (!full_tile) {     // columns past the panel edge share a stored chunk with valid ones: zero them
 #pragma unroll
@@ -187,6 +237,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, const CUtenso
 }
 
 // Called once per epilogue thread before the CTA ends: panel stores must have been written.
+// (Pending column sums are flushed by the kernels, which know whether the tile loop ended cleanly.)
 template <int EPI>
 __device__ __forceinline__ void epilogue_drain(const EpiState& st, int lane) {
     if (EPI == EPI_COEF && lane == 0 && st.stores_in_flight > 0) {

@@ -74,6 +74,10 @@ struct ScopedTiming {   // brackets one launch with events on its stream while p
     }
 };
 
+// test hook: device buffer for the in-kernel trace of CTA 0 (null = off)
+static unsigned long long* g_trace_buf = nullptr;
+static unsigned int g_trace_capacity = 0;
+
 static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 static inline size_t round_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
@@ -361,7 +365,8 @@ static int launch_gemm_t(const CUtensorMap& ta, const CUtensorMap& tb, const CUt
     auto kern = umma_gemm_kernel<EPI, A_MN, B_MN>;
     MECLIP_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_LIMIT));
     const int tiles = p.num_m_tiles * p.num_n_tiles;
-    const int grid = tiles < sm_count() ? tiles : sm_count();
+    const int units = (tiles + p.strip_len - 1) / p.strip_len;
+    const int grid = units < sm_count() ? units : sm_count();
     ScopedTiming timing(stream, t_tag, 2.0 * p.m * p.n * p.k);
     kern<<<grid, GEMM_THREADS, smem_bytes, stream>>>(ta, tb, tc, p);
     MECLIP_CUDA(cudaGetLastError());
@@ -444,7 +449,16 @@ static int launch_gemm(int epi, const Operand& a, const Operand& b, long long m,
     p.num_m_tiles = (int)((m + BM - 1) / BM);
     p.num_n_tiles = (int)((n + bn - 1) / bn);
     p.k_steps = (int)((k + BK - 1) / BK);
+    p.trace = g_trace_buf;
+    p.trace_capacity = g_trace_capacity;
     p.group_m = 16;
+    // strips: tile ids inside a group of 16 m-tiles share their columns; the sums pass keeps column
+    // partials in registers over a strip.  Shorter strips when there are few tiles per SM.
+    p.strip_len = 1;
+    if (epi == EPI_SUMS && p.col_sum != nullptr) {
+        const long long per_sm = (long long)p.num_m_tiles * p.num_n_tiles / sm_count();
+        p.strip_len = per_sm >= 64 ? 16 : per_sm >= 32 ? 8 : per_sm >= 16 ? 4 : per_sm >= 8 ? 2 : 1;
+    }
     p.idesc = umma_idesc_bf16(BM, bn, a.mn_major ? 1 : 0, b.mn_major ? 1 : 0);
     if ((long long)p.num_m_tiles * p.num_n_tiles > 0x7fffffffLL) return fail(MECLIP_EINVAL, "too many tiles");
     // shared memory: [<= 1023 B alignment slack][stages][tail]; as many stages as fit, at least 2
@@ -612,6 +626,13 @@ int meclip_read_status(const int* status, void* stream) {
     MECLIP_CUDA(cudaMemcpyAsync(&host, status, sizeof(int), cudaMemcpyDeviceToHost, (cudaStream_t)stream));
     MECLIP_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
     if (host != 0) return fail(MECLIP_ETIMEOUT, "a kernel gave up waiting on a barrier (status word %d)", host);
+    return MECLIP_OK;
+}
+
+int meclip_debug_set_trace(void* device_words, size_t n_words) {
+    if (device_words == nullptr || n_words < 5) { g_trace_buf = nullptr; g_trace_capacity = 0; return MECLIP_OK; }
+    g_trace_buf = reinterpret_cast<unsigned long long*>(device_words);
+    g_trace_capacity = (unsigned int)((n_words - 2) / 3);
     return MECLIP_OK;
 }
 

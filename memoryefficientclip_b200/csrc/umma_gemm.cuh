@@ -49,6 +49,7 @@ struct GemmParams {
     int stage_bytes;          // A_STAGE_BYTES + bn * 128
     uint32_t idesc;
     unsigned int* tile_counter;   // zeroed by the caller; null = static round-robin
+    int strip_len;            // tiles handed out together (consecutive ids share their columns), >= 1
     int a_blocked;            // A is the coefficient panel in its column-blocked layout (3-D tensor map)
     // EPI_SUMS / EPI_COEF
     float k2;                 // log2(e) / T
@@ -68,7 +69,28 @@ struct GemmParams {
     const float* acc_in;      // optional fp32 partial added before the store
     long long ld_acc;
     int* status;
+    // Optional in-kernel trace (test hook): CTA 0 appends {tag, tile, %globaltimer} records.
+    // Records of 3 words start at trace[2]; role r owns records [r*cap/3, (r+1)*cap/3); unused ones stay zero.
+    unsigned long long* trace;
+    unsigned int trace_capacity;
 };
+
+enum { TR_LOAD_BEGIN = 1, TR_LOAD_END = 2, TR_MMA_BEGIN = 10, TR_MMA_FIRST_DATA = 11, TR_MMA_END = 12,
+       TR_EPI_BEGIN = 20, TR_EPI_RELEASED = 21, TR_EPI_END = 22 };
+
+// Each role (0 producer, 1 MMA issuer, 2 epilogue) appends to its own third of the buffer with a
+// private counter, so a record is three plain stores and does not wait on memory.
+__device__ __forceinline__ void trace_event(const GemmParams& p, int role, unsigned int& count, int tag, int tile) {
+    if (p.trace == nullptr || blockIdx.x != 0) return;
+    const unsigned int per_role = p.trace_capacity / 3;
+    if (count < per_role) {
+        unsigned long long* rec = p.trace + 2 + 3ull * ((unsigned long long)role * per_role + count);
+        rec[0] = (unsigned long long)tag;
+        rec[1] = (unsigned long long)(long long)tile;
+        rec[2] = global_ns();
+        ++count;
+    }
+}
 
 // Everything in shared memory that is not an operand stage.  `scratch` is a union by use:
 // SUMS keeps per-quadrant column partials there (4 x 256 floats), COEF its TMA-store staging
@@ -188,7 +210,16 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             const uint32_t stage_tx = (uint32_t)A_STAGE_BYTES + (uint32_t)p.bn * BK * 2;
             int stage = 0, slot = 0;
             uint32_t phase = 0, sphase = 0;
-            int tile = blockIdx.x;                   // first tile is free; later ones come from the counter
+            // Work is handed out in strips of strip_len consecutive tile ids (same columns, next rows):
+            // the first strip is blockIdx.x, later ones come from the counter.  The next strip's id is
+            // requested (one atomic, ~1 us round trip) when a strip STARTS and only read when it ends,
+            // so the operand pipeline never waits for it.
+            const int strip = p.strip_len;
+            int unit = blockIdx.x;
+            int tile = unit * strip;
+            int left = strip;
+            unsigned int next_unit = 0;
+            unsigned int ntrace = 0;
             bool ok = true;
             while (ok) {
                 // publish the tile id (or -1 = no more work) to the MMA and epilogue roles
@@ -198,9 +229,14 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                 mbar_arrive(smem_u32(&tail->sched_full_bar[slot]));
                 if (++slot == SCHED_DEPTH) { slot = 0; sphase ^= 1u; }
                 if (pub < 0) break;
+                // First tile of a strip: ask for the strip after this one now.  next_unit is written by
+                // nothing but the atomic, so nothing waits for its round trip before the strip ends.
+                if (left == strip && p.tile_counter != nullptr)
+                    asm volatile("atom.global.add.u32 %0, [%1], 1;" : "=r"(next_unit) : "l"(p.tile_counter) : "memory");
                 int mt, nt;
                 tile_coords(p, tile, mt, nt);
                 const int m0 = mt * BM, n0 = nt * p.bn;
+                trace_event(p, 0, ntrace, TR_LOAD_BEGIN, tile);
                 for (int ks = 0; ks < p.k_steps; ++ks) {
                     if (!mbar_wait(smem_u32(&tail->empty_bar[stage]), phase ^ 1u, abort_flag)) { ok = false; break; }
                     const uint32_t full = smem_u32(&tail->full_bar[stage]);
@@ -229,7 +265,14 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                     }
                     if (++stage == num_stages) { stage = 0; phase ^= 1u; }
                 }
-                tile = p.tile_counter != nullptr ? (int)(atomicAdd(p.tile_counter, 1u) + gridDim.x) : tile + (int)gridDim.x;
+                trace_event(p, 0, ntrace, TR_LOAD_END, tile);
+                if (--left > 0 && tile + 1 < num_tiles) {
+                    ++tile;
+                } else {
+                    unit = p.tile_counter != nullptr ? (int)(next_unit + gridDim.x) : unit + (int)gridDim.x;
+                    tile = unit * strip;
+                    left = strip;
+                }
             }
         }
         __syncwarp();
@@ -240,6 +283,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             uint32_t phase = 0, sphase = 0;
             int acc = 0;
             uint32_t acc_phase = 0;
+            unsigned int ntrace = 0;
             bool ok = true;
             // K-major: 8-row groups 1024 B apart (SBO), 32 B per K=16 step inside the swizzle row.
             // MN-major: 64-element chunks BK*128 B apart (LBO), 8-row K groups 1024 B apart (SBO),
@@ -254,10 +298,12 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                 if (tile < 0) break;
                 if (!mbar_wait(smem_u32(&tail->tmem_empty_bar[acc]), acc_phase ^ 1u, abort_flag)) break;
                 tc_fence_after();
+                trace_event(p, 1, ntrace, TR_MMA_BEGIN, tile);
                 const uint32_t tmem_d = tmem_base + (uint32_t)acc * MAX_BN;
                 for (int ks = 0; ks < p.k_steps; ++ks) {
                     if (!mbar_wait(smem_u32(&tail->full_bar[stage]), phase, abort_flag)) { ok = false; break; }
                     tc_fence_after();
+                    if (ks == 0) trace_event(p, 1, ntrace, TR_MMA_FIRST_DATA, tile);
                     const uint32_t sa = smem_base + (uint32_t)stage * (uint32_t)p.stage_bytes;
                     const uint32_t sb = sa + A_STAGE_BYTES;
 #pragma unroll
@@ -271,6 +317,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                 }
                 if (!ok) break;
                 umma_commit(smem_u32(&tail->tmem_full_bar[acc]));     // accumulator complete
+                trace_event(p, 1, ntrace, TR_MMA_END, tile);
                 acc ^= 1;
                 if (acc == 0) acc_phase ^= 1u;
             }
@@ -282,6 +329,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         int acc = 0, slot = 0;
         uint32_t acc_phase = 0, sphase = 0;
         EpiState st;
+        unsigned int ntrace = 0;
         if (EPI == EPI_COEF) st.gscale = p.grad_out ? __ldg(p.grad_out) : 1.f;
         while (true) {
             // The eight warps wait on the same barrier phase and then agree on the verdict, so that
@@ -303,11 +351,17 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             tc_fence_after();
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)acc * MAX_BN;
             const uint32_t free_bar = smem_u32(&tail->tmem_empty_bar[acc]);
+            if (threadIdx.x == 64) trace_event(p, 2, ntrace, TR_EPI_BEGIN, tile);
             epilogue_tile<EPI>(p, &tmap_c, tail, st, taddr, mt * BM, nt * p.bn, warp, lane,
-                               [free_bar]() { mbar_arrive(free_bar); });
+                               [free_bar, &p, &ntrace, tile]() {
+                                   mbar_arrive(free_bar);
+                                   if (threadIdx.x == 64) trace_event(p, 2, ntrace, TR_EPI_RELEASED, tile);
+                               });
+            if (threadIdx.x == 64) trace_event(p, 2, ntrace, TR_EPI_END, tile);
             acc ^= 1;
             if (acc == 0) acc_phase ^= 1u;
         }
+        if (EPI == EPI_SUMS && !tail->abort_flag) flush_column_sums(p, tail, st, warp, lane);
         epilogue_drain<EPI>(st, lane);
     }
 

@@ -165,6 +165,7 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
             acc ^= 1;
             if (acc == 0) acc_phase ^= 1u;
         }
+        if (EPI == EPI_SUMS && !tail->abort_flag) flush_column_sums(p, tail, st, warp, lane);
         epilogue_drain<EPI>(st, lane);
     }
 
