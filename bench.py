@@ -5,8 +5,10 @@
 
 N = 1   CLIP fwd+bwd, B=32768, D=1152, bf16, pre-normalised inputs, T=0.07 (the configuration the
         headline metric is quoted on).  One step = one forward + backward over the whole batch.
-N > 1   ring-distributed CLIP fwd+bwd, global B=131072, D=768, bf16 (launched by torch.distributed.run,
-        one rank per GPU); fixed global batch, so scaling is "strong".
+N > 1   ring-distributed CLIP fwd+bwd, global B=262144, D=1024, bf16, T=0.03, text = normalize(image +
+        0.5 noise), normalise inside (launched by torch.distributed.run, one rank per GPU); the global
+        batch is fixed, so scaling is "strong".  --config ring_clip_b131072_d768_bf16 selects the
+        other ring configuration.
 
 The metric is TFLOP/s with the 8*B^2*D convention (forward 2, recompute 2, two gradient
 contractions 2+2).  Prints ONE JSON line on rank 0.
@@ -174,7 +176,7 @@ def run_ours(args):
     if world == 1:
         name = args.config or "clip_b32768_d1152_bf16"
     else:
-        name = args.config or "ring_clip_b131072_d768_bf16"
+        name = args.config or "ring_clip_b262144_d1024_bf16"
     kind, b_global, d, dtype, temperature, normalized_inputs, _gen = synth.CONFIGS[name]
     if args.batch:
         b_global = args.batch
@@ -303,13 +305,15 @@ def run_ours(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=None)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--config", default=None)
     ap.add_argument("--batch", type=int, default=None, help="override the global batch (debugging)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
+    if args.steps is None:      # long enough for several clock samples, short enough for a default run
+        args.steps = 3 if args.impl == "reference" else (50 if args.gpus == 1 else 10)
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
         run_reference_arm(args)

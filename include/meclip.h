@@ -85,6 +85,13 @@ int meclip_profile_begin(void);
 int meclip_profile_end(double* ms_by_tag, long long* launches_by_tag, double* flops_by_tag, int n_tags);
 
 /*
+ * dst[i] += src[i] over n fp32 values (n a multiple of 4, 16-byte aligned).  Used by the
+ * ring backward: the owner of a text shard adds the partial gradients the other ranks
+ * send it.  Has no counterpart in the reference (which is single-GPU).
+ */
+int meclip_accumulate_f32(float* dst, const float* src, int64_t n, void* stream);
+
+/*
  * x_hat = x / max(||x||_2, 1e-12) per row, written as bf16, plus inv_norm[i] =
  * 1/max(||x_i||, 1e-12).  With normalize == 0 only the dtype conversion to bf16
  * is done (inv_norm may be NULL).  Replaces F.normalize(dim=1) at

@@ -28,6 +28,7 @@ SIGNATURES = {
     "meclip_launch_count": (ctypes.c_longlong, []),
     "meclip_profile_begin": (c_int, []),
     "meclip_profile_end": (c_int, [c_void_p, c_void_p, c_void_p, c_int]),
+    "meclip_accumulate_f32": (c_int, [c_void_p, c_void_p, c_int64, c_void_p]),
     "meclip_normalize_fwd": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_int, c_void_p, c_int64, c_void_p,
                                      c_void_p]),
     "meclip_normalize_bwd": (c_int, [c_void_p, c_int, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int64,

@@ -217,6 +217,19 @@ transpose_bf16_kernel(const __nv_bfloat16* __restrict__ in, long long ld_in, lon
     }
 }
 
+// dst[i] += src[i], fp32, 16-byte accesses (the owner of a text shard adds the partial
+// gradient another rank of the ring sent it).
+__global__ void __launch_bounds__(256)
+accumulate_f32_kernel(float* __restrict__ dst, const float* __restrict__ src, long long n4) {
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += stride) {
+        float4 a = reinterpret_cast<float4*>(dst)[i];
+        const float4 b = reinterpret_cast<const float4*>(src)[i];
+        a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
+        reinterpret_cast<float4*>(dst)[i] = a;
+    }
+}
+
 // loss (+)= scale * sum_i [ w (log r_i + log c_i) - (s_ii - 1)/T ]: one block, fixed order.
 __global__ void __launch_bounds__(1024)
 loss_finalize_kernel(const float* __restrict__ r, const float* __restrict__ c, const float* __restrict__ diag,
@@ -669,6 +682,19 @@ int meclip_profile_end(double* ms_by_tag, long long* launches_by_tag, double* fl
     }
     g_prof.clear();
     if (rc) return fail(rc, "profile_end: reading an event failed");
+    return MECLIP_OK;
+}
+
+int meclip_accumulate_f32(float* dst, const float* src, int64_t n, void* stream) {
+    if (dst == nullptr || src == nullptr || n < 0 || n % 4 != 0 || !aligned16(dst) || !aligned16(src))
+        return fail(MECLIP_EINVAL, "accumulate_f32: need 16-byte aligned pointers and n a multiple of 4");
+    if (n == 0) return MECLIP_OK;
+    const long long n4 = n / 4;
+    long long blocks = (n4 + 255) / 256;
+    if (blocks > 8LL * sm_count()) blocks = 8LL * sm_count();
+    ScopedTiming timing((cudaStream_t)stream, TAG_ROW, 0.0);
+    accumulate_f32_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(dst, src, n4);
+    MECLIP_CUDA(cudaGetLastError());
     return MECLIP_OK;
 }
 

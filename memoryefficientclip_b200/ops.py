@@ -62,6 +62,13 @@ def normalize_bwd(g: torch.Tensor, x_hat: torch.Tensor, inv_norm: torch.Tensor, 
     return dx
 
 
+def accumulate_f32(dst: torch.Tensor, src: torch.Tensor) -> None:
+    """dst += src (fp32, contiguous, same shape) on the current stream."""
+    assert dst.dtype == torch.float32 and src.dtype == torch.float32 and dst.numel() == src.numel()
+    with torch.cuda.device(dst.device):
+        _lib.check(_lib.load().meclip_accumulate_f32(dst.data_ptr(), src.data_ptr(), dst.numel(), _stream(dst)))
+
+
 def as_operand(x: torch.Tensor) -> torch.Tensor:
     """bf16, unit-stride rows, 16-byte aligned: what the tile kernels read."""
     _check_matrix(x, "operand")

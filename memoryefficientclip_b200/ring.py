@@ -11,8 +11,10 @@ forward   row sums finish locally; per-shard column partial sums [N, b] are
           reduce-scattered so that each rank ends with the column sums of its own
           shard; the loss is the all-reduced sum of the local terms.
 backward  column sums are all-gathered (B floats); d(first) accumulates locally in
-          fp32 over the N steps; the d(second) partial of each visiting shard is
-          written to a [N, b, D] fp32 table and reduce-scattered at the end.
+          fp32 over the N steps; the d(second) partial a rank computes for a visiting
+          shard is sent straight to the shard's owner while the next step computes
+          (a reduce-scatter spread over the steps: only the last partial's transfer is
+          exposed, and no [N, b, D] table exists); the owner adds what it receives.
 
 The reference has no distributed code; the result is defined as the single-process
 loss on the concatenated global batch (rank-major row order).
@@ -60,6 +62,9 @@ class CudaBlockOps:
 
     def workspace(self, rows, cols, d, device):
         return ops.grad_workspace(rows, cols, d, device)
+
+    def accumulate(self, dst, src):
+        ops.accumulate_f32(dst, src)
 
     def reduce_scatter(self, out, table, group):
         dist.reduce_scatter_tensor(out.view(-1), table.view(-1), op=dist.ReduceOp.SUM, group=group)
@@ -121,6 +126,17 @@ def ring_forward(block, kind, x_hat, y_hat, temperature, group, rank, world):
     return loss, row_sum, col_sum, diag
 
 
+def _exchange_partial(send_buf, recv_buf, group, rank, world, step):
+    """The partial computed at ring step `step` belongs to shard (rank+step): send it to that rank
+    and receive, from rank (rank-step), the partial it computed for this rank's own shard."""
+    dst = (rank + step) % world
+    src = (rank - step) % world
+    dst_g = dist.get_global_rank(group, dst) if group is not None else dst
+    src_g = dist.get_global_rank(group, src) if group is not None else src
+    p2p = [dist.P2POp(dist.isend, send_buf, dst_g, group), dist.P2POp(dist.irecv, recv_buf, src_g, group)]
+    return dist.batch_isend_irecv(p2p)
+
+
 def ring_backward(block, kind, x_hat, y_hat, temperature, row_sum, col_sum, grad_out, grad_scale, group, rank, world):
     """Returns (dx fp32 [b, D], dy_own fp32 [b, D] or None) w.r.t. the normalised operands."""
     b, d = x_hat.shape
@@ -134,31 +150,41 @@ def ring_backward(block, kind, x_hat, y_hat, temperature, row_sum, col_sum, grad
         else:
             col_all = col_sum.view(1, b)
     dx = torch.zeros(b, d, dtype=torch.float32, device=dev)
-    dy_table = torch.empty(world, b, d, dtype=torch.float32, device=dev) if clip else None
+    dy = torch.empty(b, d, dtype=torch.float32, device=dev) if clip else None          # own shard: step 0 stores it
+    part = [torch.empty(b, d, dtype=torch.float32, device=dev) for _ in range(2)] if clip and world > 1 else []
+    inbox = [torch.empty(b, d, dtype=torch.float32, device=dev) for _ in range(2)] if clip and world > 1 else []
     workspace = block.workspace(b, b, d, dev)
     bufs = [y_hat, torch.empty_like(y_hat)] if world > 1 else [y_hat]
     if world > 2:
         bufs.append(torch.empty_like(y_hat))
     cur = 0
+    pending = None          # (requests, inbox buffer) of the previous step's partial exchange
     for step in range(world):
         shard = shard_at(rank, step, world)
         reqs = []
         if step + 1 < world:
             nxt = 1 + (step % 2) if world > 2 else 1
             reqs = _rotate(bufs[cur], bufs[nxt], group, rank, world)
+        out = None
+        if clip:
+            out = dy if step == 0 else part[step % 2]
         block.grad(kind, x_hat, bufs[cur], temperature, row_sum, col_all[shard] if clip else None, grad_out,
-                   grad_scale, dx, dy_table[shard] if clip else None, rank * b, shard * b, workspace)
+                   grad_scale, dx, out, rank * b, shard * b, workspace)
+        if pending is not None:          # the exchange started one step ago ran under this step's kernels
+            for r in pending[0]:
+                r.wait()
+            block.accumulate(dy, pending[1])
+            pending = None
+        if clip and step > 0:
+            pending = (_exchange_partial(part[step % 2], inbox[step % 2], group, rank, world, step), inbox[step % 2])
         for r in reqs:
             r.wait()
         if step + 1 < world:
             cur = nxt
-    dy = None
-    if clip:
-        if world > 1:
-            dy = torch.empty(b, d, dtype=torch.float32, device=dev)
-            block.reduce_scatter(dy, dy_table, group)
-        else:
-            dy = dy_table[0]
+    if pending is not None:
+        for r in pending[0]:
+            r.wait()
+        block.accumulate(dy, pending[1])
     return dx, dy
 
 

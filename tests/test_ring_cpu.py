@@ -55,6 +55,9 @@ class OracleBlockOps:
     def workspace(self, rows, cols, d, device):
         return None
 
+    def accumulate(self, dst, src):
+        dst += src
+
     def reduce_scatter(self, out, table, group):      # gloo has no reduce_scatter_tensor
         t = table.clone()
         dist.all_reduce(t, group=group)
