@@ -265,7 +265,11 @@ def run_ours(args):
     roofline = {
         "bound": "tensor", "kernel": "umma_gemm_kernel/" + dominant["kernel"], "achieved": achieved,
         "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": achieved / peaks["bf16_tflops"],
-        "peak_source": peaks["source"] + " bf16 burst", "traffic": None,
+        "peak_source": peaks["source"] + " bf16 burst",
+        # DRAM read + write bytes per launch of a contraction kernel, from the ncu capture summarised in
+        # profiles/umma_gemm_kernel_clip_b16384_d1152_ncu_full.md (1.06 GB per 537 MB panel), scaled by panel bytes
+        "traffic": (1.06e9 * (dom_flops / 6.18e11) if dominant["kernel"] in ("dx_contraction", "dy_contraction")
+                    else None),
         "step_frac_of_burst": tflops * (1 if world == 1 else 1.0 / world) / peaks["bf16_tflops"],
         "step_frac_of_sustained": tflops * (1 if world == 1 else 1.0 / world) / peaks["bf16_tflops_sustained"],
         "per_kernel": [dict(t, ms_per_step=t["ms"] / prof_steps,
@@ -313,7 +317,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     if args.steps is None:      # long enough for several clock samples, short enough for a default run
-        args.steps = 3 if args.impl == "reference" else (50 if args.gpus == 1 else 10)
+        args.steps = 3 if args.impl == "reference" else (100 if args.gpus == 1 else 10)
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
         run_reference_arm(args)
