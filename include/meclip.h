@@ -60,6 +60,14 @@ int meclip_last_error(char* buf, size_t buf_len);
 int meclip_read_status(const int* status, void* stream);
 
 /*
+ * Test hook: override the backward's blocking (rows of the coefficient matrix formed per
+ * block, a multiple of 128, and the byte budget of one panel) so that small problems run
+ * the multi-panel / multi-row-block code paths; 0, 0 restores the defaults (32768 rows,
+ * 512 MiB).  Affects meclip_grad_workspace_bytes too.  Has no counterpart in the reference.
+ */
+int meclip_debug_set_blocking(int64_t row_block, int64_t panel_bytes);
+
+/*
  * Test hook: in-kernel trace.  device_words points to n_words zeroed 64-bit words on the
  * device; while set, CTA 0 of every tile kernel appends {tag, tile, nanosecond timer}
  * records from word 2 on (the producer, the MMA issuer and the epilogue each fill their
@@ -158,6 +166,20 @@ int meclip_grad(int kind, const void* x_bf16, const void* y_bf16, int64_t rows, 
                 const float* col_sum, const float* grad_out, float grad_scale, void* dx, int dx_mode, int64_t lddx,
                 void* dy, int dy_mode, int64_t lddy, void* workspace, size_t workspace_bytes, int* status,
                 void* stream);
+
+/*
+ * meclip_grad that also accumulates *sum_g_s += sum_ij G_ij S_ij over the block (fp32 device
+ * scalar, zeroed by the caller, fp32 atomics).  With g = grad_scale * (*grad_out) the matrix G
+ * satisfies sum_ij G_ij S_ij = g * B * dL/d(1/T), so for the plain scaling (grad_scale = 1/(B T))
+ * the temperature gradient is  grad_out * dL/dT = -(1/T) * sum_g_s.  The reference treats the
+ * temperature as a constant (backward returns None for it, clip_loss.py:256); this is the
+ * learnable-temperature extension.
+ */
+int meclip_grad_t(int kind, const void* x_bf16, const void* y_bf16, int64_t rows, int64_t cols, int64_t d, int64_t ldx,
+                  int64_t ldy, float temperature, int64_t row_off, int64_t col_off, const float* row_sum,
+                  const float* col_sum, const float* grad_out, float grad_scale, void* dx, int dx_mode, int64_t lddx,
+                  void* dy, int dy_mode, int64_t lddy, float* sum_g_s, void* workspace, size_t workspace_bytes,
+                  int* status, void* stream);
 
 /*
  * meclip_grad for callers that have no device memory to give: the coefficient panel

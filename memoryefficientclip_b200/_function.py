@@ -28,14 +28,20 @@ class ContrastiveLossFn(torch.autograd.Function):
         else:
             x_hat, inv_x = ops.as_operand(x), None
             y_hat, inv_y = ops.as_operand(y), None
-        loss, row_sum, col_sum, _diag = ops.loss_forward(kind, x_hat, y_hat, temperature)
+        # A tensor temperature (e.g. an nn.Parameter) is read on the host once per forward; it then
+        # also receives a gradient, which the reference does not provide (clip_loss.py:256).
+        t_is_tensor = isinstance(temperature, torch.Tensor)
+        temperature_value = float(temperature.detach().item()) if t_is_tensor else float(temperature)
+        assert temperature_value > 0.0, "temperature must be positive"
+        loss, row_sum, col_sum, _diag = ops.loss_forward(kind, x_hat, y_hat, temperature_value)
         saved = [x_hat, y_hat, row_sum]
         if col_sum is not None:
             saved.append(col_sum)
         if normalize:
             saved += [inv_x, inv_y]
         ctx.save_for_backward(*saved)
-        ctx.meclip = (float(temperature), kind, bool(stable), bool(normalize), x.dtype, y.dtype)
+        ctx.meclip = (temperature_value, kind, bool(stable), bool(normalize), x.dtype, y.dtype)
+        ctx.meclip_t = temperature if t_is_tensor and temperature.requires_grad else None
         return loss
 
     @staticmethod
@@ -54,7 +60,16 @@ class ContrastiveLossFn(torch.autograd.Function):
         # with the fused Jacobian the contraction output stays fp32 until the Jacobian rounds once
         dx_t = torch.float32 if normalize else x_dtype
         dy_t = torch.float32 if normalize else y_dtype
-        dx, dy = ops.loss_backward(kind, x_hat, y_hat, temperature, row_sum, col_sum, go, scale, dx_t, dy_t)
+        t_param = getattr(ctx, "meclip_t", None)
+        sum_g_s = torch.zeros(1, dtype=torch.float32, device=x_hat.device) if t_param is not None else None
+        dx, dy = ops.loss_backward(kind, x_hat, y_hat, temperature, row_sum, col_sum, go, scale, dx_t, dy_t,
+                                   sum_g_s=sum_g_s)
+        ctx.meclip_dt = None
+        if sum_g_s is not None:
+            # sum_ij G_ij S_ij = g B dL/d(1/T) with g = go * scale, so go * dL/dT = -(sum / (scale B)) / T^2.
+            # (The Stable scaling only rescales the feature gradients; the temperature gets the true one.)
+            dt = sum_g_s * (-1.0 / (scale * batch * temperature * temperature))
+            ctx.meclip_dt = dt.reshape(t_param.shape).to(t_param.dtype)
         if normalize:
             dx = ops.normalize_bwd(dx, x_hat, inv_x, x_dtype)
             if want_dy:
@@ -68,4 +83,4 @@ class ContrastiveLossFn(torch.autograd.Function):
     @staticmethod
     def backward(ctx, grad_output):
         dx, dy = ContrastiveLossFn.run_backward(ctx, grad_output)
-        return dx, dy, None, None, None, None
+        return dx, dy, ctx.meclip_dt, None, None, None

@@ -24,6 +24,7 @@ SIGNATURES = {
     "meclip_status_string": (c_char_p, [c_int]),
     "meclip_last_error": (c_int, [c_char_p, c_size_t]),
     "meclip_read_status": (c_int, [c_void_p, c_void_p]),
+    "meclip_debug_set_blocking": (c_int, [c_int64, c_int64]),
     "meclip_debug_set_trace": (c_int, [c_void_p, c_size_t]),
     "meclip_launch_count": (ctypes.c_longlong, []),
     "meclip_profile_begin": (c_int, []),
@@ -41,6 +42,9 @@ SIGNATURES = {
     "meclip_grad": (c_int, [c_int, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64, c_float, c_int64,
                             c_int64, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_int, c_int64, c_void_p,
                             c_int, c_int64, c_void_p, c_size_t, c_void_p, c_void_p]),
+    "meclip_grad_t": (c_int, [c_int, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64, c_float, c_int64,
+                              c_int64, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_int, c_int64, c_void_p,
+                              c_int, c_int64, c_void_p, c_void_p, c_size_t, c_void_p, c_void_p]),
     "meclip_grad_static": (c_int, [c_int, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64, c_float,
                                    c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_int, c_int64,
                                    c_void_p, c_int, c_int64, c_void_p, c_void_p]),

@@ -27,7 +27,7 @@ class MemoryEfficientCLIPLossNormed(torch.autograd.Function):
     @staticmethod
     def backward(ctx, grad_output):
         dx, dy = ContrastiveLossFn.run_backward(ctx, grad_output)
-        return dx, dy, None
+        return dx, dy, ctx.meclip_dt
 
 
 class StableMemoryEfficientCLIPLossNormed(torch.autograd.Function):
@@ -40,7 +40,7 @@ class StableMemoryEfficientCLIPLossNormed(torch.autograd.Function):
     @staticmethod
     def backward(ctx, grad_output):
         dx, dy = ContrastiveLossFn.run_backward(ctx, grad_output)
-        return dx, dy, None
+        return dx, dy, ctx.meclip_dt
 
 
 class _CLIPLossModule(nn.Module):

@@ -129,6 +129,8 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, const CUtenso
         // tensor map).
         const float dsub = p.dcoef * st.gscale;
         const bool diag_here = __any_sync(0xffffffffu, jd >= 0);
+        const bool want_sg = p.sg_acc != nullptr;      // sum of G_ij * S_ij for the temperature gradient
+        float sg = 0.f;
         uint8_t* buf = tail->scratch + (size_t)(warp - 2) * STORE_BUF_BYTES;
         for (int u = u_begin; u < u_end; ++u) {
             if (lane == 0 && st.stores_in_flight > 0) {     // the previous store has finished reading `buf`
@@ -161,6 +163,10 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, const CUtenso
                     for (int c = 0; c < 32; ++c)
                         if (n0 + ch * 32 + c >= p.n) gv[c] = 0.f;
                 }
+                if (want_sg && rvalid) {
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) sg = fmaf(gv[c], __uint_as_float(v[c]), sg);
+                }
 #pragma unroll
                 for (int pc = 0; pc < 4; ++pc) {         // 16-byte piece index within the 128-byte row
                     uint4 pk;
@@ -182,6 +188,11 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, const CUtenso
         }
         tc_fence_before();
         release();
+        if (want_sg) {
+#pragma unroll
+            for (int o = 16; o >= 1; o >>= 1) sg += __shfl_xor_sync(0xffffffffu, sg, o);
+            if (lane == 0) atomicAdd(p.sg_acc, sg);
+        }
     } else {   // EPI_OUT
         for (int ch = u_begin; ch < u_end; ++ch) {
             uint32_t v[32];

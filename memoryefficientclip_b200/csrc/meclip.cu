@@ -418,11 +418,17 @@ static int launch_pair_t(const CUtensorMap& ta, const CUtensorMap& tb, const CUt
     return MECLIP_OK;
 }
 
-static bool pair_allowed() {
-    // Off by default: with round-robin tiles the pair kernels measure within +-3 % of the single-CTA
-    // kernels, which balance better when kernels overlap.  MECLIP_PAIR=1 switches them on.
-    static const bool on = []() { const char* v = std::getenv("MECLIP_PAIR"); return v != nullptr && v[0] == '1'; }();
-    return on;
+// MECLIP_PAIR: 0 = single-CTA kernels only (default), 1 = CTA pairs wherever B is K-major,
+// 2 = CTA pairs for the two contractions when their tile is 256 wide.  Measured: mode 2 raises
+// the isolated contraction kernels by 5-15 % at D = 768 / 1024 but leaves the power-capped step
+// time unchanged (25.0 vs 25.1 ms, 8.03 vs 8.07 ms), so the simpler kernels stay the default.
+static int pair_mode() {
+    static const int mode = []() {
+        const char* v = std::getenv("MECLIP_PAIR");
+        if (v == nullptr || v[0] == '\0') return 0;
+        return std::atoi(v);
+    }();
+    return mode;
 }
 
 // `panel` (EPI_COEF only): the bf16 output panel [m x n], column-blocked with panel_rows_alloc rows
@@ -447,7 +453,9 @@ static int launch_gemm(int epi, const Operand& a, const Operand& b, long long m,
     else                   rc = make_tmap(&ta, a.ptr, k, m, a.ld, BK, BM);
     if (rc) return rc;
     // CTA pairs (256 x bn tiles) whenever B is K-major; the single-CTA kernel keeps MN-major B
-    const bool pair = pair_allowed() && !b.mn_major && bn % 64 == 0;
+    const int pmode = pair_mode();
+    const bool pair = !b.mn_major && bn % 64 == 0 &&
+                      (pmode == 1 || (pmode == 2 && epi == EPI_OUT && bn == 256 && p.trace == nullptr && g_trace_buf == nullptr));
     if (b.mn_major) rc = make_tmap(&tb, b.ptr, n, k, b.ld, 64, BK);
     else            rc = make_tmap(&tb, b.ptr, k, n, b.ld, BK, pair ? bn / 2 : bn);
     if (rc) return rc;
@@ -530,10 +538,15 @@ struct GradPlan {
     size_t total() const { return g_bytes * g_buffers + dx_bytes + dy_bytes + counter_bytes + xt_bytes + yt_bytes; }
 };
 
+// test hook: smaller blocks so that small problems exercise the multi-block paths (0 = defaults)
+static long long g_row_block_override = 0, g_panel_bytes_override = 0;
+
 static GradPlan plan_grad(long long rows, long long cols, long long d, bool transposed_copies = true) {
     GradPlan g;
-    g.row_block = rows < ROW_BLOCK ? rows : ROW_BLOCK;
-    long long w = PANEL_BYTES / (g.row_block * 2) / 256 * 256;
+    const long long row_block_max = g_row_block_override > 0 ? g_row_block_override : ROW_BLOCK;
+    const long long panel_bytes = g_panel_bytes_override > 0 ? g_panel_bytes_override : PANEL_BYTES;
+    g.row_block = rows < row_block_max ? rows : row_block_max;
+    long long w = panel_bytes / (g.row_block * 2) / 256 * 256;
     if (w < 256) w = 256;
     if (w > 32768) w = 32768;
     if (w > cols) w = cols;
@@ -639,6 +652,14 @@ int meclip_read_status(const int* status, void* stream) {
     MECLIP_CUDA(cudaMemcpyAsync(&host, status, sizeof(int), cudaMemcpyDeviceToHost, (cudaStream_t)stream));
     MECLIP_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
     if (host != 0) return fail(MECLIP_ETIMEOUT, "a kernel gave up waiting on a barrier (status word %d)", host);
+    return MECLIP_OK;
+}
+
+int meclip_debug_set_blocking(int64_t row_block, int64_t panel_bytes) {
+    if (row_block < 0 || panel_bytes < 0 || (row_block > 0 && row_block % 128 != 0))
+        return fail(MECLIP_EINVAL, "debug_set_blocking: row_block must be a multiple of 128");
+    g_row_block_override = row_block;
+    g_panel_bytes_override = panel_bytes;
     return MECLIP_OK;
 }
 
@@ -801,7 +822,7 @@ static int grad_impl(int kind, const void* x_bf16, const void* y_bf16, int64_t r
                      int64_t ldy, float temperature, int64_t row_off, int64_t col_off, const float* row_sum,
                      const float* col_sum, const float* grad_out, float grad_scale, void* dx, int dx_mode, int64_t lddx,
                      void* dy, int dy_mode, int64_t lddy, void* workspace, size_t workspace_bytes, int* status,
-                     cudaStream_t s0, bool overlap, bool transposed_copies) {
+                     cudaStream_t s0, bool overlap, bool transposed_copies, float* sg_acc = nullptr) {
     if (kind != MECLIP_CLIP && kind != MECLIP_LIT) return fail(MECLIP_EINVAL, "grad: bad kind %d", kind);
     if (x_bf16 == nullptr || y_bf16 == nullptr || row_sum == nullptr || dx == nullptr || workspace == nullptr)
         return fail(MECLIP_EINVAL, "grad: null pointer");
@@ -883,6 +904,7 @@ static int grad_impl(int kind, const void* x_bf16, const void* y_bf16, int64_t r
                 p.grad_out = grad_out;
                 p.coef = clip ? 0.5f * grad_scale : grad_scale;
                 p.dcoef = grad_scale;
+                p.sg_acc = sg_acc;
                 p.tile_counter = counters + 3 * t;
                 p.status = status;
                 Operand a{X + r0 * ldx, ldx, false}, b{Y + c0 * ldy, ldy, false};
@@ -970,6 +992,17 @@ int meclip_grad(int kind, const void* x_bf16, const void* y_bf16, int64_t rows, 
     return grad_impl(kind, x_bf16, y_bf16, rows, cols, d, ldx, ldy, temperature, row_off, col_off, row_sum, col_sum,
                      grad_out, grad_scale, dx, dx_mode, lddx, dy, dy_mode, lddy, workspace, workspace_bytes, status,
                      (cudaStream_t)stream, overlap_allowed(), transposes_allowed());
+}
+
+int meclip_grad_t(int kind, const void* x_bf16, const void* y_bf16, int64_t rows, int64_t cols, int64_t d, int64_t ldx,
+                  int64_t ldy, float temperature, int64_t row_off, int64_t col_off, const float* row_sum,
+                  const float* col_sum, const float* grad_out, float grad_scale, void* dx, int dx_mode, int64_t lddx,
+                  void* dy, int dy_mode, int64_t lddy, float* sum_g_s, void* workspace, size_t workspace_bytes,
+                  int* status, void* stream) {
+    if (sum_g_s == nullptr) return fail(MECLIP_EINVAL, "grad_t: sum_g_s is null");
+    return grad_impl(kind, x_bf16, y_bf16, rows, cols, d, ldx, ldy, temperature, row_off, col_off, row_sum, col_sum,
+                     grad_out, grad_scale, dx, dx_mode, lddx, dy, dy_mode, lddy, workspace, workspace_bytes, status,
+                     (cudaStream_t)stream, overlap_allowed(), transposes_allowed(), sum_g_s);
 }
 
 int meclip_loss_forward(int kind, const void* x_bf16, const void* y_bf16, int64_t batch, int64_t d, int64_t ldx,

@@ -62,6 +62,7 @@ struct GemmParams {
     const float* grad_out;    // COEF: device scalar
     float coef;               // COEF: grad_scale * (0.5 for CLIP, 1 for LiT)
     float dcoef;              // COEF: grad_scale (subtracted on the diagonal)
+    float* sg_acc;            // COEF: optional, += sum_ij G_ij S_ij (fp32 G before rounding); null = off
     // EPI_OUT
     void* out;
     long long ld_out;

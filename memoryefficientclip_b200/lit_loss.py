@@ -26,7 +26,7 @@ class MemoryEfficientLiTLossNormed(torch.autograd.Function):
     @staticmethod
     def backward(ctx, grad_output):
         dx, _ = ContrastiveLossFn.run_backward(ctx, grad_output)
-        return dx, None, None
+        return dx, None, ctx.meclip_dt
 
 
 class StableMemoryEfficientLiTLossNormed(torch.autograd.Function):
@@ -37,7 +37,7 @@ class StableMemoryEfficientLiTLossNormed(torch.autograd.Function):
     @staticmethod
     def backward(ctx, grad_output):
         dx, _ = ContrastiveLossFn.run_backward(ctx, grad_output)
-        return dx, None, None
+        return dx, None, ctx.meclip_dt
 
 
 class _LiTLossModule(nn.Module):

@@ -83,6 +83,22 @@ def lit_dense(text, image, temperature=0.07, normalized_inputs=False, stable=Fal
     return loss.detach(), gx * mult
 
 
+def temperature_grad_dense(first, second, temperature, kind="clip", normalized_inputs=False, dtype=torch.float64):
+    """d loss / d temperature by autograd on the dense formulation (the reference has no such
+    gradient: its backward returns None for the temperature, clip_loss.py:256)."""
+    x = _prep(first, dtype, False)
+    y = _prep(second, dtype, False)
+    t = torch.tensor(float(temperature), dtype=dtype, requires_grad=True)
+    xn, yn = (x, y) if normalized_inputs else (F.normalize(x, dim=1), F.normalize(y, dim=1))
+    logits = xn @ yn.t() / t
+    labels = torch.arange(x.shape[0])
+    loss = F.cross_entropy(logits, labels)
+    if kind == "clip":
+        loss = 0.5 * (loss + F.cross_entropy(logits.t(), labels))
+    (gt,) = torch.autograd.grad(loss, (t,))
+    return float(gt)
+
+
 # --------------------------------------------------------------------------- #
 # closed form: the reference's algorithm without the tiling
 # --------------------------------------------------------------------------- #

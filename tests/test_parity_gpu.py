@@ -151,3 +151,24 @@ def test_medium_batch_multi_panel_properties():
     loss, dx, dy = _run_clip(img, txt, 0.07, False)
     rl, rx, ry = dense.clip_dense(img, txt, 0.07, False, dtype=torch.float32)
     dense.assert_parity(loss, rl, (dx, dy), (rx, ry), "clip_b4096_d512_f32")
+
+
+@pytest.mark.parametrize("kind,stable,b,d,t", [("clip", False, 384, 64, 0.07), ("clip", True, 256, 128, 0.2),
+                                              ("lit", False, 320, 96, 0.05)])
+def test_learnable_temperature_gradient(kind, stable, b, d, t):
+    """Extension: a tensor temperature receives d loss / dT (the reference returns None)."""
+    m = _mods()
+    x, y = _inputs(b, d, 8, False, torch.float32)
+    temp = torch.nn.Parameter(torch.tensor(t, device="cuda"))
+    cls = {("clip", False): m.MemoryEfficientCLIPLoss, ("clip", True): m.StableMemoryEfficientCLIPLoss,
+           ("lit", False): m.MemoryEfficientLiTLoss}[(kind, stable)]
+    xg = x.cuda().requires_grad_(True)
+    loss = cls(temp, False)(xg, y.cuda())
+    loss.backward(torch.tensor(2.0, device="cuda"))
+    want = 2.0 * dense.temperature_grad_dense(x, y, t, kind, False)
+    got = temp.grad.item()
+    assert abs(got - want) <= 1e-2 * abs(want), (got, want)
+    # a float temperature still gets no gradient and the feature gradients are unchanged
+    xg2 = x.cuda().requires_grad_(True)
+    cls(t, False)(xg2, y.cuda()).backward(torch.tensor(2.0, device="cuda"))
+    assert dense.grad_errors(xg.grad, xg2.grad)[0] < 1e-4      # forward sums use atomics: last-bit differences
