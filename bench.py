@@ -266,8 +266,8 @@ def run_ours(args):
         "bound": "tensor", "kernel": "umma_gemm_kernel/" + dominant["kernel"], "achieved": achieved,
         "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": achieved / peaks["bf16_tflops"],
         "peak_source": peaks["source"] + " bf16 burst",
-        # DRAM read + write bytes per launch of a contraction kernel, from the ncu capture summarised in
-        # profiles/umma_gemm_kernel_clip_b16384_d1152_ncu_full.md (1.06 GB per 537 MB panel), scaled by panel bytes
+        # DRAM read + write bytes per launch of a contraction kernel, from an ncu capture of this kernel at
+        # B=16384, D=1152 (1.06 GB per 537 MB coefficient panel), scaled by the launch's work
         "traffic": (1.06e9 * (dom_flops / 6.18e11) if dominant["kernel"] in ("dx_contraction", "dy_contraction")
                     else None),
         "step_frac_of_burst": tflops * (1 if world == 1 else 1.0 / world) / peaks["bf16_tflops"],

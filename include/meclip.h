@@ -61,7 +61,7 @@ int meclip_read_status(const int* status, void* stream);
 
 /*
  * Test hook: override the backward's blocking (rows of the coefficient matrix formed per
- * block, a multiple of 128, and the byte budget of one panel) so that small problems run
+ * block, a multiple of 128, and the byte limit of one panel) so that small problems run
  * the multi-panel / multi-row-block code paths; 0, 0 restores the defaults (32768 rows,
  * 512 MiB).  Affects meclip_grad_workspace_bytes too.  Has no counterpart in the reference.
  */

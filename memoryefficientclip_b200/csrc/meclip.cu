@@ -526,7 +526,7 @@ static int launch_gemm(int epi, const Operand& a, const Operand& b, long long m,
 // backward blocking
 // ------------------------------------------------------------------------------------
 static constexpr long long ROW_BLOCK = 32768;                  // rows of G formed per block
-static constexpr long long PANEL_BYTES = 512ll << 20;          // bf16 coefficient panel budget
+static constexpr long long PANEL_BYTES = 512ll << 20;          // most bytes one bf16 coefficient panel may take
 
 struct GradPlan {
     long long row_block, panel_w, ldg;

@@ -86,7 +86,9 @@ def run_case(ref_clip, ref_lit, kind, b, d, temperature, stable, grad_output):
 
 
 def main():
-    ref_dir = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: make_golden.py /path/to/reference/checkout")
+    ref_dir = sys.argv[1]
     sys.path.insert(0, ref_dir)
     import clip_loss as ref_clip
     import lit_loss as ref_lit
