@@ -154,7 +154,8 @@ size_t meclip_grad_workspace_bytes(int64_t rows, int64_t cols, int64_t d);
  *   CLIP: G_ij = g * (E_ij/row_sum[i] + E_ij/col_sum[j]) / 2,   LiT: G_ij = g * E_ij/row_sum[i]
  *   G_ii -= g   (the "-Y/(B T)" initialisation of clip_loss.py:235-236 folded in)
  * with g = grad_scale * (*grad_out), panel by panel in bf16, and contracts it:
- *   dX (rows x d) = G Y,     dY (cols x d) = G^T X   (dY NULL for LiT).
+ *   dX (rows x d) = G Y,     dY (cols x d) = G^T X   (dY is ignored for LiT).
+ * Either output may be NULL (a frozen tower): its contraction is skipped.
  * grad_scale is 1/(B*T) (clip_loss.py:182) or 1/sqrt(B*T) for the Stable
  * variants (clip_loss.py:299); B is the GLOBAL batch.  grad_out is a device
  * scalar (no host sync, unlike clip_loss.py:252).  Deterministic: no atomics.

@@ -56,14 +56,18 @@ class ContrastiveLossFn(torch.autograd.Function):
         # grad_output stays on the device: no host sync (the reference compares it to 1.0 on the host)
         go = grad_output.detach().to(device=x_hat.device, dtype=torch.float32).reshape(1).contiguous()
         scale = ops.grad_scale(batch, temperature, stable)
-        want_dy = kind == _lib.CLIP
+        need = tuple(ctx.needs_input_grad) + (False, False)
+        want_dx = bool(need[0])
+        want_dy = kind == _lib.CLIP and bool(need[1])      # a frozen tower costs no contraction
         # with the fused Jacobian the contraction output stays fp32 until the Jacobian rounds once
         dx_t = torch.float32 if normalize else x_dtype
         dy_t = torch.float32 if normalize else y_dtype
         t_param = getattr(ctx, "meclip_t", None)
         sum_g_s = torch.zeros(1, dtype=torch.float32, device=x_hat.device) if t_param is not None else None
+        if sum_g_s is not None and not (want_dx or want_dy):
+            want_dx = True       # the temperature sum is produced by the coefficient pass of the backward
         dx, dy = ops.loss_backward(kind, x_hat, y_hat, temperature, row_sum, col_sum, go, scale, dx_t, dy_t,
-                                   sum_g_s=sum_g_s)
+                                   sum_g_s=sum_g_s, need_dx=want_dx, need_dy=want_dy)
         ctx.meclip_dt = None
         if sum_g_s is not None:
             # sum_ij G_ij S_ij = g B dL/d(1/T) with g = go * scale, so go * dL/dT = -(sum / (scale B)) / T^2.
@@ -71,10 +75,11 @@ class ContrastiveLossFn(torch.autograd.Function):
             dt = sum_g_s * (-1.0 / (scale * batch * temperature * temperature))
             ctx.meclip_dt = dt.reshape(t_param.shape).to(t_param.dtype)
         if normalize:
-            dx = ops.normalize_bwd(dx, x_hat, inv_x, x_dtype)
-            if want_dy:
+            if dx is not None:
+                dx = ops.normalize_bwd(dx, x_hat, inv_x, x_dtype)
+            if dy is not None:
                 dy = ops.normalize_bwd(dy, y_hat, inv_y, y_dtype)
-        return dx, (dy if want_dy else None)
+        return (dx if need[0] else None), (dy if want_dy else None)
 
     @staticmethod
     def forward(ctx, x, y, temperature, kind, stable, normalize):

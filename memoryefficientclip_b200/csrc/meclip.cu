@@ -824,14 +824,17 @@ static int grad_impl(int kind, const void* x_bf16, const void* y_bf16, int64_t r
                      void* dy, int dy_mode, int64_t lddy, void* workspace, size_t workspace_bytes, int* status,
                      cudaStream_t s0, bool overlap, bool transposed_copies, float* sg_acc = nullptr) {
     if (kind != MECLIP_CLIP && kind != MECLIP_LIT) return fail(MECLIP_EINVAL, "grad: bad kind %d", kind);
-    if (x_bf16 == nullptr || y_bf16 == nullptr || row_sum == nullptr || dx == nullptr || workspace == nullptr)
+    if (x_bf16 == nullptr || y_bf16 == nullptr || row_sum == nullptr || workspace == nullptr)
         return fail(MECLIP_EINVAL, "grad: null pointer");
-    if (kind == MECLIP_CLIP && (col_sum == nullptr || dy == nullptr)) return fail(MECLIP_EINVAL, "grad: CLIP needs col_sum and dy");
-    if (rows < 1 || cols < 1 || d < 8 || d % 8 != 0 || ldx < d || ldy < d || lddx < d || (dy != nullptr && lddy < d))
+    if (kind == MECLIP_CLIP && col_sum == nullptr) return fail(MECLIP_EINVAL, "grad: CLIP needs col_sum");
+    if (kind == MECLIP_LIT) dy = nullptr;      // the second argument of LiT is frozen
+    if (dx == nullptr && dy == nullptr) return fail(MECLIP_EINVAL, "grad: null pointer (no gradient output requested)");
+    if (rows < 1 || cols < 1 || d < 8 || d % 8 != 0 || ldx < d || ldy < d || (dx != nullptr && lddx < d) || (dy != nullptr && lddy < d))
         return fail(MECLIP_EINVAL, "grad: need rows, cols >= 1, d a multiple of 8, ld >= d");
-    if (!check_out_mode(dx_mode) || (dy != nullptr && !check_out_mode(dy_mode))) return fail(MECLIP_EINVAL, "grad: bad output mode");
-    if (!aligned16(dx) || lddx % 8 != 0 || (dy != nullptr && (!aligned16(dy) || lddy % 8 != 0)))
+    if ((dx != nullptr && !check_out_mode(dx_mode)) || (dy != nullptr && !check_out_mode(dy_mode))) return fail(MECLIP_EINVAL, "grad: bad output mode");
+    if ((dx != nullptr && (!aligned16(dx) || lddx % 8 != 0)) || (dy != nullptr && (!aligned16(dy) || lddy % 8 != 0)))
         return fail(MECLIP_EINVAL, "grad: outputs must be 16-byte aligned with pitches multiples of 8");
+    const bool want_dx = dx != nullptr, want_dy = dy != nullptr;
     if ((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0) return fail(MECLIP_EINVAL, "grad: workspace must be 256-byte aligned");
     if (!(temperature > 0.f)) return fail(MECLIP_EINVAL, "grad: temperature must be positive");
     int rc = check_device();
@@ -868,12 +871,12 @@ static int grad_impl(int kind, const void* x_bf16, const void* y_bf16, int64_t r
     // the tile counters are the only part of the workspace that has to start at zero
     MECLIP_CUDA(cudaMemsetAsync(counters, 0, plan.counter_bytes, s0));
     if (transposed_copies) {
-        {
+        if (want_dx) {
             ScopedTiming timing(s0, TAG_ROW, 0.0);
             dim3 grid((unsigned)((cols + 63) / 64), (unsigned)((d + 63) / 64));
             transpose_bf16_kernel<<<grid, 256, 0, s0>>>(Y, ldy, cols, (int)d, yt, plan.ld_yt);
         }
-        if (clip) {
+        if (want_dy) {
             ScopedTiming timing(s0, TAG_ROW, 0.0);
             dim3 grid((unsigned)((rows + 63) / 64), (unsigned)((d + 63) / 64));
             transpose_bf16_kernel<<<grid, 256, 0, s0>>>(X, ldx, rows, (int)d, xt, plan.ld_xt);
@@ -891,8 +894,8 @@ static int grad_impl(int kind, const void* x_bf16, const void* y_bf16, int64_t r
             const int gb = (int)(t & 1) & (plan.g_buffers - 1);
             // (1) coefficient panel G [nr x nc] = epi(X[r0:] Y[c0:]^T), once its buffer is free again
             if (overlap && t >= 2) {
-                MECLIP_CUDA(cudaStreamWaitEvent(s0, side->dx[gb], 0));
-                if (clip) MECLIP_CUDA(cudaStreamWaitEvent(s0, side->dy[gb], 0));
+                if (want_dx) MECLIP_CUDA(cudaStreamWaitEvent(s0, side->dx[gb], 0));
+                if (want_dy) MECLIP_CUDA(cudaStreamWaitEvent(s0, side->dy[gb], 0));
             }
             {
                 GemmParams p;
@@ -914,12 +917,12 @@ static int grad_impl(int kind, const void* x_bf16, const void* y_bf16, int64_t r
             }
             if (overlap) {
                 MECLIP_CUDA(cudaEventRecord(side->coef[gb], s0));
-                MECLIP_CUDA(cudaStreamWaitEvent(sx, side->coef[gb], 0));
-                if (clip) MECLIP_CUDA(cudaStreamWaitEvent(sy, side->coef[gb], 0));
+                if (want_dx) MECLIP_CUDA(cudaStreamWaitEvent(sx, side->coef[gb], 0));
+                if (want_dy) MECLIP_CUDA(cudaStreamWaitEvent(sy, side->coef[gb], 0));
             }
             // (3) dY[c0:] (+)= G^T X[r0:]        M = nc, N = d, K = nr; A = G^T (M contiguous), B = X (N contiguous)
             //     issued before dX: its tiles are the long ones (K = nr)
-            if (clip) {
+            if (want_dy) {
                 GemmParams p;
                 std::memset(&p, 0, sizeof(p));
                 p.status = status;
@@ -944,7 +947,7 @@ static int grad_impl(int kind, const void* x_bf16, const void* y_bf16, int64_t r
                 if (overlap) MECLIP_CUDA(cudaEventRecord(side->dy[gb], sy));
             }
             // (2) dX[r0:] (+)= G Y[c0:]          M = nr, N = d, K = nc; A = G (K contiguous), B = Y (N contiguous)
-            {
+            if (want_dx) {
                 GemmParams p;
                 std::memset(&p, 0, sizeof(p));
                 p.status = status;
@@ -970,9 +973,11 @@ static int grad_impl(int kind, const void* x_bf16, const void* y_bf16, int64_t r
         }
     }
     if (overlap) {   // join: everything the side streams did is ordered before the caller's next work
-        MECLIP_CUDA(cudaEventRecord(side->join_x, sx));
-        MECLIP_CUDA(cudaStreamWaitEvent(s0, side->join_x, 0));
-        if (clip) {
+        if (want_dx) {
+            MECLIP_CUDA(cudaEventRecord(side->join_x, sx));
+            MECLIP_CUDA(cudaStreamWaitEvent(s0, side->join_x, 0));
+        }
+        if (want_dy) {
             MECLIP_CUDA(cudaEventRecord(side->join_y, sy));
             MECLIP_CUDA(cudaStreamWaitEvent(s0, side->join_y, 0));
         }

@@ -155,19 +155,23 @@ def grad_block_static(kind, x_hat, y_hat, temperature, row_sum, col_sum, grad_ou
 
 
 def loss_backward(kind, x_hat, y_hat, temperature, row_sum, col_sum, grad_out, grad_scale, dx_dtype, dy_dtype,
-                  status=None, sum_g_s=None):
-    """Whole-batch backward on one GPU.  Returns (dx, dy or None) w.r.t. the normalised operands.
+                  status=None, sum_g_s=None, need_dx=True, need_dy=True):
+    """Whole-batch backward on one GPU.  Returns (dx, dy) w.r.t. the normalised operands; an output
+    that is not needed (frozen tower, or the second argument of LiT) is None and its contraction is skipped.
     sum_g_s: optional zeroed fp32 scalar that receives sum_ij G_ij S_ij (temperature gradient)."""
     b, d = x_hat.shape
     dev = x_hat.device
-    dx = torch.empty(b, d, dtype=dx_dtype, device=dev)
-    dy = torch.empty(b, d, dtype=dy_dtype, device=dev) if kind == _lib.CLIP else None
+    need_dy = need_dy and kind == _lib.CLIP
+    if not (need_dx or need_dy):
+        return None, None
+    dx = torch.empty(b, d, dtype=dx_dtype, device=dev) if need_dx else None
+    dy = torch.empty(b, d, dtype=dy_dtype, device=dev) if need_dy else None
     ws = grad_workspace(b, b, d, dev)
     if sum_g_s is not None:
         with torch.cuda.device(dev):
             _lib.check(_lib.load().meclip_grad_t(kind, x_hat.data_ptr(), y_hat.data_ptr(), b, b, d, x_hat.stride(0),
                                                  y_hat.stride(0), float(temperature), 0, 0, row_sum.data_ptr(),
-                                                 _ptr(col_sum), _ptr(grad_out), float(grad_scale), dx.data_ptr(),
+                                                 _ptr(col_sum), _ptr(grad_out), float(grad_scale), _ptr(dx),
                                                  _MODE[dx_dtype], d, _ptr(dy),
                                                  _MODE[dy_dtype] if dy is not None else 0, d, sum_g_s.data_ptr(),
                                                  ws.data_ptr(), ws.numel(), _ptr(status), _stream(x_hat)))
@@ -175,7 +179,7 @@ def loss_backward(kind, x_hat, y_hat, temperature, row_sum, col_sum, grad_out, g
     with torch.cuda.device(dev):
         _lib.check(_lib.load().meclip_loss_backward(kind, x_hat.data_ptr(), y_hat.data_ptr(), b, d, x_hat.stride(0),
                                                     y_hat.stride(0), float(temperature), row_sum.data_ptr(),
-                                                    _ptr(col_sum), _ptr(grad_out), float(grad_scale), dx.data_ptr(),
+                                                    _ptr(col_sum), _ptr(grad_out), float(grad_scale), _ptr(dx),
                                                     _MODE[dx_dtype], d, _ptr(dy),
                                                     _MODE[dy_dtype] if dy is not None else 0, d, ws.data_ptr(),
                                                     ws.numel(), _ptr(status), _stream(x_hat)))

@@ -58,9 +58,10 @@ def test_lit_blocked_backward_and_determinism(small_blocks):
     torch.cuda.synchronize()
     rl, rx = dense.lit_dense(txt, img, 0.07, False)
     dense.assert_parity(loss.item(), rl, (grads[0].cpu(),), (rx,), "blocked lit")
-    # forward sums use atomics (last-bit differences), the blocked backward itself adds in a fixed order
+    # The forward sums use atomics: their last bits can differ between runs, which can flip the bf16
+    # rounding of single coefficients; the blocked backward itself adds in a fixed order.
     mr, cs = dense.grad_errors(grads[0], grads[1])
-    assert mr < 1e-5
+    assert mr < 1e-3
 
 
 def test_status_word_stays_clear():

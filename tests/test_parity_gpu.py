@@ -172,3 +172,27 @@ def test_learnable_temperature_gradient(kind, stable, b, d, t):
     xg2 = x.cuda().requires_grad_(True)
     cls(t, False)(xg2, y.cuda()).backward(torch.tensor(2.0, device="cuda"))
     assert dense.grad_errors(xg.grad, xg2.grad)[0] < 1e-4      # forward sums use atomics: last-bit differences
+
+
+@pytest.mark.parametrize("frozen", ["image", "text"])
+def test_clip_with_one_frozen_tower_skips_its_gradient(frozen):
+    """Only the input that requires a gradient gets one (and only its contraction is launched)."""
+    from memoryefficientclip_b200 import _lib
+    m = _mods()
+    x, y = _inputs(384, 128, 9, False, torch.bfloat16)
+    xg = x.cuda().requires_grad_(frozen != "image")
+    yg = y.cuda().requires_grad_(frozen != "text")
+    before = _lib.load().meclip_launch_count()
+    loss = m.MemoryEfficientCLIPLoss(0.07, False)(xg, yg)
+    loss.backward()
+    torch.cuda.synchronize()
+    launches = _lib.load().meclip_launch_count() - before
+    rl, rx, ry = dense.clip_dense(x, y, 0.07, False)
+    if frozen == "image":
+        assert xg.grad is None
+        dense.assert_parity(loss.item(), rl, (yg.grad.float().cpu(),), (ry,), "frozen image")
+    else:
+        assert yg.grad is None
+        dense.assert_parity(loss.item(), rl, (xg.grad.float().cpu(),), (rx,), "frozen text")
+    # normalise x2, sums, finalize | transpose, coefficient panel, one contraction, one Jacobian
+    assert launches == 8, launches
