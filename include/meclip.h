@@ -42,7 +42,7 @@ enum meclip_status {
     MECLIP_EUNSUPPORTED = 5  /* not an sm_100 device, or driver lacks TMA entry point */
 };
 
-enum meclip_kind { MECLIP_CLIP = 0, MECLIP_LIT = 1 };
+enum meclip_kind { MECLIP_CLIP = 0, MECLIP_LIT = 1, MECLIP_SIGLIP = 2 /* internal to the siglip entry points */ };
 enum meclip_dtype { MECLIP_BF16 = 0, MECLIP_F32 = 1 };
 
 /* How a gradient output buffer is written. */
@@ -169,8 +169,9 @@ int meclip_grad(int kind, const void* x_bf16, const void* y_bf16, int64_t rows, 
                 void* stream);
 
 /*
- * meclip_grad that also accumulates *sum_g_s += sum_ij G_ij S_ij over the block (fp32 device
- * scalar, zeroed by the caller, fp32 atomics).  With g = grad_scale * (*grad_out) the matrix G
+ * meclip_grad that also accumulates sum_g_s[0] += sum_ij G_ij S_ij and sum_g_s[1] += sum_ij G_ij
+ * over the block (fp32 device
+ * two-element array {sum G S, sum G}, zeroed by the caller, fp32 atomics).  With g = grad_scale * (*grad_out) the matrix G
  * satisfies sum_ij G_ij S_ij = g * B * dL/d(1/T), so for the plain scaling (grad_scale = 1/(B T))
  * the temperature gradient is  grad_out * dL/dT = -(1/T) * sum_g_s.  The reference treats the
  * temperature as a constant (backward returns None for it, clip_loss.py:256); this is the
@@ -181,6 +182,29 @@ int meclip_grad_t(int kind, const void* x_bf16, const void* y_bf16, int64_t rows
                   const float* col_sum, const float* grad_out, float grad_scale, void* dx, int dx_mode, int64_t lddx,
                   void* dy, int dy_mode, int64_t lddy, float* sum_g_s, void* workspace, size_t workspace_bytes,
                   int* status, void* stream);
+
+/*
+ * Sigmoid (SigLIP) pairwise loss on the same tile engine; the reference has no such loss.
+ *   a_ij = logit_scale * S_ij + logit_bias,   loss = (1/B) sum_ij softplus(-z_ij a_ij),  z_ii = 1, z_ij = -1
+ * meclip_siglip_sum:   row_sum[i] += sum_j softplus(-z_ij a_ij) / ln2 over the block (fp32 atomics, zero first),
+ *                      diag_s[i] = S_ii where the diagonal crosses the block (as meclip_sum_exp).
+ * meclip_siglip_loss_finalize:  loss_out (+)= scale * ln2 * sum_i row_sum[i]  (diag_s, logit_scale and
+ *                      logit_bias are accepted for symmetry and not used).
+ * meclip_siglip_grad:  G_ij = g (sigmoid(a_ij) - [i == j]),  g = grad_scale * (*grad_out),  grad_scale = t / B;
+ *                      dX = G Y, dY = G^T X (either may be NULL); sums (optional, two zeroed floats) receives
+ *                      {sum G S, sum G}:  grad_out * dL/dt = sums[0] / t,  grad_out * dL/db = sums[1] / t.
+ * Workspace as for meclip_grad (meclip_grad_workspace_bytes).
+ */
+int meclip_siglip_sum(const void* x_bf16, const void* y_bf16, int64_t rows, int64_t cols, int64_t d, int64_t ldx,
+                      int64_t ldy, float logit_scale, float logit_bias, int64_t row_off, int64_t col_off, float* row_sum,
+                      float* diag_s, unsigned int* tile_counter, int* status, void* stream);
+int meclip_siglip_loss_finalize(const float* row_sum, const float* diag_s, int64_t n, float logit_scale, float logit_bias,
+                                float scale, int accumulate, float* loss_out, void* stream);
+int meclip_siglip_grad(const void* x_bf16, const void* y_bf16, int64_t rows, int64_t cols, int64_t d, int64_t ldx,
+                       int64_t ldy, float logit_scale, float logit_bias, int64_t row_off, int64_t col_off,
+                       const float* grad_out, float grad_scale, void* dx, int dx_mode, int64_t lddx, void* dy,
+                       int dy_mode, int64_t lddy, float* sums, void* workspace, size_t workspace_bytes, int* status,
+                       void* stream);
 
 /*
  * meclip_grad for callers that have no device memory to give: the coefficient panel

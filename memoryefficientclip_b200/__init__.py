@@ -9,8 +9,10 @@ from .clip_loss import (MemoryEfficientCLIPLoss, MemoryEfficientCLIPLossNormed, 
                         StableMemoryEfficientCLIPLossNormed)
 from .lit_loss import (MemoryEfficientLiTLoss, MemoryEfficientLiTLossNormed, StableMemoryEfficientLiTLoss,
                        StableMemoryEfficientLiTLossNormed)
+from .siglip_loss import MemoryEfficientSigLIPLoss, MemoryEfficientSigLIPLossFn
 
 __all__ = [
+    "MemoryEfficientSigLIPLoss", "MemoryEfficientSigLIPLossFn",
     "MemoryEfficientCLIPLoss", "MemoryEfficientCLIPLossNormed", "StableMemoryEfficientCLIPLoss",
     "StableMemoryEfficientCLIPLossNormed", "MemoryEfficientLiTLoss", "MemoryEfficientLiTLossNormed",
     "StableMemoryEfficientLiTLoss", "StableMemoryEfficientLiTLossNormed",

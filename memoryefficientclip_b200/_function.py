@@ -63,7 +63,7 @@ class ContrastiveLossFn(torch.autograd.Function):
         dx_t = torch.float32 if normalize else x_dtype
         dy_t = torch.float32 if normalize else y_dtype
         t_param = getattr(ctx, "meclip_t", None)
-        sum_g_s = torch.zeros(1, dtype=torch.float32, device=x_hat.device) if t_param is not None else None
+        sum_g_s = torch.zeros(2, dtype=torch.float32, device=x_hat.device) if t_param is not None else None
         if sum_g_s is not None and not (want_dx or want_dy):
             want_dx = True       # the temperature sum is produced by the coefficient pass of the backward
         dx, dy = ops.loss_backward(kind, x_hat, y_hat, temperature, row_sum, col_sum, go, scale, dx_t, dy_t,
@@ -72,7 +72,7 @@ class ContrastiveLossFn(torch.autograd.Function):
         if sum_g_s is not None:
             # sum_ij G_ij S_ij = g B dL/d(1/T) with g = go * scale, so go * dL/dT = -(sum / (scale B)) / T^2.
             # (The Stable scaling only rescales the feature gradients; the temperature gets the true one.)
-            dt = sum_g_s * (-1.0 / (scale * batch * temperature * temperature))
+            dt = sum_g_s[0] * (-1.0 / (scale * batch * temperature * temperature))
             ctx.meclip_dt = dt.reshape(t_param.shape).to(t_param.dtype)
         if normalize:
             if dx is not None:

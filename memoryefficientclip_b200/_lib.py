@@ -14,7 +14,7 @@ PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(PKG_DIR, "libmeclip_sm100.so")
 
 OK, EINVAL, ENOSPC, ECUDA, ETIMEOUT, EUNSUPPORTED = range(6)
-CLIP, LIT = 0, 1
+CLIP, LIT, SIGLIP = 0, 1, 2
 BF16, F32 = 0, 1
 STORE_BF16, STORE_F32, ACCUM_F32 = 0, 1, 2
 
@@ -45,6 +45,13 @@ SIGNATURES = {
     "meclip_grad_t": (c_int, [c_int, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64, c_float, c_int64,
                               c_int64, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_int, c_int64, c_void_p,
                               c_int, c_int64, c_void_p, c_void_p, c_size_t, c_void_p, c_void_p]),
+    "meclip_siglip_sum": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64, c_float, c_float,
+                                  c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "meclip_siglip_loss_finalize": (c_int, [c_void_p, c_void_p, c_int64, c_float, c_float, c_float, c_int, c_void_p,
+                                            c_void_p]),
+    "meclip_siglip_grad": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64, c_float, c_float,
+                                   c_int64, c_int64, c_void_p, c_float, c_void_p, c_int, c_int64, c_void_p, c_int,
+                                   c_int64, c_void_p, c_void_p, c_size_t, c_void_p, c_void_p]),
     "meclip_grad_static": (c_int, [c_int, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64, c_float,
                                    c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_int, c_int64,
                                    c_void_p, c_int, c_int64, c_void_p, c_void_p]),

@@ -7,6 +7,79 @@
 
 namespace meclip {
 
+// Value summed by the forward pass: exp2(u) for the softmax losses, softplus(a)/ln2 for the sigmoid
+// loss (u = a log2(e); the loss kernel multiplies by ln2 once).
+// flip: the sigmoid loss takes softplus(-a) on the diagonal (the positive pair).  It is summed in
+// that form, not as softplus(a) - a, so that the many tiny off-diagonal terms of a row are never
+// added to a large number.
+template <bool SIG>
+__device__ __forceinline__ float fwd_value(float s, const GemmParams& p, bool flip = false) {
+    float u = fmaf(s, p.fmul, p.fadd);
+    if (!SIG) return ex2_approx(u);
+    if (flip) u = -u;
+    // log2(1 + x), x = 2^-|u| in (0, 1]: lg2.approx has an ABSOLUTE error near 1, which would dominate the
+    // many tiny terms of far-apart pairs, so small x uses the series x log2(e) (1 - x/2) instead
+    const float x = ex2_approx(-fabsf(u));
+    const float small = x * fmaf(x, -0.72134752f, 1.44269504f);
+    const float big = lg2_approx(1.f + x);
+    return fmaxf(u, 0.f) + (x < 0.00390625f ? small : big);
+}
+// Factor of the gradient coefficient: exp2(u), or sigmoid(a) = 1 / (1 + 2^-u) with u = a log2(e)
+// (relative accuracy also for the very small sigmoids of far-apart pairs).
+template <bool SIG>
+__device__ __forceinline__ float coef_value(float s, const GemmParams& p) {
+    const float u = fmaf(s, p.fmul, p.fadd);
+    if (!SIG) return ex2_approx(u);
+    return rcp_approx(1.f + ex2_approx(-u));
+}
+
+template <bool SIG>
+__device__ __forceinline__ void sums_chunk(const uint32_t (&v)[32], const GemmParams& p, bool full_tile, bool rvalid,
+                                           int col_base, bool want_cols, float (&cacc)[32], float& ra0, float& ra1,
+                                           float& ra2, float& ra3, int jdc) {
+    if (SIG && jdc >= -1 && __any_sync(0xffffffffu, jdc >= 0)) {      // a chunk the diagonal runs through
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+            float e = fwd_value<SIG>(__uint_as_float(v[c]), p, c == jdc);
+            if (!rvalid || col_base + c >= p.n) e = 0.f;
+            ra0 += e;
+        }
+        return;
+    }
+    if (full_tile) {
+#pragma unroll
+        for (int c = 0; c < 32; c += 4) {
+            const float e0 = fwd_value<SIG>(__uint_as_float(v[c]), p);
+            const float e1 = fwd_value<SIG>(__uint_as_float(v[c + 1]), p);
+            const float e2 = fwd_value<SIG>(__uint_as_float(v[c + 2]), p);
+            const float e3 = fwd_value<SIG>(__uint_as_float(v[c + 3]), p);
+            ra0 += e0; ra1 += e1; ra2 += e2; ra3 += e3;
+            if (want_cols) { cacc[c] += e0; cacc[c + 1] += e1; cacc[c + 2] += e2; cacc[c + 3] += e3; }
+        }
+    } else {
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+            float e = fwd_value<SIG>(__uint_as_float(v[c]), p);
+            if (!rvalid || col_base + c >= p.n) e = 0.f;
+            ra0 += e;
+            if (want_cols) cacc[c] += e;
+        }
+    }
+}
+
+template <bool SIG>
+__device__ __forceinline__ void coef_chunk(const uint32_t (&v)[32], const GemmParams& p, float inv_r,
+                                           const float* icol_chunk, float (&gv)[32]) {
+#pragma unroll
+    for (int c = 0; c < 32; c += 4) {
+        const float4 ic = *reinterpret_cast<const float4*>(icol_chunk + c);   // broadcast read
+        gv[c] = coef_value<SIG>(__uint_as_float(v[c]), p) * (inv_r + ic.x);
+        gv[c + 1] = coef_value<SIG>(__uint_as_float(v[c + 1]), p) * (inv_r + ic.y);
+        gv[c + 2] = coef_value<SIG>(__uint_as_float(v[c + 2]), p) * (inv_r + ic.z);
+        gv[c + 3] = coef_value<SIG>(__uint_as_float(v[c + 3]), p) * (inv_r + ic.w);
+    }
+}
+
 static constexpr int COL_SLOTS = MAX_BN / 64;   // 32-column chunks one warp group owns at most (half the tile)
 
 struct EpiState {        // per-thread state that lives across tiles
@@ -89,25 +162,9 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, const CUtenso
 #pragma unroll
                     for (int c = 0; c < 32; ++c) sdiag = (c == jdc) ? __uint_as_float(v[c]) : sdiag;
                 }
-                if (full_tile) {
-#pragma unroll
-                    for (int c = 0; c < 32; c += 4) {
-                        const float e0 = ex2_approx(fmaf(__uint_as_float(v[c]), p.k2, -p.k2));
-                        const float e1 = ex2_approx(fmaf(__uint_as_float(v[c + 1]), p.k2, -p.k2));
-                        const float e2 = ex2_approx(fmaf(__uint_as_float(v[c + 2]), p.k2, -p.k2));
-                        const float e3 = ex2_approx(fmaf(__uint_as_float(v[c + 3]), p.k2, -p.k2));
-                        ra0 += e0; ra1 += e1; ra2 += e2; ra3 += e3;
-                        if (want_cols) { st.cacc[k][c] += e0; st.cacc[k][c + 1] += e1; st.cacc[k][c + 2] += e2; st.cacc[k][c + 3] += e3; }
-                    }
-                } else {
-#pragma unroll
-                    for (int c = 0; c < 32; ++c) {
-                        float e = ex2_approx(fmaf(__uint_as_float(v[c]), p.k2, -p.k2));
-                        if (!rvalid || n0 + ch * 32 + c >= p.n) e = 0.f;
-                        ra0 += e;
-                        if (want_cols) st.cacc[k][c] += e;
-                    }
-                }
+                const int jdc_s = (diag_here && jd >= 0 && (jd >> 5) == ch) ? (jd & 31) : -1;
+                if (p.sigmoid) sums_chunk<true>(v, p, full_tile, rvalid, n0 + ch * 32, want_cols, st.cacc[k], ra0, ra1, ra2, ra3, jdc_s);
+                else           sums_chunk<false>(v, p, full_tile, rvalid, n0 + ch * 32, want_cols, st.cacc[k], ra0, ra1, ra2, ra3, -1);
             }
         }
         tc_fence_before();
@@ -122,7 +179,8 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, const CUtenso
             if (p.c != nullptr && n0 + j < p.n) v = p.coef * st.gscale / __ldg(p.c + n0 + j);
             tail->icol[j] = v;
         }
-        const float inv_r = rvalid ? p.coef * st.gscale / __ldg(p.r + grow) : 0.f;
+        // row factor: g / r_i for the softmax losses, plain g when there are no row sums (sigmoid loss)
+        const float inv_r = !rvalid ? 0.f : (p.r != nullptr ? p.coef * st.gscale / __ldg(p.r + grow) : p.coef * st.gscale);
         named_bar_sync(1, EPI_THREADS);
         // Each warp turns 32 rows x 64 columns into a 128-byte-swizzled shared tile and one lane
         // TMA-stores it (full 128-byte lines; rows and chunks outside the panel are clipped by the
@@ -130,7 +188,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, const CUtenso
         const float dsub = p.dcoef * st.gscale;
         const bool diag_here = __any_sync(0xffffffffu, jd >= 0);
         const bool want_sg = p.sg_acc != nullptr;      // sum of G_ij * S_ij for the temperature gradient
-        float sg = 0.f;
+        float sg = 0.f, sg1 = 0.f;
         uint8_t* buf = tail->scratch + (size_t)(warp - 2) * STORE_BUF_BYTES;
         for (int u = u_begin; u < u_end; ++u) {
             if (lane == 0 && st.stores_in_flight > 0) {     // the previous store has finished reading `buf`
@@ -145,18 +203,21 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, const CUtenso
                 tmem_ld32(taddr + ch * 32, v);
                 tmem_ld_wait();
                 float gv[32];
-#pragma unroll
-                for (int c = 0; c < 32; c += 4) {
-                    const float4 ic = *reinterpret_cast<const float4*>(&tail->icol[ch * 32 + c]);   // broadcast read
-                    gv[c] = ex2_approx(fmaf(__uint_as_float(v[c]), p.k2, -p.k2)) * (inv_r + ic.x);
-                    gv[c + 1] = ex2_approx(fmaf(__uint_as_float(v[c + 1]), p.k2, -p.k2)) * (inv_r + ic.y);
-                    gv[c + 2] = ex2_approx(fmaf(__uint_as_float(v[c + 2]), p.k2, -p.k2)) * (inv_r + ic.z);
-                    gv[c + 3] = ex2_approx(fmaf(__uint_as_float(v[c + 3]), p.k2, -p.k2)) * (inv_r + ic.w);
-                }
+                if (p.sigmoid) coef_chunk<true>(v, p, inv_r, &tail->icol[ch * 32], gv);
+                else           coef_chunk<false>(v, p, inv_r, &tail->icol[ch * 32], gv);
                 if (diag_here) {      // warp-uniform: only tiles that cross the diagonal pay for the correction
                     const int jdc = (jd >= 0 && (jd >> 5) == ch) ? (jd & 31) : -1;
+                    if (p.sigmoid) {
+                        // sigmoid(a) - 1 = -1 / (1 + 2^u), computed in that form: no cancellation for a confident pair
 #pragma unroll
-                    for (int c = 0; c < 32; ++c) gv[c] -= (c == jdc) ? dsub : 0.f;
+                        for (int c = 0; c < 32; ++c) {
+                            const float u = fmaf(__uint_as_float(v[c]), p.fmul, p.fadd);
+                            gv[c] = (c == jdc) ? -dsub * rcp_approx(1.f + ex2_approx(u)) : gv[c];
+                        }
+                    } else {
+#pragma unroll
+                        for (int c = 0; c < 32; ++c) gv[c] -= (c == jdc) ? dsub : 0.f;
+                    }
                 }
                 if (!full_tile) {     // columns past the panel edge share a stored chunk with valid ones: zero them
 #pragma unroll
@@ -165,7 +226,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, const CUtenso
                 }
                 if (want_sg && rvalid) {
 #pragma unroll
-                    for (int c = 0; c < 32; ++c) sg = fmaf(gv[c], __uint_as_float(v[c]), sg);
+                    for (int c = 0; c < 32; ++c) { sg = fmaf(gv[c], __uint_as_float(v[c]), sg); sg1 += gv[c]; }
                 }
 #pragma unroll
                 for (int pc = 0; pc < 4; ++pc) {         // 16-byte piece index within the 128-byte row
@@ -190,8 +251,11 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, const CUtenso
         release();
         if (want_sg) {
 #pragma unroll
-            for (int o = 16; o >= 1; o >>= 1) sg += __shfl_xor_sync(0xffffffffu, sg, o);
-            if (lane == 0) atomicAdd(p.sg_acc, sg);
+            for (int o = 16; o >= 1; o >>= 1) {
+                sg += __shfl_xor_sync(0xffffffffu, sg, o);
+                sg1 += __shfl_xor_sync(0xffffffffu, sg1, o);
+            }
+            if (lane == 0) { atomicAdd(p.sg_acc, sg); atomicAdd(p.sg_acc + 1, sg1); }
         }
     } else {   // EPI_OUT
         for (int ch = u_begin; ch < u_end; ++ch) {

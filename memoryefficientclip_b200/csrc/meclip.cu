@@ -254,6 +254,27 @@ loss_finalize_kernel(const float* __restrict__ r, const float* __restrict__ c, c
     }
 }
 
+// Sigmoid loss: loss (+)= scale * ln2 * sum_i row_sum_i, where row_sum_i holds
+// [ sum_{j != i} softplus(a_ij) + softplus(-a_ii) ] / ln2 (the tile pass flips the diagonal's sign).
+__global__ void __launch_bounds__(1024)
+siglip_finalize_kernel(const float* __restrict__ r, const float* __restrict__ diag, long long n, float t, float b,
+                       float scale, int accumulate, float* __restrict__ loss) {
+    __shared__ double part[1024];
+    double acc = 0.0;
+    for (long long i = threadIdx.x; i < n; i += 1024)
+        acc += 0.6931471805599453 * (double)r[i];
+    part[threadIdx.x] = acc;
+    __syncthreads();
+    for (int s = 512; s >= 1; s >>= 1) {
+        if ((int)threadIdx.x < s) part[threadIdx.x] += part[threadIdx.x + s];
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) {
+        const float v = (float)(part[0] * (double)scale);
+        *loss = accumulate ? *loss + v : v;
+    }
+}
+
 // ------------------------------------------------------------------------------------
 // TMA descriptors
 // ------------------------------------------------------------------------------------
@@ -782,7 +803,8 @@ int meclip_sum_exp(int kind, const void* x_bf16, const void* y_bf16, int64_t row
     if (rc) return rc;
     GemmParams p;
     std::memset(&p, 0, sizeof(p));
-    p.k2 = 1.4426950408889634f / temperature;
+    p.fmul = 1.4426950408889634f / temperature;
+    p.fadd = -p.fmul;
     p.diag_shift = (long long)row_off - (long long)col_off;
     p.row_sum = row_sum;
     p.col_sum = (kind == MECLIP_CLIP) ? col_sum : nullptr;
@@ -822,9 +844,13 @@ static int grad_impl(int kind, const void* x_bf16, const void* y_bf16, int64_t r
                      int64_t ldy, float temperature, int64_t row_off, int64_t col_off, const float* row_sum,
                      const float* col_sum, const float* grad_out, float grad_scale, void* dx, int dx_mode, int64_t lddx,
                      void* dy, int dy_mode, int64_t lddy, void* workspace, size_t workspace_bytes, int* status,
-                     cudaStream_t s0, bool overlap, bool transposed_copies, float* sg_acc = nullptr) {
-    if (kind != MECLIP_CLIP && kind != MECLIP_LIT) return fail(MECLIP_EINVAL, "grad: bad kind %d", kind);
-    if (x_bf16 == nullptr || y_bf16 == nullptr || row_sum == nullptr || workspace == nullptr)
+                     cudaStream_t s0, bool overlap, bool transposed_copies, float* sg_acc = nullptr,
+                     float logit_scale = 0.f, float logit_bias = 0.f) {
+    // kind MECLIP_SIGLIP: `temperature` is unused, the element function is sigmoid(logit_scale * s + logit_bias),
+    // there are no row / column sums and both inputs get a gradient
+    const bool siglip = (kind == MECLIP_SIGLIP);
+    if (kind != MECLIP_CLIP && kind != MECLIP_LIT && !siglip) return fail(MECLIP_EINVAL, "grad: bad kind %d", kind);
+    if (x_bf16 == nullptr || y_bf16 == nullptr || (row_sum == nullptr && !siglip) || workspace == nullptr)
         return fail(MECLIP_EINVAL, "grad: null pointer");
     if (kind == MECLIP_CLIP && col_sum == nullptr) return fail(MECLIP_EINVAL, "grad: CLIP needs col_sum");
     if (kind == MECLIP_LIT) dy = nullptr;      // the second argument of LiT is frozen
@@ -836,7 +862,7 @@ static int grad_impl(int kind, const void* x_bf16, const void* y_bf16, int64_t r
         return fail(MECLIP_EINVAL, "grad: outputs must be 16-byte aligned with pitches multiples of 8");
     const bool want_dx = dx != nullptr, want_dy = dy != nullptr;
     if ((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0) return fail(MECLIP_EINVAL, "grad: workspace must be 256-byte aligned");
-    if (!(temperature > 0.f)) return fail(MECLIP_EINVAL, "grad: temperature must be positive");
+    if (!siglip && !(temperature > 0.f)) return fail(MECLIP_EINVAL, "grad: temperature must be positive");
     int rc = check_device();
     if (rc) return rc;
     const GradPlan plan = plan_grad(rows, cols, d, transposed_copies);
@@ -900,9 +926,16 @@ static int grad_impl(int kind, const void* x_bf16, const void* y_bf16, int64_t r
             {
                 GemmParams p;
                 std::memset(&p, 0, sizeof(p));
-                p.k2 = 1.4426950408889634f / temperature;
+                if (siglip) {
+                    p.sigmoid = 1;
+                    p.fmul = logit_scale * 1.4426950408889634f;
+                    p.fadd = logit_bias * 1.4426950408889634f;
+                } else {
+                    p.fmul = 1.4426950408889634f / temperature;
+                    p.fadd = -p.fmul;
+                }
                 p.diag_shift = ((long long)row_off + r0) - ((long long)col_off + c0);
-                p.r = row_sum + r0;
+                p.r = siglip ? nullptr : row_sum + r0;
                 p.c = clip ? col_sum + c0 : nullptr;
                 p.grad_out = grad_out;
                 p.coef = clip ? 0.5f * grad_scale : grad_scale;
@@ -1008,6 +1041,53 @@ int meclip_grad_t(int kind, const void* x_bf16, const void* y_bf16, int64_t rows
     return grad_impl(kind, x_bf16, y_bf16, rows, cols, d, ldx, ldy, temperature, row_off, col_off, row_sum, col_sum,
                      grad_out, grad_scale, dx, dx_mode, lddx, dy, dy_mode, lddy, workspace, workspace_bytes, status,
                      (cudaStream_t)stream, overlap_allowed(), transposes_allowed(), sum_g_s);
+}
+
+// ---- sigmoid (SigLIP) loss on the same tile engine -------------------------------------------------
+int meclip_siglip_sum(const void* x_bf16, const void* y_bf16, int64_t rows, int64_t cols, int64_t d, int64_t ldx,
+                      int64_t ldy, float logit_scale, float logit_bias, int64_t row_off, int64_t col_off, float* row_sum,
+                      float* diag_s, unsigned int* tile_counter, int* status, void* stream) {
+    if (x_bf16 == nullptr || y_bf16 == nullptr || row_sum == nullptr || diag_s == nullptr)
+        return fail(MECLIP_EINVAL, "siglip_sum: null pointer");
+    if (rows < 1 || cols < 1 || d < 8 || d % 8 != 0 || ldx < d || ldy < d)
+        return fail(MECLIP_EINVAL, "siglip_sum: need rows, cols >= 1, d a multiple of 8, ld >= d");
+    int rc = check_device();
+    if (rc) return rc;
+    GemmParams p;
+    std::memset(&p, 0, sizeof(p));
+    p.sigmoid = 1;
+    p.fmul = logit_scale * 1.4426950408889634f;
+    p.fadd = logit_bias * 1.4426950408889634f;
+    p.diag_shift = (long long)row_off - (long long)col_off;
+    p.row_sum = row_sum;
+    p.col_sum = nullptr;
+    p.diag = diag_s;
+    p.tile_counter = tile_counter;
+    p.status = status;
+    Operand a{x_bf16, ldx, false}, b{y_bf16, ldy, false};
+    t_tag = TAG_SUMS;
+    return launch_gemm(EPI_SUMS, a, b, rows, cols, d, pick_bn(cols), p, (cudaStream_t)stream);
+}
+
+int meclip_siglip_loss_finalize(const float* row_sum, const float* diag_s, int64_t n, float logit_scale, float logit_bias,
+                                float scale, int accumulate, float* loss_out, void* stream) {
+    if (row_sum == nullptr || diag_s == nullptr || loss_out == nullptr || n < 1)
+        return fail(MECLIP_EINVAL, "siglip_loss_finalize: bad argument");
+    ScopedTiming timing((cudaStream_t)stream, TAG_ROW, 0.0);
+    siglip_finalize_kernel<<<1, 1024, 0, (cudaStream_t)stream>>>(row_sum, diag_s, n, logit_scale, logit_bias, scale,
+                                                                 accumulate, loss_out);
+    MECLIP_CUDA(cudaGetLastError());
+    return MECLIP_OK;
+}
+
+int meclip_siglip_grad(const void* x_bf16, const void* y_bf16, int64_t rows, int64_t cols, int64_t d, int64_t ldx,
+                       int64_t ldy, float logit_scale, float logit_bias, int64_t row_off, int64_t col_off,
+                       const float* grad_out, float grad_scale, void* dx, int dx_mode, int64_t lddx, void* dy,
+                       int dy_mode, int64_t lddy, float* sums, void* workspace, size_t workspace_bytes, int* status,
+                       void* stream) {
+    return grad_impl(MECLIP_SIGLIP, x_bf16, y_bf16, rows, cols, d, ldx, ldy, 1.f, row_off, col_off, nullptr, nullptr,
+                     grad_out, grad_scale, dx, dx_mode, lddx, dy, dy_mode, lddy, workspace, workspace_bytes, status,
+                     (cudaStream_t)stream, overlap_allowed(), transposes_allowed(), sums, logit_scale, logit_bias);
 }
 
 int meclip_loss_forward(int kind, const void* x_bf16, const void* y_bf16, int64_t batch, int64_t d, int64_t ldx,

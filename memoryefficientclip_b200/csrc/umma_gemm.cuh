@@ -52,7 +52,12 @@ struct GemmParams {
     int strip_len;            // tiles handed out together (consecutive ids share their columns), >= 1
     int a_blocked;            // A is the coefficient panel in its column-blocked layout (3-D tensor map)
     // EPI_SUMS / EPI_COEF
-    float k2;                 // log2(e) / T
+    // The elementwise function of the similarity s is f(fmul * s + fadd):
+    //   softmax losses (CLIP, LiT): f = exp2, fmul = log2(e)/T, fadd = -log2(e)/T
+    //   sigmoid loss: fmul = t log2(e), fadd = b log2(e); SUMS f = softplus in base-2 units,
+    //                 COEF f = sigmoid = 1 / (1 + 2^-u)
+    float fmul, fadd;
+    int sigmoid;              // 0 = exp2, 1 = the sigmoid-loss functions
     long long diag_shift;     // (row_off - col_off): row i meets column i + diag_shift
     float* row_sum;           // SUMS: accumulated with atomics
     float* col_sum;           // SUMS: may be null (LiT)
@@ -62,7 +67,7 @@ struct GemmParams {
     const float* grad_out;    // COEF: device scalar
     float coef;               // COEF: grad_scale * (0.5 for CLIP, 1 for LiT)
     float dcoef;              // COEF: grad_scale (subtracted on the diagonal)
-    float* sg_acc;            // COEF: optional, += sum_ij G_ij S_ij (fp32 G before rounding); null = off
+    float* sg_acc;            // COEF: optional, [0] += sum_ij G_ij S_ij, [1] += sum_ij G_ij (fp32 G before rounding)
     // EPI_OUT
     void* out;
     long long ld_out;

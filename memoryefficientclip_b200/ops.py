@@ -186,6 +186,44 @@ def loss_backward(kind, x_hat, y_hat, temperature, row_sum, col_sum, grad_out, g
     return dx, dy
 
 
+def siglip_forward(x_hat, y_hat, logit_scale, logit_bias, status=None):
+    """Sigmoid-loss forward for a whole batch on one GPU; returns the 0-dim fp32 loss."""
+    b, d = x_hat.shape
+    dev = x_hat.device
+    row_sum = torch.zeros(b, dtype=torch.float32, device=dev)
+    diag_s = torch.zeros(b, dtype=torch.float32, device=dev)
+    counter = torch.zeros(1, dtype=torch.int32, device=dev)
+    loss = torch.empty((), dtype=torch.float32, device=dev)
+    lib = _lib.load()
+    with torch.cuda.device(dev):
+        _lib.check(lib.meclip_siglip_sum(x_hat.data_ptr(), y_hat.data_ptr(), b, b, d, x_hat.stride(0), y_hat.stride(0),
+                                         float(logit_scale), float(logit_bias), 0, 0, row_sum.data_ptr(),
+                                         diag_s.data_ptr(), counter.data_ptr(), _ptr(status), _stream(x_hat)))
+        _lib.check(lib.meclip_siglip_loss_finalize(row_sum.data_ptr(), diag_s.data_ptr(), b, float(logit_scale),
+                                                   float(logit_bias), 1.0 / b, 0, loss.data_ptr(), _stream(x_hat)))
+    return loss
+
+
+def siglip_backward(x_hat, y_hat, logit_scale, logit_bias, grad_out, grad_scale_, dx_dtype, dy_dtype, sums=None,
+                    need_dx=True, need_dy=True, status=None):
+    """Sigmoid-loss backward for a whole batch; returns (dx, dy) w.r.t. the normalised operands.
+    sums: optional two zeroed floats that receive {sum G S, sum G} for the scale / bias gradients."""
+    b, d = x_hat.shape
+    dev = x_hat.device
+    if not (need_dx or need_dy):
+        return None, None
+    dx = torch.empty(b, d, dtype=dx_dtype, device=dev) if need_dx else None
+    dy = torch.empty(b, d, dtype=dy_dtype, device=dev) if need_dy else None
+    ws = grad_workspace(b, b, d, dev)
+    with torch.cuda.device(dev):
+        _lib.check(_lib.load().meclip_siglip_grad(x_hat.data_ptr(), y_hat.data_ptr(), b, b, d, x_hat.stride(0),
+                                                  y_hat.stride(0), float(logit_scale), float(logit_bias), 0, 0,
+                                                  _ptr(grad_out), float(grad_scale_), _ptr(dx), _MODE[dx_dtype], d,
+                                                  _ptr(dy), _MODE[dy_dtype], d, _ptr(sums), ws.data_ptr(), ws.numel(),
+                                                  _ptr(status), _stream(x_hat)))
+    return dx, dy
+
+
 def grad_scale(batch: int, temperature: float, stable: bool) -> float:
     """1/(B T) (reference clip_loss.py:182, 235) or, for the Stable variants,
     sqrt(B/T)/B = 1/sqrt(B T) (clip_loss.py:299, 352)."""

@@ -99,6 +99,22 @@ def temperature_grad_dense(first, second, temperature, kind="clip", normalized_i
     return float(gt)
 
 
+def siglip_dense(image, text, logit_scale, logit_bias, normalized_inputs=False, grad_output=1.0, dtype=torch.float64):
+    """Dense sigmoid (SigLIP) loss: (1/B) sum_ij softplus(-z_ij (t s_ij + b)), z = 2 I - 1, with
+    gradients for both inputs, the scale t and the bias b.  (Not in the reference; the checker of
+    the sigmoid-loss extension.)  Returns (loss, d_image, d_text, d_t, d_b)."""
+    x = _prep(image, dtype, True)
+    y = _prep(text, dtype, True)
+    t = torch.tensor(float(logit_scale), dtype=dtype, requires_grad=True)
+    b = torch.tensor(float(logit_bias), dtype=dtype, requires_grad=True)
+    xn, yn = (x, y) if normalized_inputs else (F.normalize(x, dim=1), F.normalize(y, dim=1))
+    a = xn @ yn.t() * t + b
+    z = 2.0 * torch.eye(x.shape[0], dtype=dtype) - 1.0
+    loss = F.softplus(-z * a).sum() / x.shape[0]
+    gx, gy, gt, gb = torch.autograd.grad(loss, (x, y, t, b))
+    return loss.detach(), gx * grad_output, gy * grad_output, float(gt) * grad_output, float(gb) * grad_output
+
+
 # --------------------------------------------------------------------------- #
 # closed form: the reference's algorithm without the tiling
 # --------------------------------------------------------------------------- #
