@@ -11,7 +11,8 @@ import threading
 from ctypes import c_char_p, c_float, c_int, c_int64, c_size_t, c_void_p
 
 PKG_DIR = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(PKG_DIR, "libmeclip_sm100.so")
+# MECLIP_LIBRARY points at another build of the same library (kernel experiments)
+LIB_PATH = os.environ.get("MECLIP_LIBRARY") or os.path.join(PKG_DIR, "libmeclip_sm100.so")
 
 OK, EINVAL, ENOSPC, ECUDA, ETIMEOUT, EUNSUPPORTED = range(6)
 CLIP, LIT, SIGLIP = 0, 1, 2

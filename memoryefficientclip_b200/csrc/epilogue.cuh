@@ -80,7 +80,7 @@ __device__ __forceinline__ void coef_chunk(const uint32_t (&v)[32], const GemmPa
     }
 }
 
-static constexpr int COL_SLOTS = MAX_BN / 64;   // 32-column chunks one warp group owns at most (half the tile)
+static constexpr int COL_SLOTS = MECLIP_STRIPS ? MAX_BN / 64 : 1;   // 32-column chunks one warp group owns at most (half the tile)
 
 struct EpiState {        // per-thread state that lives across tiles
     int stores_in_flight = 0;   // COEF: lane 0's outstanding TMA-store groups
@@ -94,7 +94,7 @@ struct EpiState {        // per-thread state that lives across tiles
 // SUMS: add the pending column accumulators of all eight warps into col_sum and clear them.
 // Every epilogue thread must call this at the same point (it uses the epilogue named barrier).
 __device__ __forceinline__ void flush_column_sums(const GemmParams& p, SharedTail* tail, EpiState& st, int warp, int lane) {
-    if (st.strip_n0 < 0) return;
+    if (!MECLIP_STRIPS || st.strip_n0 < 0) return;
     const int q = warp & 3;
     const int wg = (warp - 2) >> 2;
     const int et = (int)threadIdx.x - 64;
@@ -124,11 +124,11 @@ __device__ __forceinline__ void flush_column_sums(const GemmParams& p, SharedTai
 // tell the MMA issuer that this thread is done with the accumulator.
 template <int EPI, class Release>
 __device__ __forceinline__ void epilogue_tile(const GemmParams& p, const CUtensorMap* tmap_c, SharedTail* tail,
-                                              EpiState& st, uint32_t taddr, int m0, int n0, int warp, int lane,
-                                              Release release) {
+                                              EpiState& st, uint32_t taddr, int m0, int n0, int tile_bn, int warp,
+                                              int lane, Release release) {
     const int q = warp & 3;
-    const int wg = (warp - 2) >> 2;
-    const int et = (int)threadIdx.x - 64;                 // 0..255 within the epilogue group
+    const int wg = EPI_WARPS == 8 ? (warp - 2) >> 2 : 0;
+    const int et = (int)threadIdx.x - 64;                 // index within the epilogue group
     const int grow = m0 + q * 32 + lane;
     const bool rvalid = grow < p.m;
     const bool full_tile = (m0 + BM <= p.m) && (n0 + p.bn <= p.n);
@@ -136,12 +136,51 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, const CUtenso
     const long long jd_ll = (long long)grow + p.diag_shift - n0;
     const int jd = (jd_ll >= 0 && jd_ll < p.bn && n0 + jd_ll < p.n && rvalid) ? (int)jd_ll : -1;
     // this warp group's share of the columns, in units of 32 (SUMS, OUT) or 64 (COEF) columns
-    const int units = (EPI == EPI_COEF) ? (p.bn >> 6) : (p.bn >> 5);
-    const int u_split = (units + 1) >> 1;
+    // tile_bn differs from p.bn only for the narrower last column tile of a contraction (EPI_OUT)
+    const int units = (EPI == EPI_COEF) ? (p.bn >> 6) : (EPI == EPI_OUT ? (tile_bn >> 5) : (p.bn >> 5));
+    const int u_split = EPI_WARPS == 8 ? (units + 1) >> 1 : units;
     const int u_begin = wg == 0 ? 0 : u_split;
     const int u_end = wg == 0 ? u_split : units;
 
-    if (EPI == EPI_SUMS) {
+    if (EPI == EPI_SUMS && !MECLIP_STRIPS) {
+        // per-tile reduction of the column sums: butterfly per 32x32 block, combine the quadrants in shared memory
+        float (*colpart)[MAX_BN] = reinterpret_cast<float (*)[MAX_BN]>(tail->scratch + sizeof(tail->scratch) - 4 * MAX_BN * 4);
+        const bool want_cols = p.col_sum != nullptr;
+        float ra0 = 0.f, ra1 = 0.f, ra2 = 0.f, ra3 = 0.f;
+        float sdiag = 0.f;
+        const bool diag_here = __any_sync(0xffffffffu, jd >= 0);
+        for (int ch = u_begin; ch < u_end; ++ch) {
+            uint32_t v[32];
+            tmem_ld32(taddr + ch * 32, v);
+            tmem_ld_wait();
+            if (diag_here) {
+                const int jdc = (jd >= 0 && (jd >> 5) == ch) ? (jd & 31) : -1;
+#pragma unroll
+                for (int c = 0; c < 32; ++c) sdiag = (c == jdc) ? __uint_as_float(v[c]) : sdiag;
+            }
+            float e[32];
+#pragma unroll
+            for (int c = 0; c < 32; ++c) e[c] = 0.f;
+            const int jdc_s = (diag_here && jd >= 0 && (jd >> 5) == ch) ? (jd & 31) : -1;
+            if (p.sigmoid) sums_chunk<true>(v, p, full_tile, rvalid, n0 + ch * 32, want_cols, e, ra0, ra1, ra2, ra3, jdc_s);
+            else           sums_chunk<false>(v, p, full_tile, rvalid, n0 + ch * 32, want_cols, e, ra0, ra1, ra2, ra3, -1);
+            if (want_cols) {
+                const float cs = warp_transpose_reduce32(e, lane);
+                colpart[q][ch * 32 + lane] = cs;
+            }
+        }
+        tc_fence_before();
+        release();
+        if (rvalid && u_end > u_begin) atomicAdd(p.row_sum + grow, (ra0 + ra1) + (ra2 + ra3));
+        if (jd >= 0 && (jd >> 5) >= u_begin && (jd >> 5) < u_end) p.diag[grow] = sdiag;
+        if (want_cols) {
+            named_bar_sync(1, EPI_THREADS);
+            for (int j = et; j < p.bn; j += EPI_THREADS)
+                if (n0 + j < p.n)
+                    atomicAdd(p.col_sum + n0 + j, (colpart[0][j] + colpart[1][j]) + (colpart[2][j] + colpart[3][j]));
+            named_bar_sync(1, EPI_THREADS);
+        }
+    } else if (EPI == EPI_SUMS) {
         const bool want_cols = p.col_sum != nullptr;
         if (want_cols && st.strip_n0 != n0) {       // the columns change: hand in what was accumulated
             flush_column_sums(p, tail, st, warp, lane);

@@ -497,11 +497,22 @@ static int launch_gemm(int epi, const Operand& a, const Operand& b, long long m,
     // strips: tile ids inside a group of 16 m-tiles share their columns; the sums pass keeps column
     // partials in registers over a strip.  Shorter strips when there are few tiles per SM.
     p.strip_len = 1;
-    if (epi == EPI_SUMS && p.col_sum != nullptr) {
+    if (MECLIP_STRIPS && epi == EPI_SUMS && p.col_sum != nullptr) {
         const long long per_sm = (long long)p.num_m_tiles * p.num_n_tiles / sm_count();
         p.strip_len = per_sm >= 64 ? 16 : per_sm >= 32 ? 8 : per_sm >= 16 ? 4 : per_sm >= 8 ? 2 : 1;
     }
     p.idesc = umma_idesc_bf16(BM, bn, a.mn_major ? 1 : 0, b.mn_major ? 1 : 0);
+    p.bn_last = bn;
+    p.idesc_last = p.idesc;
+    if (epi == EPI_OUT) {      // narrower last column tile: only as many 32-column chunks as hold valid columns
+        const long long rest = n - (long long)(p.num_n_tiles - 1) * bn;
+        int last = (int)((rest + 31) / 32 * 32);
+        if (b.mn_major) last = (int)((rest + 63) / 64 * 64);
+        if (last < bn) {
+            p.bn_last = last;
+            p.idesc_last = umma_idesc_bf16(BM, last, a.mn_major ? 1 : 0, b.mn_major ? 1 : 0);
+        }
+    }
     if ((long long)p.num_m_tiles * p.num_n_tiles > 0x7fffffffLL) return fail(MECLIP_EINVAL, "too many tiles");
     // shared memory: [<= 1023 B alignment slack][stages][tail]; as many stages as fit, at least 2
     p.stage_bytes = A_STAGE_BYTES + bn * BK * 2;
@@ -515,6 +526,8 @@ static int launch_gemm(int epi, const Operand& a, const Operand& b, long long m,
     if (pair) {
         p.num_m_tiles = (int)((m + PAIR_BM - 1) / PAIR_BM);
         p.idesc = umma_idesc_bf16(PAIR_BM, bn, a.mn_major ? 1 : 0, 0);
+        p.bn_last = bn;
+        p.idesc_last = p.idesc;
         p.stage_bytes = A_STAGE_BYTES + (bn / 2) * BK * 2;
         stages = (SMEM_LIMIT - 1024 - tail_bytes(epi)) / p.stage_bytes;
         if (stages > MAX_STAGES) stages = MAX_STAGES;
@@ -596,7 +609,7 @@ struct SideStreams {
     bool ready = false;
     cudaStream_t sx = nullptr, sy = nullptr;
     cudaEvent_t coef[2] = {nullptr, nullptr}, dx[2] = {nullptr, nullptr}, dy[2] = {nullptr, nullptr};
-    cudaEvent_t join_x = nullptr, join_y = nullptr;
+    cudaEvent_t join_x = nullptr, join_y = nullptr, fork = nullptr;
     std::mutex mutex;       // one meclip_grad enqueue at a time per device: the events are shared
 };
 static SideStreams g_side[64];
@@ -611,7 +624,8 @@ static int get_side_streams(SideStreams** out) {
     if (!ss.ready) {
         MECLIP_CUDA(cudaStreamCreateWithFlags(&ss.sx, cudaStreamNonBlocking));
         MECLIP_CUDA(cudaStreamCreateWithFlags(&ss.sy, cudaStreamNonBlocking));
-        cudaEvent_t* evs[8] = {&ss.coef[0], &ss.coef[1], &ss.dx[0], &ss.dx[1], &ss.dy[0], &ss.dy[1], &ss.join_x, &ss.join_y};
+        cudaEvent_t* evs[9] = {&ss.coef[0], &ss.coef[1], &ss.dx[0], &ss.dx[1], &ss.dy[0], &ss.dy[1], &ss.join_x, &ss.join_y,
+                               &ss.fork};
         for (auto e : evs) MECLIP_CUDA(cudaEventCreateWithFlags(e, cudaEventDisableTiming));
         ss.ready = true;
     }
@@ -880,7 +894,7 @@ static int grad_impl(int kind, const void* x_bf16, const void* y_bf16, int64_t r
     __nv_bfloat16* yt = reinterpret_cast<__nv_bfloat16*>(after_g + plan.dx_bytes + plan.dy_bytes + plan.counter_bytes + plan.xt_bytes);
     const __nv_bfloat16* X = reinterpret_cast<const __nv_bfloat16*>(x_bf16);
     const __nv_bfloat16* Y = reinterpret_cast<const __nv_bfloat16*>(y_bf16);
-    const int bn_d = pick_bn(d);
+    const int bn_d = d >= 256 ? 256 : pick_bn(d);   // wide tiles; a narrower last one takes the remainder
     const size_t dx_elt = dx_mode == MECLIP_STORE_BF16 ? 2 : 4;
     const size_t dy_elt = dy_mode == MECLIP_STORE_BF16 ? 2 : 4;
 
@@ -897,15 +911,22 @@ static int grad_impl(int kind, const void* x_bf16, const void* y_bf16, int64_t r
     // the tile counters are the only part of the workspace that has to start at zero
     MECLIP_CUDA(cudaMemsetAsync(counters, 0, plan.counter_bytes, s0));
     if (transposed_copies) {
+        // Y^T is only read by the dX contractions and X^T by the dY contractions, so with side streams
+        // the transposes run there, under the first coefficient pass
+        if (overlap) {
+            MECLIP_CUDA(cudaEventRecord(side->fork, s0));
+            if (want_dx) MECLIP_CUDA(cudaStreamWaitEvent(sx, side->fork, 0));
+            if (want_dy) MECLIP_CUDA(cudaStreamWaitEvent(sy, side->fork, 0));
+        }
         if (want_dx) {
-            ScopedTiming timing(s0, TAG_ROW, 0.0);
+            ScopedTiming timing(sx, TAG_ROW, 0.0);
             dim3 grid((unsigned)((cols + 63) / 64), (unsigned)((d + 63) / 64));
-            transpose_bf16_kernel<<<grid, 256, 0, s0>>>(Y, ldy, cols, (int)d, yt, plan.ld_yt);
+            transpose_bf16_kernel<<<grid, 256, 0, sx>>>(Y, ldy, cols, (int)d, yt, plan.ld_yt);
         }
         if (want_dy) {
-            ScopedTiming timing(s0, TAG_ROW, 0.0);
+            ScopedTiming timing(sy, TAG_ROW, 0.0);
             dim3 grid((unsigned)((rows + 63) / 64), (unsigned)((d + 63) / 64));
-            transpose_bf16_kernel<<<grid, 256, 0, s0>>>(X, ldx, rows, (int)d, xt, plan.ld_xt);
+            transpose_bf16_kernel<<<grid, 256, 0, sy>>>(X, ldx, rows, (int)d, xt, plan.ld_xt);
         }
         MECLIP_CUDA(cudaGetLastError());
     }

@@ -33,8 +33,19 @@ static constexpr int MAX_STAGES = 8;
 static constexpr int SCHED_DEPTH = 4;     // tile ids in flight between the scheduler and the consumers
 static constexpr int A_STAGE_BYTES = BM * BK * 2;        // 16 KiB
 static constexpr int TMEM_COLS = 512;     // two accumulators of up to 256 columns
-static constexpr int GEMM_THREADS = 320;   // producer warp + MMA warp + 8 epilogue warps
-static constexpr int EPI_THREADS = 256;
+// Build-time shape of the epilogue: 4 or 8 warps, and whether the sums pass keeps its column partials in
+// registers over a strip of tiles (needs 8 warps: 128 accumulators per thread) or reduces them per tile.
+#ifndef MECLIP_EPI_WARPS
+#define MECLIP_EPI_WARPS 8
+#endif
+#ifndef MECLIP_STRIPS
+#define MECLIP_STRIPS (MECLIP_EPI_WARPS == 8)
+#endif
+static constexpr int EPI_WARPS = MECLIP_EPI_WARPS;
+static constexpr int GEMM_THREADS = 64 + 32 * EPI_WARPS;   // producer warp + MMA warp + epilogue warps
+static constexpr int EPI_THREADS = 32 * EPI_WARPS;
+static_assert(EPI_WARPS == 4 || EPI_WARPS == 8, "4 or 8 epilogue warps");
+static_assert(!MECLIP_STRIPS || EPI_WARPS == 8, "strip accumulators need 8 epilogue warps");
 static constexpr int SMEM_LIMIT = 232448; // 227 KiB: most dynamic shared memory one CTA can have
 static constexpr int STORE_BUF_BYTES = 32 * 128;   // one warp's 32 rows x 64 bf16 staging tile
 
@@ -48,6 +59,10 @@ struct GemmParams {
     int num_stages;           // operand ring depth, from the shared memory left over
     int stage_bytes;          // A_STAGE_BYTES + bn * 128
     uint32_t idesc;
+    // The last column tile may be narrower (EPI_OUT only): 1152 columns = 4 tiles of 256 + one of 128, which
+    // feeds the tensor cores better than six tiles of 192.  bn_last == bn when there is no such tile.
+    int bn_last;
+    uint32_t idesc_last;
     unsigned int* tile_counter;   // zeroed by the caller; null = static round-robin
     int strip_len;            // tiles handed out together (consecutive ids share their columns), >= 1
     int a_blocked;            // A is the coefficient panel in its column-blocked layout (3-D tensor map)
@@ -305,6 +320,9 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                 if (!mbar_wait(smem_u32(&tail->tmem_empty_bar[acc]), acc_phase ^ 1u, abort_flag)) break;
                 tc_fence_after();
                 trace_event(p, 1, ntrace, TR_MMA_BEGIN, tile);
+                int mt_, nt_;
+                tile_coords(p, tile, mt_, nt_);
+                const uint32_t idesc = (nt_ == p.num_n_tiles - 1) ? p.idesc_last : p.idesc;
                 const uint32_t tmem_d = tmem_base + (uint32_t)acc * MAX_BN;
                 for (int ks = 0; ks < p.k_steps; ++ks) {
                     if (!mbar_wait(smem_u32(&tail->full_bar[stage]), phase, abort_flag)) { ok = false; break; }
@@ -316,7 +334,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                     for (int kk = 0; kk < BK / 16; ++kk) {
                         const uint64_t ad = umma_smem_desc(sa + kk * A_KSTEP, A_LBO, 1024);
                         const uint64_t bd = umma_smem_desc(sb + kk * B_KSTEP, B_LBO, 1024);
-                        umma_bf16(tmem_d, ad, bd, p.idesc, (ks | kk) != 0 ? 1u : 0u);
+                        umma_bf16(tmem_d, ad, bd, idesc, (ks | kk) != 0 ? 1u : 0u);
                     }
                     umma_commit(smem_u32(&tail->empty_bar[stage]));   // frees the stage when these MMAs retire
                     if (++stage == num_stages) { stage = 0; phase ^= 1u; }
@@ -358,7 +376,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)acc * MAX_BN;
             const uint32_t free_bar = smem_u32(&tail->tmem_empty_bar[acc]);
             if (threadIdx.x == 64) trace_event(p, 2, ntrace, TR_EPI_BEGIN, tile);
-            epilogue_tile<EPI>(p, &tmap_c, tail, st, taddr, mt * BM, nt * p.bn, warp, lane,
+            epilogue_tile<EPI>(p, &tmap_c, tail, st, taddr, mt * BM, nt * p.bn, (nt == p.num_n_tiles - 1) ? p.bn_last : p.bn,
+                               warp, lane,
                                [free_bar, &p, &ntrace, tile]() {
                                    mbar_arrive(free_bar);
                                    if (threadIdx.x == 64) trace_event(p, 2, ntrace, TR_EPI_RELEASED, tile);

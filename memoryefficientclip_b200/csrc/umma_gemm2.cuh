@@ -51,7 +51,7 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(smem_u32(&tail->tmem_full_bar[a]), 1);
-            mbar_init(smem_u32(&tail->tmem_empty_bar[a]), 16);  // 8 epilogue warps x 2 CTAs (leader only)
+            mbar_init(smem_u32(&tail->tmem_empty_bar[a]), 2 * EPI_WARPS);  // epilogue warps of both CTAs (leader only)
         }
         fence_barrier_init();
         tma_prefetch_desc(&tmap_a);
@@ -157,7 +157,7 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
             tc_fence_after();
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)acc * MAX_BN;
             const uint32_t free_bar = mapa_u32(smem_u32(&tail->tmem_empty_bar[acc]), 0);   // the leader's barrier
-            epilogue_tile<EPI>(p, &tmap_c, tail, st, taddr, mt * PAIR_BM + (int)rank * BM, nt * p.bn, warp, lane,
+            epilogue_tile<EPI>(p, &tmap_c, tail, st, taddr, mt * PAIR_BM + (int)rank * BM, nt * p.bn, p.bn, warp, lane,
                                [free_bar, lane]() {
                                    __syncwarp();
                                    if (lane == 0) mbar_arrive_cluster(free_bar);
