@@ -319,14 +319,8 @@ static int make_tmap_blocked(CUtensorMap* tm, const void* base, long long rows, 
     EncodeTiledFn enc = get_encode_fn();
     if (enc == nullptr) return fail(MECLIP_EUNSUPPORTED, "cuTensorMapEncodeTiled not available from this driver");
     cuuint64_t dims[3] = {64, (cuuint64_t)rows, (cuuint64_t)chunks};
-    // MECLIP_PANEL_ROWMAJOR=1 (experiments): same 3-D view over a plain row-major panel whose pitch
-    // is chunks_alloc * 64 elements; chunk c then starts 128 bytes after chunk c-1 inside a row.
-    static const bool rowmajor = []() {
-        const char* v = std::getenv("MECLIP_PANEL_ROWMAJOR");
-        return v != nullptr && v[0] == '1';
-    }();
     cuuint64_t strides[2] = {128, (cuuint64_t)rows_alloc * 128};
-    if (rowmajor) { strides[0] = (cuuint64_t)chunks_alloc * 128; strides[1] = 128; }
+    (void)chunks_alloc;
     cuuint32_t box[3] = {64, (cuuint32_t)box_rows, 1};
     cuuint32_t estr[3] = {1, 1, 1};
     CUresult r = enc(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,

@@ -55,3 +55,27 @@ def test_more_tiles_than_sms():
     # 40 x 9 = 360 tiles on 148 persistent CTAs, long K: pipeline wrap-around and TMEM double buffering
     _run(5120, 1152, 2048, False, True, 128)
     _run(2048, 4096, 1152, False, False, 256)
+
+
+def test_in_kernel_trace_hook():
+    """meclip_debug_set_trace: CTA 0 records load / MMA / epilogue timestamps per tile, in order."""
+    from memoryefficientclip_b200 import _lib, ops
+    lib = _lib.load()
+    a = torch.randn(1024, 256).bfloat16().cuda()
+    b = torch.randn(512, 256).bfloat16().cuda()
+    cap = 300
+    buf = torch.zeros(2 + 3 * cap, dtype=torch.int64, device="cuda")
+    try:
+        _lib.check(lib.meclip_debug_set_trace(buf.data_ptr(), buf.numel()))
+        ops.debug_gemm(a, b, False, False, 1024, 512, 256, 256)
+        torch.cuda.synchronize()
+    finally:
+        lib.meclip_debug_set_trace(None, 0)
+    rec = [r for r in buf[2:].view(cap, 3).cpu().tolist() if r[0] != 0]
+    tags = {r[0] for r in rec}
+    assert {1, 2, 10, 11, 12, 20, 21, 22} <= tags, tags
+    by_tile = {}
+    for tag, tile, t in rec:
+        by_tile.setdefault(tile, {})[tag] = t
+    for tile, ev in by_tile.items():
+        assert ev[1] <= ev[11] <= ev[12] <= ev[21] <= ev[22], (tile, ev)     # loads, data, last MMA, release, end
