@@ -196,3 +196,13 @@ def test_clip_with_one_frozen_tower_skips_its_gradient(frozen):
         dense.assert_parity(loss.item(), rl, (xg.grad.float().cpu(),), (rx,), "frozen text")
     # normalise x2, sums, finalize | transpose, coefficient panel, one contraction, one Jacobian
     assert launches == 8, launches
+
+
+def test_noisy_positive_pairs_low_temperature():
+    """The distribution of the B=262144 ring configuration at a size the dense oracle handles:
+    text = normalize(image + 0.5 noise), T = 0.03, bf16, normalise inside."""
+    from memoryefficientclip_b200 import synth
+    img, txt = synth.noisy_pair(2048, 1024, 0.5)
+    loss, dx, dy = _run_clip(img, txt, 0.03, False)
+    rl, rx, ry = dense.clip_dense(img, txt, 0.03, False)
+    dense.assert_parity(loss, rl, (dx, dy), (rx, ry), "noisy pairs T=0.03")

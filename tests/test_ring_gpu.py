@@ -84,6 +84,49 @@ def test_ring_two_gpus(kind, b, d, dtype, normalize):
     _run(2, kind, b, d, dtype, normalize)
 
 
+def _large_worker(rank, world, port, outdir):
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        from memoryefficientclip_b200 import ring, synth
+        b_global, d = 16384, 768
+        b = b_global // world
+        img, txt = synth.clip_pair(b_global, d, torch.bfloat16, True, row_start=rank * b, rows=b)
+        xl, yl = img.cuda().requires_grad_(True), txt.cuda().requires_grad_(True)
+        loss = ring.RingMemoryEfficientCLIPLoss(0.07, True)(xl, yl)
+        loss.backward()
+        torch.cuda.synchronize()
+        torch.save({"loss": loss.item(), "dx": xl.grad.float().cpu(), "dy": yl.grad.float().cpu()},
+                   os.path.join(outdir, f"r{rank}.pt"))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_ring_two_gpus_large_against_streaming_oracle():
+    """Global B = 16384, D = 768 (several tiles, panels and a real overlap of transfers and kernels):
+    exact loss and sampled gradient rows from the row-blocked CPU oracle."""
+    world = 2
+    if torch.cuda.device_count() < world:
+        pytest.skip("needs 2 GPUs")
+    from memoryefficientclip_b200 import synth
+    with tempfile.TemporaryDirectory() as outdir:
+        mp.spawn(_large_worker, args=(world, _free_port(), outdir), nprocs=world, join=True)
+        res = [torch.load(os.path.join(outdir, f"r{r}.pt")) for r in range(world)]
+    img, txt = synth.clip_pair(16384, 768, torch.bfloat16, True)
+    rows = [0, 127, 4096, 8191, 8192, 12000, 16383]
+    ref = dense.clip_streaming(img.float(), txt.float(), 0.07, rows)
+    dx = torch.cat([r["dx"] for r in res])
+    dy = torch.cat([r["dy"] for r in res])
+    for r in res:
+        assert dense.loss_rel_err(r["loss"], ref["loss"]) <= dense.LOSS_RTOL
+    for got, want in ((dx[rows], ref["dx_rows"]), (dy[rows], ref["dy_rows"])):
+        max_rel, cos = dense.grad_errors(got, want)
+        assert max_rel <= dense.GRAD_MAX_REL and cos >= dense.GRAD_COS_MIN, (max_rel, cos)
+
+
 def test_ring_four_gpus():
     _run(4, "clip", 2048, 128, "bfloat16", False)
 
