@@ -16,8 +16,10 @@
  *  - Return value: MECLIP_OK or an error code; meclip_last_error() gives text.
  *    Nothing here calls exit/abort or throws.
  *  - Matrices are row-major with a leading dimension in ELEMENTS (ld >= D).
- *    Operand matrices of the tile kernels are bf16; D must be a multiple of 8
- *    and base pointers / row pitches 16-byte aligned (TMA requirements).
+ *    Operand matrices of the tile kernels are bf16; their D must be a multiple of 8
+ *    and base pointers / row pitches 16-byte aligned (TMA requirements).  The two
+ *    row kernels (meclip_normalize_fwd / _bwd) take and give any D, pitch, alignment
+ *    and fp32 / bf16 / fp16, and produce such operands by zero padding.
  *  - `status` is a device int the kernels set non-zero when a bounded wait inside
  *    a kernel ran out (MECLIP_ETIMEOUT); read it with meclip_read_status().
  *
@@ -43,7 +45,7 @@ enum meclip_status {
 };
 
 enum meclip_kind { MECLIP_CLIP = 0, MECLIP_LIT = 1, MECLIP_SIGLIP = 2 /* internal to the siglip entry points */ };
-enum meclip_dtype { MECLIP_BF16 = 0, MECLIP_F32 = 1 };
+enum meclip_dtype { MECLIP_BF16 = 0, MECLIP_F32 = 1, MECLIP_F16 = 2 /* row kernels only */ };
 
 /* How a gradient output buffer is written. */
 enum meclip_out_mode {
@@ -102,8 +104,10 @@ int meclip_accumulate_f32(float* dst, const float* src, int64_t n, void* stream)
 /*
  * x_hat = x / max(||x||_2, 1e-12) per row, written as bf16, plus inv_norm[i] =
  * 1/max(||x_i||, 1e-12).  With normalize == 0 only the dtype conversion to bf16
- * is done (inv_norm may be NULL).  Replaces F.normalize(dim=1) at
- * clip_loss.py:266-268 / lit_loss.py:257-259 and the fp32 -> bf16 staging.
+ * is done (inv_norm may be NULL).  x may be fp32, bf16 or fp16, with ANY d >= 1, pitch
+ * and alignment; x_hat gets round_up(d, 8) columns (the extra ones zero, ldh at least
+ * that), which is the operand form the tile kernels need.  Replaces F.normalize(dim=1)
+ * at clip_loss.py:266-268 / lit_loss.py:257-259 and the fp32 -> bf16 staging.
  */
 int meclip_normalize_fwd(const void* x, int x_dtype, int64_t rows, int64_t d, int64_t ldx, int normalize,
                          void* x_hat_bf16, int64_t ldh, float* inv_norm, void* stream);
@@ -111,7 +115,9 @@ int meclip_normalize_fwd(const void* x, int x_dtype, int64_t rows, int64_t d, in
 /*
  * Jacobian of the row normalisation: dx = (g - x_hat * (x_hat . g)) * inv_norm.
  * Replaces the autograd node PyTorch records for F.normalize
- * (clip_loss.py:266-268).  g is fp32 or bf16; dx takes dx_dtype.
+ * (clip_loss.py:266-268).  g (fp32 or bf16) and x_hat have round_up(d, 8) columns;
+ * dx takes dx_dtype (fp32, bf16 or fp16), any pitch >= d and any alignment.
+ * inv_norm == NULL: plain conversion dx = g (x_hat may then be NULL too).
  */
 int meclip_normalize_bwd(const void* g, int g_dtype, int64_t ldg, const void* x_hat_bf16, int64_t ldh,
                          const float* inv_norm, int64_t rows, int64_t d, void* dx, int dx_dtype, int64_t lddx,

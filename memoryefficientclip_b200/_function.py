@@ -40,13 +40,13 @@ class ContrastiveLossFn(torch.autograd.Function):
         if normalize:
             saved += [inv_x, inv_y]
         ctx.save_for_backward(*saved)
-        ctx.meclip = (temperature_value, kind, bool(stable), bool(normalize), x.dtype, y.dtype)
+        ctx.meclip = (temperature_value, kind, bool(stable), bool(normalize), x.dtype, y.dtype, x.shape[1])
         ctx.meclip_t = temperature if t_is_tensor and temperature.requires_grad else None
         return loss
 
     @staticmethod
     def run_backward(ctx, grad_output):
-        temperature, kind, stable, normalize, x_dtype, y_dtype = ctx.meclip
+        temperature, kind, stable, normalize, x_dtype, y_dtype, d = ctx.meclip
         saved = list(ctx.saved_tensors)
         x_hat, y_hat, row_sum = saved[:3]
         rest = saved[3:]
@@ -59,9 +59,12 @@ class ContrastiveLossFn(torch.autograd.Function):
         need = tuple(ctx.needs_input_grad) + (False, False)
         want_dx = bool(need[0])
         want_dy = kind == _lib.CLIP and bool(need[1])      # a frozen tower costs no contraction
-        # with the fused Jacobian the contraction output stays fp32 until the Jacobian rounds once
-        dx_t = torch.float32 if normalize else x_dtype
-        dy_t = torch.float32 if normalize else y_dtype
+        # with the fused Jacobian the contraction output stays fp32 until the Jacobian rounds once; the same
+        # row kernel converts when the contraction cannot write the input's dtype or feature count itself
+        post_x = normalize or not ops.direct_grad_dtype(x_dtype, d)
+        post_y = normalize or not ops.direct_grad_dtype(y_dtype, d)
+        dx_t = torch.float32 if post_x else x_dtype
+        dy_t = torch.float32 if post_y else y_dtype
         t_param = getattr(ctx, "meclip_t", None)
         sum_g_s = torch.zeros(2, dtype=torch.float32, device=x_hat.device) if t_param is not None else None
         if sum_g_s is not None and not (want_dx or want_dy):
@@ -74,11 +77,10 @@ class ContrastiveLossFn(torch.autograd.Function):
             # (The Stable scaling only rescales the feature gradients; the temperature gets the true one.)
             dt = sum_g_s[0] * (-1.0 / (scale * batch * temperature * temperature))
             ctx.meclip_dt = dt.reshape(t_param.shape).to(t_param.dtype)
-        if normalize:
-            if dx is not None:
-                dx = ops.normalize_bwd(dx, x_hat, inv_x, x_dtype)
-            if dy is not None:
-                dy = ops.normalize_bwd(dy, y_hat, inv_y, y_dtype)
+        if post_x and dx is not None:
+            dx = ops.normalize_bwd(dx, x_hat, inv_x, x_dtype, d)
+        if post_y and dy is not None:
+            dy = ops.normalize_bwd(dy, y_hat, inv_y, y_dtype, d)
         return (dx if need[0] else None), (dy if want_dy else None)
 
     @staticmethod

@@ -16,7 +16,7 @@ LIB_PATH = os.environ.get("MECLIP_LIBRARY") or os.path.join(PKG_DIR, "libmeclip_
 
 OK, EINVAL, ENOSPC, ECUDA, ETIMEOUT, EUNSUPPORTED = range(6)
 CLIP, LIT, SIGLIP = 0, 1, 2
-BF16, F32 = 0, 1
+BF16, F32, F16 = 0, 1, 2
 STORE_BF16, STORE_F32, ACCUM_F32 = 0, 1, 2
 
 # name -> (restype, argtypes); mirrors include/meclip.h declaration by declaration

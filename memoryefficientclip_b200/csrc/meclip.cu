@@ -99,6 +99,29 @@ __device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&v)[8]) {
         v[2 * i + 1] = f.y;
     }
 }
+__device__ __forceinline__ void load8(const __half* p, float (&v)[8]) {
+    const uint4 u = *reinterpret_cast<const uint4*>(p);
+    const __half2* h = reinterpret_cast<const __half2*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 f = __half22float2(h[i]);
+        v[2 * i] = f.x;
+        v[2 * i + 1] = f.y;
+    }
+}
+__device__ __forceinline__ float load1(const float* p) { return *p; }
+__device__ __forceinline__ float load1(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+__device__ __forceinline__ float load1(const __half* p) { return __half2float(*p); }
+__device__ __forceinline__ void store1(float* p, float v) { *p = v; }
+__device__ __forceinline__ void store1(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
+__device__ __forceinline__ void store1(__half* p, float v) { *p = __float2half_rn(v); }
+__device__ __forceinline__ void store8(__half* p, const float (&v)[8]) {
+    uint4 u;
+    __half2* h = reinterpret_cast<__half2*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h[i] = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
+    *reinterpret_cast<uint4*>(p) = u;
+}
 __device__ __forceinline__ void store8(float* p, const float (&v)[8]) {
     *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
     *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
@@ -119,9 +142,11 @@ __device__ __forceinline__ float warp_sum(float v) {
 static constexpr int ROW_KERNEL_THREADS = 256;
 
 // x_hat = x / max(||x||, 1e-12) as bf16 (+ inv_norm); normalize == 0: dtype conversion only.
+// The output row has dpad = round_up(d, 8) columns, the ones past d are zero, so that the tile kernels
+// always see 16-byte rows.  vec == 0 (d not a multiple of 8, or an unaligned input): element-wise reads.
 template <typename TIn>
 __global__ void __launch_bounds__(ROW_KERNEL_THREADS)
-normalize_fwd_kernel(const TIn* __restrict__ x, long long ldx, long long rows, int d, int normalize,
+normalize_fwd_kernel(const TIn* __restrict__ x, long long ldx, long long rows, int d, int dpad, int normalize, int vec,
                      __nv_bfloat16* __restrict__ out, long long ldh, float* __restrict__ inv_norm) {
     const long long row = (long long)blockIdx.x * (ROW_KERNEL_THREADS / 32) + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
@@ -130,55 +155,78 @@ normalize_fwd_kernel(const TIn* __restrict__ x, long long ldx, long long rows, i
     float inv = 1.f;
     if (normalize) {
         float ss = 0.f;
-        for (int c = lane * 8; c < d; c += 256) {
-            float v[8];
-            load8(xr + c, v);
+        if (vec) {
+            for (int c = lane * 8; c < d; c += 256) {
+                float v[8];
+                load8(xr + c, v);
 #pragma unroll
-            for (int i = 0; i < 8; ++i) ss = fmaf(v[i], v[i], ss);
+                for (int i = 0; i < 8; ++i) ss = fmaf(v[i], v[i], ss);
+            }
+        } else {
+            for (int c = lane; c < d; c += 32) { const float v = load1(xr + c); ss = fmaf(v, v, ss); }
         }
         ss = warp_sum(ss);
         inv = 1.f / fmaxf(sqrtf(ss), 1e-12f);
         if (lane == 0 && inv_norm != nullptr) inv_norm[row] = inv;
     }
     __nv_bfloat16* orow = out + row * ldh;
-    for (int c = lane * 8; c < d; c += 256) {
-        float v[8];
-        load8(xr + c, v);
+    if (vec) {
+        for (int c = lane * 8; c < d; c += 256) {
+            float v[8];
+            load8(xr + c, v);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) v[i] *= inv;
-        store8(orow + c, v);
+            for (int i = 0; i < 8; ++i) v[i] *= inv;
+            store8(orow + c, v);
+        }
+    } else {
+        for (int c = lane; c < dpad; c += 32) store1(orow + c, c < d ? load1(xr + c) * inv : 0.f);
     }
 }
 
-// dx = (g - x_hat (x_hat . g)) * inv_norm
+// dx = (g - x_hat (x_hat . g)) * inv_norm; inv_norm == nullptr: dx = g (dtype conversion of a gradient).
+// g and x_hat are this library's own 16-byte-aligned buffers; vec_out == 0: element-wise stores of dx.
 template <typename TG, typename TOut>
 __global__ void __launch_bounds__(ROW_KERNEL_THREADS)
 normalize_bwd_kernel(const TG* __restrict__ g, long long ldg, const __nv_bfloat16* __restrict__ xh, long long ldh,
-                     const float* __restrict__ inv_norm, long long rows, int d, TOut* __restrict__ dx,
+                     const float* __restrict__ inv_norm, long long rows, int d, int vec_out, TOut* __restrict__ dx,
                      long long lddx) {
     const long long row = (long long)blockIdx.x * (ROW_KERNEL_THREADS / 32) + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
     if (row >= rows) return;
     const TG* gr = g + row * ldg;
     const __nv_bfloat16* hr = xh + row * ldh;
+    const bool jac = inv_norm != nullptr;
     float dot = 0.f;
-    for (int c = lane * 8; c < d; c += 256) {
-        float gv[8], hv[8];
-        load8(gr + c, gv);
-        load8(hr + c, hv);
+    if (jac) {
+        const int dpad = (d + 7) & ~7;          // x_hat is zero past d, so the padded columns add nothing
+        for (int c = lane * 8; c < dpad; c += 256) {
+            float gv[8], hv[8];
+            load8(gr + c, gv);
+            load8(hr + c, hv);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) dot = fmaf(gv[i], hv[i], dot);
+            for (int i = 0; i < 8; ++i) dot = fmaf(gv[i], hv[i], dot);
+        }
+        dot = warp_sum(dot);
     }
-    dot = warp_sum(dot);
-    const float inv = inv_norm[row];
+    const float inv = jac ? inv_norm[row] : 1.f;
     TOut* orow = dx + row * lddx;
-    for (int c = lane * 8; c < d; c += 256) {
-        float gv[8], hv[8];
-        load8(gr + c, gv);
-        load8(hr + c, hv);
+    if (vec_out) {
+        for (int c = lane * 8; c < d; c += 256) {
+            float gv[8], hv[8];
+            load8(gr + c, gv);
+            if (jac) {
+                load8(hr + c, hv);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) gv[i] = (gv[i] - hv[i] * dot) * inv;
-        store8(orow + c, gv);
+                for (int i = 0; i < 8; ++i) gv[i] = (gv[i] - hv[i] * dot) * inv;
+            }
+            store8(orow + c, gv);
+        }
+    } else {
+        for (int c = lane; c < d; c += 32) {
+            float v = load1(gr + c);
+            if (jac) v = (v - load1(hr + c) * dot) * inv;
+            store1(orow + c, v);
+        }
     }
 }
 
@@ -770,48 +818,72 @@ int meclip_accumulate_f32(float* dst, const float* src, int64_t n, void* stream)
 int meclip_normalize_fwd(const void* x, int x_dtype, int64_t rows, int64_t d, int64_t ldx, int normalize,
                          void* x_hat_bf16, int64_t ldh, float* inv_norm, void* stream) {
     if (x == nullptr || x_hat_bf16 == nullptr) return fail(MECLIP_EINVAL, "normalize_fwd: null pointer");
-    if (rows < 1 || d < 8 || d % 8 != 0 || ldx < d || ldh < d) return fail(MECLIP_EINVAL, "normalize_fwd: need rows >= 1, d a multiple of 8, ld >= d");
-    if (!aligned16(x) || !aligned16(x_hat_bf16) || ldx % 8 != 0 || ldh % 8 != 0)
-        return fail(MECLIP_EINVAL, "normalize_fwd: pointers must be 16-byte aligned and pitches multiples of 8");
+    const int64_t dpad = (d + 7) / 8 * 8;
+    if (rows < 1 || d < 1 || ldx < d || ldh < dpad) return fail(MECLIP_EINVAL, "normalize_fwd: need rows, d >= 1, ldx >= d, ldh >= round_up(d, 8)");
+    if (!aligned16(x_hat_bf16) || ldh % 8 != 0)
+        return fail(MECLIP_EINVAL, "normalize_fwd: x_hat must be 16-byte aligned with a pitch that is a multiple of 8");
     if (normalize && inv_norm == nullptr) return fail(MECLIP_EINVAL, "normalize_fwd: inv_norm is null");
+    const int elt = x_dtype == MECLIP_F32 ? 4 : 2;
+    const int vec = (d % 8 == 0) && aligned16(x) && ((ldx * elt) % 16 == 0);
     const int wpb = ROW_KERNEL_THREADS / 32;
     const unsigned grid = (unsigned)((rows + wpb - 1) / wpb);
     cudaStream_t s = (cudaStream_t)stream;
     ScopedTiming timing(s, TAG_ROW, 0.0);
+    __nv_bfloat16* out = (__nv_bfloat16*)x_hat_bf16;
     if (x_dtype == MECLIP_F32)
-        normalize_fwd_kernel<float><<<grid, ROW_KERNEL_THREADS, 0, s>>>((const float*)x, ldx, rows, (int)d, normalize, (__nv_bfloat16*)x_hat_bf16, ldh, inv_norm);
+        normalize_fwd_kernel<float><<<grid, ROW_KERNEL_THREADS, 0, s>>>((const float*)x, ldx, rows, (int)d, (int)dpad, normalize, vec, out, ldh, inv_norm);
     else if (x_dtype == MECLIP_BF16)
-        normalize_fwd_kernel<__nv_bfloat16><<<grid, ROW_KERNEL_THREADS, 0, s>>>((const __nv_bfloat16*)x, ldx, rows, (int)d, normalize, (__nv_bfloat16*)x_hat_bf16, ldh, inv_norm);
+        normalize_fwd_kernel<__nv_bfloat16><<<grid, ROW_KERNEL_THREADS, 0, s>>>((const __nv_bfloat16*)x, ldx, rows, (int)d, (int)dpad, normalize, vec, out, ldh, inv_norm);
+    else if (x_dtype == MECLIP_F16)
+        normalize_fwd_kernel<__half><<<grid, ROW_KERNEL_THREADS, 0, s>>>((const __half*)x, ldx, rows, (int)d, (int)dpad, normalize, vec, out, ldh, inv_norm);
     else
         return fail(MECLIP_EINVAL, "normalize_fwd: bad dtype %d", x_dtype);
     MECLIP_CUDA(cudaGetLastError());
     return MECLIP_OK;
 }
 
+}  // extern "C"
+
+namespace {
+template <typename TG>
+int launch_normalize_bwd(const TG* g, int64_t ldg, const __nv_bfloat16* xh, int64_t ldh, const float* inv_norm, int64_t rows,
+                         int64_t d, void* dx, int dx_dtype, int64_t lddx, int vec_out, unsigned grid, cudaStream_t s) {
+    if (dx_dtype == MECLIP_F32)
+        normalize_bwd_kernel<TG, float><<<grid, ROW_KERNEL_THREADS, 0, s>>>(g, ldg, xh, ldh, inv_norm, rows, (int)d, vec_out, (float*)dx, lddx);
+    else if (dx_dtype == MECLIP_BF16)
+        normalize_bwd_kernel<TG, __nv_bfloat16><<<grid, ROW_KERNEL_THREADS, 0, s>>>(g, ldg, xh, ldh, inv_norm, rows, (int)d, vec_out, (__nv_bfloat16*)dx, lddx);
+    else if (dx_dtype == MECLIP_F16)
+        normalize_bwd_kernel<TG, __half><<<grid, ROW_KERNEL_THREADS, 0, s>>>(g, ldg, xh, ldh, inv_norm, rows, (int)d, vec_out, (__half*)dx, lddx);
+    else
+        return fail(MECLIP_EINVAL, "normalize_bwd: bad output dtype %d", dx_dtype);
+    return MECLIP_OK;
+}
+}  // namespace
+
+extern "C" {
+
 int meclip_normalize_bwd(const void* g, int g_dtype, int64_t ldg, const void* x_hat_bf16, int64_t ldh,
                          const float* inv_norm, int64_t rows, int64_t d, void* dx, int dx_dtype, int64_t lddx,
                          void* stream) {
-    if (g == nullptr || x_hat_bf16 == nullptr || inv_norm == nullptr || dx == nullptr)
+    if (g == nullptr || dx == nullptr || (inv_norm != nullptr && x_hat_bf16 == nullptr))
         return fail(MECLIP_EINVAL, "normalize_bwd: null pointer");
-    if (rows < 1 || d < 8 || d % 8 != 0 || ldg < d || ldh < d || lddx < d)
-        return fail(MECLIP_EINVAL, "normalize_bwd: need rows >= 1, d a multiple of 8, ld >= d");
-    if (!aligned16(g) || !aligned16(x_hat_bf16) || !aligned16(dx) || ldg % 8 != 0 || ldh % 8 != 0 || lddx % 8 != 0)
-        return fail(MECLIP_EINVAL, "normalize_bwd: pointers must be 16-byte aligned and pitches multiples of 8");
+    const int64_t dpad = (d + 7) / 8 * 8;
+    if (rows < 1 || d < 1 || ldg < dpad || (x_hat_bf16 != nullptr && ldh < dpad) || lddx < d)
+        return fail(MECLIP_EINVAL, "normalize_bwd: need rows, d >= 1, ldg and ldh >= round_up(d, 8), lddx >= d");
+    if (!aligned16(g) || (x_hat_bf16 != nullptr && !aligned16(x_hat_bf16)) || ldg % 8 != 0 || (x_hat_bf16 != nullptr && ldh % 8 != 0))
+        return fail(MECLIP_EINVAL, "normalize_bwd: g and x_hat must be 16-byte aligned with pitches multiples of 8");
+    const int oelt = dx_dtype == MECLIP_F32 ? 4 : 2;
+    const int vec_out = (d % 8 == 0) && aligned16(dx) && ((lddx * oelt) % 16 == 0);
     const int wpb = ROW_KERNEL_THREADS / 32;
     const unsigned grid = (unsigned)((rows + wpb - 1) / wpb);
     cudaStream_t s = (cudaStream_t)stream;
     ScopedTiming timing(s, TAG_ROW, 0.0);
     const __nv_bfloat16* xh = (const __nv_bfloat16*)x_hat_bf16;
-    if (g_dtype == MECLIP_F32 && dx_dtype == MECLIP_F32)
-        normalize_bwd_kernel<float, float><<<grid, ROW_KERNEL_THREADS, 0, s>>>((const float*)g, ldg, xh, ldh, inv_norm, rows, (int)d, (float*)dx, lddx);
-    else if (g_dtype == MECLIP_F32 && dx_dtype == MECLIP_BF16)
-        normalize_bwd_kernel<float, __nv_bfloat16><<<grid, ROW_KERNEL_THREADS, 0, s>>>((const float*)g, ldg, xh, ldh, inv_norm, rows, (int)d, (__nv_bfloat16*)dx, lddx);
-    else if (g_dtype == MECLIP_BF16 && dx_dtype == MECLIP_F32)
-        normalize_bwd_kernel<__nv_bfloat16, float><<<grid, ROW_KERNEL_THREADS, 0, s>>>((const __nv_bfloat16*)g, ldg, xh, ldh, inv_norm, rows, (int)d, (float*)dx, lddx);
-    else if (g_dtype == MECLIP_BF16 && dx_dtype == MECLIP_BF16)
-        normalize_bwd_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, ROW_KERNEL_THREADS, 0, s>>>((const __nv_bfloat16*)g, ldg, xh, ldh, inv_norm, rows, (int)d, (__nv_bfloat16*)dx, lddx);
-    else
-        return fail(MECLIP_EINVAL, "normalize_bwd: bad dtype");
+    int rc;
+    if (g_dtype == MECLIP_F32) rc = launch_normalize_bwd<float>((const float*)g, ldg, xh, ldh, inv_norm, rows, d, dx, dx_dtype, lddx, vec_out, grid, s);
+    else if (g_dtype == MECLIP_BF16) rc = launch_normalize_bwd<__nv_bfloat16>((const __nv_bfloat16*)g, ldg, xh, ldh, inv_norm, rows, d, dx, dx_dtype, lddx, vec_out, grid, s);
+    else return fail(MECLIP_EINVAL, "normalize_bwd: bad dtype %d", g_dtype);
+    if (rc) return rc;
     MECLIP_CUDA(cudaGetLastError());
     return MECLIP_OK;
 }

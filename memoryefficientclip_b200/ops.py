@@ -10,7 +10,7 @@ import torch
 
 from . import _lib
 
-_DT = {torch.bfloat16: _lib.BF16, torch.float32: _lib.F32}
+_DT = {torch.bfloat16: _lib.BF16, torch.float32: _lib.F32, torch.float16: _lib.F16}
 
 
 def _ptr(t):
@@ -24,9 +24,13 @@ def _stream(t: torch.Tensor):
 def _check_matrix(t: torch.Tensor, name: str):
     assert t.is_cuda, f"{name} must be a CUDA tensor"
     assert t.dim() == 2, f"{name} must be 2-D [batch, features]"
-    assert t.dtype in _DT, f"{name}: dtype {t.dtype} not supported (float32 or bfloat16)"
-    assert t.shape[1] % 8 == 0 and t.shape[1] >= 8, \
-        f"{name}: feature dimension {t.shape[1]} must be a multiple of 8 (16-byte rows for the TMA tile loads)"
+    assert t.dtype in _DT, f"{name}: dtype {t.dtype} not supported (float32, bfloat16 or float16)"
+    assert t.shape[0] >= 1 and t.shape[1] >= 1, f"{name}: empty input"
+
+
+def padded(d: int) -> int:
+    """Columns of a bf16 operand: the tile loads need 16-byte rows."""
+    return (d + 7) // 8 * 8
 
 
 def new_status(device) -> torch.Tensor:
@@ -40,25 +44,33 @@ def read_status(status: torch.Tensor) -> None:
 
 
 def normalize_fwd(x: torch.Tensor, normalize: bool = True):
-    """Returns (x_hat bf16 [rows, d], inv_norm fp32 [rows] or None)."""
+    """Returns (x_hat bf16 [rows, padded(d)], inv_norm fp32 [rows] or None); columns past d are zero.
+
+    Any feature count, row pitch and alignment is taken as it is (the kernel reads element-wise when
+    16-byte loads are not possible); only a non-unit column stride costs a copy."""
     _check_matrix(x, "x")
-    x = x if x.stride(1) == 1 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 else x.contiguous()
+    x = x if x.stride(1) == 1 else x.contiguous()
     rows, d = x.shape
-    out = torch.empty(rows, d, dtype=torch.bfloat16, device=x.device)
+    dp = padded(d)
+    out = torch.empty(rows, dp, dtype=torch.bfloat16, device=x.device)
     inv = torch.empty(rows, dtype=torch.float32, device=x.device) if normalize else None
     with torch.cuda.device(x.device):
-        _lib.check(_lib.load().meclip_normalize_fwd(x.data_ptr(), _DT[x.dtype], rows, d, x.stride(0), int(normalize),
-                                                    out.data_ptr(), d, _ptr(inv), _stream(x)))
+        _lib.check(_lib.load().meclip_normalize_fwd(x.data_ptr(), _DT[x.dtype], rows, d, max(x.stride(0), d),
+                                                    int(normalize), out.data_ptr(), dp, _ptr(inv), _stream(x)))
     return out, inv
 
 
-def normalize_bwd(g: torch.Tensor, x_hat: torch.Tensor, inv_norm: torch.Tensor, out_dtype) -> torch.Tensor:
-    rows, d = g.shape
+def normalize_bwd(g: torch.Tensor, x_hat, inv_norm, out_dtype, d: int | None = None) -> torch.Tensor:
+    """Gradient w.r.t. the un-normalised input, [rows, d] in out_dtype, from g (fp32 or bf16, padded(d)
+    columns).  inv_norm None: the inputs were already normalised, so this is the conversion of g only."""
+    rows = g.shape[0]
+    d = g.shape[1] if d is None else d
+    assert g.shape[1] == padded(d) and g.stride(1) == 1
     dx = torch.empty(rows, d, dtype=out_dtype, device=g.device)
     with torch.cuda.device(g.device):
-        _lib.check(_lib.load().meclip_normalize_bwd(g.data_ptr(), _DT[g.dtype], g.stride(0), x_hat.data_ptr(),
-                                                    x_hat.stride(0), inv_norm.data_ptr(), rows, d, dx.data_ptr(),
-                                                    _DT[out_dtype], d, _stream(g)))
+        _lib.check(_lib.load().meclip_normalize_bwd(g.data_ptr(), _DT[g.dtype], g.stride(0), _ptr(x_hat),
+                                                    x_hat.stride(0) if x_hat is not None else 0, _ptr(inv_norm),
+                                                    rows, d, dx.data_ptr(), _DT[out_dtype], d, _stream(g)))
     return dx
 
 
@@ -70,13 +82,18 @@ def accumulate_f32(dst: torch.Tensor, src: torch.Tensor) -> None:
 
 
 def as_operand(x: torch.Tensor) -> torch.Tensor:
-    """bf16, unit-stride rows, 16-byte aligned: what the tile kernels read."""
+    """bf16, unit-stride rows of padded(d) columns, 16-byte aligned: what the tile kernels read."""
     _check_matrix(x, "operand")
-    if x.dtype == torch.bfloat16 and x.stride(1) == 1 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0:
+    if (x.dtype == torch.bfloat16 and x.shape[1] % 8 == 0 and x.stride(1) == 1 and x.stride(0) % 8 == 0
+            and x.data_ptr() % 16 == 0):
         return x
-    if x.dtype == torch.bfloat16:
-        return x.contiguous()
     return normalize_fwd(x, normalize=False)[0]
+
+
+def direct_grad_dtype(dtype, d: int) -> bool:
+    """True when the contraction kernels can write the gradient of an input of this dtype and feature
+    count themselves; otherwise they write fp32 with padded(d) columns and normalize_bwd converts."""
+    return d % 8 == 0 and dtype in (torch.float32, torch.bfloat16)
 
 
 def sum_exp(kind, x_hat, y_hat, temperature, row_sum, col_sum, diag_s, row_off=0, col_off=0, status=None):

@@ -72,12 +72,10 @@ class CudaBlockOps:
     def all_gather(self, table, part, group):
         dist.all_gather_into_tensor(table.view(-1), part.contiguous().view(-1), group=group)
 
-    def finish_grad(self, g_f32, x_hat, inv_norm, out_dtype):
-        if inv_norm is not None:
-            return ops.normalize_bwd(g_f32, x_hat, inv_norm, out_dtype)
-        if out_dtype == torch.float32:
+    def finish_grad(self, g_f32, x_hat, inv_norm, out_dtype, d):
+        if inv_norm is None and out_dtype == torch.float32 and d == g_f32.shape[1]:
             return g_f32
-        return ops.normalize_fwd(g_f32, False)[0]
+        return ops.normalize_bwd(g_f32, x_hat, inv_norm, out_dtype, d)
 
 
 def _rotate(cur: torch.Tensor, nxt: torch.Tensor, group, rank: int, world: int):
@@ -206,12 +204,13 @@ class RingContrastiveLossFn(torch.autograd.Function):
         if normalize:
             saved += [inv_x, inv_y]
         ctx.save_for_backward(*saved)
-        ctx.ring = (float(temperature), kind, bool(stable), bool(normalize), x.dtype, y.dtype, group, rank, world, block)
+        ctx.ring = (float(temperature), kind, bool(stable), bool(normalize), x.dtype, y.dtype, x.shape[1], group, rank,
+                    world, block)
         return loss
 
     @staticmethod
     def backward(ctx, grad_output):
-        temperature, kind, stable, normalize, x_dtype, y_dtype, group, rank, world, block = ctx.ring
+        temperature, kind, stable, normalize, x_dtype, y_dtype, d, group, rank, world, block = ctx.ring
         saved = list(ctx.saved_tensors)
         x_hat, y_hat, row_sum = saved[:3]
         rest = saved[3:]
@@ -221,9 +220,9 @@ class RingContrastiveLossFn(torch.autograd.Function):
         go = grad_output.detach().to(device=x_hat.device, dtype=torch.float32).reshape(1).contiguous()
         scale = ops.grad_scale(b * world, temperature, stable)
         dx, dy = ring_backward(block, kind, x_hat, y_hat, temperature, row_sum, col_sum, go, scale, group, rank, world)
-        dx = block.finish_grad(dx, x_hat, inv_x, x_dtype)
+        dx = block.finish_grad(dx, x_hat, inv_x, x_dtype, d)
         if dy is not None:
-            dy = block.finish_grad(dy, y_hat, inv_y, y_dtype)
+            dy = block.finish_grad(dy, y_hat, inv_y, y_dtype, d)
         return dx, dy, None, None, None, None, None, None
 
 

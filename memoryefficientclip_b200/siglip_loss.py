@@ -39,14 +39,14 @@ class MemoryEfficientSigLIPLossFn(torch.autograd.Function):
         loss = ops.siglip_forward(x_hat, y_hat, t, b)
         saved = [x_hat, y_hat] + ([inv_x, inv_y] if normalize else [])
         ctx.save_for_backward(*saved)
-        ctx.sig = (t, b, bool(normalize), x.dtype, y.dtype,
+        ctx.sig = (t, b, bool(normalize), x.dtype, y.dtype, x.shape[1],
                    (logit_scale.shape, logit_scale.dtype) if isinstance(logit_scale, torch.Tensor) else None,
                    (logit_bias.shape, logit_bias.dtype) if isinstance(logit_bias, torch.Tensor) else None)
         return loss
 
     @staticmethod
     def backward(ctx, grad_output):
-        t, b, normalize, x_dtype, y_dtype, t_tensor, b_tensor = ctx.sig
+        t, b, normalize, x_dtype, y_dtype, d, t_tensor, b_tensor = ctx.sig
         saved = list(ctx.saved_tensors)
         x_hat, y_hat = saved[:2]
         inv_x, inv_y = saved[2:] if normalize else (None, None)
@@ -58,14 +58,15 @@ class MemoryEfficientSigLIPLossFn(torch.autograd.Function):
         if want_tb and not (want_dx or want_dy):
             want_dx = True
         sums = torch.zeros(2, dtype=torch.float32, device=x_hat.device) if want_tb else None
-        dx_t = torch.float32 if normalize else x_dtype
-        dy_t = torch.float32 if normalize else y_dtype
+        post_x = normalize or not ops.direct_grad_dtype(x_dtype, d)
+        post_y = normalize or not ops.direct_grad_dtype(y_dtype, d)
+        dx_t = torch.float32 if post_x else x_dtype
+        dy_t = torch.float32 if post_y else y_dtype
         dx, dy = ops.siglip_backward(x_hat, y_hat, t, b, go, t / batch, dx_t, dy_t, sums, want_dx, want_dy)
-        if normalize:
-            if dx is not None:
-                dx = ops.normalize_bwd(dx, x_hat, inv_x, x_dtype)
-            if dy is not None:
-                dy = ops.normalize_bwd(dy, y_hat, inv_y, y_dtype)
+        if post_x and dx is not None:
+            dx = ops.normalize_bwd(dx, x_hat, inv_x, x_dtype, d)
+        if post_y and dy is not None:
+            dy = ops.normalize_bwd(dy, y_hat, inv_y, y_dtype, d)
         dt = db = None
         if want_tb:
             # G = g (sigmoid(a) - I) with g = grad_out * t / B, so grad_out * dL/dt = sum(G S) / t, dL/db = sum(G) / t

@@ -57,9 +57,12 @@ def test_bad_arguments_return_error_codes(lib):
     assert lib.meclip_sum_exp(7, fake, fake, 8, 8, 8, 8, 8, 0.07, 0, 0, fake, fake, fake, None, None, None) == _lib.EINVAL
     # non-positive temperature
     assert lib.meclip_sum_exp(0, fake, fake, 8, 8, 8, 8, 8, 0.0, 0, 0, fake, fake, fake, None, None, None) == _lib.EINVAL
-    # misaligned normalise input
+    # normalise: the OUTPUT operand must be 16-byte aligned with padded rows (the input may be anything)
     odd = ctypes.c_void_p(0x1004)
-    assert lib.meclip_normalize_fwd(odd, 1, 4, 8, 8, 1, fake, 8, fake, None) == _lib.EINVAL
+    assert lib.meclip_normalize_fwd(fake, 1, 4, 8, 8, 1, odd, 8, fake, None) == _lib.EINVAL
+    assert lib.meclip_normalize_fwd(fake, 1, 4, 12, 12, 1, fake, 12, fake, None) == _lib.EINVAL     # ldh < round_up(d, 8)
+    assert lib.meclip_normalize_fwd(fake, 9, 4, 8, 8, 1, fake, 8, fake, None) == _lib.EINVAL        # bad dtype
+    assert lib.meclip_normalize_bwd(fake, 2, 8, fake, 8, fake, 4, 8, fake, 1, 8, None) == _lib.EINVAL  # g is fp32 or bf16
     # grad: workspace too small is reported before any launch... but only after the device check,
     # so here only the argument validation is exercised
     assert lib.meclip_grad(0, fake, fake, 8, 8, 8, 8, 8, 0.07, 0, 0, fake, None, None, 1.0, fake, 0, 8, None, 0, 8,

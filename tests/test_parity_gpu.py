@@ -206,3 +206,27 @@ def test_noisy_positive_pairs_low_temperature():
     loss, dx, dy = _run_clip(img, txt, 0.03, False)
     rl, rx, ry = dense.clip_dense(img, txt, 0.03, False)
     dense.assert_parity(loss, rl, (dx, dy), (rx, ry), "noisy pairs T=0.03")
+
+
+@pytest.mark.parametrize("b,d,dtype,normalized", [(200, 13, torch.float32, True), (256, 100, torch.bfloat16, False),
+                                                  (130, 515, torch.float32, False), (256, 64, torch.float16, True),
+                                                  (192, 84, torch.float16, False), (64, 1, torch.float32, False)])
+def test_any_feature_count_and_fp16_inputs(b, d, dtype, normalized):
+    """The reference takes any D (it masks the last feature block, clip_loss.py:33-38) and any float dtype
+    Triton loads; here operands are zero padded to 16-byte rows and fp16 is converted by the row kernels."""
+    x, y = _inputs(b, d, 9, normalized, dtype)
+    loss, dx, dy = _run_clip(x, y, 0.07, normalized)
+    assert dx.shape == (b, d) and dy.shape == (b, d)
+    rl, rx, ry = dense.clip_dense(x, y, 0.07, normalized)
+    if d == 1:       # every similarity is +-1: only check the loss and that the gradients are finite
+        assert dense.loss_rel_err(loss, rl) <= dense.LOSS_RTOL
+        assert torch.isfinite(dx).all() and torch.isfinite(dy).all()
+        return
+    dense.assert_parity(loss, rl, (dx, dy), (rx, ry), f"clip b={b} d={d} {dtype}")
+
+
+def test_lit_odd_feature_count_fp16():
+    txt, img = _inputs(160, 50, 10, False, torch.float16)
+    loss, dx = _run_lit(txt, img, 0.07, False)
+    rl, rx = dense.lit_dense(txt, img, 0.07, False)
+    dense.assert_parity(loss, rl, (dx,), (rx,), "lit fp16 d=50")

@@ -68,7 +68,7 @@ class OracleBlockOps:
         dist.all_gather(parts, part.contiguous(), group=group)
         table.copy_(torch.stack(parts))
 
-    def finish_grad(self, g, x_hat, inv_norm, out_dtype):
+    def finish_grad(self, g, x_hat, inv_norm, out_dtype, d):
         if inv_norm is not None:
             g = (g.double() - x_hat * (x_hat * g.double()).sum(dim=1, keepdim=True)) * inv_norm[:, None]
         return g.to(out_dtype)

@@ -79,7 +79,9 @@ def _run(world, kind, b_global, d, dtype_name, normalize):
 
 @pytest.mark.parametrize("kind,b,d,dtype,normalize", [("clip", 1024, 128, "bfloat16", False),
                                                       ("clip", 768, 64, "float32", True),
-                                                      ("lit", 512, 256, "bfloat16", True)])
+                                                      ("lit", 512, 256, "bfloat16", True),
+                                                      ("clip", 512, 100, "float16", True),
+                                                      ("clip", 640, 52, "float32", False)])
 def test_ring_two_gpus(kind, b, d, dtype, normalize):
     _run(2, kind, b, d, dtype, normalize)
 
