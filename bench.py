@@ -30,7 +30,9 @@ import torch
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-TAGS = ["sum_exp", "coef_panel", "dx_contraction", "dy_contraction", "row_kernels"]
+TAGS = ["sum_exp", "coef_panel", "dx_contraction", "dy_contraction", "loss_finalize", "normalize_fwd", "normalize_bwd",
+        "transpose", "accumulate_f32"]
+N_TENSOR_TAGS = 4          # the first four are tensor-bound; the rest are HBM-bound passes whose "flops" are bytes
 
 
 def load_peaks():
@@ -152,7 +154,12 @@ def profile_tags(lib):
     cnt = (ctypes.c_longlong * n)()
     fl = (ctypes.c_double * n)()
     lib.meclip_profile_end(ms, cnt, fl, n)
-    return [{"kernel": TAGS[i], "launches": int(cnt[i]), "ms": float(ms[i]), "flops": float(fl[i])} for i in range(n)]
+    out = []
+    for i in range(n):
+        t = {"kernel": TAGS[i], "launches": int(cnt[i]), "ms": float(ms[i])}
+        t["flops" if i < N_TENSOR_TAGS else "bytes"] = float(fl[i])
+        out.append(t)
+    return out
 
 
 def run_ours(args):
@@ -287,7 +294,7 @@ def run_ours(args):
 
     peaks = load_peaks()
     tflops = flops / (ms_value / 1e3) / 1e12
-    dominant = max(tags[:4], key=lambda t: t["ms"])
+    dominant = max(tags[:N_TENSOR_TAGS], key=lambda t: t["ms"])
     dom_ms = dominant["ms"] / max(1, dominant["launches"])
     dom_flops = dominant["flops"] / max(1, dominant["launches"])
     achieved = dom_flops / (dom_ms / 1e3) / 1e12 if dom_ms > 0 else 0.0
@@ -304,7 +311,14 @@ def run_ours(args):
         "step_frac_of_burst": tflops * (1 if world == 1 else 1.0 / world) / peaks["bf16_tflops"],
         "step_frac_of_sustained": tflops * (1 if world == 1 else 1.0 / world) / peaks["bf16_tflops_sustained"],
         "per_kernel": [dict(t, ms_per_step=t["ms"] / prof_steps,
-                            tflops=(t["flops"] / (t["ms"] / 1e3) / 1e12 if t["ms"] > 0 else 0.0)) for t in tags],
+                            tflops=(t["flops"] / (t["ms"] / 1e3) / 1e12 if t["ms"] > 0 else 0.0))
+                       for t in tags[:N_TENSOR_TAGS]],
+        # the HBM-bound passes (normalise, transposes, accumulation): algorithmic bytes / CUDA-event time against
+        # the measured copy bandwidth
+        "hbm_passes": [dict(t, ms_per_step=t["ms"] / prof_steps, gbs=t["bytes"] / (t["ms"] / 1e3) / 1e9,
+                            frac_of_hbm_peak=t["bytes"] / (t["ms"] / 1e3) / 1e9 / peaks["hbm_gbs"])
+                       for t in tags[N_TENSOR_TAGS:] if t["launches"] > 0 and t["ms"] > 0 and t["bytes"] > 0],
+        "hbm_peak_gbs": peaks["hbm_gbs"],
     }
 
     cpu = None

@@ -87,7 +87,10 @@ long long meclip_launch_count(void);
  * Per-kernel timing with CUDA events on the launch stream.  Between begin and end
  * every launch is bracketed by an event pair; end synchronises on them and sums
  * milliseconds, launches and useful FLOPs per tag: 0 sums pass, 1 coefficient
- * panel, 2 dX contraction, 3 dY contraction, 4 row kernels (normalise, loss).
+ * panel, 2 dX contraction, 3 dY contraction, and for the HBM-bound passes, whose
+ * third figure is algorithmic BYTES (read + written) instead of FLOPs: 4 loss
+ * finalisation, 5 normalise / convert forward, 6 normalise Jacobian / convert
+ * backward, 7 operand transposes, 8 fp32 accumulation (ring).  n_tags <= 9.
  * Meant for benchmarks; the events serialise nothing but add launch overhead.
  * Has no counterpart in the reference.
  */

@@ -47,7 +47,9 @@ static int fail(int code, const char* fmt, ...) {
 // launch counter and optional per-kernel CUDA-event timing
 // ------------------------------------------------------------------------------------
 static std::atomic<long long> g_launches{0};
-enum { TAG_SUMS = 0, TAG_COEF = 1, TAG_DX = 2, TAG_DY = 3, TAG_ROW = 4, TAG_COUNT = 5 };
+// tags >= TAG_ROW are HBM-bound passes: their `flops` field carries algorithmic BYTES (read + written)
+enum { TAG_SUMS = 0, TAG_COEF = 1, TAG_DX = 2, TAG_DY = 3, TAG_ROW = 4, TAG_NORM_FWD = 5, TAG_NORM_BWD = 6,
+       TAG_TRANSPOSE = 7, TAG_ACCUM = 8, TAG_COUNT = 9 };
 struct ProfileRecord { int tag; cudaEvent_t start, stop; double flops; };
 static std::mutex g_prof_mutex;
 static bool g_prof_on = false;
@@ -233,34 +235,44 @@ normalize_bwd_kernel(const TG* __restrict__ g, long long ldg, const __nv_bfloat1
 // out[c][r] = in[r][c] for a bf16 matrix: 64 x 64 tiles through shared memory, 16-byte global accesses.
 // The contractions read X^T / Y^T as K-major B operands (K-major tiles feed the tensor cores
 // measurably faster than MN-major ones when A is the transposed panel).
+// One CTA moves a 64 x 64 tile with 16-byte global accesses on both sides.  Shared memory holds the tile
+// already transposed as 32-bit words T[c][p] = (in[2p][c], in[2p+1][c]); the word index is XOR-swizzled by the
+// 8-column chunk of c in units of four words, which makes the 32-bit stores of a warp (8 chunks x 4 row pairs)
+// and the 16-byte loads of the write-out hit all 32 banks once.
 __global__ void __launch_bounds__(256)
 transpose_bf16_kernel(const __nv_bfloat16* __restrict__ in, long long ld_in, long long rows, int cols,
                       __nv_bfloat16* __restrict__ out, long long ld_out) {
-    __shared__ __nv_bfloat16 tile[64][64 + 8];
+    __shared__ __align__(16) uint32_t tile[64][32];
     const long long r0 = (long long)blockIdx.x * 64;
     const int c0 = blockIdx.y * 64;
     const int t = threadIdx.x;
-    const int cc = (t & 7) * 8;
+    {
+        const int k = t & 7;                  // 8-column chunk of the input row
+        const int rp = t >> 3;                // row pair
+        const long long r = r0 + 2 * rp;
+        const int c = c0 + 8 * k;
+        uint4 a = make_uint4(0, 0, 0, 0), b = make_uint4(0, 0, 0, 0);
+        if (c < cols) {                       // cols is a multiple of 8: a chunk is inside or outside as a whole
+            if (r < rows) a = __ldg(reinterpret_cast<const uint4*>(in + r * ld_in + c));
+            if (r + 1 < rows) b = __ldg(reinterpret_cast<const uint4*>(in + (r + 1) * ld_in + c));
+        }
+        const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
+        const int pw = rp ^ (k << 2);
 #pragma unroll
-    for (int h = 0; h < 2; ++h) {
-        const int rr = (t >> 3) + h * 32;
-        uint4 v = make_uint4(0, 0, 0, 0);
-        if (r0 + rr < rows && c0 + cc < cols) v = *reinterpret_cast<const uint4*>(in + (r0 + rr) * ld_in + c0 + cc);
-        const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(&v);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) tile[cc + i][rr] = e[i];
+        for (int m = 0; m < 4; ++m) {
+            tile[8 * k + 2 * m][pw] = __byte_perm(aw[m], bw[m], 0x5410);
+            tile[8 * k + 2 * m + 1][pw] = __byte_perm(aw[m], bw[m], 0x7632);
+        }
     }
     __syncthreads();
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
         const int oc = (t >> 3) + h * 32;     // output row = input column
-        const int orr = (t & 7) * 8;          // 8 consecutive output columns = input rows
-        if (c0 + oc < cols && r0 + orr < rows) {   // rows is padded to a multiple of 8 in ld_out, stores stay in the pitch
-            uint4 v;
-            __nv_bfloat16* e = reinterpret_cast<__nv_bfloat16*>(&v);
-#pragma unroll
-            for (int i = 0; i < 8; ++i) e[i] = tile[oc][orr + i];
-            *reinterpret_cast<uint4*>(out + (long long)(c0 + oc) * ld_out + r0 + orr) = v;
+        const int g = t & 7;                  // 8 consecutive output columns = input rows 8g .. 8g+7
+        // rows is padded to a multiple of 8 in ld_out, so a 16-byte store stays inside the pitch
+        if (c0 + oc < cols && r0 + 8 * g < rows) {
+            const uint4 v = *reinterpret_cast<const uint4*>(&tile[oc][4 * (g ^ ((oc >> 3) & 7))]);
+            *reinterpret_cast<uint4*>(out + (long long)(c0 + oc) * ld_out + r0 + 8 * g) = v;
         }
     }
 }
@@ -284,11 +296,26 @@ loss_finalize_kernel(const float* __restrict__ r, const float* __restrict__ c, c
                      long long n, float inv_t, float scale, int accumulate, float* __restrict__ loss) {
     __shared__ double part[1024];
     double acc = 0.0;
-    for (long long i = threadIdx.x; i < n; i += 1024) {
-        // fp32 logarithms (fp64 transcendentals are slow on this part), fp64 accumulation
-        double t = (double)logf(r[i]);
-        if (c != nullptr) t = 0.5 * (t + (double)logf(c[i]));
-        acc += t - ((double)diag[i] - 1.0) * (double)inv_t;
+    // eight independent elements per thread and trip, so that the loads of a trip are all in flight together
+    // (one block with one load at a time is bound by the load latency); out-of-range slots contribute 0
+    for (long long i0 = threadIdx.x; i0 < n; i0 += 8 * 1024) {
+        float rv[8], cv[8], dv[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const long long i = i0 + (long long)u * 1024;
+            const bool in = i < n;
+            rv[u] = in ? __ldg(r + i) : 1.f;
+            cv[u] = (in && c != nullptr) ? __ldg(c + i) : 1.f;
+            dv[u] = in ? __ldg(diag + i) : 1.f;
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            // lg2.approx (absolute error 2^-22, the sums themselves come from ex2.approx) instead of logf: the
+            // single block is instruction-bound and logf costs about 30 instructions; fp64 accumulation
+            float t = lg2_approx(rv[u]);
+            if (c != nullptr) t = 0.5f * (t + lg2_approx(cv[u]));
+            acc += (double)(0.6931471805599453f * t) - (double)((dv[u] - 1.f) * inv_t);
+        }
     }
     part[threadIdx.x] = acc;
     __syncthreads();
@@ -309,8 +336,16 @@ siglip_finalize_kernel(const float* __restrict__ r, const float* __restrict__ di
                        float scale, int accumulate, float* __restrict__ loss) {
     __shared__ double part[1024];
     double acc = 0.0;
-    for (long long i = threadIdx.x; i < n; i += 1024)
-        acc += 0.6931471805599453 * (double)r[i];
+    for (long long i0 = threadIdx.x; i0 < n; i0 += 8 * 1024) {
+        float rv[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const long long i = i0 + (long long)u * 1024;
+            rv[u] = i < n ? __ldg(r + i) : 0.f;
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) acc += 0.6931471805599453 * (double)rv[u];
+    }
     part[threadIdx.x] = acc;
     __syncthreads();
     for (int s = 512; s >= 1; s >>= 1) {
@@ -809,7 +844,7 @@ int meclip_accumulate_f32(float* dst, const float* src, int64_t n, void* stream)
     const long long n4 = n / 4;
     long long blocks = (n4 + 255) / 256;
     if (blocks > 8LL * sm_count()) blocks = 8LL * sm_count();
-    ScopedTiming timing((cudaStream_t)stream, TAG_ROW, 0.0);
+    ScopedTiming timing((cudaStream_t)stream, TAG_ACCUM, 12.0 * (double)n);
     accumulate_f32_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(dst, src, n4);
     MECLIP_CUDA(cudaGetLastError());
     return MECLIP_OK;
@@ -828,7 +863,7 @@ int meclip_normalize_fwd(const void* x, int x_dtype, int64_t rows, int64_t d, in
     const int wpb = ROW_KERNEL_THREADS / 32;
     const unsigned grid = (unsigned)((rows + wpb - 1) / wpb);
     cudaStream_t s = (cudaStream_t)stream;
-    ScopedTiming timing(s, TAG_ROW, 0.0);
+    ScopedTiming timing(s, TAG_NORM_FWD, (double)rows * ((double)d * elt + (double)dpad * 2 + (normalize ? 4 : 0)));
     __nv_bfloat16* out = (__nv_bfloat16*)x_hat_bf16;
     if (x_dtype == MECLIP_F32)
         normalize_fwd_kernel<float><<<grid, ROW_KERNEL_THREADS, 0, s>>>((const float*)x, ldx, rows, (int)d, (int)dpad, normalize, vec, out, ldh, inv_norm);
@@ -877,7 +912,8 @@ int meclip_normalize_bwd(const void* g, int g_dtype, int64_t ldg, const void* x_
     const int wpb = ROW_KERNEL_THREADS / 32;
     const unsigned grid = (unsigned)((rows + wpb - 1) / wpb);
     cudaStream_t s = (cudaStream_t)stream;
-    ScopedTiming timing(s, TAG_ROW, 0.0);
+    ScopedTiming timing(s, TAG_NORM_BWD, (double)rows * ((double)dpad * ((g_dtype == MECLIP_F32 ? 4 : 2) + (inv_norm ? 2 : 0)) +
+                                                       (double)d * oelt + (inv_norm ? 4 : 0)));
     const __nv_bfloat16* xh = (const __nv_bfloat16*)x_hat_bf16;
     int rc;
     if (g_dtype == MECLIP_F32) rc = launch_normalize_bwd<float>((const float*)g, ldg, xh, ldh, inv_norm, rows, d, dx, dx_dtype, lddx, vec_out, grid, s);
@@ -921,7 +957,7 @@ int meclip_loss_finalize(int kind, const float* row_sum, const float* col_sum, c
     if (row_sum == nullptr || diag_s == nullptr || loss_out == nullptr || n < 1 || !(temperature > 0.f))
         return fail(MECLIP_EINVAL, "loss_finalize: bad argument");
     if (kind == MECLIP_CLIP && col_sum == nullptr) return fail(MECLIP_EINVAL, "loss_finalize: CLIP needs col_sum");
-    ScopedTiming timing((cudaStream_t)stream, TAG_ROW, 0.0);
+    ScopedTiming timing((cudaStream_t)stream, TAG_ROW, (double)n * (kind == MECLIP_CLIP ? 12.0 : 8.0));
     loss_finalize_kernel<<<1, 1024, 0, (cudaStream_t)stream>>>(row_sum, kind == MECLIP_CLIP ? col_sum : nullptr, diag_s, n,
                                                                1.f / temperature, scale, accumulate, loss_out);
     MECLIP_CUDA(cudaGetLastError());
@@ -1004,12 +1040,12 @@ static int grad_impl(int kind, const void* x_bf16, const void* y_bf16, int64_t r
             if (want_dy) MECLIP_CUDA(cudaStreamWaitEvent(sy, side->fork, 0));
         }
         if (want_dx) {
-            ScopedTiming timing(sx, TAG_ROW, 0.0);
+            ScopedTiming timing(sx, TAG_TRANSPOSE, 4.0 * (double)cols * (double)d);
             dim3 grid((unsigned)((cols + 63) / 64), (unsigned)((d + 63) / 64));
             transpose_bf16_kernel<<<grid, 256, 0, sx>>>(Y, ldy, cols, (int)d, yt, plan.ld_yt);
         }
         if (want_dy) {
-            ScopedTiming timing(sy, TAG_ROW, 0.0);
+            ScopedTiming timing(sy, TAG_TRANSPOSE, 4.0 * (double)rows * (double)d);
             dim3 grid((unsigned)((rows + 63) / 64), (unsigned)((d + 63) / 64));
             transpose_bf16_kernel<<<grid, 256, 0, sy>>>(X, ldx, rows, (int)d, xt, plan.ld_xt);
         }
