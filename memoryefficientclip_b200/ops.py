@@ -141,18 +141,22 @@ def grad_workspace(rows, cols, d, device) -> torch.Tensor:
 
 
 def grad_block(kind, x_hat, y_hat, temperature, row_sum, col_sum, grad_out, grad_scale, dx, dx_mode, dy, dy_mode,
-               row_off=0, col_off=0, workspace=None, status=None):
-    """One rows x cols block of the backward (see meclip_grad in include/meclip.h)."""
+               row_off=0, col_off=0, workspace=None, status=None, sum_g_s=None):
+    """One rows x cols block of the backward (see meclip_grad in include/meclip.h).
+    sum_g_s: optional fp32 pair; its first element gets sum_ij G_ij S_ij of the block ADDED (meclip_grad_t)."""
     rows, d = x_hat.shape
     cols = y_hat.shape[0]
     if workspace is None:
         workspace = grad_workspace(rows, cols, d, x_hat.device)
+    head = (kind, x_hat.data_ptr(), y_hat.data_ptr(), rows, cols, d, x_hat.stride(0), y_hat.stride(0), float(temperature),
+            row_off, col_off, row_sum.data_ptr(), _ptr(col_sum), _ptr(grad_out), float(grad_scale), dx.data_ptr(), dx_mode,
+            dx.stride(0), _ptr(dy), dy_mode, dy.stride(0) if dy is not None else 0)
+    tail = (workspace.data_ptr(), workspace.numel(), _ptr(status), _stream(x_hat))
     with torch.cuda.device(x_hat.device):
-        _lib.check(_lib.load().meclip_grad(kind, x_hat.data_ptr(), y_hat.data_ptr(), rows, cols, d, x_hat.stride(0),
-                                           y_hat.stride(0), float(temperature), row_off, col_off, row_sum.data_ptr(),
-                                           _ptr(col_sum), _ptr(grad_out), float(grad_scale), dx.data_ptr(), dx_mode,
-                                           dx.stride(0), _ptr(dy), dy_mode, dy.stride(0) if dy is not None else 0,
-                                           workspace.data_ptr(), workspace.numel(), _ptr(status), _stream(x_hat)))
+        if sum_g_s is None:
+            _lib.check(_lib.load().meclip_grad(*head, *tail))
+        else:
+            _lib.check(_lib.load().meclip_grad_t(*head, sum_g_s.data_ptr(), *tail))
 
 
 def grad_block_static(kind, x_hat, y_hat, temperature, row_sum, col_sum, grad_out, grad_scale, dx, dx_mode, dy, dy_mode,
@@ -203,22 +207,52 @@ def loss_backward(kind, x_hat, y_hat, temperature, row_sum, col_sum, grad_out, g
     return dx, dy
 
 
+def siglip_sum(x_hat, y_hat, logit_scale, logit_bias, row_sum, diag_s, row_off=0, col_off=0, status=None):
+    """One rows x cols block of the sigmoid-loss forward: row_sum[i] += sum_j softplus(-z_ij a_ij) / ln2."""
+    rows, d = x_hat.shape
+    cols = y_hat.shape[0]
+    counter = torch.zeros(1, dtype=torch.int32, device=x_hat.device)
+    with torch.cuda.device(x_hat.device):
+        _lib.check(_lib.load().meclip_siglip_sum(x_hat.data_ptr(), y_hat.data_ptr(), rows, cols, d, x_hat.stride(0),
+                                                 y_hat.stride(0), float(logit_scale), float(logit_bias), row_off, col_off,
+                                                 row_sum.data_ptr(), diag_s.data_ptr(), counter.data_ptr(), _ptr(status),
+                                                 _stream(x_hat)))
+
+
+def siglip_loss_finalize(row_sum, diag_s, logit_scale, logit_bias, scale, loss_out, accumulate=False):
+    with torch.cuda.device(row_sum.device):
+        _lib.check(_lib.load().meclip_siglip_loss_finalize(row_sum.data_ptr(), diag_s.data_ptr(), row_sum.numel(),
+                                                           float(logit_scale), float(logit_bias), float(scale),
+                                                           int(accumulate), loss_out.data_ptr(), _stream(row_sum)))
+
+
 def siglip_forward(x_hat, y_hat, logit_scale, logit_bias, status=None):
     """Sigmoid-loss forward for a whole batch on one GPU; returns the 0-dim fp32 loss."""
-    b, d = x_hat.shape
+    b = x_hat.shape[0]
     dev = x_hat.device
     row_sum = torch.zeros(b, dtype=torch.float32, device=dev)
     diag_s = torch.zeros(b, dtype=torch.float32, device=dev)
-    counter = torch.zeros(1, dtype=torch.int32, device=dev)
     loss = torch.empty((), dtype=torch.float32, device=dev)
-    lib = _lib.load()
-    with torch.cuda.device(dev):
-        _lib.check(lib.meclip_siglip_sum(x_hat.data_ptr(), y_hat.data_ptr(), b, b, d, x_hat.stride(0), y_hat.stride(0),
-                                         float(logit_scale), float(logit_bias), 0, 0, row_sum.data_ptr(),
-                                         diag_s.data_ptr(), counter.data_ptr(), _ptr(status), _stream(x_hat)))
-        _lib.check(lib.meclip_siglip_loss_finalize(row_sum.data_ptr(), diag_s.data_ptr(), b, float(logit_scale),
-                                                   float(logit_bias), 1.0 / b, 0, loss.data_ptr(), _stream(x_hat)))
+    siglip_sum(x_hat, y_hat, logit_scale, logit_bias, row_sum, diag_s, 0, 0, status)
+    siglip_loss_finalize(row_sum, diag_s, logit_scale, logit_bias, 1.0 / b, loss)
     return loss
+
+
+def siglip_grad_block(x_hat, y_hat, logit_scale, logit_bias, grad_out, grad_scale_, dx, dx_mode, dy, dy_mode,
+                      row_off=0, col_off=0, workspace=None, sums=None, status=None):
+    """One rows x cols block of the sigmoid-loss backward (meclip_siglip_grad)."""
+    rows, d = x_hat.shape
+    cols = y_hat.shape[0]
+    if workspace is None:
+        workspace = grad_workspace(rows, cols, d, x_hat.device)
+    with torch.cuda.device(x_hat.device):
+        _lib.check(_lib.load().meclip_siglip_grad(x_hat.data_ptr(), y_hat.data_ptr(), rows, cols, d, x_hat.stride(0),
+                                                  y_hat.stride(0), float(logit_scale), float(logit_bias), row_off,
+                                                  col_off, _ptr(grad_out), float(grad_scale_), _ptr(dx), dx_mode,
+                                                  dx.stride(0) if dx is not None else 0, _ptr(dy), dy_mode,
+                                                  dy.stride(0) if dy is not None else 0, _ptr(sums),
+                                                  workspace.data_ptr(), workspace.numel(), _ptr(status),
+                                                  _stream(x_hat)))
 
 
 def siglip_backward(x_hat, y_hat, logit_scale, logit_bias, grad_out, grad_scale_, dx_dtype, dy_dtype, sums=None,

@@ -56,9 +56,26 @@ class CudaBlockOps:
         ops.loss_finalize(kind, row_sum, col_sum, diag, t, scale, out)
         return out
 
-    def grad(self, kind, x_hat, y_hat, t, row_sum, col_sum, go, scale, dx_acc, dy_out, row_off, col_off, workspace):
+    def grad(self, kind, x_hat, y_hat, t, row_sum, col_sum, go, scale, dx_acc, dy_out, row_off, col_off, workspace,
+             sum_g_s=None):
         ops.grad_block(kind, x_hat, y_hat, t, row_sum, col_sum, go, scale, dx_acc, _lib.ACCUM_F32, dy_out,
-                       _lib.STORE_F32, row_off, col_off, workspace)
+                       _lib.STORE_F32, row_off, col_off, workspace, sum_g_s=sum_g_s)
+
+    def new_sum(self, device):
+        return torch.zeros(2, dtype=torch.float32, device=device)
+
+    def siglip_sum(self, x_hat, y_hat, logit_scale, logit_bias, row_sum, diag, row_off, col_off):
+        ops.siglip_sum(x_hat, y_hat, logit_scale, logit_bias, row_sum, diag, row_off, col_off)
+
+    def siglip_local_loss(self, row_sum, diag, logit_scale, logit_bias, scale):
+        out = torch.empty((), dtype=torch.float32, device=row_sum.device)
+        ops.siglip_loss_finalize(row_sum, diag, logit_scale, logit_bias, scale, out)
+        return out
+
+    def siglip_grad(self, x_hat, y_hat, logit_scale, logit_bias, go, scale, dx_acc, dy_out, row_off, col_off, workspace,
+                    sums):
+        ops.siglip_grad_block(x_hat, y_hat, logit_scale, logit_bias, go, scale, dx_acc, _lib.ACCUM_F32, dy_out,
+                              _lib.STORE_F32, row_off, col_off, workspace, sums)
 
     def workspace(self, rows, cols, d, device):
         return ops.grad_workspace(rows, cols, d, device)
@@ -135,22 +152,15 @@ def _exchange_partial(send_buf, recv_buf, group, rank, world, step):
     return dist.batch_isend_irecv(p2p)
 
 
-def ring_backward(block, kind, x_hat, y_hat, temperature, row_sum, col_sum, grad_out, grad_scale, group, rank, world):
-    """Returns (dx fp32 [b, D], dy_own fp32 [b, D] or None) w.r.t. the normalised operands."""
+def _ring_backward_loop(block, x_hat, y_hat, group, rank, world, want_dy, grad_call):
+    """The backward choreography shared by the softmax and the sigmoid losses.  grad_call(y_shard, shard,
+    dx_acc, dy_out, workspace) runs the block kernels: dx_acc accumulates in fp32, dy_out is stored."""
     b, d = x_hat.shape
     dev = x_hat.device
-    clip = kind == _lib.CLIP
-    col_all = None
-    if clip:
-        if world > 1:
-            col_all = torch.empty(world, b, dtype=torch.float32, device=dev)
-            block.all_gather(col_all, col_sum, group)
-        else:
-            col_all = col_sum.view(1, b)
     dx = torch.zeros(b, d, dtype=torch.float32, device=dev)
-    dy = torch.empty(b, d, dtype=torch.float32, device=dev) if clip else None          # own shard: step 0 stores it
-    part = [torch.empty(b, d, dtype=torch.float32, device=dev) for _ in range(2)] if clip and world > 1 else []
-    inbox = [torch.empty(b, d, dtype=torch.float32, device=dev) for _ in range(2)] if clip and world > 1 else []
+    dy = torch.empty(b, d, dtype=torch.float32, device=dev) if want_dy else None       # own shard: step 0 stores it
+    part = [torch.empty(b, d, dtype=torch.float32, device=dev) for _ in range(2)] if want_dy and world > 1 else []
+    inbox = [torch.empty(b, d, dtype=torch.float32, device=dev) for _ in range(2)] if want_dy and world > 1 else []
     workspace = block.workspace(b, b, d, dev)
     bufs = [y_hat, torch.empty_like(y_hat)] if world > 1 else [y_hat]
     if world > 2:
@@ -164,16 +174,15 @@ def ring_backward(block, kind, x_hat, y_hat, temperature, row_sum, col_sum, grad
             nxt = 1 + (step % 2) if world > 2 else 1
             reqs = _rotate(bufs[cur], bufs[nxt], group, rank, world)
         out = None
-        if clip:
+        if want_dy:
             out = dy if step == 0 else part[step % 2]
-        block.grad(kind, x_hat, bufs[cur], temperature, row_sum, col_all[shard] if clip else None, grad_out,
-                   grad_scale, dx, out, rank * b, shard * b, workspace)
+        grad_call(bufs[cur], shard, dx, out, workspace)
         if pending is not None:          # the exchange started one step ago ran under this step's kernels
             for r in pending[0]:
                 r.wait()
             block.accumulate(dy, pending[1])
             pending = None
-        if clip and step > 0:
+        if want_dy and step > 0:
             pending = (_exchange_partial(part[step % 2], inbox[step % 2], group, rank, world, step), inbox[step % 2])
         for r in reqs:
             r.wait()
@@ -186,12 +195,84 @@ def ring_backward(block, kind, x_hat, y_hat, temperature, row_sum, col_sum, grad
     return dx, dy
 
 
+def ring_backward(block, kind, x_hat, y_hat, temperature, row_sum, col_sum, grad_out, grad_scale, group, rank, world,
+                  sum_g_s=None):
+    """Returns (dx fp32 [b, D], dy_own fp32 [b, D] or None) w.r.t. the normalised operands.
+    sum_g_s: optional zeroed pair; element 0 receives sum_ij G_ij S_ij over this rank's rows and ALL columns."""
+    b = x_hat.shape[0]
+    clip = kind == _lib.CLIP
+    col_all = None
+    if clip:
+        if world > 1:
+            col_all = torch.empty(world, b, dtype=torch.float32, device=x_hat.device)
+            block.all_gather(col_all, col_sum, group)
+        else:
+            col_all = col_sum.view(1, b)
+    extra = {} if sum_g_s is None else {"sum_g_s": sum_g_s}
+
+    def grad_call(y_shard, shard, dx_acc, dy_out, workspace):
+        block.grad(kind, x_hat, y_shard, temperature, row_sum, col_all[shard] if clip else None, grad_out, grad_scale,
+                   dx_acc, dy_out, rank * b, shard * b, workspace, **extra)
+
+    return _ring_backward_loop(block, x_hat, y_hat, group, rank, world, clip, grad_call)
+
+
+def ring_siglip_forward(block, x_hat, y_hat, logit_scale, logit_bias, group, rank, world):
+    """Sigmoid loss of the global batch: every block is independent (no row or column sums to finish)."""
+    b = x_hat.shape[0]
+    dev = x_hat.device
+    row_sum = torch.zeros(b, dtype=torch.float32, device=dev)
+    diag = torch.zeros(b, dtype=torch.float32, device=dev)
+    bufs = [y_hat, torch.empty_like(y_hat)] if world > 1 else [y_hat]
+    if world > 2:
+        bufs.append(torch.empty_like(y_hat))
+    cur = 0
+    for step in range(world):
+        shard = shard_at(rank, step, world)
+        reqs = []
+        if step + 1 < world:
+            nxt = 1 + (step % 2) if world > 2 else 1
+            reqs = _rotate(bufs[cur], bufs[nxt], group, rank, world)
+        block.siglip_sum(x_hat, bufs[cur], logit_scale, logit_bias, row_sum, diag, rank * b, shard * b)
+        for r in reqs:
+            r.wait()
+        if step + 1 < world:
+            cur = nxt
+    loss = block.siglip_local_loss(row_sum, diag, logit_scale, logit_bias, 1.0 / (b * world))
+    if world > 1:
+        dist.all_reduce(loss, op=dist.ReduceOp.SUM, group=group)
+    return loss
+
+
+def ring_siglip_backward(block, x_hat, y_hat, logit_scale, logit_bias, grad_out, grad_scale, group, rank, world,
+                         sums=None):
+    """Returns (dx, dy_own) fp32; sums (optional zeroed pair) receives {sum G S, sum G} over this rank's rows."""
+    b = x_hat.shape[0]
+
+    def grad_call(y_shard, shard, dx_acc, dy_out, workspace):
+        block.siglip_grad(x_hat, y_shard, logit_scale, logit_bias, grad_out, grad_scale, dx_acc, dy_out, rank * b,
+                          shard * b, workspace, sums)
+
+    return _ring_backward_loop(block, x_hat, y_hat, group, rank, world, True, grad_call)
+
+
 class RingContrastiveLossFn(torch.autograd.Function):
-    """apply(x_local, y_local, temperature, kind, stable, normalize, group, block_ops) -> global loss."""
+    """apply(x_local, y_local, temperature, kind, stable, normalize, group, block_ops, temperature_grad)
+    -> global loss.
+
+    A tensor temperature that requires grad receives a gradient (the reference has none, clip_loss.py:256):
+    temperature_grad "local" gives each rank the part of dL/dT that comes from its own rows, so the parts
+    of all ranks ADD UP to the global dL/dT - the same convention as the feature gradients, which are
+    d(global loss)/d(local features); "global" all-reduces, every rank gets the whole dL/dT."""
 
     @staticmethod
-    def forward(ctx, x, y, temperature, kind, stable, normalize, group, block):
+    def forward(ctx, x, y, temperature, kind, stable, normalize, group, block, temperature_grad="local"):
         assert x.shape == y.shape and x.dim() == 2
+        assert temperature_grad in ("local", "global")
+        t_is_tensor = isinstance(temperature, torch.Tensor)
+        ctx.ring_t = (temperature, temperature_grad) if t_is_tensor and temperature.requires_grad else None
+        temperature = float(temperature.detach().item()) if t_is_tensor else float(temperature)
+        assert temperature > 0.0, "temperature must be positive"
         world = dist.get_world_size(group) if dist.is_initialized() else 1
         rank = dist.get_rank(group) if dist.is_initialized() else 0
         block = block or CudaBlockOps()
@@ -219,27 +300,41 @@ class RingContrastiveLossFn(torch.autograd.Function):
         b = x_hat.shape[0]
         go = grad_output.detach().to(device=x_hat.device, dtype=torch.float32).reshape(1).contiguous()
         scale = ops.grad_scale(b * world, temperature, stable)
-        dx, dy = ring_backward(block, kind, x_hat, y_hat, temperature, row_sum, col_sum, go, scale, group, rank, world)
+        t_info = getattr(ctx, "ring_t", None)
+        sum_g_s = block.new_sum(x_hat.device) if t_info is not None else None
+        dx, dy = ring_backward(block, kind, x_hat, y_hat, temperature, row_sum, col_sum, go, scale, group, rank, world,
+                               sum_g_s=sum_g_s)
         dx = block.finish_grad(dx, x_hat, inv_x, x_dtype, d)
         if dy is not None:
             dy = block.finish_grad(dy, y_hat, inv_y, y_dtype, d)
-        return dx, dy, None, None, None, None, None, None
+        dt = None
+        if t_info is not None:
+            t_param, mode = t_info
+            if mode == "global" and world > 1:
+                dist.all_reduce(sum_g_s, op=dist.ReduceOp.SUM, group=group)
+            # sum_ij G_ij S_ij = g B dL/d(1/T) with g = grad_out * scale and B the global batch
+            dt = (sum_g_s[0] * (-1.0 / (scale * b * world * temperature * temperature))).reshape(t_param.shape)
+            dt = dt.to(t_param.dtype)
+        return dx, dy, dt, None, None, None, None, None, None
 
 
 class _RingLoss(nn.Module):
     _kind = _lib.CLIP
     _stable = False
 
-    def __init__(self, temperature=0.07, normalized_inputs=False, process_group=None, block_ops=None):
+    def __init__(self, temperature=0.07, normalized_inputs=False, process_group=None, block_ops=None,
+                 temperature_grad="local"):
         super().__init__()
-        self.temperature = temperature
+        self.temperature = temperature          # a float, or a 0-dim tensor / nn.Parameter to learn it
         self.normalized_inputs = normalized_inputs
         self.process_group = process_group
         self.block_ops = block_ops
+        self.temperature_grad = temperature_grad
 
     def forward(self, first_local, second_local):
         return RingContrastiveLossFn.apply(first_local, second_local, self.temperature, self._kind, self._stable,
-                                           not self.normalized_inputs, self.process_group, self.block_ops)
+                                           not self.normalized_inputs, self.process_group, self.block_ops,
+                                           self.temperature_grad)
 
 
 class RingMemoryEfficientCLIPLoss(_RingLoss):
@@ -260,3 +355,80 @@ class RingMemoryEfficientLiTLoss(_RingLoss):
 class RingStableMemoryEfficientLiTLoss(_RingLoss):
     _kind = _lib.LIT
     _stable = True
+
+
+class RingSigLIPLossFn(torch.autograd.Function):
+    """apply(x_local, y_local, logit_scale, logit_bias, normalize, group, block_ops, param_grad) -> global
+    sigmoid loss (1/B) sum_ij softplus(-z_ij (t <x_i, y_j> + b)) over the concatenated batch.
+
+    Gradients: d(global loss)/d(local features); for a tensor scale / bias, param_grad "local" returns the part
+    that comes from this rank's rows (the parts of all ranks add up to the global gradient), "global" all-reduces."""
+
+    @staticmethod
+    def forward(ctx, x, y, logit_scale, logit_bias, normalize, group, block, param_grad="local"):
+        assert x.shape == y.shape and x.dim() == 2
+        assert param_grad in ("local", "global")
+        world = dist.get_world_size(group) if dist.is_initialized() else 1
+        rank = dist.get_rank(group) if dist.is_initialized() else 0
+        block = block or CudaBlockOps()
+        x_hat, inv_x = block.prepare(x, normalize)
+        y_hat, inv_y = block.prepare(y, normalize)
+        t = float(logit_scale.detach().item()) if isinstance(logit_scale, torch.Tensor) else float(logit_scale)
+        bias = float(logit_bias.detach().item()) if isinstance(logit_bias, torch.Tensor) else float(logit_bias)
+        loss = ring_siglip_forward(block, x_hat, y_hat, t, bias, group, rank, world)
+        ctx.save_for_backward(*([x_hat, y_hat] + ([inv_x, inv_y] if normalize else [])))
+        ctx.ring = (t, bias, bool(normalize), x.dtype, y.dtype, x.shape[1], group, rank, world, block, param_grad,
+                    (logit_scale.shape, logit_scale.dtype) if isinstance(logit_scale, torch.Tensor) else None,
+                    (logit_bias.shape, logit_bias.dtype) if isinstance(logit_bias, torch.Tensor) else None)
+        return loss
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        t, bias, normalize, x_dtype, y_dtype, d, group, rank, world, block, param_grad, t_tensor, b_tensor = ctx.ring
+        saved = list(ctx.saved_tensors)
+        x_hat, y_hat = saved[:2]
+        inv_x, inv_y = saved[2:] if normalize else (None, None)
+        need = ctx.needs_input_grad
+        b = x_hat.shape[0]
+        go = grad_output.detach().to(device=x_hat.device, dtype=torch.float32).reshape(1).contiguous()
+        want_tb = bool(need[2] or need[3])
+        sums = block.new_sum(x_hat.device) if want_tb else None
+        dx, dy = ring_siglip_backward(block, x_hat, y_hat, t, bias, go, t / (b * world), group, rank, world, sums)
+        dx = block.finish_grad(dx, x_hat, inv_x, x_dtype, d)
+        dy = block.finish_grad(dy, y_hat, inv_y, y_dtype, d)
+        dt = db = None
+        if want_tb:
+            if param_grad == "global" and world > 1:
+                dist.all_reduce(sums, op=dist.ReduceOp.SUM, group=group)
+            # G = g (sigmoid(a) - I) with g = grad_out * t / B: grad_out * dL/dt = sum(G S) / t, dL/db = sum(G) / t
+            if need[2] and t_tensor is not None:
+                dt = (sums[0] / t).reshape(t_tensor[0]).to(t_tensor[1])
+            if need[3] and b_tensor is not None:
+                db = (sums[1] / t).reshape(b_tensor[0]).to(b_tensor[1])
+        return dx, dy, dt, db, None, None, None, None
+
+
+class RingMemoryEfficientSigLIPLoss(nn.Module):
+    """forward(image_features_local, text_features_local): sigmoid loss of the global batch, with
+    log_logit_scale and logit_bias as parameters (t = exp(log_logit_scale)) unless learnable=False."""
+
+    def __init__(self, init_logit_scale=10.0, init_logit_bias=-10.0, normalized_inputs=False, learnable=True,
+                 process_group=None, block_ops=None, param_grad="local"):
+        super().__init__()
+        import math
+        self.normalized_inputs = normalized_inputs
+        self.process_group = process_group
+        self.block_ops = block_ops
+        self.param_grad = param_grad
+        ls = torch.tensor(math.log(init_logit_scale), dtype=torch.float32)
+        lb = torch.tensor(float(init_logit_bias), dtype=torch.float32)
+        if learnable:
+            self.log_logit_scale = nn.Parameter(ls)
+            self.logit_bias = nn.Parameter(lb)
+        else:
+            self.register_buffer("log_logit_scale", ls)
+            self.register_buffer("logit_bias", lb)
+
+    def forward(self, first_local, second_local):
+        return RingSigLIPLossFn.apply(first_local, second_local, self.log_logit_scale.exp(), self.logit_bias,
+                                      not self.normalized_inputs, self.process_group, self.block_ops, self.param_grad)

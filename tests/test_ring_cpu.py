@@ -38,7 +38,11 @@ class OracleBlockOps:
             term = 0.5 * (term + torch.log(col_sum.double()))
         return ((term - (diag.double() - 1.0) / t).sum() * scale).float()
 
-    def grad(self, kind, x_hat, y_hat, t, row_sum, col_sum, go, scale, dx_acc, dy_out, row_off, col_off, workspace):
+    def new_sum(self, device):
+        return torch.zeros(2, dtype=torch.float64)
+
+    def grad(self, kind, x_hat, y_hat, t, row_sum, col_sum, go, scale, dx_acc, dy_out, row_off, col_off, workspace,
+             sum_g_s=None):
         e, _, _ = dense.sum_exp(x_hat.numpy(), y_hat.numpy(), t)
         e = torch.from_numpy(e)
         g = float(go) * scale
@@ -48,12 +52,37 @@ class OracleBlockOps:
             coef = e / row_sum.double()[:, None] * g
         if row_off == col_off:
             coef -= torch.eye(e.shape[0], dtype=torch.float64) * g
+        if sum_g_s is not None:
+            sum_g_s[0] += (coef * (x_hat @ y_hat.t())).sum()
         dx_acc += (coef @ y_hat).to(dx_acc.dtype)
         if dy_out is not None:
             dy_out.copy_((coef.t() @ x_hat).to(dy_out.dtype))
 
     def workspace(self, rows, cols, d, device):
         return None
+
+    def _siglip_a_z(self, x_hat, y_hat, t, bias, row_off, col_off):
+        a = (x_hat @ y_hat.t()) * t + bias
+        z = -torch.ones_like(a)
+        if row_off == col_off:
+            z += 2.0 * torch.eye(a.shape[0], dtype=a.dtype)
+        return a, z
+
+    def siglip_sum(self, x_hat, y_hat, t, bias, row_sum, diag, row_off, col_off):
+        a, z = self._siglip_a_z(x_hat, y_hat, t, bias, row_off, col_off)
+        row_sum += (torch.nn.functional.softplus(-z * a).sum(dim=1) / np.log(2.0)).to(row_sum.dtype)
+
+    def siglip_local_loss(self, row_sum, diag, t, bias, scale):
+        return (row_sum.double().sum() * np.log(2.0) * scale).float()
+
+    def siglip_grad(self, x_hat, y_hat, t, bias, go, scale, dx_acc, dy_out, row_off, col_off, workspace, sums):
+        a, z = self._siglip_a_z(x_hat, y_hat, t, bias, row_off, col_off)
+        coef = (torch.sigmoid(a) - (z + 1.0) / 2.0) * (float(go) * scale)
+        if sums is not None:
+            sums[0] += (coef * (x_hat @ y_hat.t())).sum()
+            sums[1] += coef.sum()
+        dx_acc += (coef @ y_hat).to(dx_acc.dtype)
+        dy_out.copy_((coef.t() @ x_hat).to(dy_out.dtype))
 
     def accumulate(self, dst, src):
         dst += src
@@ -128,6 +157,93 @@ def test_ring_equals_global_dense(world, kind_name, normalize, stable):
             np.testing.assert_allclose(res[r][2], gy[r * b:(r + 1) * b].numpy(), rtol=1e-4, atol=1e-7)
         else:
             assert res[r][2] is None
+
+
+def _worker_t(rank, world, port, kind_name, stable, mode, out):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from memoryefficientclip_b200 import ring
+        b, d = 20, 12
+        g = torch.Generator().manual_seed(3)
+        x = torch.randn(world * b, d, generator=g, dtype=torch.float64)
+        y = torch.randn(world * b, d, generator=g, dtype=torch.float64)
+        xl = x[rank * b:(rank + 1) * b].clone().requires_grad_(True)
+        yl = y[rank * b:(rank + 1) * b].clone().requires_grad_(True)
+        t = torch.nn.Parameter(torch.tensor(0.2, dtype=torch.float64))
+        cls = {("clip", False): ring.RingMemoryEfficientCLIPLoss, ("clip", True): ring.RingStableMemoryEfficientCLIPLoss,
+               ("lit", False): ring.RingMemoryEfficientLiTLoss}[(kind_name, stable)]
+        mod = cls(t, False, None, OracleBlockOps(), temperature_grad=mode)
+        assert list(mod.parameters()) == [t]
+        (mod(xl, yl) * 1.5).backward()
+        out[rank] = (float(t.grad), x.numpy(), y.numpy())
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("kind_name,stable,mode", [("clip", False, "local"), ("clip", True, "global"), ("lit", False, "local")])
+def test_ring_temperature_gradient(kind_name, stable, mode):
+    """A tensor temperature gets dL/dT: per-rank parts that add up to it ("local"), or all of it on every rank."""
+    world = 2
+    port = _free_port()
+    with mp.Manager() as mgr:
+        out = mgr.dict()
+        mp.spawn(_worker_t, args=(world, port, kind_name, stable, mode, out), nprocs=world, join=True)
+        res = dict(out)
+    x, y = torch.from_numpy(res[0][1]), torch.from_numpy(res[0][2])
+    want = 1.5 * dense.temperature_grad_dense(x, y, 0.2, kind_name, False)   # Stable rescales feature gradients only
+    if mode == "local":
+        assert abs(sum(res[r][0] for r in range(world)) - want) < 1e-6 * max(1.0, abs(want))   # the ring keeps its sums in fp32
+        assert abs(res[0][0] - res[1][0]) > 0            # the parts are different numbers
+    else:
+        for r in range(world):
+            assert abs(res[r][0] - want) < 1e-6 * max(1.0, abs(want))   # the ring keeps its sums in fp32
+
+
+def _worker_sig(rank, world, port, mode, out):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from memoryefficientclip_b200 import ring
+        b, d = 16, 12
+        g = torch.Generator().manual_seed(5)
+        x = torch.randn(world * b, d, generator=g, dtype=torch.float64)
+        y = torch.randn(world * b, d, generator=g, dtype=torch.float64)
+        xl = x[rank * b:(rank + 1) * b].clone().requires_grad_(True)
+        yl = y[rank * b:(rank + 1) * b].clone().requires_grad_(True)
+        mod = ring.RingMemoryEfficientSigLIPLoss(5.0, -3.0, False, True, None, OracleBlockOps(), mode).double()
+        loss = mod(xl, yl)
+        loss.backward()
+        out[rank] = (float(loss.detach()), xl.grad.numpy().copy(), yl.grad.numpy().copy(),
+                     float(mod.log_logit_scale.grad), float(mod.logit_bias.grad), x.numpy(), y.numpy())
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world,mode", [(2, "local"), (3, "global")])
+def test_ring_siglip_equals_global_dense(world, mode):
+    port = _free_port()
+    with mp.Manager() as mgr:
+        out = mgr.dict()
+        mp.spawn(_worker_sig, args=(world, port, mode, out), nprocs=world, join=True)
+        res = dict(out)
+    b = 16
+    x, y = torch.from_numpy(res[0][5]), torch.from_numpy(res[0][6])
+    loss, gx, gy, gt, gb = dense.siglip_dense(x, y, 5.0, -3.0, False)
+    g_log_t = float(gt) * 5.0                  # the module learns log t
+    for r in range(world):
+        assert abs(res[r][0] - float(loss)) < 1e-5 * abs(float(loss))
+        np.testing.assert_allclose(res[r][1], gx[r * b:(r + 1) * b].numpy(), rtol=1e-4, atol=1e-7)
+        np.testing.assert_allclose(res[r][2], gy[r * b:(r + 1) * b].numpy(), rtol=1e-4, atol=1e-7)
+    if mode == "local":
+        assert abs(sum(res[r][3] for r in range(world)) - g_log_t) < 1e-5 * abs(g_log_t)
+        assert abs(sum(res[r][4] for r in range(world)) - float(gb)) < 1e-5 * abs(float(gb))
+    else:
+        for r in range(world):
+            assert abs(res[r][3] - g_log_t) < 1e-5 * abs(g_log_t)
+            assert abs(res[r][4] - float(gb)) < 1e-5 * abs(float(gb))
 
 
 def test_shard_schedule():

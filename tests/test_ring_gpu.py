@@ -129,6 +129,97 @@ def test_ring_two_gpus_large_against_streaming_oracle():
         assert max_rel <= dense.GRAD_MAX_REL and cos >= dense.GRAD_COS_MIN, (max_rel, cos)
 
 
+def _temperature_worker(rank, world, port, mode, outdir):
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        from memoryefficientclip_b200 import ring
+        b_global, d = 768, 96
+        g = torch.Generator().manual_seed(4)
+        x = torch.randn(b_global, d, generator=g)
+        y = torch.randn(b_global, d, generator=g)
+        b = b_global // world
+        xl = x[rank * b:(rank + 1) * b].cuda().requires_grad_(True)
+        yl = y[rank * b:(rank + 1) * b].cuda().requires_grad_(True)
+        t = torch.nn.Parameter(torch.tensor(0.1, device="cuda"))
+        loss = ring.RingMemoryEfficientCLIPLoss(t, False, temperature_grad=mode)(xl, yl)
+        loss.backward()
+        torch.cuda.synchronize()
+        torch.save({"dt": t.grad.item()}, os.path.join(outdir, f"r{rank}.pt"))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("mode", ["local", "global"])
+def test_ring_two_gpus_temperature_gradient(mode):
+    world = 2
+    if torch.cuda.device_count() < world:
+        pytest.skip("needs 2 GPUs")
+    with tempfile.TemporaryDirectory() as outdir:
+        mp.spawn(_temperature_worker, args=(world, _free_port(), mode, outdir), nprocs=world, join=True)
+        res = [torch.load(os.path.join(outdir, f"r{r}.pt"))["dt"] for r in range(world)]
+    g = torch.Generator().manual_seed(4)
+    x = torch.randn(768, 96, generator=g)
+    y = torch.randn(768, 96, generator=g)
+    want = dense.temperature_grad_dense(x, y, 0.1, "clip", False)
+    got = [sum(res)] if mode == "local" else res
+    for v in got:
+        assert abs(v - want) <= 1e-2 * abs(want), (v, want)
+
+
+def _siglip_inputs(b_global, d):
+    g = torch.Generator().manual_seed(17)
+    img = torch.randn(b_global, d, generator=g)
+    txt = img + 0.7 * torch.randn(b_global, d, generator=g)
+    return img.bfloat16(), txt.bfloat16()
+
+
+def _siglip_worker(rank, world, port, outdir):
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        from memoryefficientclip_b200 import ring
+        b_global, d = 1024, 256
+        img, txt = _siglip_inputs(b_global, d)
+        b = b_global // world
+        xl = img[rank * b:(rank + 1) * b].cuda().requires_grad_(True)
+        yl = txt[rank * b:(rank + 1) * b].cuda().requires_grad_(True)
+        mod = ring.RingMemoryEfficientSigLIPLoss(10.0, -10.0, False, param_grad="global").cuda()
+        loss = mod(xl, yl)
+        loss.backward()
+        torch.cuda.synchronize()
+        torch.save({"loss": loss.item(), "dx": xl.grad.float().cpu(), "dy": yl.grad.float().cpu(),
+                    "dlogt": mod.log_logit_scale.grad.item(), "db": mod.logit_bias.grad.item()},
+                   os.path.join(outdir, f"r{rank}.pt"))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_ring_two_gpus_siglip():
+    """The sigmoid loss over the ring: every block is independent; text-gradient partials go to their owners."""
+    world = 2
+    if torch.cuda.device_count() < world:
+        pytest.skip("needs 2 GPUs")
+    with tempfile.TemporaryDirectory() as outdir:
+        mp.spawn(_siglip_worker, args=(world, _free_port(), outdir), nprocs=world, join=True)
+        res = [torch.load(os.path.join(outdir, f"r{r}.pt")) for r in range(world)]
+    img, txt = _siglip_inputs(1024, 256)
+    rl, rx, ry, rt, rb = dense.siglip_dense(img, txt, 10.0, -10.0, False)
+    dx = torch.cat([r["dx"] for r in res])
+    dy = torch.cat([r["dy"] for r in res])
+    for r in res:
+        assert dense.loss_rel_err(r["loss"], rl) <= dense.LOSS_RTOL
+        assert abs(r["dlogt"] / 10.0 - rt) <= 1e-2 * max(abs(rt), 1e-6), (r["dlogt"] / 10.0, rt)
+        assert abs(r["db"] - rb) <= 1e-2 * max(abs(rb), 1e-6), (r["db"], rb)
+    dense.assert_parity(res[0]["loss"], rl, (dx, dy), (rx, ry), "ring2 siglip")
+
+
 def test_ring_four_gpus():
     _run(4, "clip", 2048, 128, "bfloat16", False)
 
