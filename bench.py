@@ -192,6 +192,8 @@ def run_ours(args):
     first, second = synth.make(name, b_global, row_start=rank * b_local, rows=b_local)
     host_a = first.pin_memory()
     host_b = second.pin_memory()
+    n_probe = min(4096, b_local)
+    diag_cos = float(torch.nn.functional.cosine_similarity(first[:n_probe].float(), second[:n_probe].float(), dim=1).mean())
     if world == 1:
         module = MemoryEfficientCLIPLoss(temperature, normalized_inputs)
     else:
@@ -211,18 +213,23 @@ def run_ours(args):
         if sampler:
             sampler.start()
         launches0 = lib.meclip_launch_count()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(steps):
+        # one event before the first step and one after every step: the first and the last bracket exactly the
+        # K steps (the reported time), the ones between give the per-step spread
+        marks = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
+        marks[0].record()
+        for i in range(steps):
             run_step()
-        e1.record()
+            marks[i + 1].record()
         sync_all()
         launches = lib.meclip_launch_count() - launches0
         clocks = sampler.stop() if sampler else None
-        ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+        per_step = [marks[i].elapsed_time(marks[i + 1]) for i in range(steps)]
+        ms = torch.tensor([marks[0].elapsed_time(marks[steps])] + per_step, device=dev)
         if world > 1:
             dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-        return ms.item() / steps, launches, clocks
+        ms = ms.tolist()
+        spread = {"median": statistics.median(ms[1:]), "min": min(ms[1:]), "max": max(ms[1:])}
+        return ms[0] / steps, launches, clocks, spread
 
     # ---- device-resident inputs (value) ---------------------------------------------------
     a_dev = host_a.to(dev).requires_grad_(True)
@@ -234,7 +241,7 @@ def run_ours(args):
         loss = module(a_dev, t_dev)
         loss.backward()
 
-    ms_value, launches, clocks = timed(step_resident, args.steps, args.warmup, sample_clocks=True)
+    ms_value, launches, clocks, spread = timed(step_resident, args.steps, args.warmup, sample_clocks=True)
 
     # ---- end to end: pinned host -> device, module, loss back to the host (e2e) ------------
     loss_host = torch.empty((), dtype=torch.float32).pin_memory()
@@ -270,7 +277,7 @@ def run_ours(args):
         free[cur].record(torch.cuda.current_stream(dev))
         loss_host.copy_(loss.detach(), non_blocking=True)
 
-    ms_e2e, _, _ = timed(step_e2e, max(2, args.steps // 2), 1)
+    ms_e2e, _, _, _ = timed(step_e2e, max(2, args.steps // 2), 1)
 
     # ---- per-kernel durations with CUDA events on the launch stream -----------------------
     # (the library runs its kernels one after the other while this timing is on; one untimed step first)
@@ -330,13 +337,16 @@ def run_ours(args):
 
     line = {
         "metric": "clip_fwd_bwd_tflops", "value": tflops, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": ms_value, "higher_is_better": True, "scaling": "strong",
+        "warmup": args.warmup, "ms_per_step": ms_value, "ms_per_step_spread": spread, "higher_is_better": True,
+        "scaling": "strong",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": name, "global_batch": b_global, "feature_dim": d, "temperature": temperature,
                    "normalized_inputs": normalized_inputs, "flop_convention": "8*B^2*D",
                    "parallelism": "single" if world == 1 else f"ring{world}",
                    "l2": "inputs and workspace larger than L2 (no flush needed)",
-                   "samples_per_s": b_global / (ms_value / 1e3)},
+                   "samples_per_s": b_global / (ms_value / 1e3),
+                   # mean cosine of the positive pairs of rank 0's rows: shows how the synthetic pairs were drawn
+                   "mean_diagonal_cosine": diag_cos},
         "roofline": roofline,
         "cpu_baseline": cpu,
         "e2e": {"value": flops / (ms_e2e / 1e3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms_e2e,
