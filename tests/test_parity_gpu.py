@@ -230,3 +230,33 @@ def test_lit_odd_feature_count_fp16():
     loss, dx = _run_lit(txt, img, 0.07, False)
     rl, rx = dense.lit_dense(txt, img, 0.07, False)
     dense.assert_parity(loss, rl, (dx,), (rx,), "lit fp16 d=50")
+
+
+@pytest.mark.parametrize("b,d", [(1, 8), (2, 16), (3, 5), (127, 24), (129, 40), (257, 8)])
+def test_tiny_and_ragged_batches(b, d):
+    """One row, fewer rows than a warp, one more or one less than a tile: every B >= 1 is exact here (the
+    reference sums its padding columns in unless B is a multiple of 128, clip_loss.py:40-56)."""
+    # normalised inputs already rounded to bf16: with so few rows and features nothing averages the operand
+    # rounding out, so the kernels and the oracle are given the same representable values
+    x, y = _inputs(b, d, 12, True, torch.bfloat16)
+    x, y = x.float(), y.float()
+    loss, dx, dy = _run_clip(x, y, 0.07, True)
+    rl, rx, ry = dense.clip_dense(x, y, 0.07, True)
+    if b == 1:          # a single pair: the loss is exactly 0 and so are the gradients
+        assert abs(loss) <= 1e-5 and float(dx.abs().max()) <= 1e-5 and float(dy.abs().max()) <= 1e-5
+        return
+    dense.assert_parity(loss, rl, (dx, dy), (rx, ry), f"clip b={b} d={d}")
+    tl, tx = _run_lit(x, y, 0.07, True)
+    ll, lx = dense.lit_dense(x, y, 0.07, True)
+    dense.assert_parity(tl, ll, (tx,), (lx,), f"lit b={b} d={d}")
+
+
+def test_empty_and_mismatched_inputs_are_rejected():
+    m = _mods()
+    mod = m.MemoryEfficientCLIPLoss(0.07, False)
+    with pytest.raises(AssertionError):
+        mod(torch.empty(0, 16, device="cuda"), torch.empty(0, 16, device="cuda"))
+    with pytest.raises(AssertionError):
+        mod(torch.randn(8, 16, device="cuda"), torch.randn(8, 24, device="cuda"))      # reference clip_loss.py:167
+    with pytest.raises(AssertionError):
+        mod(torch.randn(8, 16), torch.randn(8, 16))                                        # reference clip_loss.py:166
