@@ -528,21 +528,26 @@ static int launch_pair_t(const CUtensorMap& ta, const CUtensorMap& tb, const CUt
     }
     const int cap = (dev >= 0 && dev < 64) ? max_clusters[dev] : sm_count() / 2;
     const int tiles = p.num_m_tiles * p.num_n_tiles;
-    const int clusters = tiles < cap ? tiles : cap;
+    const int units = (tiles + p.strip_len - 1) / p.strip_len;
+    const int clusters = units < cap ? units : cap;
     ScopedTiming timing(stream, t_tag, 2.0 * p.m * p.n * p.k);
     kern<<<2 * clusters, GEMM_THREADS, smem_bytes, stream>>>(ta, tb, tc, p);
     MECLIP_CUDA(cudaGetLastError());
     return MECLIP_OK;
 }
 
-// MECLIP_PAIR: 0 = single-CTA kernels only (default), 1 = CTA pairs wherever B is K-major,
-// 2 = CTA pairs for the two contractions when their tile is 256 wide.  Measured: mode 2 raises
-// the isolated contraction kernels by 5-15 % at D = 768 / 1024 but leaves the power-capped step
-// time unchanged (25.0 vs 25.1 ms, 8.03 vs 8.07 ms), so the simpler kernels stay the default.
+// MECLIP_PAIR: unset = auto (below), 0 = single-CTA kernels only, 1 = CTA pairs (256 x bn tiles, cta_group::2)
+// wherever B is K-major, 2 = CTA pairs for the two contractions only.  A pair stages 32 KiB per CTA and K-step
+// instead of 48 KiB, so six stages fit instead of four, but every tile pays a few cross-CTA round trips.
+// Measured on the power-capped step at B = 32768 (ms, modes 0 / 1 / 2, same GPU and call): D = 256 2.96 / 3.14 /
+// 2.81, D = 512 4.33 / 4.55 / 4.30, D = 640 5.51 / 5.59 / 5.35, D = 768 6.12 / 6.06 / 6.06, D = 1152 9.25 / 8.59 /
+// 8.94.  Auto: the contractions (K = panel width, thousands) always run as pairs; the sums and coefficient
+// passes (K = D) do from PAIR_MIN_K on.
+static constexpr long long PAIR_MIN_K = 800;
 static int pair_mode() {
     static const int mode = []() {
         const char* v = std::getenv("MECLIP_PAIR");
-        if (v == nullptr || v[0] == '\0') return 0;
+        if (v == nullptr || v[0] == '\0') return -1;      // auto
         return std::atoi(v);
     }();
     return mode;
@@ -571,8 +576,9 @@ static int launch_gemm(int epi, const Operand& a, const Operand& b, long long m,
     if (rc) return rc;
     // CTA pairs (256 x bn tiles) whenever B is K-major; the single-CTA kernel keeps MN-major B
     const int pmode = pair_mode();
-    const bool pair = !b.mn_major && bn % 64 == 0 &&
-                      (pmode == 1 || (pmode == 2 && epi == EPI_OUT && bn == 256 && p.trace == nullptr && g_trace_buf == nullptr));
+    const bool pair = !b.mn_major && bn % 64 == 0 && g_trace_buf == nullptr &&      // the in-kernel trace is a single-CTA hook
+                      (pmode == 1 || ((pmode == 2 || pmode < 0) && epi == EPI_OUT && bn == 256) ||
+                       (pmode < 0 && epi != EPI_OUT && bn == 256 && k >= PAIR_MIN_K));
     if (b.mn_major) rc = make_tmap(&tb, b.ptr, n, k, b.ld, 64, BK);
     else            rc = make_tmap(&tb, b.ptr, k, n, b.ld, BK, pair ? bn / 2 : bn);
     if (rc) return rc;
@@ -622,8 +628,7 @@ static int launch_gemm(int epi, const Operand& a, const Operand& b, long long m,
     if (pair) {
         p.num_m_tiles = (int)((m + PAIR_BM - 1) / PAIR_BM);
         p.idesc = umma_idesc_bf16(PAIR_BM, bn, a.mn_major ? 1 : 0, 0);
-        p.bn_last = bn;
-        p.idesc_last = p.idesc;
+        p.idesc_last = p.bn_last < bn ? umma_idesc_bf16(PAIR_BM, p.bn_last, a.mn_major ? 1 : 0, 0) : p.idesc;
         p.stage_bytes = A_STAGE_BYTES + (bn / 2) * BK * 2;
         stages = (SMEM_LIMIT - 1024 - tail_bytes(epi)) / p.stage_bytes;
         if (stages > MAX_STAGES) stages = MAX_STAGES;

@@ -181,6 +181,40 @@ __device__ __forceinline__ uint32_t mapa_u32(uint32_t local_addr, uint32_t rank)
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_addr), "r"(rank));
     return r;
 }
+// 32-bit store into the shared memory of another CTA of the cluster (address from mapa_u32).
+__device__ __forceinline__ void st_cluster_u32(uint32_t cluster_addr, uint32_t v) {
+    asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
+}
+// try_wait whose acquire reaches cluster scope: pairs with mbar_arrive_cluster (release.cluster) of a thread
+// in the peer CTA, so that what that thread stored before arriving is visible after the wait.
+__device__ __forceinline__ uint32_t mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok;
+}
+// mbar_wait with the cluster-scope acquire (same bounds and abort rules).
+__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                                  bool watch_flag = true) {
+    if (mbar_try_wait_cluster(bar, parity)) return true;
+    const unsigned long long t0 = global_ns();
+    uint32_t spins = 0;
+    while (!mbar_try_wait_cluster(bar, parity)) {
+        if ((++spins & 255u) == 0u) {
+            if (watch_flag && *abort_flag) return false;
+            if (global_ns() - t0 > WAIT_LIMIT_NS) {
+                *abort_flag = 1;
+                return false;
+            }
+        }
+    }
+    return true;
+}
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }

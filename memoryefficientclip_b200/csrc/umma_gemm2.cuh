@@ -12,7 +12,11 @@
 //           epilogue warps tell the leader that an accumulator is free with a remote arrive
 // B is K-major here (the backward keeps transposed copies of X and Y); A is K-major or the
 // column-blocked coefficient panel read as G (K-major) or G^T (MN-major).
-// Tiles are dealt round-robin over the clusters.
+// Tiles come from the same atomic counter as in the single-CTA kernel (strips included): the leader's
+// scheduler lane fetches them and publishes each tile id into the ring of BOTH CTAs (a remote store followed by
+// a remote release-arrive; the peer waits with a cluster-scope acquire).  A ring slot is free again when the
+// consumers of both CTAs have arrived on the leader's `sched_empty` barrier (one arrive per warp).
+// The last column tile of an output kernel may be narrower (bn_last), as in the single-CTA kernel.
 #pragma once
 #include "umma_gemm.cuh"
 
@@ -37,7 +41,7 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
     const int lane = threadIdx.x & 31;
     const uint32_t rank = cluster_ctarank();          // 0 = leader of the pair
     const int num_tiles = p.num_m_tiles * p.num_n_tiles;
-    const int num_clusters = gridDim.x >> 1;
+    const int num_clusters = (int)(gridDim.x >> 1);
     const int cluster_id = blockIdx.x >> 1;
     const int num_stages = p.num_stages;
     const int half_bn = p.bn >> 1;
@@ -52,6 +56,11 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
         for (int a = 0; a < 2; ++a) {
             mbar_init(smem_u32(&tail->tmem_full_bar[a]), 1);
             mbar_init(smem_u32(&tail->tmem_empty_bar[a]), 2 * EPI_WARPS);  // epilogue warps of both CTAs (leader only)
+        }
+        for (int s = 0; s < SCHED_DEPTH; ++s) {
+            mbar_init(smem_u32(&tail->sched_full_bar[s]), 1);                   // the leader's scheduler arrives in both CTAs
+            // leader only: its MMA lane and epilogue warps, the peer's producer lane and epilogue warps
+            mbar_init(smem_u32(&tail->sched_empty_bar[s]), 2 + 2 * EPI_WARPS);
         }
         fence_barrier_init();
         tma_prefetch_desc(&tmap_a);
@@ -69,17 +78,41 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
     const uint32_t tmem_base = tail->tmem_base;
 
     if (warp == 0) {
-        // ------------------------------ TMA producer ------------------------------
+        // ---------------- tile scheduler (leader) + TMA producer (both CTAs) ----------------
         if (lane == 0) {
             const uint32_t tx_per_cta = (uint32_t)A_STAGE_BYTES + (uint32_t)half_bn * BK * 2;
-            int stage = 0;
-            uint32_t phase = 0;
+            int stage = 0, slot = 0;
+            uint32_t phase = 0, sphase = 0;
             bool ok = true;
-            for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
+            // leader only: strips of consecutive tile ids, the next strip requested when one starts
+            const int strip = p.strip_len;
+            int unit = cluster_id;
+            int next_tile = unit * strip;
+            int left = strip;
+            unsigned int next_unit = 0;
+            while (ok) {
+                int tile;
+                if (rank == 0) {
+                    if (!mbar_wait_cluster(smem_u32(&tail->sched_empty_bar[slot]), sphase ^ 1u, abort_flag)) break;
+                    tile = next_tile < num_tiles ? next_tile : -1;
+                    tail->sched_tile[slot] = tile;
+                    st_cluster_u32(mapa_u32(smem_u32(&tail->sched_tile[slot]), 1), (uint32_t)tile);
+                    mbar_arrive(smem_u32(&tail->sched_full_bar[slot]));
+                    mbar_arrive_cluster(mapa_u32(smem_u32(&tail->sched_full_bar[slot]), 1));
+                    if (tile >= 0 && left == strip && p.tile_counter != nullptr)
+                        asm volatile("atom.global.add.u32 %0, [%1], 1;" : "=r"(next_unit) : "l"(p.tile_counter) : "memory");
+                } else {
+                    if (!mbar_wait_cluster(smem_u32(&tail->sched_full_bar[slot]), sphase, abort_flag)) break;
+                    tile = tail->sched_tile[slot];
+                    mbar_arrive_cluster(mapa_u32(smem_u32(&tail->sched_empty_bar[slot]), 0));
+                }
+                if (++slot == SCHED_DEPTH) { slot = 0; sphase ^= 1u; }
+                if (tile < 0) break;
                 int mt, nt;
                 tile_coords(p, tile, mt, nt);
-                const int m0 = mt * PAIR_BM + (int)rank * BM;         // this CTA's rows
-                const int n0 = nt * p.bn + (int)rank * half_bn;       // this CTA's share of the B rows
+                const int tile_bn = (nt == p.num_n_tiles - 1) ? p.bn_last : p.bn;
+                const int m0 = mt * PAIR_BM + (int)rank * BM;              // this CTA's rows
+                const int n0 = nt * p.bn + (int)rank * (tile_bn >> 1);      // this CTA's share of the B rows
                 for (int ks = 0; ks < p.k_steps; ++ks) {
                     if (!mbar_wait(smem_u32(&tail->empty_bar[stage]), phase ^ 1u, abort_flag)) { ok = false; break; }
                     const uint32_t full_local = smem_u32(&tail->full_bar[stage]);
@@ -101,8 +134,18 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
                     } else {
                         tma_load_2d_pair(sa, &tmap_a, full, k0, m0);
                     }
-                    tma_load_2d_pair(sb, &tmap_b, full, k0, n0);      // box = half_bn rows
+                    // the box always has half_bn rows; a narrower last tile uses the first tile_bn / 2 of them
+                    tma_load_2d_pair(sb, &tmap_b, full, k0, n0);
                     if (++stage == num_stages) { stage = 0; phase ^= 1u; }
+                }
+                if (rank == 0) {
+                    if (--left > 0 && next_tile + 1 < num_tiles) {
+                        ++next_tile;
+                    } else {
+                        unit = p.tile_counter != nullptr ? (int)next_unit + num_clusters : unit + num_clusters;
+                        next_tile = unit * strip;
+                        left = strip;
+                    }
                 }
             }
         }
@@ -110,15 +153,23 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
     } else if (warp == 1) {
         // ------------------------------ MMA issuer (leader CTA only) ---------------
         if (lane == 0 && rank == 0) {
-            int stage = 0;
-            uint32_t phase = 0;
+            int stage = 0, slot = 0;
+            uint32_t phase = 0, sphase = 0;
             int acc = 0;
             uint32_t acc_phase = 0;
             bool ok = true;
             constexpr uint32_t A_LBO = A_MN ? BK * 128 : 16, A_KSTEP = A_MN ? 2048 : 32;
-            for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
-                if (!mbar_wait(smem_u32(&tail->tmem_empty_bar[acc]), acc_phase ^ 1u, abort_flag)) break;
+            while (ok) {
+                if (!mbar_wait(smem_u32(&tail->sched_full_bar[slot]), sphase, abort_flag)) break;
+                const int tile = tail->sched_tile[slot];
+                mbar_arrive(smem_u32(&tail->sched_empty_bar[slot]));
+                if (++slot == SCHED_DEPTH) { slot = 0; sphase ^= 1u; }
+                if (tile < 0) break;
+                if (!mbar_wait_cluster(smem_u32(&tail->tmem_empty_bar[acc]), acc_phase ^ 1u, abort_flag)) break;
                 tc_fence_after();
+                int mt_, nt_;
+                tile_coords(p, tile, mt_, nt_);
+                const uint32_t idesc = (nt_ == p.num_n_tiles - 1) ? p.idesc_last : p.idesc;
                 const uint32_t tmem_d = tmem_base + (uint32_t)acc * MAX_BN;
                 for (int ks = 0; ks < p.k_steps; ++ks) {
                     if (!mbar_wait(smem_u32(&tail->full_bar[stage]), phase, abort_flag)) { ok = false; break; }
@@ -129,7 +180,7 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
                     for (int kk = 0; kk < BK / 16; ++kk) {
                         const uint64_t ad = umma_smem_desc(sa + kk * A_KSTEP, A_LBO, 1024);
                         const uint64_t bd = umma_smem_desc(sb + kk * 32, 16, 1024);
-                        umma_bf16_pair(tmem_d, ad, bd, p.idesc, (ks | kk) != 0 ? 1u : 0u);
+                        umma_bf16_pair(tmem_d, ad, bd, idesc, (ks | kk) != 0 ? 1u : 0u);
                     }
                     umma_commit_pair(smem_u32(&tail->empty_bar[stage]), 3);     // frees the stage in both CTAs
                     if (++stage == num_stages) { stage = 0; phase ^= 1u; }
@@ -144,20 +195,30 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
     } else {
         // ------------------------------ epilogue -----------------------------------
         const int q = warp & 3;
-        int acc = 0;
-        uint32_t acc_phase = 0;
+        int acc = 0, slot = 0;
+        uint32_t acc_phase = 0, sphase = 0;
         EpiState st;
         if (EPI == EPI_COEF) st.gscale = p.grad_out ? __ldg(p.grad_out) : 1.f;
-        for (int tile = cluster_id; tile < num_tiles; tile += num_clusters) {
+        const uint32_t sched_free0 = mapa_u32(smem_u32(&tail->sched_empty_bar[0]), 0);     // the leader's ring
+        while (true) {
+            // as in the single-CTA kernel the eight warps reach one verdict per wait and leave together
+            bool ok = mbar_wait_cluster(smem_u32(&tail->sched_full_bar[slot]), sphase, abort_flag, false);
+            const int tile = ok ? tail->sched_tile[slot] : -1;
+            __syncwarp();
+            if (ok && lane == 0) mbar_arrive_cluster(sched_free0 + (uint32_t)slot * 8u);
+            if (++slot == SCHED_DEPTH) { slot = 0; sphase ^= 1u; }
+            ok = named_bar_and(2, EPI_THREADS, ok);
+            if (!ok || tile < 0) break;
             int mt, nt;
             tile_coords(p, tile, mt, nt);
-            bool ok = mbar_wait(smem_u32(&tail->tmem_full_bar[acc]), acc_phase, abort_flag, false);
+            ok = mbar_wait(smem_u32(&tail->tmem_full_bar[acc]), acc_phase, abort_flag, false);
             ok = named_bar_and(2, EPI_THREADS, ok);
             if (!ok) break;
             tc_fence_after();
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)acc * MAX_BN;
             const uint32_t free_bar = mapa_u32(smem_u32(&tail->tmem_empty_bar[acc]), 0);   // the leader's barrier
-            epilogue_tile<EPI>(p, &tmap_c, tail, st, taddr, mt * PAIR_BM + (int)rank * BM, nt * p.bn, p.bn, warp, lane,
+            epilogue_tile<EPI>(p, &tmap_c, tail, st, taddr, mt * PAIR_BM + (int)rank * BM, nt * p.bn,
+                               (nt == p.num_n_tiles - 1) ? p.bn_last : p.bn, warp, lane,
                                [free_bar, lane]() {
                                    __syncwarp();
                                    if (lane == 0) mbar_arrive_cluster(free_bar);
