@@ -461,9 +461,13 @@ static int pick_bn(long long n) {
 // Column-tile width of a contraction (m rows, n columns).  Kernels that share the GPU (side streams,
 // dynamic tiles) fill each other's last wave, so there the widest tile wins; a kernel that runs alone
 // pays for a partly filled last wave, so there the width is chosen by waves x tile cost.
-static int pick_contraction_bn(long long m, long long n, bool shares_gpu) {
+static int pair_mode();
+static int pick_contraction_bn(long long m, long long n, bool shares_gpu, bool b_k_major) {
     if (n < 256) return pick_bn(n);
     if (shares_gpu) return 256;
+    // CTA pairs: 256-wide tiles even when alone (measured: a 192-wide pair tile loses more per column than the
+    // fuller last wave gains: dX 960 vs 1127 TFLOP/s, dY 915 vs 923 at B = 32768, D = 1152)
+    if (b_k_major && pair_mode() != 0) return 256;
     const int cand[2] = {256, 192};
     const double cost_per_col[2] = {1.0, 1.07};      // measured: a 192-wide tile costs ~7 % more per column
     int best = 256;
@@ -1122,7 +1126,7 @@ static int grad_impl(int kind, const void* x_bf16, const void* y_bf16, int64_t r
                 Operand a{gpanel[gb], plan.ldg / 64, true, plan.row_block}, b{X + r0 * ldx, ldx, true};
                 if (transposed_copies) b = Operand{xt + r0, plan.ld_xt, false};   // [d][K = rows] K-major
                 t_tag = TAG_DY;
-                rc = launch_gemm(EPI_OUT, a, b, nc, d, nr, pick_contraction_bn(nc, d, overlap), p, sy);
+                rc = launch_gemm(EPI_OUT, a, b, nc, d, nr, pick_contraction_bn(nc, d, overlap, transposed_copies), p, sy);
                 if (rc) return rc;
                 if (overlap) MECLIP_CUDA(cudaEventRecord(side->dy[gb], sy));
             }
@@ -1146,7 +1150,7 @@ static int grad_impl(int kind, const void* x_bf16, const void* y_bf16, int64_t r
                 Operand a{gpanel[gb], plan.ldg / 64, false, plan.row_block}, b{Y + c0 * ldy, ldy, true};
                 if (transposed_copies) b = Operand{yt + c0, plan.ld_yt, false};   // [d][K = cols] K-major
                 t_tag = TAG_DX;
-                rc = launch_gemm(EPI_OUT, a, b, nr, d, nc, pick_contraction_bn(nr, d, overlap), p, sx);
+                rc = launch_gemm(EPI_OUT, a, b, nr, d, nc, pick_contraction_bn(nr, d, overlap, transposed_copies), p, sx);
                 if (rc) return rc;
                 if (overlap) MECLIP_CUDA(cudaEventRecord(side->dx[gb], sx));
             }
