@@ -166,7 +166,8 @@ def run_ours(args):
     import torch.distributed as dist
     from memoryefficientclip_b200 import _lib, synth
     from memoryefficientclip_b200.clip_loss import MemoryEfficientCLIPLoss
-    from memoryefficientclip_b200.ring import RingMemoryEfficientCLIPLoss
+    from memoryefficientclip_b200.lit_loss import MemoryEfficientLiTLoss
+    from memoryefficientclip_b200.ring import RingMemoryEfficientCLIPLoss, RingMemoryEfficientLiTLoss
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -187,7 +188,7 @@ def run_ours(args):
     kind, b_global, d, dtype, temperature, normalized_inputs, _gen = synth.CONFIGS[name]
     if args.batch:
         b_global = args.batch
-    assert kind == "clip", "bench.py times the CLIP configurations"
+    lit = kind == "lit"        # LiT: forward(text, image), the image side is frozen, 6 B^2 D FLOPs
     b_local = b_global // world
     first, second = synth.make(name, b_global, row_start=rank * b_local, rows=b_local)
     host_a = first.pin_memory()
@@ -195,10 +196,10 @@ def run_ours(args):
     n_probe = min(4096, b_local)
     diag_cos = float(torch.nn.functional.cosine_similarity(first[:n_probe].float(), second[:n_probe].float(), dim=1).mean())
     if world == 1:
-        module = MemoryEfficientCLIPLoss(temperature, normalized_inputs)
+        module = (MemoryEfficientLiTLoss if lit else MemoryEfficientCLIPLoss)(temperature, normalized_inputs)
     else:
-        module = RingMemoryEfficientCLIPLoss(temperature, normalized_inputs)
-    flops = 8.0 * b_global * b_global * d
+        module = (RingMemoryEfficientLiTLoss if lit else RingMemoryEfficientCLIPLoss)(temperature, normalized_inputs)
+    flops = (6.0 if lit else 8.0) * b_global * b_global * d
 
     def sync_all():
         if world > 1:
@@ -233,7 +234,7 @@ def run_ours(args):
 
     # ---- device-resident inputs (value) ---------------------------------------------------
     a_dev = host_a.to(dev).requires_grad_(True)
-    t_dev = host_b.to(dev).requires_grad_(True)
+    t_dev = host_b.to(dev).requires_grad_(not lit)
 
     def step_resident():
         a_dev.grad = None
@@ -271,7 +272,7 @@ def run_ours(args):
         start_copy(1 - cur)                                 # one host -> device copy of a full batch per step
         torch.cuda.current_stream(dev).wait_event(ready[cur])
         a = dev_bufs[cur][0].detach().requires_grad_(True)
-        t = dev_bufs[cur][1].detach().requires_grad_(True)
+        t = dev_bufs[cur][1].detach().requires_grad_(not lit)
         loss = module(a, t)
         loss.backward()
         free[cur].record(torch.cuda.current_stream(dev))
@@ -334,14 +335,18 @@ def run_ours(args):
         val, sec, cores = cpu_dense_step_tflops(cb, cd, temperature, 2)
         cpu = {"value": val, "unit": "TFLOP/s", "cores": cores, "kind": "port", "seconds": sec,
                "sample": f"dense fp32 PyTorch CLIP fwd+bwd on host CPU at B={cb}, D={cd} (1/16 of the tile pairs), best of 2"}
+        # the smallest benchmark configuration (B = 4096, D = 512) fits the host as a whole: timed as well
+        v1, s1, _ = cpu_dense_step_tflops(4096, 512, 0.07, 2)
+        cpu["b4096_d512"] = {"value": v1, "unit": "TFLOP/s", "seconds": s1}
 
     line = {
-        "metric": "clip_fwd_bwd_tflops", "value": tflops, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+        "metric": "lit_fwd_bwd_tflops" if lit else "clip_fwd_bwd_tflops", "value": tflops, "unit": "TFLOP/s",
+        "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_value, "ms_per_step_spread": spread, "higher_is_better": True,
         "scaling": "strong",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": name, "global_batch": b_global, "feature_dim": d, "temperature": temperature,
-                   "normalized_inputs": normalized_inputs, "flop_convention": "8*B^2*D",
+                   "normalized_inputs": normalized_inputs, "flop_convention": "6*B^2*D" if lit else "8*B^2*D",
                    "parallelism": "single" if world == 1 else f"ring{world}",
                    "l2": "inputs and workspace larger than L2 (no flush needed)",
                    "samples_per_s": b_global / (ms_value / 1e3),
