@@ -351,7 +351,11 @@ def run_ours(args):
                    "l2": "inputs and workspace larger than L2 (no flush needed)",
                    "samples_per_s": b_global / (ms_value / 1e3),
                    # mean cosine of the positive pairs of rank 0's rows: shows how the synthetic pairs were drawn
-                   "mean_diagonal_cosine": diag_cos},
+                   "mean_diagonal_cosine": diag_cos,
+                   **({"executed_flops_per_step": 4.0 * b_global * b_global * (d + 8),
+                       "note": "LiT runs in one tile pass (forward contracts E with [Y | 1], backward is a row kernel): "
+                               "4*B^2*(D+8) FLOPs are executed for the 6*B^2*D of the two-pass formulation that the "
+                               "metric counts"} if lit and world == 1 else {})},
         "roofline": roofline,
         "cpu_baseline": cpu,
         "e2e": {"value": flops / (ms_e2e / 1e3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms_e2e,

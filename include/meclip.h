@@ -193,6 +193,30 @@ int meclip_grad_t(int kind, const void* x_bf16, const void* y_bf16, int64_t rows
                   int* status, void* stream);
 
 /*
+ * LiT with the backward's contraction done in the forward.  The LiT coefficients separate,
+ * G_ij = g E_ij / r_i - g [i == j], so dX = g (diag(1/r) E Y - Y): one pass that forms E panel by panel
+ * and contracts it with [Y | 1] yields U = [E Y | r | 0...] and the whole step costs 4 B^2 D FLOPs
+ * instead of the reference's 6 B^2 D (sum kernel lit_loss.py:9-62 + recomputing gradient kernel
+ * lit_loss.py:65-148); the backward proper is a row kernel.
+ *   meclip_lit_extend          y[i][d] = 1, y[i][d+1..d+7] = 0 in a bf16 matrix with ld >= d + 8
+ *   meclip_lit_fused_forward   u [rows x (d+8)] fp32 (=|+=) E [Y_ext]; block offsets as in meclip_grad;
+ *                              workspace of meclip_grad_workspace_bytes(rows, cols, d + 8)
+ *   meclip_lit_fused_stats     row_sum[i] = u[i][d], diag_s[i] = <x_i, y_i> (feeds meclip_loss_finalize)
+ *   meclip_lit_fused_backward  dx[i][0..d) = g (u[i][:] / row_sum[i] - y[i][:]), g = grad_scale * (*grad_out)
+ * Used by the single-GPU LiT modules when the first input needs a gradient and the temperature is a
+ * constant; the two-pass entry points above remain for everything else.
+ */
+int meclip_lit_extend(void* y_bf16, int64_t rows, int64_t d, int64_t ldy, void* stream);
+int meclip_lit_fused_forward(const void* x_bf16, const void* y_ext_bf16, int64_t rows, int64_t cols, int64_t d, int64_t ldx,
+                             int64_t ldy, float temperature, int64_t row_off, int64_t col_off, float* u, int u_mode,
+                             int64_t ldu, void* workspace, size_t workspace_bytes, int* status, void* stream);
+int meclip_lit_fused_stats(const void* x_bf16, int64_t ldx, const void* y_ext_bf16, int64_t ldy, const float* u, int64_t ldu,
+                           int64_t rows, int64_t d, float* row_sum, float* diag_s, void* stream);
+int meclip_lit_fused_backward(const float* u, int64_t ldu, const void* y_ext_bf16, int64_t ldy, const float* row_sum,
+                              const float* grad_out, float grad_scale, int64_t rows, int64_t d, void* dx, int dx_dtype,
+                              int64_t lddx, void* stream);
+
+/*
  * Sigmoid (SigLIP) pairwise loss on the same tile engine; the reference has no such loss.
  *   a_ij = logit_scale * S_ij + logit_bias,   loss = (1/B) sum_ij softplus(-z_ij a_ij),  z_ii = 1, z_ij = -1
  * meclip_siglip_sum:   row_sum[i] += sum_j softplus(-z_ij a_ij) / ln2 over the block (fp32 atomics, zero first),

@@ -9,7 +9,12 @@ from __future__ import annotations
 
 import torch
 
+import os
+
 from . import _lib, ops
+
+# MECLIP_LIT_FUSED=0 keeps LiT on the two-pass path (sums, then recomputing backward) for A/B measurements
+_LIT_FUSED = os.environ.get("MECLIP_LIT_FUSED", "1") != "0"
 
 
 class ContrastiveLossFn(torch.autograd.Function):
@@ -22,17 +27,31 @@ class ContrastiveLossFn(torch.autograd.Function):
         ops._check_matrix(x, "first input")
         ops._check_matrix(y, "second input")
         assert x.device == y.device
+        # A tensor temperature (e.g. an nn.Parameter) is read on the host once per forward; it then
+        # also receives a gradient, which the reference does not provide (clip_loss.py:256).
+        t_is_tensor = isinstance(temperature, torch.Tensor)
+        temperature_value = float(temperature.detach().item()) if t_is_tensor else float(temperature)
+        assert temperature_value > 0.0, "temperature must be positive"
+        learn_t = t_is_tensor and temperature.requires_grad
+        # LiT's coefficients separate (G_ij = g E_ij / r_i - g [i == j]), so when the first input needs a gradient the
+        # forward also contracts E with [Y | 1] and the backward is a row kernel: 4 B^2 D FLOPs instead of 6 B^2 D
+        if kind == _lib.LIT and _LIT_FUSED and ctx.needs_input_grad[0] and not learn_t:
+            x_hat, inv_x = ops.normalize_fwd(x, True) if normalize else (ops.as_operand(x), None)
+            y_ext, _inv_y = ops.normalize_fwd(y, normalize, extra_cols=8)
+            d_pad = x_hat.shape[1]
+            loss, u, row_sum = ops.lit_fused_forward(x_hat, y_ext, d_pad, temperature_value)
+            ctx.save_for_backward(*([u, y_ext, row_sum] + ([x_hat, inv_x] if normalize else [])))
+            ctx.meclip = (temperature_value, kind, bool(stable), bool(normalize), x.dtype, y.dtype, x.shape[1])
+            ctx.meclip_t = None
+            ctx.meclip_fused = True
+            return loss
+        ctx.meclip_fused = False
         if normalize:
             x_hat, inv_x = ops.normalize_fwd(x, True)
             y_hat, inv_y = ops.normalize_fwd(y, True)
         else:
             x_hat, inv_x = ops.as_operand(x), None
             y_hat, inv_y = ops.as_operand(y), None
-        # A tensor temperature (e.g. an nn.Parameter) is read on the host once per forward; it then
-        # also receives a gradient, which the reference does not provide (clip_loss.py:256).
-        t_is_tensor = isinstance(temperature, torch.Tensor)
-        temperature_value = float(temperature.detach().item()) if t_is_tensor else float(temperature)
-        assert temperature_value > 0.0, "temperature must be positive"
         loss, row_sum, col_sum, _diag = ops.loss_forward(kind, x_hat, y_hat, temperature_value)
         saved = [x_hat, y_hat, row_sum]
         if col_sum is not None:
@@ -48,6 +67,16 @@ class ContrastiveLossFn(torch.autograd.Function):
     def run_backward(ctx, grad_output):
         temperature, kind, stable, normalize, x_dtype, y_dtype, d = ctx.meclip
         saved = list(ctx.saved_tensors)
+        if getattr(ctx, "meclip_fused", False):
+            u, y_ext, row_sum = saved[:3]
+            go = grad_output.detach().to(device=u.device, dtype=torch.float32).reshape(1).contiguous()
+            scale = ops.grad_scale(u.shape[0], temperature, stable)
+            ctx.meclip_dt = None
+            if normalize:
+                x_hat, inv_x = saved[3:]
+                g32 = ops.lit_fused_backward(u, y_ext, row_sum, go, scale, x_hat.shape[1], torch.float32)
+                return ops.normalize_bwd(g32, x_hat, inv_x, x_dtype, d), None
+            return ops.lit_fused_backward(u, y_ext, row_sum, go, scale, d, x_dtype), None
         x_hat, y_hat, row_sum = saved[:3]
         rest = saved[3:]
         col_sum = rest.pop(0) if kind == _lib.CLIP else None

@@ -46,6 +46,13 @@ SIGNATURES = {
     "meclip_grad_t": (c_int, [c_int, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64, c_float, c_int64,
                               c_int64, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_int, c_int64, c_void_p,
                               c_int, c_int64, c_void_p, c_void_p, c_size_t, c_void_p, c_void_p]),
+    "meclip_lit_extend": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_void_p]),
+    "meclip_lit_fused_forward": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64, c_float, c_int64,
+                                         c_int64, c_void_p, c_int, c_int64, c_void_p, c_size_t, c_void_p, c_void_p]),
+    "meclip_lit_fused_stats": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int64, c_int64, c_void_p,
+                                       c_void_p, c_void_p]),
+    "meclip_lit_fused_backward": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_float, c_int64, c_int64,
+                                          c_void_p, c_int, c_int64, c_void_p]),
     "meclip_siglip_sum": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64, c_float, c_float,
                                   c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "meclip_siglip_loss_finalize": (c_int, [c_void_p, c_void_p, c_int64, c_float, c_float, c_float, c_int, c_void_p,

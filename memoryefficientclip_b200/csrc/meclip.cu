@@ -232,6 +232,68 @@ normalize_bwd_kernel(const TG* __restrict__ g, long long ldg, const __nv_bfloat1
     }
 }
 
+// ---- LiT in one tile pass (its coefficients separate: G_ij = g E_ij / r_i - g [i == j]) -----------------
+// y[row][col] = 1, y[row][col+1 .. col+7] = 0: the ones column that makes the contraction E [Y | 1] also
+// produce the row sums of E.
+__global__ void __launch_bounds__(256)
+ones_column_kernel(__nv_bfloat16* __restrict__ y, long long rows, long long col, long long ld) {
+    const long long r = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (r >= rows) return;
+    uint4 v = make_uint4(0x00003F80u, 0u, 0u, 0u);       // bf16 1.0 in the low half, seven zeros
+    *reinterpret_cast<uint4*>(y + r * ld + col) = v;
+}
+
+// row_sum[i] = U[i][d] (the ones column), diag[i] = <x_i, y_i>: what the loss needs besides U.
+__global__ void __launch_bounds__(ROW_KERNEL_THREADS)
+lit_fused_stats_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const __nv_bfloat16* __restrict__ y, long long ldy,
+                       const float* __restrict__ u, long long ldu, long long rows, int d, float* __restrict__ row_sum,
+                       float* __restrict__ diag) {
+    const long long row = (long long)blockIdx.x * (ROW_KERNEL_THREADS / 32) + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (row >= rows) return;
+    float dot = 0.f;
+    for (int c = lane * 8; c < d; c += 256) {
+        float a[8], b[8];
+        load8(x + row * ldx + c, a);
+        load8(y + row * ldy + c, b);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) dot = fmaf(a[i], b[i], dot);
+    }
+    dot = warp_sum(dot);
+    if (lane == 0) {
+        diag[row] = dot;
+        row_sum[row] = u[row * ldu + d];
+    }
+}
+
+// dx[i][:] = g (U[i][:] / r_i - y[i][:]) over the first d columns, g = grad_scale * (*grad_out).
+template <typename TOut>
+__global__ void __launch_bounds__(ROW_KERNEL_THREADS)
+lit_fused_bwd_kernel(const float* __restrict__ u, long long ldu, const __nv_bfloat16* __restrict__ y, long long ldy,
+                     const float* __restrict__ row_sum, const float* __restrict__ grad_out, float grad_scale, long long rows,
+                     int d, int vec_out, TOut* __restrict__ dx, long long lddx) {
+    const long long row = (long long)blockIdx.x * (ROW_KERNEL_THREADS / 32) + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (row >= rows) return;
+    const float g = grad_scale * (grad_out != nullptr ? __ldg(grad_out) : 1.f);
+    const float gr = g / __ldg(row_sum + row);
+    const float* ur = u + row * ldu;
+    const __nv_bfloat16* yr = y + row * ldy;
+    TOut* orow = dx + row * lddx;
+    if (vec_out) {
+        for (int c = lane * 8; c < d; c += 256) {
+            float uv[8], yv[8];
+            load8(ur + c, uv);
+            load8(yr + c, yv);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) uv[i] = fmaf(uv[i], gr, -g * yv[i]);
+            store8(orow + c, uv);
+        }
+    } else {
+        for (int c = lane; c < d; c += 32) store1(orow + c, fmaf(ur[c], gr, -g * load1(yr + c)));
+    }
+}
+
 // out[c][r] = in[r][c] for a bf16 matrix: 64 x 64 tiles through shared memory, 16-byte global accesses.
 // The contractions read X^T / Y^T as K-major B operands (K-major tiles feed the tensor cores
 // measurably faster than MN-major ones when A is the transposed panel).
@@ -989,17 +1051,21 @@ static int grad_impl(int kind, const void* x_bf16, const void* y_bf16, int64_t r
                      const float* col_sum, const float* grad_out, float grad_scale, void* dx, int dx_mode, int64_t lddx,
                      void* dy, int dy_mode, int64_t lddy, void* workspace, size_t workspace_bytes, int* status,
                      cudaStream_t s0, bool overlap, bool transposed_copies, float* sg_acc = nullptr,
-                     float logit_scale = 0.f, float logit_bias = 0.f) {
+                     float logit_scale = 0.f, float logit_bias = 0.f, int64_t n_extra = 0, bool plain_e = false) {
     // kind MECLIP_SIGLIP: `temperature` is unused, the element function is sigmoid(logit_scale * s + logit_bias),
     // there are no row / column sums and both inputs get a gradient
+    // plain_e (LiT only): the panel holds E itself (no 1/r, no diagonal term) and the contraction runs over
+    // d + n_extra columns of Y, whose column d is all ones: dx receives [E Y | row sums of E | 0 ...]
     const bool siglip = (kind == MECLIP_SIGLIP);
+    const int64_t dn = d + n_extra;       // columns of the contraction outputs and of the transposed copies
     if (kind != MECLIP_CLIP && kind != MECLIP_LIT && !siglip) return fail(MECLIP_EINVAL, "grad: bad kind %d", kind);
-    if (x_bf16 == nullptr || y_bf16 == nullptr || (row_sum == nullptr && !siglip) || workspace == nullptr)
+    if (x_bf16 == nullptr || y_bf16 == nullptr || (row_sum == nullptr && !siglip && !plain_e) || workspace == nullptr)
         return fail(MECLIP_EINVAL, "grad: null pointer");
+    if (plain_e && (kind != MECLIP_LIT || n_extra < 0 || n_extra % 8 != 0)) return fail(MECLIP_EINVAL, "grad: bad fused-forward arguments");
     if (kind == MECLIP_CLIP && col_sum == nullptr) return fail(MECLIP_EINVAL, "grad: CLIP needs col_sum");
     if (kind == MECLIP_LIT) dy = nullptr;      // the second argument of LiT is frozen
     if (dx == nullptr && dy == nullptr) return fail(MECLIP_EINVAL, "grad: null pointer (no gradient output requested)");
-    if (rows < 1 || cols < 1 || d < 8 || d % 8 != 0 || ldx < d || ldy < d || (dx != nullptr && lddx < d) || (dy != nullptr && lddy < d))
+    if (rows < 1 || cols < 1 || d < 8 || d % 8 != 0 || ldx < d || ldy < dn || (dx != nullptr && lddx < dn) || (dy != nullptr && lddy < d))
         return fail(MECLIP_EINVAL, "grad: need rows, cols >= 1, d a multiple of 8, ld >= d");
     if ((dx != nullptr && !check_out_mode(dx_mode)) || (dy != nullptr && !check_out_mode(dy_mode))) return fail(MECLIP_EINVAL, "grad: bad output mode");
     if ((dx != nullptr && (!aligned16(dx) || lddx % 8 != 0)) || (dy != nullptr && (!aligned16(dy) || lddy % 8 != 0)))
@@ -1009,7 +1075,7 @@ static int grad_impl(int kind, const void* x_bf16, const void* y_bf16, int64_t r
     if (!siglip && !(temperature > 0.f)) return fail(MECLIP_EINVAL, "grad: temperature must be positive");
     int rc = check_device();
     if (rc) return rc;
-    const GradPlan plan = plan_grad(rows, cols, d, transposed_copies);
+    const GradPlan plan = plan_grad(rows, cols, dn, transposed_copies);
     if (workspace_bytes < plan.total())
         return fail(MECLIP_ENOSPC, "grad: workspace %zu < %zu bytes", workspace_bytes, plan.total());
     const bool clip = (kind == MECLIP_CLIP);
@@ -1049,9 +1115,9 @@ static int grad_impl(int kind, const void* x_bf16, const void* y_bf16, int64_t r
             if (want_dy) MECLIP_CUDA(cudaStreamWaitEvent(sy, side->fork, 0));
         }
         if (want_dx) {
-            ScopedTiming timing(sx, TAG_TRANSPOSE, 4.0 * (double)cols * (double)d);
-            dim3 grid((unsigned)((cols + 63) / 64), (unsigned)((d + 63) / 64));
-            transpose_bf16_kernel<<<grid, 256, 0, sx>>>(Y, ldy, cols, (int)d, yt, plan.ld_yt);
+            ScopedTiming timing(sx, TAG_TRANSPOSE, 4.0 * (double)cols * (double)dn);
+            dim3 grid((unsigned)((cols + 63) / 64), (unsigned)((dn + 63) / 64));
+            transpose_bf16_kernel<<<grid, 256, 0, sx>>>(Y, ldy, cols, (int)dn, yt, plan.ld_yt);
         }
         if (want_dy) {
             ScopedTiming timing(sy, TAG_TRANSPOSE, 4.0 * (double)rows * (double)d);
@@ -1086,11 +1152,11 @@ static int grad_impl(int kind, const void* x_bf16, const void* y_bf16, int64_t r
                     p.fadd = -p.fmul;
                 }
                 p.diag_shift = ((long long)row_off + r0) - ((long long)col_off + c0);
-                p.r = siglip ? nullptr : row_sum + r0;
+                p.r = (siglip || plain_e) ? nullptr : row_sum + r0;
                 p.c = clip ? col_sum + c0 : nullptr;
                 p.grad_out = grad_out;
                 p.coef = clip ? 0.5f * grad_scale : grad_scale;
-                p.dcoef = grad_scale;
+                p.dcoef = plain_e ? 0.f : grad_scale;
                 p.sg_acc = sg_acc;
                 p.tile_counter = counters + 3 * t;
                 p.status = status;
@@ -1143,14 +1209,14 @@ static int grad_impl(int kind, const void* x_bf16, const void* y_bf16, int64_t r
                 } else if (plan.n_panels == 1) {
                     p.out = user; p.ld_out = lddx; p.out_bf16 = (dx_mode == MECLIP_STORE_BF16);
                 } else {
-                    if (cp > 0) { p.acc_in = dx_scratch; p.ld_acc = d; }
+                    if (cp > 0) { p.acc_in = dx_scratch; p.ld_acc = dn; }
                     if (cp == plan.n_panels - 1) { p.out = user; p.ld_out = lddx; p.out_bf16 = (dx_mode == MECLIP_STORE_BF16); }
-                    else { p.out = dx_scratch; p.ld_out = d; p.out_bf16 = 0; }
+                    else { p.out = dx_scratch; p.ld_out = dn; p.out_bf16 = 0; }
                 }
                 Operand a{gpanel[gb], plan.ldg / 64, false, plan.row_block}, b{Y + c0 * ldy, ldy, true};
                 if (transposed_copies) b = Operand{yt + c0, plan.ld_yt, false};   // [d][K = cols] K-major
                 t_tag = TAG_DX;
-                rc = launch_gemm(EPI_OUT, a, b, nr, d, nc, pick_contraction_bn(nr, d, overlap, transposed_copies), p, sx);
+                rc = launch_gemm(EPI_OUT, a, b, nr, dn, nc, pick_contraction_bn(nr, dn, overlap, transposed_copies), p, sx);
                 if (rc) return rc;
                 if (overlap) MECLIP_CUDA(cudaEventRecord(side->dx[gb], sx));
             }
@@ -1192,6 +1258,67 @@ int meclip_grad_t(int kind, const void* x_bf16, const void* y_bf16, int64_t rows
     return grad_impl(kind, x_bf16, y_bf16, rows, cols, d, ldx, ldy, temperature, row_off, col_off, row_sum, col_sum,
                      grad_out, grad_scale, dx, dx_mode, lddx, dy, dy_mode, lddy, workspace, workspace_bytes, status,
                      (cudaStream_t)stream, overlap_allowed(), transposes_allowed(), sum_g_s);
+}
+
+// ---- LiT forward that already holds the gradient's contraction ------------------------------------
+int meclip_lit_extend(void* y_bf16, int64_t rows, int64_t d, int64_t ldy, void* stream) {
+    if (y_bf16 == nullptr || rows < 1 || d < 8 || d % 8 != 0 || ldy < d + 8 || ldy % 8 != 0 || !aligned16(y_bf16))
+        return fail(MECLIP_EINVAL, "lit_extend: need a 16-byte aligned matrix with d a multiple of 8 and ld >= d + 8");
+    ScopedTiming timing((cudaStream_t)stream, TAG_ROW, (double)rows * 16.0);
+    ones_column_kernel<<<(unsigned)((rows + 255) / 256), 256, 0, (cudaStream_t)stream>>>((__nv_bfloat16*)y_bf16, rows, d, ldy);
+    MECLIP_CUDA(cudaGetLastError());
+    return MECLIP_OK;
+}
+
+int meclip_lit_fused_forward(const void* x_bf16, const void* y_ext_bf16, int64_t rows, int64_t cols, int64_t d, int64_t ldx,
+                             int64_t ldy, float temperature, int64_t row_off, int64_t col_off, float* u, int u_mode,
+                             int64_t ldu, void* workspace, size_t workspace_bytes, int* status, void* stream) {
+    if (u == nullptr) return fail(MECLIP_EINVAL, "lit_fused_forward: u is null");
+    if (u_mode != MECLIP_STORE_F32 && u_mode != MECLIP_ACCUM_F32) return fail(MECLIP_EINVAL, "lit_fused_forward: u is fp32");
+    return grad_impl(MECLIP_LIT, x_bf16, y_ext_bf16, rows, cols, d, ldx, ldy, temperature, row_off, col_off, nullptr, nullptr,
+                     nullptr, 1.f, u, u_mode, ldu, nullptr, 0, 0, workspace, workspace_bytes, status, (cudaStream_t)stream,
+                     overlap_allowed(), transposes_allowed(), nullptr, 0.f, 0.f, 8, true);
+}
+
+int meclip_lit_fused_stats(const void* x_bf16, int64_t ldx, const void* y_ext_bf16, int64_t ldy, const float* u, int64_t ldu,
+                           int64_t rows, int64_t d, float* row_sum, float* diag_s, void* stream) {
+    if (x_bf16 == nullptr || y_ext_bf16 == nullptr || u == nullptr || row_sum == nullptr || diag_s == nullptr)
+        return fail(MECLIP_EINVAL, "lit_fused_stats: null pointer");
+    if (rows < 1 || d < 8 || d % 8 != 0 || ldx < d || ldy < d + 8 || ldu < d + 8 || ldx % 8 != 0 || ldy % 8 != 0 ||
+        !aligned16(x_bf16) || !aligned16(y_ext_bf16))
+        return fail(MECLIP_EINVAL, "lit_fused_stats: bad shape or alignment");
+    const int wpb = ROW_KERNEL_THREADS / 32;
+    ScopedTiming timing((cudaStream_t)stream, TAG_ROW, (double)rows * ((double)d * 4 + 12));
+    lit_fused_stats_kernel<<<(unsigned)((rows + wpb - 1) / wpb), ROW_KERNEL_THREADS, 0, (cudaStream_t)stream>>>(
+        (const __nv_bfloat16*)x_bf16, ldx, (const __nv_bfloat16*)y_ext_bf16, ldy, u, ldu, rows, (int)d, row_sum, diag_s);
+    MECLIP_CUDA(cudaGetLastError());
+    return MECLIP_OK;
+}
+
+int meclip_lit_fused_backward(const float* u, int64_t ldu, const void* y_ext_bf16, int64_t ldy, const float* row_sum,
+                              const float* grad_out, float grad_scale, int64_t rows, int64_t d, void* dx, int dx_dtype,
+                              int64_t lddx, void* stream) {
+    if (u == nullptr || y_ext_bf16 == nullptr || row_sum == nullptr || dx == nullptr)
+        return fail(MECLIP_EINVAL, "lit_fused_backward: null pointer");
+    if (rows < 1 || d < 1 || ldu < d || ldy < d || lddx < d || ldu % 4 != 0 || ldy % 8 != 0 || !aligned16(u) || !aligned16(y_ext_bf16))
+        return fail(MECLIP_EINVAL, "lit_fused_backward: bad shape or alignment");
+    const int oelt = dx_dtype == MECLIP_F32 ? 4 : 2;
+    const int vec_out = (d % 8 == 0) && aligned16(dx) && ((lddx * oelt) % 16 == 0);
+    const int wpb = ROW_KERNEL_THREADS / 32;
+    const unsigned grid = (unsigned)((rows + wpb - 1) / wpb);
+    cudaStream_t s = (cudaStream_t)stream;
+    const __nv_bfloat16* y = (const __nv_bfloat16*)y_ext_bf16;
+    ScopedTiming timing(s, TAG_NORM_BWD, (double)rows * (double)d * (6.0 + oelt));
+    if (dx_dtype == MECLIP_F32)
+        lit_fused_bwd_kernel<float><<<grid, ROW_KERNEL_THREADS, 0, s>>>(u, ldu, y, ldy, row_sum, grad_out, grad_scale, rows, (int)d, vec_out, (float*)dx, lddx);
+    else if (dx_dtype == MECLIP_BF16)
+        lit_fused_bwd_kernel<__nv_bfloat16><<<grid, ROW_KERNEL_THREADS, 0, s>>>(u, ldu, y, ldy, row_sum, grad_out, grad_scale, rows, (int)d, vec_out, (__nv_bfloat16*)dx, lddx);
+    else if (dx_dtype == MECLIP_F16)
+        lit_fused_bwd_kernel<__half><<<grid, ROW_KERNEL_THREADS, 0, s>>>(u, ldu, y, ldy, row_sum, grad_out, grad_scale, rows, (int)d, vec_out, (__half*)dx, lddx);
+    else
+        return fail(MECLIP_EINVAL, "lit_fused_backward: bad output dtype %d", dx_dtype);
+    MECLIP_CUDA(cudaGetLastError());
+    return MECLIP_OK;
 }
 
 // ---- sigmoid (SigLIP) loss on the same tile engine -------------------------------------------------

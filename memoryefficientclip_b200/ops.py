@@ -43,8 +43,9 @@ def read_status(status: torch.Tensor) -> None:
         _lib.check(_lib.load().meclip_read_status(status.data_ptr(), _stream(status)))
 
 
-def normalize_fwd(x: torch.Tensor, normalize: bool = True):
-    """Returns (x_hat bf16 [rows, padded(d)], inv_norm fp32 [rows] or None); columns past d are zero.
+def normalize_fwd(x: torch.Tensor, normalize: bool = True, extra_cols: int = 0):
+    """Returns (x_hat bf16 [rows, padded(d) + extra_cols], inv_norm fp32 [rows] or None); columns past d are
+    zero up to padded(d); extra_cols (a multiple of 8) are left for the caller to fill.
 
     Any feature count, row pitch and alignment is taken as it is (the kernel reads element-wise when
     16-byte loads are not possible); only a non-unit column stride costs a copy."""
@@ -52,11 +53,12 @@ def normalize_fwd(x: torch.Tensor, normalize: bool = True):
     x = x if x.stride(1) == 1 else x.contiguous()
     rows, d = x.shape
     dp = padded(d)
-    out = torch.empty(rows, dp, dtype=torch.bfloat16, device=x.device)
+    out = torch.empty(rows, dp + extra_cols, dtype=torch.bfloat16, device=x.device)
     inv = torch.empty(rows, dtype=torch.float32, device=x.device) if normalize else None
     with torch.cuda.device(x.device):
         _lib.check(_lib.load().meclip_normalize_fwd(x.data_ptr(), _DT[x.dtype], rows, d, max(x.stride(0), d),
-                                                    int(normalize), out.data_ptr(), dp, _ptr(inv), _stream(x)))
+                                                    int(normalize), out.data_ptr(), dp + extra_cols, _ptr(inv),
+                                                    _stream(x)))
     return out, inv
 
 
@@ -273,6 +275,42 @@ def siglip_backward(x_hat, y_hat, logit_scale, logit_bias, grad_out, grad_scale_
                                                   _ptr(dy), _MODE[dy_dtype], d, _ptr(sums), ws.data_ptr(), ws.numel(),
                                                   _ptr(status), _stream(x_hat)))
     return dx, dy
+
+
+def lit_fused_forward(x_hat, y_ext, d_pad, temperature, status=None):
+    """LiT forward that also does the gradient's contraction (meclip_lit_fused_forward): x_hat [b, d_pad],
+    y_ext [b, d_pad + 8] whose column d_pad gets the ones.  Returns (loss, u fp32 [b, d_pad + 8], row_sum)."""
+    b = x_hat.shape[0]
+    dev = x_hat.device
+    lib = _lib.load()
+    u = torch.empty(b, d_pad + 8, dtype=torch.float32, device=dev)
+    row_sum = torch.empty(b, dtype=torch.float32, device=dev)
+    diag_s = torch.empty(b, dtype=torch.float32, device=dev)
+    loss = torch.empty((), dtype=torch.float32, device=dev)
+    ws = grad_workspace(b, b, d_pad + 8, dev)
+    st = _stream(x_hat)
+    with torch.cuda.device(dev):
+        _lib.check(lib.meclip_lit_extend(y_ext.data_ptr(), b, d_pad, y_ext.stride(0), st))
+        _lib.check(lib.meclip_lit_fused_forward(x_hat.data_ptr(), y_ext.data_ptr(), b, b, d_pad, x_hat.stride(0),
+                                                y_ext.stride(0), float(temperature), 0, 0, u.data_ptr(), _lib.STORE_F32,
+                                                u.stride(0), ws.data_ptr(), ws.numel(), _ptr(status), st))
+        _lib.check(lib.meclip_lit_fused_stats(x_hat.data_ptr(), x_hat.stride(0), y_ext.data_ptr(), y_ext.stride(0),
+                                              u.data_ptr(), u.stride(0), b, d_pad, row_sum.data_ptr(), diag_s.data_ptr(),
+                                              st))
+        _lib.check(lib.meclip_loss_finalize(_lib.LIT, row_sum.data_ptr(), None, diag_s.data_ptr(), b, float(temperature),
+                                            1.0 / b, 0, loss.data_ptr(), st))
+    return loss, u, row_sum
+
+
+def lit_fused_backward(u, y_ext, row_sum, grad_out, grad_scale_, d_out, out_dtype):
+    """dx [b, d_out] in out_dtype from the saved u (meclip_lit_fused_backward)."""
+    b = u.shape[0]
+    dx = torch.empty(b, d_out, dtype=out_dtype, device=u.device)
+    with torch.cuda.device(u.device):
+        _lib.check(_lib.load().meclip_lit_fused_backward(u.data_ptr(), u.stride(0), y_ext.data_ptr(), y_ext.stride(0),
+                                                         row_sum.data_ptr(), _ptr(grad_out), float(grad_scale_), b, d_out,
+                                                         dx.data_ptr(), _DT[out_dtype], dx.stride(0), _stream(u)))
+    return dx
 
 
 def grad_scale(batch: int, temperature: float, stable: bool) -> float:
