@@ -100,3 +100,22 @@ def test_replay_is_faster_than_eager_for_a_small_batch():
     graph_ms = timed(graph.replay)
     print(f"eager {eager_ms * 1e3:.1f} us/step, graph replay {graph_ms * 1e3:.1f} us/step")
     assert graph_ms < eager_ms
+
+
+def test_make_graphed_callables_on_the_module():
+    """torch.cuda.make_graphed_callables captures the module's forward and backward as two graphs and keeps the
+    autograd interface: the drop-in way to run small batches at kernel speed."""
+    import memoryefficientclip_b200 as m
+    b, d = 2048, 512
+    mod = m.MemoryEfficientCLIPLoss(0.07, False)
+    sx, sy = _fresh(b, d, 30)
+    graphed = torch.cuda.make_graphed_callables(mod, (sx.cuda().requires_grad_(True), sy.cuda().requires_grad_(True)))
+    for seed in (31, 32):
+        nx, ny = _fresh(b, d, seed)
+        x = nx.cuda().requires_grad_(True)
+        y = ny.cuda().requires_grad_(True)
+        loss = graphed(x, y)
+        loss.backward()
+        torch.cuda.synchronize()
+        rl, rx, ry = dense.clip_dense(nx, ny, 0.07, False)
+        dense.assert_parity(loss.item(), rl, (x.grad.cpu(), y.grad.cpu()), (rx, ry), f"graphed callable seed {seed}")
