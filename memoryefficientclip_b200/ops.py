@@ -277,28 +277,47 @@ def siglip_backward(x_hat, y_hat, logit_scale, logit_bias, grad_out, grad_scale_
     return dx, dy
 
 
+def lit_extend(y_ext, d_pad):
+    """Writes the ones column (and seven zeros) at column d_pad of y_ext [rows, d_pad + 8]."""
+    with torch.cuda.device(y_ext.device):
+        _lib.check(_lib.load().meclip_lit_extend(y_ext.data_ptr(), y_ext.shape[0], d_pad, y_ext.stride(0), _stream(y_ext)))
+
+
+def lit_fused_block(x_hat, y_ext, d_pad, temperature, u, u_mode, row_off=0, col_off=0, workspace=None, status=None):
+    """One rows x cols block of the one-pass LiT forward: u (=|+=) E [y_ext] (meclip_lit_fused_forward)."""
+    rows, cols = x_hat.shape[0], y_ext.shape[0]
+    if workspace is None:
+        workspace = grad_workspace(rows, cols, d_pad + 8, x_hat.device)
+    with torch.cuda.device(x_hat.device):
+        _lib.check(_lib.load().meclip_lit_fused_forward(x_hat.data_ptr(), y_ext.data_ptr(), rows, cols, d_pad,
+                                                        x_hat.stride(0), y_ext.stride(0), float(temperature), row_off,
+                                                        col_off, u.data_ptr(), u_mode, u.stride(0), workspace.data_ptr(),
+                                                        workspace.numel(), _ptr(status), _stream(x_hat)))
+
+
+def lit_fused_stats(x_hat, y_ext, u, d_pad):
+    """(row_sum, diag_s) of the rows of u: row_sum = u[:, d_pad], diag_s[i] = <x_i, y_i>."""
+    b = x_hat.shape[0]
+    row_sum = torch.empty(b, dtype=torch.float32, device=u.device)
+    diag_s = torch.empty(b, dtype=torch.float32, device=u.device)
+    with torch.cuda.device(u.device):
+        _lib.check(_lib.load().meclip_lit_fused_stats(x_hat.data_ptr(), x_hat.stride(0), y_ext.data_ptr(), y_ext.stride(0),
+                                                      u.data_ptr(), u.stride(0), b, d_pad, row_sum.data_ptr(),
+                                                      diag_s.data_ptr(), _stream(u)))
+    return row_sum, diag_s
+
+
 def lit_fused_forward(x_hat, y_ext, d_pad, temperature, status=None):
-    """LiT forward that also does the gradient's contraction (meclip_lit_fused_forward): x_hat [b, d_pad],
-    y_ext [b, d_pad + 8] whose column d_pad gets the ones.  Returns (loss, u fp32 [b, d_pad + 8], row_sum)."""
+    """LiT forward that also does the gradient's contraction: x_hat [b, d_pad], y_ext [b, d_pad + 8] whose
+    column d_pad gets the ones.  Returns (loss, u fp32 [b, d_pad + 8], row_sum)."""
     b = x_hat.shape[0]
     dev = x_hat.device
-    lib = _lib.load()
     u = torch.empty(b, d_pad + 8, dtype=torch.float32, device=dev)
-    row_sum = torch.empty(b, dtype=torch.float32, device=dev)
-    diag_s = torch.empty(b, dtype=torch.float32, device=dev)
     loss = torch.empty((), dtype=torch.float32, device=dev)
-    ws = grad_workspace(b, b, d_pad + 8, dev)
-    st = _stream(x_hat)
-    with torch.cuda.device(dev):
-        _lib.check(lib.meclip_lit_extend(y_ext.data_ptr(), b, d_pad, y_ext.stride(0), st))
-        _lib.check(lib.meclip_lit_fused_forward(x_hat.data_ptr(), y_ext.data_ptr(), b, b, d_pad, x_hat.stride(0),
-                                                y_ext.stride(0), float(temperature), 0, 0, u.data_ptr(), _lib.STORE_F32,
-                                                u.stride(0), ws.data_ptr(), ws.numel(), _ptr(status), st))
-        _lib.check(lib.meclip_lit_fused_stats(x_hat.data_ptr(), x_hat.stride(0), y_ext.data_ptr(), y_ext.stride(0),
-                                              u.data_ptr(), u.stride(0), b, d_pad, row_sum.data_ptr(), diag_s.data_ptr(),
-                                              st))
-        _lib.check(lib.meclip_loss_finalize(_lib.LIT, row_sum.data_ptr(), None, diag_s.data_ptr(), b, float(temperature),
-                                            1.0 / b, 0, loss.data_ptr(), st))
+    lit_extend(y_ext, d_pad)
+    lit_fused_block(x_hat, y_ext, d_pad, temperature, u, _lib.STORE_F32, 0, 0, None, status)
+    row_sum, diag_s = lit_fused_stats(x_hat, y_ext, u, d_pad)
+    loss_finalize(_lib.LIT, row_sum, None, diag_s, temperature, 1.0 / b, loss)
     return loss, u, row_sum
 
 

@@ -64,6 +64,27 @@ class CudaBlockOps:
     def new_sum(self, device):
         return torch.zeros(2, dtype=torch.float32, device=device)
 
+    # one-pass LiT (the forward contracts E with [Y | 1]; no ring backward at all)
+    lit_one_pass = True
+
+    def prepare_ext(self, y, normalize):
+        y_ext, _inv = ops.normalize_fwd(y, normalize, extra_cols=8)
+        d_pad = y_ext.shape[1] - 8
+        ops.lit_extend(y_ext, d_pad)
+        return y_ext, d_pad
+
+    def new_u(self, rows, d_pad, device):
+        return torch.zeros(rows, d_pad + 8, dtype=torch.float32, device=device)
+
+    def lit_fused_block(self, x_hat, y_ext, d_pad, t, u, row_off, col_off, workspace):
+        ops.lit_fused_block(x_hat, y_ext, d_pad, t, u, _lib.ACCUM_F32, row_off, col_off, workspace)
+
+    def lit_fused_stats(self, x_hat, y_ext, u, d_pad):
+        return ops.lit_fused_stats(x_hat, y_ext, u, d_pad)
+
+    def lit_fused_bwd(self, u, y_ext, row_sum, go, scale, d_out, out_dtype):
+        return ops.lit_fused_backward(u, y_ext, row_sum, go, scale, d_out, out_dtype)
+
     def siglip_sum(self, x_hat, y_hat, logit_scale, logit_bias, row_sum, diag, row_off, col_off):
         ops.siglip_sum(x_hat, y_hat, logit_scale, logit_bias, row_sum, diag, row_off, col_off)
 
@@ -217,6 +238,35 @@ def ring_backward(block, kind, x_hat, y_hat, temperature, row_sum, col_sum, grad
     return _ring_backward_loop(block, x_hat, y_hat, group, rank, world, clip, grad_call)
 
 
+def ring_lit_fused_forward(block, x_hat, y_ext, d_pad, temperature, group, rank, world):
+    """One-pass LiT over the ring: at every step the visiting shard's block adds E_block [Y_shard | 1] to u, so
+    after the N steps u = [E Y | r | 0...] for the local rows and the backward needs no ring at all.
+    Returns (loss, u, row_sum)."""
+    b = x_hat.shape[0]
+    u = block.new_u(b, d_pad, x_hat.device)
+    workspace = block.workspace(b, b, d_pad + 8, x_hat.device)
+    bufs = [y_ext, torch.empty_like(y_ext)] if world > 1 else [y_ext]
+    if world > 2:
+        bufs.append(torch.empty_like(y_ext))
+    cur = 0
+    for step in range(world):
+        shard = shard_at(rank, step, world)
+        reqs = []
+        if step + 1 < world:
+            nxt = 1 + (step % 2) if world > 2 else 1
+            reqs = _rotate(bufs[cur], bufs[nxt], group, rank, world)
+        block.lit_fused_block(x_hat, bufs[cur], d_pad, temperature, u, rank * b, shard * b, workspace)
+        for r in reqs:
+            r.wait()
+        if step + 1 < world:
+            cur = nxt
+    row_sum, diag = block.lit_fused_stats(x_hat, y_ext, u, d_pad)        # the positives are the own shard's rows
+    loss = block.local_loss_sum(_lib.LIT, row_sum, None, diag, temperature, 1.0 / (b * world))
+    if world > 1:
+        dist.all_reduce(loss, op=dist.ReduceOp.SUM, group=group)
+    return loss, u, row_sum
+
+
 def ring_siglip_forward(block, x_hat, y_hat, logit_scale, logit_bias, group, rank, world):
     """Sigmoid loss of the global batch: every block is independent (no row or column sums to finish)."""
     b = x_hat.shape[0]
@@ -276,6 +326,17 @@ class RingContrastiveLossFn(torch.autograd.Function):
         world = dist.get_world_size(group) if dist.is_initialized() else 1
         rank = dist.get_rank(group) if dist.is_initialized() else 0
         block = block or CudaBlockOps()
+        from . import _function
+        ctx.ring_fused = (kind == _lib.LIT and _function._LIT_FUSED and ctx.needs_input_grad[0] and ctx.ring_t is None
+                          and getattr(block, "lit_one_pass", False))
+        if ctx.ring_fused:
+            x_hat, inv_x = block.prepare(x, normalize)
+            y_ext, d_pad = block.prepare_ext(y, normalize)
+            loss, u, row_sum = ring_lit_fused_forward(block, x_hat, y_ext, d_pad, temperature, group, rank, world)
+            ctx.save_for_backward(*([u, y_ext, row_sum] + ([x_hat, inv_x] if normalize else [])))
+            ctx.ring = (float(temperature), kind, bool(stable), bool(normalize), x.dtype, y.dtype, x.shape[1], group, rank,
+                        world, block)
+            return loss
         x_hat, inv_x = block.prepare(x, normalize)
         y_hat, inv_y = block.prepare(y, normalize)
         loss, row_sum, col_sum, _diag = ring_forward(block, kind, x_hat, y_hat, temperature, group, rank, world)
@@ -293,6 +354,17 @@ class RingContrastiveLossFn(torch.autograd.Function):
     def backward(ctx, grad_output):
         temperature, kind, stable, normalize, x_dtype, y_dtype, d, group, rank, world, block = ctx.ring
         saved = list(ctx.saved_tensors)
+        if getattr(ctx, "ring_fused", False):
+            u, y_ext, row_sum = saved[:3]
+            go = grad_output.detach().to(device=u.device, dtype=torch.float32).reshape(1).contiguous()
+            scale = ops.grad_scale(u.shape[0] * world, temperature, stable)
+            if normalize:
+                x_hat, inv_x = saved[3:]
+                g32 = block.lit_fused_bwd(u, y_ext, row_sum, go, scale, x_hat.shape[1], torch.float32)
+                dx = block.finish_grad(g32, x_hat, inv_x, x_dtype, d)
+            else:
+                dx = block.lit_fused_bwd(u, y_ext, row_sum, go, scale, d, x_dtype)
+            return dx, None, None, None, None, None, None, None, None
         x_hat, y_hat, row_sum = saved[:3]
         rest = saved[3:]
         col_sum = rest.pop(0) if kind == _lib.CLIP else None

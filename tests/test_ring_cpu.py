@@ -61,6 +61,29 @@ class OracleBlockOps:
     def workspace(self, rows, cols, d, device):
         return None
 
+    # one-pass LiT: u += E_block [Y_shard | 1 | 0...]
+    lit_one_pass = True
+
+    def prepare_ext(self, y, normalize):
+        y_hat, _ = self.prepare(y, normalize)
+        ext = torch.zeros(y_hat.shape[0], 8, dtype=y_hat.dtype)
+        ext[:, 0] = 1.0
+        return torch.cat([y_hat, ext], dim=1), y_hat.shape[1]
+
+    def new_u(self, rows, d_pad, device):
+        return torch.zeros(rows, d_pad + 8, dtype=torch.float64)
+
+    def lit_fused_block(self, x_hat, y_ext, d_pad, t, u, row_off, col_off, workspace):
+        e, _, _ = dense.sum_exp(x_hat.numpy(), y_ext[:, :d_pad].contiguous().numpy(), t)
+        u += torch.from_numpy(e) @ y_ext
+
+    def lit_fused_stats(self, x_hat, y_ext, u, d_pad):
+        return u[:, d_pad].clone(), (x_hat * y_ext[:, :d_pad]).sum(dim=1)
+
+    def lit_fused_bwd(self, u, y_ext, row_sum, go, scale, d_out, out_dtype):
+        g = float(go) * scale
+        return (g * (u[:, :d_out] / row_sum[:, None] - y_ext[:, :d_out])).to(out_dtype)
+
     def _siglip_a_z(self, x_hat, y_hat, t, bias, row_off, col_off):
         a = (x_hat @ y_hat.t()) * t + bias
         z = -torch.ones_like(a)
