@@ -661,7 +661,13 @@ static int launch_gemm(int epi, const Operand& a, const Operand& b, long long m,
     p.k_steps = (int)((k + BK - 1) / BK);
     p.trace = g_trace_buf;
     p.trace_capacity = g_trace_capacity;
-    p.group_m = 16;
+    // Tile ids walk group_m row tiles of one column tile, then the next column tile.  The sums pass wants tall
+    // groups (a strip shares its columns).  A contraction streams its A operand (the coefficient panel) from HBM:
+    // with short groups the column tiles that share panel rows run at the same time and hit L2, which is worth
+    // 6 % on the isolated contraction (1086 -> 1152 TFLOP/s sustained, 0.91 -> 0.86 pJ/FLOP) and 2.5 % on the step.
+    p.group_m = epi == EPI_OUT ? 2 : 16;
+    static const int env_group_m = []() { const char* v = std::getenv("MECLIP_GROUP_M"); return v ? std::atoi(v) : 0; }();
+    if (env_group_m > 0 && epi == EPI_OUT) p.group_m = env_group_m;
     // strips: tile ids inside a group of 16 m-tiles share their columns; the sums pass keeps column
     // partials in registers over a strip.  Shorter strips when there are few tiles per SM.
     p.strip_len = 1;
