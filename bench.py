@@ -313,8 +313,8 @@ def run_ours(args):
         "peak": peaks["bf16_tflops_sustained"], "unit": "TFLOP/s", "frac": achieved / peaks["bf16_tflops_sustained"],
         "peak_source": peaks["source"] + " bf16 sustained", "frac_of_burst": achieved / peaks["bf16_tflops"],
         # DRAM read + write bytes per launch of a contraction kernel, from an ncu capture of this kernel at
-        # B=16384, D=1152 (1.16 GB per 537 MB coefficient panel), scaled by the launch's work
-        "traffic": (1.159e9 * (dom_flops / 6.18e11) if dominant["kernel"] in ("dx_contraction", "dy_contraction")
+        # B=16384, D=1152 (0.83 GB per 537 MB coefficient panel), scaled by the launch's work
+        "traffic": (0.827e9 * (dom_flops / 6.18e11) if dominant["kernel"] in ("dx_contraction", "dy_contraction")
                     else None),
         "step_frac_of_burst": tflops * (1 if world == 1 else 1.0 / world) / peaks["bf16_tflops"],
         "step_frac_of_sustained": tflops * (1 if world == 1 else 1.0 / world) / peaks["bf16_tflops_sustained"],
