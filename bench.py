@@ -10,6 +10,9 @@ N > 1   ring-distributed CLIP fwd+bwd, global B=262144, D=1024, bf16, T=0.03, te
         batch is fixed, so scaling is "strong".  --config ring_clip_b131072_d768_bf16 selects the
         other ring configuration.
 
+--config also takes clip_b4096_d512_f32 (the smallest configuration) and lit_b32768_d1152_bf16 (LiT: the metric
+counts 6*B^2*D, the one-pass route executes 4*B^2*(D+8), see config.note in the line).
+
 The metric is TFLOP/s with the 8*B^2*D convention (forward 2, recompute 2, two gradient
 contractions 2+2).  Prints ONE JSON line on rank 0.
 """
