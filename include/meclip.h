@@ -21,7 +21,9 @@
  *    row kernels (meclip_normalize_fwd / _bwd) take and give any D, pitch, alignment
  *    and fp32 / bf16 / fp16, and produce such operands by zero padding.
  *  - `status` is a device int the kernels set non-zero when a bounded wait inside
- *    a kernel ran out (MECLIP_ETIMEOUT); read it with meclip_read_status().
+ *    a kernel ran out (MECLIP_ETIMEOUT); read it with meclip_read_status().  The bound
+ *    is 2 s of wall time per wait (environment MECLIP_WAIT_LIMIT_MS changes it, e.g. for
+ *    a GPU that is time-sliced between processes).
  *
  * Reference = b0nce/MemoryEfficientCLIP (clip_loss.py, lit_loss.py).
  */
@@ -60,6 +62,38 @@ const char* meclip_status_string(int code);
 int meclip_last_error(char* buf, size_t buf_len);
 /* Synchronises `stream`, copies *status to the host and maps non-zero to MECLIP_ETIMEOUT. */
 int meclip_read_status(const int* status, void* stream);
+
+/*
+ * Scalars that live on the device.  The entry points below take the temperature (softmax losses) or the
+ * logit scale and bias (sigmoid loss) as host floats, as the reference does (clip_loss.py:181).  A trainer that
+ * LEARNS them holds them in device memory; reading them back for every step would stall the host.  This call
+ * binds device addresses for the NEXT tile-pass or loss-finalisation call made by the same host thread
+ * (meclip_sum_exp, meclip_loss_finalize, meclip_loss_forward, meclip_grad, meclip_grad_t, meclip_grad_static,
+ * meclip_loss_backward, meclip_lit_fused_forward, meclip_lit_fused_backward, meclip_siglip_sum,
+ * meclip_siglip_grad); that call consumes the binding whether it succeeds or not and ignores its float
+ * temperature / scale / bias arguments in favour of the bound values:
+ *   temperature_or_scale  fp32 device scalar: T for CLIP / LiT, t for the sigmoid loss
+ *   logit_bias            fp32 device scalar or NULL (sigmoid loss only; NULL keeps the float argument)
+ *   grad_scale_rule       how a backward completes its grad_scale argument, which the caller then forms for
+ *                         T = 1: 0 as given, 1 divided by T (grad_scale = 1/B), 2 divided by sqrt(T)
+ *                         (Stable variants, 1/sqrt(B)), 3 multiplied by t (sigmoid loss, 1/B)
+ * The scalars are read by the kernels when they run, so the memory must stay valid until then.  The
+ * binding is per host thread; nothing is shared between threads.  The reference has no counterpart (its
+ * temperature is a Python float and gets no gradient, clip_loss.py:256).
+ */
+enum meclip_grad_scale_rule {
+    MECLIP_GSCALE_FIXED = 0, MECLIP_GSCALE_OVER_T = 1, MECLIP_GSCALE_OVER_SQRT_T = 2, MECLIP_GSCALE_TIMES_T = 3
+};
+int meclip_bind_device_scalars(const float* temperature_or_scale, const float* logit_bias, int grad_scale_rule);
+
+/*
+ * Test hook: one tiny kernel (one CTA, no tile loads, no tensor memory) that waits on a barrier nobody
+ * arrives on, with the same bounded-wait routine the tile kernels use and a limit of limit_ns nanoseconds
+ * (at most 100 ms).  The wait runs out, the kernel sets *status non-zero and ends normally, so that
+ * meclip_read_status() reports MECLIP_ETIMEOUT while the context stays usable: the way to exercise the
+ * time-out reporting without disturbing a real kernel.  Has no counterpart in the reference.
+ */
+int meclip_debug_wait_probe(uint64_t limit_ns, int* status, void* stream);
 
 /*
  * Test hook: override the backward's blocking (rows of the coefficient matrix formed per

@@ -27,19 +27,26 @@ class ContrastiveLossFn(torch.autograd.Function):
         ops._check_matrix(x, "first input")
         ops._check_matrix(y, "second input")
         assert x.device == y.device
-        # A tensor temperature (e.g. an nn.Parameter) is read on the host once per forward; it then
-        # also receives a gradient, which the reference does not provide (clip_loss.py:256).
+        # A tensor temperature (e.g. an nn.Parameter) stays on the device: the kernels read it there, so a
+        # learnable temperature costs no host synchronisation.  It then also receives a gradient, which the
+        # reference does not provide (clip_loss.py:256).
         t_is_tensor = isinstance(temperature, torch.Tensor)
-        temperature_value = float(temperature.detach().item()) if t_is_tensor else float(temperature)
-        assert temperature_value > 0.0, "temperature must be positive"
+        if t_is_tensor:
+            assert temperature.numel() == 1, "temperature must be a scalar"
+            temperature_value = temperature.detach()
+        else:
+            temperature_value = float(temperature)
+            assert temperature_value > 0.0, "temperature must be positive"
         learn_t = t_is_tensor and temperature.requires_grad
+        status = ops.status_word(x.device)
+        ops.poll_status(x.device)           # raises if a kernel of an earlier step gave up a bounded wait
         # LiT's coefficients separate (G_ij = g E_ij / r_i - g [i == j]), so when the first input needs a gradient the
         # forward also contracts E with [Y | 1] and the backward is a row kernel: 4 B^2 D FLOPs instead of 6 B^2 D
         if kind == _lib.LIT and _LIT_FUSED and ctx.needs_input_grad[0] and not learn_t:
             x_hat, inv_x = ops.normalize_fwd(x, True) if normalize else (ops.as_operand(x), None)
             y_ext, _inv_y = ops.normalize_fwd(y, normalize, extra_cols=8)
             d_pad = x_hat.shape[1]
-            loss, u, row_sum = ops.lit_fused_forward(x_hat, y_ext, d_pad, temperature_value)
+            loss, u, row_sum = ops.lit_fused_forward(x_hat, y_ext, d_pad, temperature_value, status=status)
             ctx.save_for_backward(*([u, y_ext, row_sum] + ([x_hat, inv_x] if normalize else [])))
             ctx.meclip = (temperature_value, kind, bool(stable), bool(normalize), x.dtype, y.dtype, x.shape[1])
             ctx.meclip_t = None
@@ -52,7 +59,9 @@ class ContrastiveLossFn(torch.autograd.Function):
         else:
             x_hat, inv_x = ops.as_operand(x), None
             y_hat, inv_y = ops.as_operand(y), None
-        loss, row_sum, col_sum, _diag = ops.loss_forward(kind, x_hat, y_hat, temperature_value)
+        loss, row_sum, col_sum, _diag = ops.loss_forward(kind, x_hat, y_hat, temperature_value, status=status)
+        if not any(ctx.needs_input_grad[:3]):
+            ops.post_status(x.device)       # no backward will follow this forward
         saved = [x_hat, y_hat, row_sum]
         if col_sum is not None:
             saved.append(col_sum)
@@ -70,13 +79,17 @@ class ContrastiveLossFn(torch.autograd.Function):
         if getattr(ctx, "meclip_fused", False):
             u, y_ext, row_sum = saved[:3]
             go = grad_output.detach().to(device=u.device, dtype=torch.float32).reshape(1).contiguous()
-            scale = ops.grad_scale(u.shape[0], temperature, stable)
+            scale, rule = ops.grad_scale_args(u.shape[0], temperature, stable)
             ctx.meclip_dt = None
             if normalize:
                 x_hat, inv_x = saved[3:]
-                g32 = ops.lit_fused_backward(u, y_ext, row_sum, go, scale, x_hat.shape[1], torch.float32)
-                return ops.normalize_bwd(g32, x_hat, inv_x, x_dtype, d), None
-            return ops.lit_fused_backward(u, y_ext, row_sum, go, scale, d, x_dtype), None
+                g32 = ops.lit_fused_backward(u, y_ext, row_sum, go, scale, x_hat.shape[1], torch.float32, temperature,
+                                             rule)
+                dx = ops.normalize_bwd(g32, x_hat, inv_x, x_dtype, d)
+            else:
+                dx = ops.lit_fused_backward(u, y_ext, row_sum, go, scale, d, x_dtype, temperature, rule)
+            ops.post_status(u.device)
+            return dx, None
         x_hat, y_hat, row_sum = saved[:3]
         rest = saved[3:]
         col_sum = rest.pop(0) if kind == _lib.CLIP else None
@@ -84,7 +97,8 @@ class ContrastiveLossFn(torch.autograd.Function):
         batch = x_hat.shape[0]
         # grad_output stays on the device: no host sync (the reference compares it to 1.0 on the host)
         go = grad_output.detach().to(device=x_hat.device, dtype=torch.float32).reshape(1).contiguous()
-        scale = ops.grad_scale(batch, temperature, stable)
+        scale, rule = ops.grad_scale_args(batch, temperature, stable)
+        status = ops.status_word(x_hat.device)
         need = tuple(ctx.needs_input_grad) + (False, False)
         want_dx = bool(need[0])
         want_dy = kind == _lib.CLIP and bool(need[1])      # a frozen tower costs no contraction
@@ -99,17 +113,22 @@ class ContrastiveLossFn(torch.autograd.Function):
         if sum_g_s is not None and not (want_dx or want_dy):
             want_dx = True       # the temperature sum is produced by the coefficient pass of the backward
         dx, dy = ops.loss_backward(kind, x_hat, y_hat, temperature, row_sum, col_sum, go, scale, dx_t, dy_t,
-                                   sum_g_s=sum_g_s, need_dx=want_dx, need_dy=want_dy)
+                                   status=status, sum_g_s=sum_g_s, need_dx=want_dx, need_dy=want_dy, scale_rule=rule)
         ctx.meclip_dt = None
         if sum_g_s is not None:
             # sum_ij G_ij S_ij = g B dL/d(1/T) with g = go * scale, so go * dL/dT = -(sum / (scale B)) / T^2.
             # (The Stable scaling only rescales the feature gradients; the temperature gets the true one.)
-            dt = sum_g_s[0] * (-1.0 / (scale * batch * temperature * temperature))
+            # The temperature is a device tensor here; scale was formed for T = 1 and the kernels completed it
+            # with 1/T (Stable: 1/sqrt(T)), so the same factor is applied in tensor arithmetic: no host read.
+            t32 = temperature.to(torch.float32).reshape(())
+            scale_t = scale / (torch.sqrt(t32) if stable else t32)
+            dt = -sum_g_s[0] / (scale_t * batch * t32 * t32)
             ctx.meclip_dt = dt.reshape(t_param.shape).to(t_param.dtype)
         if post_x and dx is not None:
             dx = ops.normalize_bwd(dx, x_hat, inv_x, x_dtype, d)
         if post_y and dy is not None:
             dy = ops.normalize_bwd(dy, y_hat, inv_y, y_dtype, d)
+        ops.post_status(x_hat.device)       # looked at by the next forward, without stalling this step
         return (dx if need[0] else None), (dy if want_dy else None)
 
     @staticmethod

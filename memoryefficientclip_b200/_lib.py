@@ -25,6 +25,8 @@ SIGNATURES = {
     "meclip_status_string": (c_char_p, [c_int]),
     "meclip_last_error": (c_int, [c_char_p, c_size_t]),
     "meclip_read_status": (c_int, [c_void_p, c_void_p]),
+    "meclip_bind_device_scalars": (c_int, [c_void_p, c_void_p, c_int]),
+    "meclip_debug_wait_probe": (c_int, [ctypes.c_uint64, c_void_p, c_void_p]),
     "meclip_debug_set_blocking": (c_int, [c_int64, c_int64]),
     "meclip_debug_set_trace": (c_int, [c_void_p, c_size_t]),
     "meclip_launch_count": (ctypes.c_longlong, []),

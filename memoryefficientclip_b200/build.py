@@ -13,7 +13,9 @@ PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG_DIR, "csrc")
 LIB_PATH = os.path.join(PKG_DIR, "libmeclip_sm100.so")
 SOURCES = ["meclip.cu"]
-HEADERS = ["sm100_ptx.cuh", "umma_gemm.cuh", os.path.join("..", "..", "include", "meclip.h")]
+# every header under csrc/ plus the public one: an edit to any of them makes the library stale
+HEADERS = sorted(f for f in os.listdir(CSRC) if f.endswith((".cuh", ".h"))) + [
+    os.path.join("..", "..", "include", "meclip.h")]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

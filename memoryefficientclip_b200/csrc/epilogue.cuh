@@ -13,8 +13,8 @@ namespace meclip {
 // that form, not as softplus(a) - a, so that the many tiny off-diagonal terms of a row are never
 // added to a large number.
 template <bool SIG>
-__device__ __forceinline__ float fwd_value(float s, const GemmParams& p, bool flip = false) {
-    float u = fmaf(s, p.fmul, p.fadd);
+__device__ __forceinline__ float fwd_value(float s, float fmul, float fadd, bool flip = false) {
+    float u = fmaf(s, fmul, fadd);
     if (!SIG) return ex2_approx(u);
     if (flip) u = -u;
     // log2(1 + x), x = 2^-|u| in (0, 1]: lg2.approx has an ABSOLUTE error near 1, which would dominate the
@@ -27,20 +27,20 @@ __device__ __forceinline__ float fwd_value(float s, const GemmParams& p, bool fl
 // Factor of the gradient coefficient: exp2(u), or sigmoid(a) = 1 / (1 + 2^-u) with u = a log2(e)
 // (relative accuracy also for the very small sigmoids of far-apart pairs).
 template <bool SIG>
-__device__ __forceinline__ float coef_value(float s, const GemmParams& p) {
-    const float u = fmaf(s, p.fmul, p.fadd);
+__device__ __forceinline__ float coef_value(float s, float fmul, float fadd) {
+    const float u = fmaf(s, fmul, fadd);
     if (!SIG) return ex2_approx(u);
     return rcp_approx(1.f + ex2_approx(-u));
 }
 
 template <bool SIG>
-__device__ __forceinline__ void sums_chunk(const uint32_t (&v)[32], const GemmParams& p, bool full_tile, bool rvalid,
-                                           int col_base, bool want_cols, float (&cacc)[32], float& ra0, float& ra1,
-                                           float& ra2, float& ra3, int jdc) {
+__device__ __forceinline__ void sums_chunk(const uint32_t (&v)[32], const GemmParams& p, float fmul, float fadd,
+                                           bool full_tile, bool rvalid, int col_base, bool want_cols,
+                                           float (&cacc)[32], float& ra0, float& ra1, float& ra2, float& ra3, int jdc) {
     if (SIG && jdc >= -1 && __any_sync(0xffffffffu, jdc >= 0)) {      // a chunk the diagonal runs through
 #pragma unroll
         for (int c = 0; c < 32; ++c) {
-            float e = fwd_value<SIG>(__uint_as_float(v[c]), p, c == jdc);
+            float e = fwd_value<SIG>(__uint_as_float(v[c]), fmul, fadd, c == jdc);
             if (!rvalid || col_base + c >= p.n) e = 0.f;
             ra0 += e;
         }
@@ -49,17 +49,17 @@ __device__ __forceinline__ void sums_chunk(const uint32_t (&v)[32], const GemmPa
     if (full_tile) {
 #pragma unroll
         for (int c = 0; c < 32; c += 4) {
-            const float e0 = fwd_value<SIG>(__uint_as_float(v[c]), p);
-            const float e1 = fwd_value<SIG>(__uint_as_float(v[c + 1]), p);
-            const float e2 = fwd_value<SIG>(__uint_as_float(v[c + 2]), p);
-            const float e3 = fwd_value<SIG>(__uint_as_float(v[c + 3]), p);
+            const float e0 = fwd_value<SIG>(__uint_as_float(v[c]), fmul, fadd);
+            const float e1 = fwd_value<SIG>(__uint_as_float(v[c + 1]), fmul, fadd);
+            const float e2 = fwd_value<SIG>(__uint_as_float(v[c + 2]), fmul, fadd);
+            const float e3 = fwd_value<SIG>(__uint_as_float(v[c + 3]), fmul, fadd);
             ra0 += e0; ra1 += e1; ra2 += e2; ra3 += e3;
             if (want_cols) { cacc[c] += e0; cacc[c + 1] += e1; cacc[c + 2] += e2; cacc[c + 3] += e3; }
         }
     } else {
 #pragma unroll
         for (int c = 0; c < 32; ++c) {
-            float e = fwd_value<SIG>(__uint_as_float(v[c]), p);
+            float e = fwd_value<SIG>(__uint_as_float(v[c]), fmul, fadd);
             if (!rvalid || col_base + c >= p.n) e = 0.f;
             ra0 += e;
             if (want_cols) cacc[c] += e;
@@ -68,15 +68,15 @@ __device__ __forceinline__ void sums_chunk(const uint32_t (&v)[32], const GemmPa
 }
 
 template <bool SIG>
-__device__ __forceinline__ void coef_chunk(const uint32_t (&v)[32], const GemmParams& p, float inv_r,
+__device__ __forceinline__ void coef_chunk(const uint32_t (&v)[32], float fmul, float fadd, float inv_r,
                                            const float* icol_chunk, float (&gv)[32]) {
 #pragma unroll
     for (int c = 0; c < 32; c += 4) {
         const float4 ic = *reinterpret_cast<const float4*>(icol_chunk + c);   // broadcast read
-        gv[c] = coef_value<SIG>(__uint_as_float(v[c]), p) * (inv_r + ic.x);
-        gv[c + 1] = coef_value<SIG>(__uint_as_float(v[c + 1]), p) * (inv_r + ic.y);
-        gv[c + 2] = coef_value<SIG>(__uint_as_float(v[c + 2]), p) * (inv_r + ic.z);
-        gv[c + 3] = coef_value<SIG>(__uint_as_float(v[c + 3]), p) * (inv_r + ic.w);
+        gv[c] = coef_value<SIG>(__uint_as_float(v[c]), fmul, fadd) * (inv_r + ic.x);
+        gv[c + 1] = coef_value<SIG>(__uint_as_float(v[c + 1]), fmul, fadd) * (inv_r + ic.y);
+        gv[c + 2] = coef_value<SIG>(__uint_as_float(v[c + 2]), fmul, fadd) * (inv_r + ic.z);
+        gv[c + 3] = coef_value<SIG>(__uint_as_float(v[c + 3]), fmul, fadd) * (inv_r + ic.w);
     }
 }
 
@@ -84,12 +84,34 @@ static constexpr int COL_SLOTS = MECLIP_STRIPS ? MAX_BN / 64 : 1;   // 32-column
 
 struct EpiState {        // per-thread state that lives across tiles
     int stores_in_flight = 0;   // COEF: lane 0's outstanding TMA-store groups
-    float gscale = 1.f;         // COEF: *grad_out
+    float gscale = 1.f;         // COEF: *grad_out (times a power of the device-resident temperature, if any)
+    float fmul = 0.f, fadd = 0.f;   // the elementwise function's affine part, from the host or from device scalars
     // SUMS: column sums of this thread's row, kept in registers over a strip of tiles that share
     // their columns; reduced across rows (shuffles, shared memory, atomics) once per strip
     float cacc[COL_SLOTS][32] = {};
     int strip_n0 = -1;          // first column of the tiles accumulated so far, -1 = nothing pending
 };
+
+// Per-thread set-up of the epilogue state: the affine part of the elementwise function and the
+// coefficient scale, from the host values or from scalars that live on the device.
+template <int EPI>
+__device__ __forceinline__ void epilogue_init(const GemmParams& p, EpiState& st) {
+    st.fmul = p.fmul;
+    st.fadd = p.fadd;
+    float gfac = 1.f;
+    if (p.t_dev != nullptr) {
+        const float t = __ldg(p.t_dev);
+        if (p.sigmoid) {
+            st.fmul = t * 1.4426950408889634f;
+            if (p.b_dev != nullptr) st.fadd = __ldg(p.b_dev) * 1.4426950408889634f;
+        } else {
+            st.fmul = 1.4426950408889634f / t;
+            st.fadd = -st.fmul;
+        }
+        gfac = p.g_rule == 1 ? 1.f / t : p.g_rule == 2 ? rsqrtf(t) : p.g_rule == 3 ? t : 1.f;
+    }
+    if (EPI == EPI_COEF) st.gscale = (p.grad_out ? __ldg(p.grad_out) : 1.f) * gfac;
+}
 
 // SUMS: add the pending column accumulators of all eight warps into col_sum and clear them.
 // Every epilogue thread must call this at the same point (it uses the epilogue named barrier).
@@ -162,8 +184,8 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, const CUtenso
 #pragma unroll
             for (int c = 0; c < 32; ++c) e[c] = 0.f;
             const int jdc_s = (diag_here && jd >= 0 && (jd >> 5) == ch) ? (jd & 31) : -1;
-            if (p.sigmoid) sums_chunk<true>(v, p, full_tile, rvalid, n0 + ch * 32, want_cols, e, ra0, ra1, ra2, ra3, jdc_s);
-            else           sums_chunk<false>(v, p, full_tile, rvalid, n0 + ch * 32, want_cols, e, ra0, ra1, ra2, ra3, -1);
+            if (p.sigmoid) sums_chunk<true>(v, p, st.fmul, st.fadd, full_tile, rvalid, n0 + ch * 32, want_cols, e, ra0, ra1, ra2, ra3, jdc_s);
+            else           sums_chunk<false>(v, p, st.fmul, st.fadd, full_tile, rvalid, n0 + ch * 32, want_cols, e, ra0, ra1, ra2, ra3, -1);
             if (want_cols) {
                 const float cs = warp_transpose_reduce32(e, lane);
                 colpart[q][ch * 32 + lane] = cs;
@@ -202,8 +224,8 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, const CUtenso
                     for (int c = 0; c < 32; ++c) sdiag = (c == jdc) ? __uint_as_float(v[c]) : sdiag;
                 }
                 const int jdc_s = (diag_here && jd >= 0 && (jd >> 5) == ch) ? (jd & 31) : -1;
-                if (p.sigmoid) sums_chunk<true>(v, p, full_tile, rvalid, n0 + ch * 32, want_cols, st.cacc[k], ra0, ra1, ra2, ra3, jdc_s);
-                else           sums_chunk<false>(v, p, full_tile, rvalid, n0 + ch * 32, want_cols, st.cacc[k], ra0, ra1, ra2, ra3, -1);
+                if (p.sigmoid) sums_chunk<true>(v, p, st.fmul, st.fadd, full_tile, rvalid, n0 + ch * 32, want_cols, st.cacc[k], ra0, ra1, ra2, ra3, jdc_s);
+                else           sums_chunk<false>(v, p, st.fmul, st.fadd, full_tile, rvalid, n0 + ch * 32, want_cols, st.cacc[k], ra0, ra1, ra2, ra3, -1);
             }
         }
         tc_fence_before();
@@ -242,15 +264,15 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, const CUtenso
                 tmem_ld32(taddr + ch * 32, v);
                 tmem_ld_wait();
                 float gv[32];
-                if (p.sigmoid) coef_chunk<true>(v, p, inv_r, &tail->icol[ch * 32], gv);
-                else           coef_chunk<false>(v, p, inv_r, &tail->icol[ch * 32], gv);
+                if (p.sigmoid) coef_chunk<true>(v, st.fmul, st.fadd, inv_r, &tail->icol[ch * 32], gv);
+                else           coef_chunk<false>(v, st.fmul, st.fadd, inv_r, &tail->icol[ch * 32], gv);
                 if (diag_here) {      // warp-uniform: only tiles that cross the diagonal pay for the correction
                     const int jdc = (jd >= 0 && (jd >> 5) == ch) ? (jd & 31) : -1;
                     if (p.sigmoid) {
                         // sigmoid(a) - 1 = -1 / (1 + 2^u), computed in that form: no cancellation for a confident pair
 #pragma unroll
                         for (int c = 0; c < 32; ++c) {
-                            const float u = fmaf(__uint_as_float(v[c]), p.fmul, p.fadd);
+                            const float u = fmaf(__uint_as_float(v[c]), st.fmul, st.fadd);
                             gv[c] = (c == jdc) ? -dsub * rcp_approx(1.f + ex2_approx(u)) : gv[c];
                         }
                     } else {

@@ -14,6 +14,8 @@
 #include <vector>
 #include <string>
 
+#include <nvtx3/nvToolsExt.h>
+
 #include "../../include/meclip.h"
 #include "umma_gemm.cuh"
 #include "umma_gemm2.cuh"
@@ -76,9 +78,36 @@ struct ScopedTiming {   // brackets one launch with events on its stream while p
     }
 };
 
+// NVTX range around an entry point (header-only NVTX: a no-op unless a profiler is attached)
+struct NvtxRange {
+    explicit NvtxRange(const char* name) { nvtxRangePushA(name); }
+    ~NvtxRange() { nvtxRangePop(); }
+};
+
 // test hook: device buffer for the in-kernel trace of CTA 0 (null = off)
 static unsigned long long* g_trace_buf = nullptr;
 static unsigned int g_trace_capacity = 0;
+
+// Scalars that live on the device (learnable temperature, logit scale / bias): bound by
+// meclip_bind_device_scalars for the next tile-pass call of the same host thread, consumed by it.
+struct DeviceScalars { const float* t = nullptr; const float* b = nullptr; int g_rule = 0; };
+static thread_local DeviceScalars t_scalars;
+static DeviceScalars take_scalars() {
+    const DeviceScalars ds = t_scalars;
+    t_scalars = DeviceScalars();
+    return ds;
+}
+
+// Bound of every barrier wait inside the tile kernels: 2 s unless MECLIP_WAIT_LIMIT_MS says otherwise
+// (a context that is time-sliced with other processes for longer than the limit would trip it spuriously).
+static unsigned long long wait_limit_ns() {
+    static const unsigned long long ns = []() -> unsigned long long {
+        const char* v = std::getenv("MECLIP_WAIT_LIMIT_MS");
+        const long long ms = v ? std::atoll(v) : 0;
+        return ms > 0 ? (unsigned long long)ms * 1000000ull : WAIT_LIMIT_NS;
+    }();
+    return ns;
+}
 
 static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 static inline size_t round_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
@@ -270,12 +299,17 @@ lit_fused_stats_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const
 template <typename TOut>
 __global__ void __launch_bounds__(ROW_KERNEL_THREADS)
 lit_fused_bwd_kernel(const float* __restrict__ u, long long ldu, const __nv_bfloat16* __restrict__ y, long long ldy,
-                     const float* __restrict__ row_sum, const float* __restrict__ grad_out, float grad_scale, long long rows,
+                     const float* __restrict__ row_sum, const float* __restrict__ grad_out, float grad_scale,
+                     const float* __restrict__ t_dev, int g_rule, long long rows,
                      int d, int vec_out, TOut* __restrict__ dx, long long lddx) {
     const long long row = (long long)blockIdx.x * (ROW_KERNEL_THREADS / 32) + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
     if (row >= rows) return;
-    const float g = grad_scale * (grad_out != nullptr ? __ldg(grad_out) : 1.f);
+    float g = grad_scale * (grad_out != nullptr ? __ldg(grad_out) : 1.f);
+    if (t_dev != nullptr) {       // temperature on the device: grad_scale was formed with T = 1
+        const float t = __ldg(t_dev);
+        g *= g_rule == 1 ? 1.f / t : g_rule == 2 ? rsqrtf(t) : 1.f;
+    }
     const float gr = g / __ldg(row_sum + row);
     const float* ur = u + row * ldu;
     const __nv_bfloat16* yr = y + row * ldy;
@@ -355,9 +389,11 @@ accumulate_f32_kernel(float* __restrict__ dst, const float* __restrict__ src, lo
 // loss (+)= scale * sum_i [ w (log r_i + log c_i) - (s_ii - 1)/T ]: one block, fixed order.
 __global__ void __launch_bounds__(1024)
 loss_finalize_kernel(const float* __restrict__ r, const float* __restrict__ c, const float* __restrict__ diag,
-                     long long n, float inv_t, float scale, int accumulate, float* __restrict__ loss) {
+                     long long n, float inv_t, const float* __restrict__ t_dev, float scale, int accumulate,
+                     float* __restrict__ loss) {
     __shared__ double part[1024];
     double acc = 0.0;
+    if (t_dev != nullptr) inv_t = 1.f / __ldg(t_dev);       // a temperature that lives on the device
     // eight independent elements per thread and trip, so that the loads of a trip are all in flight together
     // (one block with one load at a time is bound by the load latency); out-of-range slots contribute 0
     for (long long i0 = threadIdx.x; i0 < n; i0 += 8 * 1024) {
@@ -418,6 +454,25 @@ siglip_finalize_kernel(const float* __restrict__ r, const float* __restrict__ di
         const float v = (float)(part[0] * (double)scale);
         *loss = accumulate ? *loss + v : v;
     }
+}
+
+// Test hook: a bounded wait that is meant to run out.  One CTA initialises an mbarrier nobody ever arrives
+// on and waits on it with the tile kernels' own wait routine; when the limit has passed the wait returns
+// false, the CTA records that in the status word and ends normally (no TMA, no tensor memory involved).
+__global__ void __launch_bounds__(64)
+wait_probe_kernel(unsigned long long limit_ns, int* __restrict__ status) {
+    __shared__ unsigned long long bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        mbar_init(smem_u32(&bar), 1);
+        fence_barrier_init();
+    }
+    __syncthreads();
+    // warp 0 waits on its own time limit, warp 1 also watches the abort flag (the two ways a role gives up)
+    const bool ok = mbar_wait(smem_u32(&bar), 0u, &abort_flag, threadIdx.x >= 32, limit_ns);
+    __syncthreads();
+    if (threadIdx.x == 0 && (!ok || abort_flag) && status != nullptr) atomicExch(status, 1);
 }
 
 // ------------------------------------------------------------------------------------
@@ -661,6 +716,7 @@ static int launch_gemm(int epi, const Operand& a, const Operand& b, long long m,
     p.k_steps = (int)((k + BK - 1) / BK);
     p.trace = g_trace_buf;
     p.trace_capacity = g_trace_capacity;
+    p.wait_limit_ns = wait_limit_ns();
     // Tile ids walk group_m row tiles of one column tile, then the next column tile.  The sums pass wants tall
     // groups (a strip shares its columns).  A contraction streams its A operand (the coefficient panel) from HBM:
     // with short groups the column tiles that share panel rows run at the same time and hit L2, which is worth
@@ -697,8 +753,17 @@ static int launch_gemm(int epi, const Operand& a, const Operand& b, long long m,
     if (env_max_stages >= 2 && stages > env_max_stages) stages = env_max_stages;
     if (env_static) p.tile_counter = nullptr;
     if (stages < 2) return fail(MECLIP_EINVAL, "tile does not fit shared memory");
+    if (pair) p.num_m_tiles = (int)((m + PAIR_BM - 1) / PAIR_BM);
+    if (epi == EPI_OUT && p.bn_last < bn && p.num_n_tiles >= 2) {
+        // Narrow tiles last (MECLIP_NARROW_LAST: 0 never, 1 when the launch has fewer than four waves of tiles,
+        // 2 always).  Few long tiles: the short ones even out the last wave.  Many tiles: the walk that keeps a
+        // row tile's column tiles together re-uses the A operand from L2 and wins.
+        static const int env_narrow = []() { const char* v = std::getenv("MECLIP_NARROW_LAST"); return v ? std::atoi(v) : 1; }();
+        const long long slots = pair ? sm_count() / 2 : sm_count();
+        const long long tiles_all = (long long)p.num_m_tiles * p.num_n_tiles;
+        if (env_narrow == 2 || (env_narrow == 1 && tiles_all < 4 * slots)) p.narrow_last = 1;
+    }
     if (pair) {
-        p.num_m_tiles = (int)((m + PAIR_BM - 1) / PAIR_BM);
         p.idesc = umma_idesc_bf16(PAIR_BM, bn, a.mn_major ? 1 : 0, 0);
         p.idesc_last = p.bn_last < bn ? umma_idesc_bf16(PAIR_BM, p.bn_last, a.mn_major ? 1 : 0, 0) : p.idesc;
         p.stage_bytes = A_STAGE_BYTES + (bn / 2) * BK * 2;
@@ -748,10 +813,27 @@ struct GradPlan {
 // test hook: smaller blocks so that small problems exercise the multi-block paths (0 = defaults)
 static long long g_row_block_override = 0, g_panel_bytes_override = 0;
 
-static GradPlan plan_grad(long long rows, long long cols, long long d, bool transposed_copies = true) {
+// A/B switches: MECLIP_ROW_BLOCK (rows, a multiple of 128) and MECLIP_PANEL_MIB change the built-in blocking
+// for the whole process (the test hook above takes precedence).
+static long long env_ll(const char* name) {
+    const char* v = std::getenv(name);
+    return v ? std::atoll(v) : 0;
+}
+
+// honour_overrides == false: the built-in constants, whatever the test hook or the environment say
+// (meclip_grad_static promises a plan that fits its fixed scratch).
+static GradPlan plan_grad(long long rows, long long cols, long long d, bool transposed_copies = true,
+                          bool honour_overrides = true) {
     GradPlan g;
-    const long long row_block_max = g_row_block_override > 0 ? g_row_block_override : ROW_BLOCK;
-    const long long panel_bytes = g_panel_bytes_override > 0 ? g_panel_bytes_override : PANEL_BYTES;
+    static const long long env_row_block = env_ll("MECLIP_ROW_BLOCK") / 128 * 128;
+    static const long long env_panel_bytes = env_ll("MECLIP_PANEL_MIB") << 20;
+    long long row_block_max = ROW_BLOCK, panel_bytes = PANEL_BYTES;
+    if (honour_overrides) {
+        if (env_row_block > 0) row_block_max = env_row_block;
+        if (env_panel_bytes > 0) panel_bytes = env_panel_bytes;
+        if (g_row_block_override > 0) row_block_max = g_row_block_override;
+        if (g_panel_bytes_override > 0) panel_bytes = g_panel_bytes_override;
+    }
     g.row_block = rows < row_block_max ? rows : row_block_max;
     long long w = panel_bytes / (g.row_block * 2) / 256 * 256;
     if (w < 256) w = 256;
@@ -1001,22 +1083,27 @@ int meclip_normalize_bwd(const void* g, int g_dtype, int64_t ldg, const void* x_
     return MECLIP_OK;
 }
 
-int meclip_sum_exp(int kind, const void* x_bf16, const void* y_bf16, int64_t rows, int64_t cols, int64_t d,
-                   int64_t ldx, int64_t ldy, float temperature, int64_t row_off, int64_t col_off, float* row_sum,
-                   float* col_sum, float* diag_s, unsigned int* tile_counter, int* status, void* stream) {
+}  // extern "C"
+
+namespace meclip {
+static int sum_exp_impl(int kind, const void* x_bf16, const void* y_bf16, int64_t rows, int64_t cols, int64_t d,
+                        int64_t ldx, int64_t ldy, float temperature, int64_t row_off, int64_t col_off, float* row_sum,
+                        float* col_sum, float* diag_s, unsigned int* tile_counter, int* status, void* stream,
+                        const DeviceScalars& ds) {
     if (kind != MECLIP_CLIP && kind != MECLIP_LIT) return fail(MECLIP_EINVAL, "sum_exp: bad kind %d", kind);
     if (x_bf16 == nullptr || y_bf16 == nullptr || row_sum == nullptr || diag_s == nullptr)
         return fail(MECLIP_EINVAL, "sum_exp: null pointer");
     if (kind == MECLIP_CLIP && col_sum == nullptr) return fail(MECLIP_EINVAL, "sum_exp: CLIP needs col_sum");
     if (rows < 1 || cols < 1 || d < 8 || d % 8 != 0 || ldx < d || ldy < d)
         return fail(MECLIP_EINVAL, "sum_exp: need rows, cols >= 1, d a multiple of 8 (got %lld), ld >= d", (long long)d);
-    if (!(temperature > 0.f)) return fail(MECLIP_EINVAL, "sum_exp: temperature must be positive");
+    if (ds.t == nullptr && !(temperature > 0.f)) return fail(MECLIP_EINVAL, "sum_exp: temperature must be positive");
     int rc = check_device();
     if (rc) return rc;
     GemmParams p;
     std::memset(&p, 0, sizeof(p));
     p.fmul = 1.4426950408889634f / temperature;
     p.fadd = -p.fmul;
+    p.t_dev = ds.t;
     p.diag_shift = (long long)row_off - (long long)col_off;
     p.row_sum = row_sum;
     p.col_sum = (kind == MECLIP_CLIP) ? col_sum : nullptr;
@@ -1028,17 +1115,44 @@ int meclip_sum_exp(int kind, const void* x_bf16, const void* y_bf16, int64_t row
     return launch_gemm(EPI_SUMS, a, b, rows, cols, d, pick_bn(cols), p, (cudaStream_t)stream);
 }
 
-int meclip_loss_finalize(int kind, const float* row_sum, const float* col_sum, const float* diag_s, int64_t n,
-                         float temperature, float scale, int accumulate, float* loss_out, void* stream) {
+static int loss_finalize_impl(int kind, const float* row_sum, const float* col_sum, const float* diag_s, int64_t n,
+                              float temperature, float scale, int accumulate, float* loss_out, void* stream,
+                              const DeviceScalars& ds) {
     if (kind != MECLIP_CLIP && kind != MECLIP_LIT) return fail(MECLIP_EINVAL, "loss_finalize: bad kind %d", kind);
-    if (row_sum == nullptr || diag_s == nullptr || loss_out == nullptr || n < 1 || !(temperature > 0.f))
+    if (row_sum == nullptr || diag_s == nullptr || loss_out == nullptr || n < 1 || (ds.t == nullptr && !(temperature > 0.f)))
         return fail(MECLIP_EINVAL, "loss_finalize: bad argument");
     if (kind == MECLIP_CLIP && col_sum == nullptr) return fail(MECLIP_EINVAL, "loss_finalize: CLIP needs col_sum");
     ScopedTiming timing((cudaStream_t)stream, TAG_ROW, (double)n * (kind == MECLIP_CLIP ? 12.0 : 8.0));
     loss_finalize_kernel<<<1, 1024, 0, (cudaStream_t)stream>>>(row_sum, kind == MECLIP_CLIP ? col_sum : nullptr, diag_s, n,
-                                                               1.f / temperature, scale, accumulate, loss_out);
+                                                               1.f / temperature, ds.t, scale, accumulate, loss_out);
     MECLIP_CUDA(cudaGetLastError());
     return MECLIP_OK;
+}
+}  // namespace meclip
+
+extern "C" {
+
+int meclip_bind_device_scalars(const float* temperature_or_scale, const float* logit_bias, int grad_scale_rule) {
+    if (grad_scale_rule < 0 || grad_scale_rule > 3) return fail(MECLIP_EINVAL, "bind_device_scalars: bad rule %d", grad_scale_rule);
+    t_scalars.t = temperature_or_scale;
+    t_scalars.b = logit_bias;
+    t_scalars.g_rule = temperature_or_scale != nullptr ? grad_scale_rule : 0;
+    return MECLIP_OK;
+}
+
+int meclip_sum_exp(int kind, const void* x_bf16, const void* y_bf16, int64_t rows, int64_t cols, int64_t d,
+                   int64_t ldx, int64_t ldy, float temperature, int64_t row_off, int64_t col_off, float* row_sum,
+                   float* col_sum, float* diag_s, unsigned int* tile_counter, int* status, void* stream) {
+    const DeviceScalars ds = take_scalars();
+    NvtxRange range("meclip_sum_exp");
+    return sum_exp_impl(kind, x_bf16, y_bf16, rows, cols, d, ldx, ldy, temperature, row_off, col_off, row_sum, col_sum,
+                        diag_s, tile_counter, status, stream, ds);
+}
+
+int meclip_loss_finalize(int kind, const float* row_sum, const float* col_sum, const float* diag_s, int64_t n,
+                         float temperature, float scale, int accumulate, float* loss_out, void* stream) {
+    const DeviceScalars ds = take_scalars();
+    return loss_finalize_impl(kind, row_sum, col_sum, diag_s, n, temperature, scale, accumulate, loss_out, stream, ds);
 }
 
 size_t meclip_grad_workspace_bytes(int64_t rows, int64_t cols, int64_t d) {
@@ -1057,7 +1171,9 @@ static int grad_impl(int kind, const void* x_bf16, const void* y_bf16, int64_t r
                      const float* col_sum, const float* grad_out, float grad_scale, void* dx, int dx_mode, int64_t lddx,
                      void* dy, int dy_mode, int64_t lddy, void* workspace, size_t workspace_bytes, int* status,
                      cudaStream_t s0, bool overlap, bool transposed_copies, float* sg_acc = nullptr,
-                     float logit_scale = 0.f, float logit_bias = 0.f, int64_t n_extra = 0, bool plain_e = false) {
+                     float logit_scale = 0.f, float logit_bias = 0.f, int64_t n_extra = 0, bool plain_e = false,
+                     const DeviceScalars& ds = DeviceScalars(), bool honour_overrides = true) {
+    NvtxRange range("meclip_grad");
     // kind MECLIP_SIGLIP: `temperature` is unused, the element function is sigmoid(logit_scale * s + logit_bias),
     // there are no row / column sums and both inputs get a gradient
     // plain_e (LiT only): the panel holds E itself (no 1/r, no diagonal term) and the contraction runs over
@@ -1078,10 +1194,10 @@ static int grad_impl(int kind, const void* x_bf16, const void* y_bf16, int64_t r
         return fail(MECLIP_EINVAL, "grad: outputs must be 16-byte aligned with pitches multiples of 8");
     const bool want_dx = dx != nullptr, want_dy = dy != nullptr;
     if ((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0) return fail(MECLIP_EINVAL, "grad: workspace must be 256-byte aligned");
-    if (!siglip && !(temperature > 0.f)) return fail(MECLIP_EINVAL, "grad: temperature must be positive");
+    if (!siglip && ds.t == nullptr && !(temperature > 0.f)) return fail(MECLIP_EINVAL, "grad: temperature must be positive");
     int rc = check_device();
     if (rc) return rc;
-    const GradPlan plan = plan_grad(rows, cols, dn, transposed_copies);
+    const GradPlan plan = plan_grad(rows, cols, dn, transposed_copies, honour_overrides);
     if (workspace_bytes < plan.total())
         return fail(MECLIP_ENOSPC, "grad: workspace %zu < %zu bytes", workspace_bytes, plan.total());
     const bool clip = (kind == MECLIP_CLIP);
@@ -1164,6 +1280,9 @@ static int grad_impl(int kind, const void* x_bf16, const void* y_bf16, int64_t r
                 p.coef = clip ? 0.5f * grad_scale : grad_scale;
                 p.dcoef = plain_e ? 0.f : grad_scale;
                 p.sg_acc = sg_acc;
+                p.t_dev = ds.t;
+                p.b_dev = ds.b;
+                p.g_rule = ds.g_rule;
                 p.tile_counter = counters + 3 * t;
                 p.status = status;
                 Operand a{X + r0 * ldx, ldx, false}, b{Y + c0 * ldy, ldy, false};
@@ -1250,9 +1369,10 @@ int meclip_grad(int kind, const void* x_bf16, const void* y_bf16, int64_t rows, 
                 const float* col_sum, const float* grad_out, float grad_scale, void* dx, int dx_mode, int64_t lddx,
                 void* dy, int dy_mode, int64_t lddy, void* workspace, size_t workspace_bytes, int* status,
                 void* stream) {
+    const DeviceScalars ds = take_scalars();
     return grad_impl(kind, x_bf16, y_bf16, rows, cols, d, ldx, ldy, temperature, row_off, col_off, row_sum, col_sum,
                      grad_out, grad_scale, dx, dx_mode, lddx, dy, dy_mode, lddy, workspace, workspace_bytes, status,
-                     (cudaStream_t)stream, overlap_allowed(), transposes_allowed());
+                     (cudaStream_t)stream, overlap_allowed(), transposes_allowed(), nullptr, 0.f, 0.f, 0, false, ds);
 }
 
 int meclip_grad_t(int kind, const void* x_bf16, const void* y_bf16, int64_t rows, int64_t cols, int64_t d, int64_t ldx,
@@ -1260,10 +1380,11 @@ int meclip_grad_t(int kind, const void* x_bf16, const void* y_bf16, int64_t rows
                   const float* col_sum, const float* grad_out, float grad_scale, void* dx, int dx_mode, int64_t lddx,
                   void* dy, int dy_mode, int64_t lddy, float* sum_g_s, void* workspace, size_t workspace_bytes,
                   int* status, void* stream) {
+    const DeviceScalars ds = take_scalars();
     if (sum_g_s == nullptr) return fail(MECLIP_EINVAL, "grad_t: sum_g_s is null");
     return grad_impl(kind, x_bf16, y_bf16, rows, cols, d, ldx, ldy, temperature, row_off, col_off, row_sum, col_sum,
                      grad_out, grad_scale, dx, dx_mode, lddx, dy, dy_mode, lddy, workspace, workspace_bytes, status,
-                     (cudaStream_t)stream, overlap_allowed(), transposes_allowed(), sum_g_s);
+                     (cudaStream_t)stream, overlap_allowed(), transposes_allowed(), sum_g_s, 0.f, 0.f, 0, false, ds);
 }
 
 // ---- LiT forward that already holds the gradient's contraction ------------------------------------
@@ -1279,11 +1400,13 @@ int meclip_lit_extend(void* y_bf16, int64_t rows, int64_t d, int64_t ldy, void* 
 int meclip_lit_fused_forward(const void* x_bf16, const void* y_ext_bf16, int64_t rows, int64_t cols, int64_t d, int64_t ldx,
                              int64_t ldy, float temperature, int64_t row_off, int64_t col_off, float* u, int u_mode,
                              int64_t ldu, void* workspace, size_t workspace_bytes, int* status, void* stream) {
+    DeviceScalars ds = take_scalars();
+    ds.g_rule = 0;            // the panel holds E itself here: no gradient scale to adjust
     if (u == nullptr) return fail(MECLIP_EINVAL, "lit_fused_forward: u is null");
     if (u_mode != MECLIP_STORE_F32 && u_mode != MECLIP_ACCUM_F32) return fail(MECLIP_EINVAL, "lit_fused_forward: u is fp32");
     return grad_impl(MECLIP_LIT, x_bf16, y_ext_bf16, rows, cols, d, ldx, ldy, temperature, row_off, col_off, nullptr, nullptr,
                      nullptr, 1.f, u, u_mode, ldu, nullptr, 0, 0, workspace, workspace_bytes, status, (cudaStream_t)stream,
-                     overlap_allowed(), transposes_allowed(), nullptr, 0.f, 0.f, 8, true);
+                     overlap_allowed(), transposes_allowed(), nullptr, 0.f, 0.f, 8, true, ds);
 }
 
 int meclip_lit_fused_stats(const void* x_bf16, int64_t ldx, const void* y_ext_bf16, int64_t ldy, const float* u, int64_t ldu,
@@ -1304,6 +1427,7 @@ int meclip_lit_fused_stats(const void* x_bf16, int64_t ldx, const void* y_ext_bf
 int meclip_lit_fused_backward(const float* u, int64_t ldu, const void* y_ext_bf16, int64_t ldy, const float* row_sum,
                               const float* grad_out, float grad_scale, int64_t rows, int64_t d, void* dx, int dx_dtype,
                               int64_t lddx, void* stream) {
+    const DeviceScalars ds = take_scalars();
     if (u == nullptr || y_ext_bf16 == nullptr || row_sum == nullptr || dx == nullptr)
         return fail(MECLIP_EINVAL, "lit_fused_backward: null pointer");
     if (rows < 1 || d < 1 || ldu < d || ldy < d || lddx < d || ldu % 4 != 0 || ldy % 8 != 0 || !aligned16(u) || !aligned16(y_ext_bf16))
@@ -1316,11 +1440,11 @@ int meclip_lit_fused_backward(const float* u, int64_t ldu, const void* y_ext_bf1
     const __nv_bfloat16* y = (const __nv_bfloat16*)y_ext_bf16;
     ScopedTiming timing(s, TAG_NORM_BWD, (double)rows * (double)d * (6.0 + oelt));
     if (dx_dtype == MECLIP_F32)
-        lit_fused_bwd_kernel<float><<<grid, ROW_KERNEL_THREADS, 0, s>>>(u, ldu, y, ldy, row_sum, grad_out, grad_scale, rows, (int)d, vec_out, (float*)dx, lddx);
+        lit_fused_bwd_kernel<float><<<grid, ROW_KERNEL_THREADS, 0, s>>>(u, ldu, y, ldy, row_sum, grad_out, grad_scale, ds.t, ds.g_rule, rows, (int)d, vec_out, (float*)dx, lddx);
     else if (dx_dtype == MECLIP_BF16)
-        lit_fused_bwd_kernel<__nv_bfloat16><<<grid, ROW_KERNEL_THREADS, 0, s>>>(u, ldu, y, ldy, row_sum, grad_out, grad_scale, rows, (int)d, vec_out, (__nv_bfloat16*)dx, lddx);
+        lit_fused_bwd_kernel<__nv_bfloat16><<<grid, ROW_KERNEL_THREADS, 0, s>>>(u, ldu, y, ldy, row_sum, grad_out, grad_scale, ds.t, ds.g_rule, rows, (int)d, vec_out, (__nv_bfloat16*)dx, lddx);
     else if (dx_dtype == MECLIP_F16)
-        lit_fused_bwd_kernel<__half><<<grid, ROW_KERNEL_THREADS, 0, s>>>(u, ldu, y, ldy, row_sum, grad_out, grad_scale, rows, (int)d, vec_out, (__half*)dx, lddx);
+        lit_fused_bwd_kernel<__half><<<grid, ROW_KERNEL_THREADS, 0, s>>>(u, ldu, y, ldy, row_sum, grad_out, grad_scale, ds.t, ds.g_rule, rows, (int)d, vec_out, (__half*)dx, lddx);
     else
         return fail(MECLIP_EINVAL, "lit_fused_backward: bad output dtype %d", dx_dtype);
     MECLIP_CUDA(cudaGetLastError());
@@ -1331,6 +1455,7 @@ int meclip_lit_fused_backward(const float* u, int64_t ldu, const void* y_ext_bf1
 int meclip_siglip_sum(const void* x_bf16, const void* y_bf16, int64_t rows, int64_t cols, int64_t d, int64_t ldx,
                       int64_t ldy, float logit_scale, float logit_bias, int64_t row_off, int64_t col_off, float* row_sum,
                       float* diag_s, unsigned int* tile_counter, int* status, void* stream) {
+    const DeviceScalars ds = take_scalars();
     if (x_bf16 == nullptr || y_bf16 == nullptr || row_sum == nullptr || diag_s == nullptr)
         return fail(MECLIP_EINVAL, "siglip_sum: null pointer");
     if (rows < 1 || cols < 1 || d < 8 || d % 8 != 0 || ldx < d || ldy < d)
@@ -1342,6 +1467,8 @@ int meclip_siglip_sum(const void* x_bf16, const void* y_bf16, int64_t rows, int6
     p.sigmoid = 1;
     p.fmul = logit_scale * 1.4426950408889634f;
     p.fadd = logit_bias * 1.4426950408889634f;
+    p.t_dev = ds.t;
+    p.b_dev = ds.b;
     p.diag_shift = (long long)row_off - (long long)col_off;
     p.row_sum = row_sum;
     p.col_sum = nullptr;
@@ -1369,14 +1496,18 @@ int meclip_siglip_grad(const void* x_bf16, const void* y_bf16, int64_t rows, int
                        const float* grad_out, float grad_scale, void* dx, int dx_mode, int64_t lddx, void* dy,
                        int dy_mode, int64_t lddy, float* sums, void* workspace, size_t workspace_bytes, int* status,
                        void* stream) {
+    const DeviceScalars ds = take_scalars();
     return grad_impl(MECLIP_SIGLIP, x_bf16, y_bf16, rows, cols, d, ldx, ldy, 1.f, row_off, col_off, nullptr, nullptr,
                      grad_out, grad_scale, dx, dx_mode, lddx, dy, dy_mode, lddy, workspace, workspace_bytes, status,
-                     (cudaStream_t)stream, overlap_allowed(), transposes_allowed(), sums, logit_scale, logit_bias);
+                     (cudaStream_t)stream, overlap_allowed(), transposes_allowed(), sums, logit_scale, logit_bias, 0, false,
+                     ds);
 }
 
 int meclip_loss_forward(int kind, const void* x_bf16, const void* y_bf16, int64_t batch, int64_t d, int64_t ldx,
                         int64_t ldy, float temperature, float* row_sum, float* col_sum, float* diag_s, float* loss_out,
                         unsigned int* tile_counter, int* status, void* stream) {
+    const DeviceScalars ds = take_scalars();
+    NvtxRange range("meclip_loss_forward");
     if (batch < 1 || row_sum == nullptr || diag_s == nullptr || loss_out == nullptr)
         return fail(MECLIP_EINVAL, "loss_forward: bad argument");
     cudaStream_t s = (cudaStream_t)stream;
@@ -1384,11 +1515,11 @@ int meclip_loss_forward(int kind, const void* x_bf16, const void* y_bf16, int64_
     if (kind == MECLIP_CLIP && col_sum != nullptr) MECLIP_CUDA(cudaMemsetAsync(col_sum, 0, (size_t)batch * sizeof(float), s));
     MECLIP_CUDA(cudaMemsetAsync(diag_s, 0, (size_t)batch * sizeof(float), s));
     if (tile_counter != nullptr) MECLIP_CUDA(cudaMemsetAsync(tile_counter, 0, sizeof(unsigned int), s));
-    int rc = meclip_sum_exp(kind, x_bf16, y_bf16, batch, batch, d, ldx, ldy, temperature, 0, 0, row_sum, col_sum, diag_s,
-                            tile_counter, status, stream);
+    int rc = sum_exp_impl(kind, x_bf16, y_bf16, batch, batch, d, ldx, ldy, temperature, 0, 0, row_sum, col_sum, diag_s,
+                          tile_counter, status, stream, ds);
     if (rc) return rc;
-    return meclip_loss_finalize(kind, row_sum, col_sum, diag_s, batch, temperature, 1.0f / (float)batch, 0, loss_out,
-                                stream);
+    return loss_finalize_impl(kind, row_sum, col_sum, diag_s, batch, temperature, 1.0f / (float)batch, 0, loss_out,
+                              stream, ds);
 }
 
 int meclip_loss_backward(int kind, const void* x_bf16, const void* y_bf16, int64_t batch, int64_t d, int64_t ldx,
@@ -1435,6 +1566,7 @@ int meclip_grad_static(int kind, const void* x_bf16, const void* y_bf16, int64_t
                        int64_t ldx, int64_t ldy, float temperature, int64_t row_off, int64_t col_off,
                        const float* row_sum, const float* col_sum, const float* grad_out, float grad_scale, void* dx,
                        int dx_mode, int64_t lddx, void* dy, int dy_mode, int64_t lddy, int* status, void* stream) {
+    const DeviceScalars ds = take_scalars();
     if (rows < 1 || cols < 1) return fail(MECLIP_EINVAL, "grad_static: rows and cols must be >= 1");
     if (rows > STATIC_MAX_ROWS || cols > STATIC_MAX_COLS)
         return fail(MECLIP_ENOSPC,
@@ -1449,9 +1581,20 @@ int meclip_grad_static(int kind, const void* x_bf16, const void* y_bf16, int64_t
     // written.  The tile counters behind it must start at zero and are cleared on the stream first.
     // All launches stay on the caller's stream; no stream, event or memory is created, and the
     // contractions read X and Y as they are (no transposed copies, which would need more scratch).
+    // The plan is made from the built-in constants: the test hook and the environment switches that change the
+    // blocking of meclip_grad do not apply here, so every block within the limit fits the scratch as one panel.
     return grad_impl(kind, x_bf16, y_bf16, rows, cols, d, ldx, ldy, temperature, row_off, col_off, row_sum, col_sum,
                      grad_out, grad_scale, dx, dx_mode, lddx, dy, dy_mode, lddy, scratch, STATIC_SCRATCH_BYTES,
-                     status, (cudaStream_t)stream, false, false);
+                     status, (cudaStream_t)stream, false, false, nullptr, 0.f, 0.f, 0, false, ds, false);
+}
+
+int meclip_debug_wait_probe(uint64_t limit_ns, int* status, void* stream) {
+    if (status == nullptr) return fail(MECLIP_EINVAL, "wait_probe: status is null");
+    if (limit_ns == 0 || limit_ns > 100000000ull) return fail(MECLIP_EINVAL, "wait_probe: limit must be in (0, 100 ms]");
+    ScopedTiming timing((cudaStream_t)stream, TAG_ROW, 0.0);
+    wait_probe_kernel<<<1, 64, 0, (cudaStream_t)stream>>>((unsigned long long)limit_ns, status);
+    MECLIP_CUDA(cudaGetLastError());
+    return MECLIP_OK;
 }
 
 int meclip_debug_gemm(const void* a_bf16, int64_t lda, int a_mn_major, const void* b_bf16, int64_t ldb, int b_mn_major,

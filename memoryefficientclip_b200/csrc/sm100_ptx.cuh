@@ -1,7 +1,8 @@
 // Thin inline-PTX wrappers for the Blackwell (sm_100a) features the loss kernels
 // use: mbarriers, TMA tile loads, tcgen05 MMAs with TMEM accumulators.
-// Every wait on a barrier is bounded: it gives up after WAIT_LIMIT_NS of wall
-// time so that a programming error becomes an error code, never a hung GPU.
+// Every wait on a barrier is bounded: it gives up after a limit of wall time (WAIT_LIMIT_NS
+// unless the host passes another one) so that a programming error becomes an error code,
+// never a hung GPU.
 #pragma once
 #include <cstdint>
 #include <cuda_bf16.h>
@@ -51,14 +52,14 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
 // With watch_flag == false only the caller's own time limit ends the wait (used where
 // several warps must reach the same verdict about the same barrier phase).
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                          bool watch_flag = true) {
+                                          bool watch_flag = true, unsigned long long limit_ns = WAIT_LIMIT_NS) {
     if (mbar_try_wait(bar, parity)) return true;
     const unsigned long long t0 = global_ns();
     uint32_t spins = 0;
     while (!mbar_try_wait(bar, parity)) {
         if ((++spins & 255u) == 0u) {
             if (watch_flag && *abort_flag) return false;
-            if (global_ns() - t0 > WAIT_LIMIT_NS) {
+            if (global_ns() - t0 > limit_ns) {
                 *abort_flag = 1;
                 return false;
             }
@@ -200,14 +201,14 @@ __device__ __forceinline__ uint32_t mbar_try_wait_cluster(uint32_t bar, uint32_t
 }
 // mbar_wait with the cluster-scope acquire (same bounds and abort rules).
 __device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                                  bool watch_flag = true) {
+                                                  bool watch_flag = true, unsigned long long limit_ns = WAIT_LIMIT_NS) {
     if (mbar_try_wait_cluster(bar, parity)) return true;
     const unsigned long long t0 = global_ns();
     uint32_t spins = 0;
     while (!mbar_try_wait_cluster(bar, parity)) {
         if ((++spins & 255u) == 0u) {
             if (watch_flag && *abort_flag) return false;
-            if (global_ns() - t0 > WAIT_LIMIT_NS) {
+            if (global_ns() - t0 > limit_ns) {
                 *abort_flag = 1;
                 return false;
             }

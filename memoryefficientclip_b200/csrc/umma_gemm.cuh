@@ -90,6 +90,16 @@ struct GemmParams {
     const float* acc_in;      // optional fp32 partial added before the store
     long long ld_acc;
     int* status;
+    unsigned long long wait_limit_ns;   // bound of every barrier wait inside the kernel
+    // Scalars that live on the device (a learnable temperature / logit scale / bias): when t_dev is set the
+    // epilogues derive fmul / fadd from it instead of using the host values above, and the coefficient scale
+    // g = coef * (*grad_out) is multiplied by a power of it (g_rule: 0 none, 1 1/T, 2 1/sqrt(T), 3 t).
+    const float* t_dev;
+    const float* b_dev;       // sigmoid loss: logit bias on the device (null: fadd as given)
+    int g_rule;
+    // EPI_OUT with a narrower last column tile: hand out all full-width tiles first and the narrow ones last,
+    // so that the short tiles fill the end of the launch (longest-processing-time order)
+    int narrow_last;
     // Optional in-kernel trace (test hook): CTA 0 appends {tag, tile, %globaltimer} records.
     // Records of 3 words start at trace[2]; role r owns records [r*cap/3, (r+1)*cap/3); unused ones stay zero.
     unsigned long long* trace;
@@ -158,7 +168,15 @@ __device__ __forceinline__ float warp_transpose_reduce32(float (&v)[32], int lan
 }
 
 __device__ __forceinline__ void tile_coords(const GemmParams& p, int tile, int& mt, int& nt) {
-    const int per_group = p.group_m * p.num_n_tiles;
+    int n_tiles = p.num_n_tiles;
+    if (p.narrow_last) {
+        // ids [0, m_tiles * (n_tiles - 1)) walk the full-width column tiles in groups as below,
+        // the remaining m_tiles ids are the narrow last column tile of every row tile
+        n_tiles = p.num_n_tiles - 1;
+        const int full = p.num_m_tiles * n_tiles;
+        if (tile >= full) { mt = tile - full; nt = n_tiles; return; }
+    }
+    const int per_group = p.group_m * n_tiles;
     const int grp = tile / per_group;
     const int first_m = grp * p.group_m;
     const int rows_in_group = min(p.group_m, p.num_m_tiles - first_m);
@@ -196,6 +214,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     const int num_tiles = p.num_m_tiles * p.num_n_tiles;
     const int num_stages = p.num_stages;
     volatile int* abort_flag = &tail->abort_flag;
+    const unsigned long long wl = p.wait_limit_ns;      // bound of every wait below (host-set, 2 s by default)
 
     if (threadIdx.x == 0) {
         tail->abort_flag = 0;
@@ -244,7 +263,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             bool ok = true;
             while (ok) {
                 // publish the tile id (or -1 = no more work) to the MMA and epilogue roles
-                if (!mbar_wait(smem_u32(&tail->sched_empty_bar[slot]), sphase ^ 1u, abort_flag)) break;
+                if (!mbar_wait(smem_u32(&tail->sched_empty_bar[slot]), sphase ^ 1u, abort_flag, true, wl)) break;
                 const int pub = tile < num_tiles ? tile : -1;
                 tail->sched_tile[slot] = pub;
                 mbar_arrive(smem_u32(&tail->sched_full_bar[slot]));
@@ -259,7 +278,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                 const int m0 = mt * BM, n0 = nt * p.bn;
                 trace_event(p, 0, ntrace, TR_LOAD_BEGIN, tile);
                 for (int ks = 0; ks < p.k_steps; ++ks) {
-                    if (!mbar_wait(smem_u32(&tail->empty_bar[stage]), phase ^ 1u, abort_flag)) { ok = false; break; }
+                    if (!mbar_wait(smem_u32(&tail->empty_bar[stage]), phase ^ 1u, abort_flag, true, wl)) { ok = false; break; }
                     const uint32_t full = smem_u32(&tail->full_bar[stage]);
                     mbar_expect_tx(full, stage_tx);
                     const uint32_t sa = smem_base + (uint32_t)stage * (uint32_t)p.stage_bytes;
@@ -312,12 +331,12 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             constexpr uint32_t A_LBO = A_MN ? BK * 128 : 16, A_KSTEP = A_MN ? 2048 : 32;
             constexpr uint32_t B_LBO = B_MN ? BK * 128 : 16, B_KSTEP = B_MN ? 2048 : 32;
             while (ok) {
-                if (!mbar_wait(smem_u32(&tail->sched_full_bar[slot]), sphase, abort_flag)) break;
+                if (!mbar_wait(smem_u32(&tail->sched_full_bar[slot]), sphase, abort_flag, true, wl)) break;
                 const int tile = tail->sched_tile[slot];
                 mbar_arrive(smem_u32(&tail->sched_empty_bar[slot]));
                 if (++slot == SCHED_DEPTH) { slot = 0; sphase ^= 1u; }
                 if (tile < 0) break;
-                if (!mbar_wait(smem_u32(&tail->tmem_empty_bar[acc]), acc_phase ^ 1u, abort_flag)) break;
+                if (!mbar_wait(smem_u32(&tail->tmem_empty_bar[acc]), acc_phase ^ 1u, abort_flag, true, wl)) break;
                 tc_fence_after();
                 trace_event(p, 1, ntrace, TR_MMA_BEGIN, tile);
                 int mt_, nt_;
@@ -325,7 +344,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                 const uint32_t idesc = (nt_ == p.num_n_tiles - 1) ? p.idesc_last : p.idesc;
                 const uint32_t tmem_d = tmem_base + (uint32_t)acc * MAX_BN;
                 for (int ks = 0; ks < p.k_steps; ++ks) {
-                    if (!mbar_wait(smem_u32(&tail->full_bar[stage]), phase, abort_flag)) { ok = false; break; }
+                    if (!mbar_wait(smem_u32(&tail->full_bar[stage]), phase, abort_flag, true, wl)) { ok = false; break; }
                     tc_fence_after();
                     if (ks == 0) trace_event(p, 1, ntrace, TR_MMA_FIRST_DATA, tile);
                     const uint32_t sa = smem_base + (uint32_t)stage * (uint32_t)p.stage_bytes;
@@ -354,11 +373,11 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         uint32_t acc_phase = 0, sphase = 0;
         EpiState st;
         unsigned int ntrace = 0;
-        if (EPI == EPI_COEF) st.gscale = p.grad_out ? __ldg(p.grad_out) : 1.f;
+        epilogue_init<EPI>(p, st);
         while (true) {
             // The eight warps wait on the same barrier phase and then agree on the verdict, so that
             // they always leave the tile loop (and its named barriers) together.
-            bool ok = mbar_wait(smem_u32(&tail->sched_full_bar[slot]), sphase, abort_flag, false);
+            bool ok = mbar_wait(smem_u32(&tail->sched_full_bar[slot]), sphase, abort_flag, false, wl);
             int tile = -1;
             if (ok) {
                 tile = tail->sched_tile[slot];
@@ -369,7 +388,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             if (!ok || tile < 0) break;
             int mt, nt;
             tile_coords(p, tile, mt, nt);
-            ok = mbar_wait(smem_u32(&tail->tmem_full_bar[acc]), acc_phase, abort_flag, false);
+            ok = mbar_wait(smem_u32(&tail->tmem_full_bar[acc]), acc_phase, abort_flag, false, wl);
             ok = named_bar_and(2, EPI_THREADS, ok);
             if (!ok) break;
             tc_fence_after();

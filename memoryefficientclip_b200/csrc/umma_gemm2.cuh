@@ -46,6 +46,7 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
     const int num_stages = p.num_stages;
     const int half_bn = p.bn >> 1;
     volatile int* abort_flag = &tail->abort_flag;
+    const unsigned long long wl = p.wait_limit_ns;      // bound of every wait below (host-set, 2 s by default)
 
     if (threadIdx.x == 0) {
         tail->abort_flag = 0;
@@ -93,7 +94,7 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
             while (ok) {
                 int tile;
                 if (rank == 0) {
-                    if (!mbar_wait_cluster(smem_u32(&tail->sched_empty_bar[slot]), sphase ^ 1u, abort_flag)) break;
+                    if (!mbar_wait_cluster(smem_u32(&tail->sched_empty_bar[slot]), sphase ^ 1u, abort_flag, true, wl)) break;
                     tile = next_tile < num_tiles ? next_tile : -1;
                     tail->sched_tile[slot] = tile;
                     st_cluster_u32(mapa_u32(smem_u32(&tail->sched_tile[slot]), 1), (uint32_t)tile);
@@ -102,7 +103,7 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
                     if (tile >= 0 && left == strip && p.tile_counter != nullptr)
                         asm volatile("atom.global.add.u32 %0, [%1], 1;" : "=r"(next_unit) : "l"(p.tile_counter) : "memory");
                 } else {
-                    if (!mbar_wait_cluster(smem_u32(&tail->sched_full_bar[slot]), sphase, abort_flag)) break;
+                    if (!mbar_wait_cluster(smem_u32(&tail->sched_full_bar[slot]), sphase, abort_flag, true, wl)) break;
                     tile = tail->sched_tile[slot];
                     mbar_arrive_cluster(mapa_u32(smem_u32(&tail->sched_empty_bar[slot]), 0));
                 }
@@ -114,7 +115,7 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
                 const int m0 = mt * PAIR_BM + (int)rank * BM;              // this CTA's rows
                 const int n0 = nt * p.bn + (int)rank * (tile_bn >> 1);      // this CTA's share of the B rows
                 for (int ks = 0; ks < p.k_steps; ++ks) {
-                    if (!mbar_wait(smem_u32(&tail->empty_bar[stage]), phase ^ 1u, abort_flag)) { ok = false; break; }
+                    if (!mbar_wait(smem_u32(&tail->empty_bar[stage]), phase ^ 1u, abort_flag, true, wl)) { ok = false; break; }
                     const uint32_t full_local = smem_u32(&tail->full_bar[stage]);
                     const uint32_t full = mapa_u32(full_local, 0);    // the leader's barrier counts both CTAs' bytes
                     if (rank == 0) mbar_expect_tx(full_local, 2u * tx_per_cta);
@@ -160,19 +161,19 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
             bool ok = true;
             constexpr uint32_t A_LBO = A_MN ? BK * 128 : 16, A_KSTEP = A_MN ? 2048 : 32;
             while (ok) {
-                if (!mbar_wait(smem_u32(&tail->sched_full_bar[slot]), sphase, abort_flag)) break;
+                if (!mbar_wait(smem_u32(&tail->sched_full_bar[slot]), sphase, abort_flag, true, wl)) break;
                 const int tile = tail->sched_tile[slot];
                 mbar_arrive(smem_u32(&tail->sched_empty_bar[slot]));
                 if (++slot == SCHED_DEPTH) { slot = 0; sphase ^= 1u; }
                 if (tile < 0) break;
-                if (!mbar_wait_cluster(smem_u32(&tail->tmem_empty_bar[acc]), acc_phase ^ 1u, abort_flag)) break;
+                if (!mbar_wait_cluster(smem_u32(&tail->tmem_empty_bar[acc]), acc_phase ^ 1u, abort_flag, true, wl)) break;
                 tc_fence_after();
                 int mt_, nt_;
                 tile_coords(p, tile, mt_, nt_);
                 const uint32_t idesc = (nt_ == p.num_n_tiles - 1) ? p.idesc_last : p.idesc;
                 const uint32_t tmem_d = tmem_base + (uint32_t)acc * MAX_BN;
                 for (int ks = 0; ks < p.k_steps; ++ks) {
-                    if (!mbar_wait(smem_u32(&tail->full_bar[stage]), phase, abort_flag)) { ok = false; break; }
+                    if (!mbar_wait(smem_u32(&tail->full_bar[stage]), phase, abort_flag, true, wl)) { ok = false; break; }
                     tc_fence_after();
                     const uint32_t sa = smem_base + (uint32_t)stage * (uint32_t)p.stage_bytes;
                     const uint32_t sb = sa + A_STAGE_BYTES;
@@ -198,11 +199,11 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
         int acc = 0, slot = 0;
         uint32_t acc_phase = 0, sphase = 0;
         EpiState st;
-        if (EPI == EPI_COEF) st.gscale = p.grad_out ? __ldg(p.grad_out) : 1.f;
+        epilogue_init<EPI>(p, st);
         const uint32_t sched_free0 = mapa_u32(smem_u32(&tail->sched_empty_bar[0]), 0);     // the leader's ring
         while (true) {
             // as in the single-CTA kernel the eight warps reach one verdict per wait and leave together
-            bool ok = mbar_wait_cluster(smem_u32(&tail->sched_full_bar[slot]), sphase, abort_flag, false);
+            bool ok = mbar_wait_cluster(smem_u32(&tail->sched_full_bar[slot]), sphase, abort_flag, false, wl);
             const int tile = ok ? tail->sched_tile[slot] : -1;
             __syncwarp();
             if (ok && lane == 0) mbar_arrive_cluster(sched_free0 + (uint32_t)slot * 8u);
@@ -211,7 +212,7 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
             if (!ok || tile < 0) break;
             int mt, nt;
             tile_coords(p, tile, mt, nt);
-            ok = mbar_wait(smem_u32(&tail->tmem_full_bar[acc]), acc_phase, abort_flag, false);
+            ok = mbar_wait(smem_u32(&tail->tmem_full_bar[acc]), acc_phase, abort_flag, false, wl);
             ok = named_bar_and(2, EPI_THREADS, ok);
             if (!ok) break;
             tc_fence_after();

@@ -43,6 +43,114 @@ def read_status(status: torch.Tensor) -> None:
         _lib.check(_lib.load().meclip_read_status(status.data_ptr(), _stream(status)))
 
 
+# ---- scalars that may live on the device ----------------------------------------------------------------
+GSCALE_FIXED, GSCALE_OVER_T, GSCALE_OVER_SQRT_T, GSCALE_TIMES_T = 0, 1, 2, 3
+
+
+def _dev_scalar(v, device):
+    """fp32 one-element view / copy of a tensor scalar on `device` (no host synchronisation)."""
+    v = v.detach()
+    if v.dtype != torch.float32 or v.device != device:
+        v = v.to(device=device, dtype=torch.float32)
+    return v.reshape(1)
+
+
+def _bind(temperature, device, rule=GSCALE_FIXED, bias=None):
+    """Prepares the scalar arguments of the next library call.  A float goes through as it is.  A tensor
+    (a learnable temperature / logit scale / bias) stays on the device: its address is bound for the next
+    call of this thread (meclip_bind_device_scalars) and the float argument is a placeholder.
+    Returns (float for the temperature argument, float for the bias argument, tensors to keep alive)."""
+    t_is, b_is = isinstance(temperature, torch.Tensor), isinstance(bias, torch.Tensor)
+    if not (t_is or b_is):
+        return float(temperature), (0.0 if bias is None else float(bias)), ()
+    t_dev = _dev_scalar(temperature, device) if t_is else torch.full((1,), float(temperature), dtype=torch.float32,
+                                                                      device=device)
+    b_dev = None
+    if bias is not None:
+        b_dev = _dev_scalar(bias, device) if b_is else torch.full((1,), float(bias), dtype=torch.float32, device=device)
+    _lib.check(_lib.load().meclip_bind_device_scalars(t_dev.data_ptr(), _ptr(b_dev), rule))
+    return 1.0, 0.0, (t_dev, b_dev)
+
+
+def is_dev(v) -> bool:
+    return isinstance(v, torch.Tensor)
+
+
+# ---- the status word of the module path -----------------------------------------------------------------
+class _DeviceStatus:
+    """One status word per device for everything the modules launch, checked without stalling the step:
+    after a backward the word is copied to pinned host memory behind an event; the next forward looks at
+    the copy if the event has completed and raises MeclipError(ETIMEOUT) when a kernel gave up a bounded
+    wait.  MECLIP_CHECK_STATUS=1 checks synchronously after every forward and backward instead."""
+
+    def __init__(self, device):
+        self.word = torch.zeros(1, dtype=torch.int32, device=device)
+        self.host = torch.zeros(1, dtype=torch.int32).pin_memory()
+        self.event = torch.cuda.Event()
+        self.pending = False
+
+
+_status_by_device = {}
+_SYNC_CHECK = __import__("os").environ.get("MECLIP_CHECK_STATUS", "0") not in ("", "0")
+
+
+def _dev_status(device) -> _DeviceStatus:
+    key = device.index if device.index is not None else torch.cuda.current_device()
+    st = _status_by_device.get(key)
+    if st is None:
+        st = _status_by_device[key] = _DeviceStatus(torch.device("cuda", key))
+    return st
+
+
+def status_word(device) -> torch.Tensor:
+    """The device's shared status word (int32[1]); pass it as `status=` to the functions below."""
+    return _dev_status(device).word
+
+
+def _raise_timeout(st: _DeviceStatus):
+    st.word.zero_()
+    st.host.zero_()
+    st.pending = False
+    raise _lib.MeclipError(_lib.ETIMEOUT, "a kernel of an earlier step gave up a bounded wait on a barrier; "
+                           "its results (loss, gradients) are incomplete")
+
+
+def poll_status(device) -> None:
+    """Non-blocking: raises if the last posted copy of the status word has arrived and is non-zero."""
+    st = _dev_status(device)
+    if not st.pending or torch.cuda.is_current_stream_capturing():
+        return
+    if st.event.query():
+        st.pending = False
+        if int(st.host[0]) != 0:
+            _raise_timeout(st)
+
+
+def post_status(device) -> None:
+    """Queue a copy of the status word to pinned host memory on the current stream (no synchronisation)."""
+    st = _dev_status(device)
+    if torch.cuda.is_current_stream_capturing():
+        return
+    if _SYNC_CHECK:
+        check_status(device)
+        return
+    st.host.copy_(st.word, non_blocking=True)
+    st.event.record(torch.cuda.current_stream(st.word.device))
+    st.pending = True
+
+
+def check_status(device=None) -> None:
+    """Synchronous check of the module path's status word: waits for the device's current stream and raises
+    MeclipError(ETIMEOUT) if any kernel launched by the modules recorded an expired wait."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    st = _dev_status(device)
+    try:
+        read_status(st.word)
+    except _lib.MeclipError:
+        _raise_timeout(st)
+    st.pending = False
+
+
 def normalize_fwd(x: torch.Tensor, normalize: bool = True, extra_cols: int = 0):
     """Returns (x_hat bf16 [rows, padded(d) + extra_cols], inv_norm fp32 [rows] or None); columns past d are
     zero up to padded(d); extra_cols (a multiple of 8) are left for the caller to fill.
@@ -103,16 +211,18 @@ def sum_exp(kind, x_hat, y_hat, temperature, row_sum, col_sum, diag_s, row_off=0
     cols = y_hat.shape[0]
     counter = torch.zeros(1, dtype=torch.int32, device=x_hat.device)     # dynamic tile hand-out
     with torch.cuda.device(x_hat.device):
+        t, _b, _keep = _bind(temperature, x_hat.device)
         _lib.check(_lib.load().meclip_sum_exp(kind, x_hat.data_ptr(), y_hat.data_ptr(), rows, cols, d, x_hat.stride(0),
-                                              y_hat.stride(0), float(temperature), row_off, col_off, row_sum.data_ptr(),
+                                              y_hat.stride(0), t, row_off, col_off, row_sum.data_ptr(),
                                               _ptr(col_sum), diag_s.data_ptr(), counter.data_ptr(), _ptr(status),
                                               _stream(x_hat)))
 
 
 def loss_finalize(kind, row_sum, col_sum, diag_s, temperature, scale, loss_out, accumulate=False):
     with torch.cuda.device(row_sum.device):
+        t, _b, _keep = _bind(temperature, row_sum.device)
         _lib.check(_lib.load().meclip_loss_finalize(kind, row_sum.data_ptr(), _ptr(col_sum), diag_s.data_ptr(),
-                                                    row_sum.numel(), float(temperature), float(scale), int(accumulate),
+                                                    row_sum.numel(), t, float(scale), int(accumulate),
                                                     loss_out.data_ptr(), _stream(row_sum)))
 
 
@@ -127,8 +237,9 @@ def loss_forward(kind, x_hat, y_hat, temperature, status=None):
     loss = torch.empty((), dtype=torch.float32, device=dev)
     counter = torch.empty(1, dtype=torch.int32, device=dev)              # cleared by the call
     with torch.cuda.device(dev):
+        t, _b, _keep = _bind(temperature, dev)
         _lib.check(_lib.load().meclip_loss_forward(kind, x_hat.data_ptr(), y_hat.data_ptr(), b, d, x_hat.stride(0),
-                                                   y_hat.stride(0), float(temperature), row_sum.data_ptr(),
+                                                   y_hat.stride(0), t, row_sum.data_ptr(),
                                                    _ptr(col_sum), diag_s.data_ptr(), loss.data_ptr(),
                                                    counter.data_ptr(), _ptr(status), _stream(x_hat)))
     return loss, row_sum, col_sum, diag_s
@@ -143,18 +254,21 @@ def grad_workspace(rows, cols, d, device) -> torch.Tensor:
 
 
 def grad_block(kind, x_hat, y_hat, temperature, row_sum, col_sum, grad_out, grad_scale, dx, dx_mode, dy, dy_mode,
-               row_off=0, col_off=0, workspace=None, status=None, sum_g_s=None):
+               row_off=0, col_off=0, workspace=None, status=None, sum_g_s=None, scale_rule=GSCALE_FIXED):
     """One rows x cols block of the backward (see meclip_grad in include/meclip.h).
-    sum_g_s: optional fp32 pair; its first element gets sum_ij G_ij S_ij of the block ADDED (meclip_grad_t)."""
+    sum_g_s: optional fp32 pair; its first element gets sum_ij G_ij S_ij of the block ADDED (meclip_grad_t).
+    A tensor temperature stays on the device; grad_scale is then the scale for T = 1 and scale_rule says how
+    the kernel completes it (see grad_scale_args)."""
     rows, d = x_hat.shape
     cols = y_hat.shape[0]
     if workspace is None:
         workspace = grad_workspace(rows, cols, d, x_hat.device)
-    head = (kind, x_hat.data_ptr(), y_hat.data_ptr(), rows, cols, d, x_hat.stride(0), y_hat.stride(0), float(temperature),
-            row_off, col_off, row_sum.data_ptr(), _ptr(col_sum), _ptr(grad_out), float(grad_scale), dx.data_ptr(), dx_mode,
-            dx.stride(0), _ptr(dy), dy_mode, dy.stride(0) if dy is not None else 0)
-    tail = (workspace.data_ptr(), workspace.numel(), _ptr(status), _stream(x_hat))
     with torch.cuda.device(x_hat.device):
+        t, _b, _keep = _bind(temperature, x_hat.device, scale_rule)
+        head = (kind, x_hat.data_ptr(), y_hat.data_ptr(), rows, cols, d, x_hat.stride(0), y_hat.stride(0), t,
+                row_off, col_off, row_sum.data_ptr(), _ptr(col_sum), _ptr(grad_out), float(grad_scale), dx.data_ptr(), dx_mode,
+                dx.stride(0), _ptr(dy), dy_mode, dy.stride(0) if dy is not None else 0)
+        tail = (workspace.data_ptr(), workspace.numel(), _ptr(status), _stream(x_hat))
         if sum_g_s is None:
             _lib.check(_lib.load().meclip_grad(*head, *tail))
         else:
@@ -178,7 +292,7 @@ def grad_block_static(kind, x_hat, y_hat, temperature, row_sum, col_sum, grad_ou
 
 
 def loss_backward(kind, x_hat, y_hat, temperature, row_sum, col_sum, grad_out, grad_scale, dx_dtype, dy_dtype,
-                  status=None, sum_g_s=None, need_dx=True, need_dy=True):
+                  status=None, sum_g_s=None, need_dx=True, need_dy=True, scale_rule=GSCALE_FIXED):
     """Whole-batch backward on one GPU.  Returns (dx, dy) w.r.t. the normalised operands; an output
     that is not needed (frozen tower, or the second argument of LiT) is None and its contraction is skipped.
     sum_g_s: optional zeroed fp32 scalar that receives sum_ij G_ij S_ij (temperature gradient)."""
@@ -192,16 +306,18 @@ def loss_backward(kind, x_hat, y_hat, temperature, row_sum, col_sum, grad_out, g
     ws = grad_workspace(b, b, d, dev)
     if sum_g_s is not None:
         with torch.cuda.device(dev):
+            t, _b, _keep = _bind(temperature, dev, scale_rule)
             _lib.check(_lib.load().meclip_grad_t(kind, x_hat.data_ptr(), y_hat.data_ptr(), b, b, d, x_hat.stride(0),
-                                                 y_hat.stride(0), float(temperature), 0, 0, row_sum.data_ptr(),
+                                                 y_hat.stride(0), t, 0, 0, row_sum.data_ptr(),
                                                  _ptr(col_sum), _ptr(grad_out), float(grad_scale), _ptr(dx),
                                                  _MODE[dx_dtype], d, _ptr(dy),
                                                  _MODE[dy_dtype] if dy is not None else 0, d, sum_g_s.data_ptr(),
                                                  ws.data_ptr(), ws.numel(), _ptr(status), _stream(x_hat)))
         return dx, dy
     with torch.cuda.device(dev):
+        t, _b, _keep = _bind(temperature, dev, scale_rule)
         _lib.check(_lib.load().meclip_loss_backward(kind, x_hat.data_ptr(), y_hat.data_ptr(), b, d, x_hat.stride(0),
-                                                    y_hat.stride(0), float(temperature), row_sum.data_ptr(),
+                                                    y_hat.stride(0), t, row_sum.data_ptr(),
                                                     _ptr(col_sum), _ptr(grad_out), float(grad_scale), _ptr(dx),
                                                     _MODE[dx_dtype], d, _ptr(dy),
                                                     _MODE[dy_dtype] if dy is not None else 0, d, ws.data_ptr(),
@@ -215,8 +331,9 @@ def siglip_sum(x_hat, y_hat, logit_scale, logit_bias, row_sum, diag_s, row_off=0
     cols = y_hat.shape[0]
     counter = torch.zeros(1, dtype=torch.int32, device=x_hat.device)
     with torch.cuda.device(x_hat.device):
+        t, b, _keep = _bind(logit_scale, x_hat.device, GSCALE_FIXED, logit_bias)
         _lib.check(_lib.load().meclip_siglip_sum(x_hat.data_ptr(), y_hat.data_ptr(), rows, cols, d, x_hat.stride(0),
-                                                 y_hat.stride(0), float(logit_scale), float(logit_bias), row_off, col_off,
+                                                 y_hat.stride(0), t, b, row_off, col_off,
                                                  row_sum.data_ptr(), diag_s.data_ptr(), counter.data_ptr(), _ptr(status),
                                                  _stream(x_hat)))
 
@@ -224,7 +341,7 @@ def siglip_sum(x_hat, y_hat, logit_scale, logit_bias, row_sum, diag_s, row_off=0
 def siglip_loss_finalize(row_sum, diag_s, logit_scale, logit_bias, scale, loss_out, accumulate=False):
     with torch.cuda.device(row_sum.device):
         _lib.check(_lib.load().meclip_siglip_loss_finalize(row_sum.data_ptr(), diag_s.data_ptr(), row_sum.numel(),
-                                                           float(logit_scale), float(logit_bias), float(scale),
+                                                           0.0, 0.0, float(scale),
                                                            int(accumulate), loss_out.data_ptr(), _stream(row_sum)))
 
 
@@ -248,8 +365,10 @@ def siglip_grad_block(x_hat, y_hat, logit_scale, logit_bias, grad_out, grad_scal
     if workspace is None:
         workspace = grad_workspace(rows, cols, d, x_hat.device)
     with torch.cuda.device(x_hat.device):
+        t, b, _keep = _bind(logit_scale, x_hat.device, GSCALE_TIMES_T if is_dev(logit_scale) else GSCALE_FIXED,
+                            logit_bias)
         _lib.check(_lib.load().meclip_siglip_grad(x_hat.data_ptr(), y_hat.data_ptr(), rows, cols, d, x_hat.stride(0),
-                                                  y_hat.stride(0), float(logit_scale), float(logit_bias), row_off,
+                                                  y_hat.stride(0), t, b, row_off,
                                                   col_off, _ptr(grad_out), float(grad_scale_), _ptr(dx), dx_mode,
                                                   dx.stride(0) if dx is not None else 0, _ptr(dy), dy_mode,
                                                   dy.stride(0) if dy is not None else 0, _ptr(sums),
@@ -269,8 +388,9 @@ def siglip_backward(x_hat, y_hat, logit_scale, logit_bias, grad_out, grad_scale_
     dy = torch.empty(b, d, dtype=dy_dtype, device=dev) if need_dy else None
     ws = grad_workspace(b, b, d, dev)
     with torch.cuda.device(dev):
+        t, bias, _keep = _bind(logit_scale, dev, GSCALE_TIMES_T if is_dev(logit_scale) else GSCALE_FIXED, logit_bias)
         _lib.check(_lib.load().meclip_siglip_grad(x_hat.data_ptr(), y_hat.data_ptr(), b, b, d, x_hat.stride(0),
-                                                  y_hat.stride(0), float(logit_scale), float(logit_bias), 0, 0,
+                                                  y_hat.stride(0), t, bias, 0, 0,
                                                   _ptr(grad_out), float(grad_scale_), _ptr(dx), _MODE[dx_dtype], d,
                                                   _ptr(dy), _MODE[dy_dtype], d, _ptr(sums), ws.data_ptr(), ws.numel(),
                                                   _ptr(status), _stream(x_hat)))
@@ -289,8 +409,9 @@ def lit_fused_block(x_hat, y_ext, d_pad, temperature, u, u_mode, row_off=0, col_
     if workspace is None:
         workspace = grad_workspace(rows, cols, d_pad + 8, x_hat.device)
     with torch.cuda.device(x_hat.device):
+        t, _b, _keep = _bind(temperature, x_hat.device)
         _lib.check(_lib.load().meclip_lit_fused_forward(x_hat.data_ptr(), y_ext.data_ptr(), rows, cols, d_pad,
-                                                        x_hat.stride(0), y_ext.stride(0), float(temperature), row_off,
+                                                        x_hat.stride(0), y_ext.stride(0), t, row_off,
                                                         col_off, u.data_ptr(), u_mode, u.stride(0), workspace.data_ptr(),
                                                         workspace.numel(), _ptr(status), _stream(x_hat)))
 
@@ -321,11 +442,15 @@ def lit_fused_forward(x_hat, y_ext, d_pad, temperature, status=None):
     return loss, u, row_sum
 
 
-def lit_fused_backward(u, y_ext, row_sum, grad_out, grad_scale_, d_out, out_dtype):
-    """dx [b, d_out] in out_dtype from the saved u (meclip_lit_fused_backward)."""
+def lit_fused_backward(u, y_ext, row_sum, grad_out, grad_scale_, d_out, out_dtype, temperature=None,
+                       scale_rule=GSCALE_FIXED):
+    """dx [b, d_out] in out_dtype from the saved u (meclip_lit_fused_backward).  temperature: only needed
+    when it is a tensor (grad_scale_ is then the scale for T = 1, completed on the device by scale_rule)."""
     b = u.shape[0]
     dx = torch.empty(b, d_out, dtype=out_dtype, device=u.device)
     with torch.cuda.device(u.device):
+        if is_dev(temperature):
+            _t, _b, _keep = _bind(temperature, u.device, scale_rule)
         _lib.check(_lib.load().meclip_lit_fused_backward(u.data_ptr(), u.stride(0), y_ext.data_ptr(), y_ext.stride(0),
                                                          row_sum.data_ptr(), _ptr(grad_out), float(grad_scale_), b, d_out,
                                                          dx.data_ptr(), _DT[out_dtype], dx.stride(0), _stream(u)))
@@ -336,6 +461,21 @@ def grad_scale(batch: int, temperature: float, stable: bool) -> float:
     """1/(B T) (reference clip_loss.py:182, 235) or, for the Stable variants,
     sqrt(B/T)/B = 1/sqrt(B T) (clip_loss.py:299, 352)."""
     return 1.0 / math.sqrt(batch * temperature) if stable else 1.0 / (batch * temperature)
+
+
+def grad_scale_args(batch: int, temperature, stable: bool):
+    """(grad_scale, scale_rule) for the backward entry points.  A float temperature gives the finished
+    scale and GSCALE_FIXED.  A tensor temperature stays on the device: the scale is formed for T = 1 and
+    the kernels divide by T (or sqrt(T) for the Stable variants) themselves."""
+    if is_dev(temperature):
+        return grad_scale(batch, 1.0, stable), (GSCALE_OVER_SQRT_T if stable else GSCALE_OVER_T)
+    return grad_scale(batch, float(temperature), stable), GSCALE_FIXED
+
+
+def debug_wait_probe(status: torch.Tensor, limit_ns: int = 1_000_000) -> None:
+    """Test hook: one tiny kernel whose bounded wait is meant to run out (it sets the status word)."""
+    with torch.cuda.device(status.device):
+        _lib.check(_lib.load().meclip_debug_wait_probe(int(limit_ns), status.data_ptr(), _stream(status)))
 
 
 def debug_gemm(a, b, a_mn_major, b_mn_major, m, n, k, tile_n=0, c_in=None, status=None) -> torch.Tensor:

@@ -41,7 +41,21 @@ def ring_neighbours(rank: int, world: int):
 
 
 class CudaBlockOps:
-    """Block primitives on the sm_100a kernels (the only product implementation)."""
+    """Block primitives on the sm_100a kernels (the only product implementation).  Every launch gets the
+    device's shared status word, so a bounded wait that ran out surfaces at the next forward."""
+
+    # tensor temperatures / logit scales are read by the kernels on the device (no host synchronisation)
+    device_scalars = True
+
+    @staticmethod
+    def _st(t):
+        return ops.status_word(t.device)
+
+    def begin_step(self, device):
+        ops.poll_status(device)
+
+    def end_step(self, device):
+        ops.post_status(device)
 
     def prepare(self, x, normalize):
         if normalize:
@@ -49,7 +63,7 @@ class CudaBlockOps:
         return ops.as_operand(x), None
 
     def sum_exp(self, kind, x_hat, y_hat, t, row_sum, col_sum, diag, row_off, col_off):
-        ops.sum_exp(kind, x_hat, y_hat, t, row_sum, col_sum, diag, row_off, col_off)
+        ops.sum_exp(kind, x_hat, y_hat, t, row_sum, col_sum, diag, row_off, col_off, status=self._st(x_hat))
 
     def local_loss_sum(self, kind, row_sum, col_sum, diag, t, scale):
         out = torch.empty((), dtype=torch.float32, device=row_sum.device)
@@ -57,9 +71,10 @@ class CudaBlockOps:
         return out
 
     def grad(self, kind, x_hat, y_hat, t, row_sum, col_sum, go, scale, dx_acc, dy_out, row_off, col_off, workspace,
-             sum_g_s=None):
+             sum_g_s=None, scale_rule=0):
         ops.grad_block(kind, x_hat, y_hat, t, row_sum, col_sum, go, scale, dx_acc, _lib.ACCUM_F32, dy_out,
-                       _lib.STORE_F32, row_off, col_off, workspace, sum_g_s=sum_g_s)
+                       _lib.STORE_F32, row_off, col_off, workspace, status=self._st(x_hat), sum_g_s=sum_g_s,
+                       scale_rule=scale_rule)
 
     def new_sum(self, device):
         return torch.zeros(2, dtype=torch.float32, device=device)
@@ -77,16 +92,17 @@ class CudaBlockOps:
         return torch.zeros(rows, d_pad + 8, dtype=torch.float32, device=device)
 
     def lit_fused_block(self, x_hat, y_ext, d_pad, t, u, row_off, col_off, workspace):
-        ops.lit_fused_block(x_hat, y_ext, d_pad, t, u, _lib.ACCUM_F32, row_off, col_off, workspace)
+        ops.lit_fused_block(x_hat, y_ext, d_pad, t, u, _lib.ACCUM_F32, row_off, col_off, workspace,
+                            status=self._st(x_hat))
 
     def lit_fused_stats(self, x_hat, y_ext, u, d_pad):
         return ops.lit_fused_stats(x_hat, y_ext, u, d_pad)
 
-    def lit_fused_bwd(self, u, y_ext, row_sum, go, scale, d_out, out_dtype):
-        return ops.lit_fused_backward(u, y_ext, row_sum, go, scale, d_out, out_dtype)
+    def lit_fused_bwd(self, u, y_ext, row_sum, go, scale, d_out, out_dtype, temperature=None, scale_rule=0):
+        return ops.lit_fused_backward(u, y_ext, row_sum, go, scale, d_out, out_dtype, temperature, scale_rule)
 
     def siglip_sum(self, x_hat, y_hat, logit_scale, logit_bias, row_sum, diag, row_off, col_off):
-        ops.siglip_sum(x_hat, y_hat, logit_scale, logit_bias, row_sum, diag, row_off, col_off)
+        ops.siglip_sum(x_hat, y_hat, logit_scale, logit_bias, row_sum, diag, row_off, col_off, status=self._st(x_hat))
 
     def siglip_local_loss(self, row_sum, diag, logit_scale, logit_bias, scale):
         out = torch.empty((), dtype=torch.float32, device=row_sum.device)
@@ -96,7 +112,7 @@ class CudaBlockOps:
     def siglip_grad(self, x_hat, y_hat, logit_scale, logit_bias, go, scale, dx_acc, dy_out, row_off, col_off, workspace,
                     sums):
         ops.siglip_grad_block(x_hat, y_hat, logit_scale, logit_bias, go, scale, dx_acc, _lib.ACCUM_F32, dy_out,
-                              _lib.STORE_F32, row_off, col_off, workspace, sums)
+                              _lib.STORE_F32, row_off, col_off, workspace, sums, status=self._st(x_hat))
 
     def workspace(self, rows, cols, d, device):
         return ops.grad_workspace(rows, cols, d, device)
@@ -217,7 +233,7 @@ def _ring_backward_loop(block, x_hat, y_hat, group, rank, world, want_dy, grad_c
 
 
 def ring_backward(block, kind, x_hat, y_hat, temperature, row_sum, col_sum, grad_out, grad_scale, group, rank, world,
-                  sum_g_s=None):
+                  sum_g_s=None, scale_rule=0):
     """Returns (dx fp32 [b, D], dy_own fp32 [b, D] or None) w.r.t. the normalised operands.
     sum_g_s: optional zeroed pair; element 0 receives sum_ij G_ij S_ij over this rank's rows and ALL columns."""
     b = x_hat.shape[0]
@@ -230,6 +246,8 @@ def ring_backward(block, kind, x_hat, y_hat, temperature, row_sum, col_sum, grad
         else:
             col_all = col_sum.view(1, b)
     extra = {} if sum_g_s is None else {"sum_g_s": sum_g_s}
+    if scale_rule:
+        extra["scale_rule"] = scale_rule
 
     def grad_call(y_shard, shard, dx_acc, dy_out, workspace):
         block.grad(kind, x_hat, y_shard, temperature, row_sum, col_all[shard] if clip else None, grad_out, grad_scale,
@@ -321,11 +339,16 @@ class RingContrastiveLossFn(torch.autograd.Function):
         assert temperature_grad in ("local", "global")
         t_is_tensor = isinstance(temperature, torch.Tensor)
         ctx.ring_t = (temperature, temperature_grad) if t_is_tensor and temperature.requires_grad else None
-        temperature = float(temperature.detach().item()) if t_is_tensor else float(temperature)
-        assert temperature > 0.0, "temperature must be positive"
         world = dist.get_world_size(group) if dist.is_initialized() else 1
         rank = dist.get_rank(group) if dist.is_initialized() else 0
         block = block or CudaBlockOps()
+        if t_is_tensor and getattr(block, "device_scalars", False):
+            temperature = temperature.detach()       # stays on the device: the kernels read it there
+        else:
+            temperature = float(temperature.detach().item()) if t_is_tensor else float(temperature)
+            assert temperature > 0.0, "temperature must be positive"
+        if hasattr(block, "begin_step"):
+            block.begin_step(x.device)
         from . import _function
         ctx.ring_fused = (kind == _lib.LIT and _function._LIT_FUSED and ctx.needs_input_grad[0] and ctx.ring_t is None
                           and getattr(block, "lit_one_pass", False))
@@ -334,7 +357,7 @@ class RingContrastiveLossFn(torch.autograd.Function):
             y_ext, d_pad = block.prepare_ext(y, normalize)
             loss, u, row_sum = ring_lit_fused_forward(block, x_hat, y_ext, d_pad, temperature, group, rank, world)
             ctx.save_for_backward(*([u, y_ext, row_sum] + ([x_hat, inv_x] if normalize else [])))
-            ctx.ring = (float(temperature), kind, bool(stable), bool(normalize), x.dtype, y.dtype, x.shape[1], group, rank,
+            ctx.ring = (temperature, kind, bool(stable), bool(normalize), x.dtype, y.dtype, x.shape[1], group, rank,
                         world, block)
             return loss
         x_hat, inv_x = block.prepare(x, normalize)
@@ -346,7 +369,7 @@ class RingContrastiveLossFn(torch.autograd.Function):
         if normalize:
             saved += [inv_x, inv_y]
         ctx.save_for_backward(*saved)
-        ctx.ring = (float(temperature), kind, bool(stable), bool(normalize), x.dtype, y.dtype, x.shape[1], group, rank,
+        ctx.ring = (temperature, kind, bool(stable), bool(normalize), x.dtype, y.dtype, x.shape[1], group, rank,
                     world, block)
         return loss
 
@@ -357,13 +380,16 @@ class RingContrastiveLossFn(torch.autograd.Function):
         if getattr(ctx, "ring_fused", False):
             u, y_ext, row_sum = saved[:3]
             go = grad_output.detach().to(device=u.device, dtype=torch.float32).reshape(1).contiguous()
-            scale = ops.grad_scale(u.shape[0] * world, temperature, stable)
+            scale, rule = ops.grad_scale_args(u.shape[0] * world, temperature, stable)
+            t_kw = {"temperature": temperature, "scale_rule": rule} if rule else {}
             if normalize:
                 x_hat, inv_x = saved[3:]
-                g32 = block.lit_fused_bwd(u, y_ext, row_sum, go, scale, x_hat.shape[1], torch.float32)
+                g32 = block.lit_fused_bwd(u, y_ext, row_sum, go, scale, x_hat.shape[1], torch.float32, **t_kw)
                 dx = block.finish_grad(g32, x_hat, inv_x, x_dtype, d)
             else:
-                dx = block.lit_fused_bwd(u, y_ext, row_sum, go, scale, d, x_dtype)
+                dx = block.lit_fused_bwd(u, y_ext, row_sum, go, scale, d, x_dtype, **t_kw)
+            if hasattr(block, "end_step"):
+                block.end_step(u.device)
             return dx, None, None, None, None, None, None, None, None
         x_hat, y_hat, row_sum = saved[:3]
         rest = saved[3:]
@@ -371,11 +397,11 @@ class RingContrastiveLossFn(torch.autograd.Function):
         inv_x, inv_y = rest if normalize else (None, None)
         b = x_hat.shape[0]
         go = grad_output.detach().to(device=x_hat.device, dtype=torch.float32).reshape(1).contiguous()
-        scale = ops.grad_scale(b * world, temperature, stable)
+        scale, rule = ops.grad_scale_args(b * world, temperature, stable)
         t_info = getattr(ctx, "ring_t", None)
         sum_g_s = block.new_sum(x_hat.device) if t_info is not None else None
         dx, dy = ring_backward(block, kind, x_hat, y_hat, temperature, row_sum, col_sum, go, scale, group, rank, world,
-                               sum_g_s=sum_g_s)
+                               sum_g_s=sum_g_s, scale_rule=rule)
         dx = block.finish_grad(dx, x_hat, inv_x, x_dtype, d)
         if dy is not None:
             dy = block.finish_grad(dy, y_hat, inv_y, y_dtype, d)
@@ -384,9 +410,18 @@ class RingContrastiveLossFn(torch.autograd.Function):
             t_param, mode = t_info
             if mode == "global" and world > 1:
                 dist.all_reduce(sum_g_s, op=dist.ReduceOp.SUM, group=group)
-            # sum_ij G_ij S_ij = g B dL/d(1/T) with g = grad_out * scale and B the global batch
-            dt = (sum_g_s[0] * (-1.0 / (scale * b * world * temperature * temperature))).reshape(t_param.shape)
+            # sum_ij G_ij S_ij = g B dL/d(1/T) with g = grad_out * scale and B the global batch.  With a
+            # device-resident temperature `scale` was formed for T = 1 and completed by the kernels, so the
+            # same power of T is applied here in tensor arithmetic (no host read).
+            if rule:
+                t32 = temperature.to(torch.float32).reshape(())
+                scale_t = scale / (torch.sqrt(t32) if stable else t32)
+                dt = (-sum_g_s[0] / (scale_t * (b * world) * t32 * t32)).reshape(t_param.shape)
+            else:
+                dt = (sum_g_s[0] * (-1.0 / (scale * b * world * temperature * temperature))).reshape(t_param.shape)
             dt = dt.to(t_param.dtype)
+        if hasattr(block, "end_step"):
+            block.end_step(x_hat.device)
         return dx, dy, dt, None, None, None, None, None, None
 
 
@@ -445,8 +480,14 @@ class RingSigLIPLossFn(torch.autograd.Function):
         block = block or CudaBlockOps()
         x_hat, inv_x = block.prepare(x, normalize)
         y_hat, inv_y = block.prepare(y, normalize)
-        t = float(logit_scale.detach().item()) if isinstance(logit_scale, torch.Tensor) else float(logit_scale)
-        bias = float(logit_bias.detach().item()) if isinstance(logit_bias, torch.Tensor) else float(logit_bias)
+        if getattr(block, "device_scalars", False):
+            t = logit_scale.detach() if isinstance(logit_scale, torch.Tensor) else float(logit_scale)
+            bias = logit_bias.detach() if isinstance(logit_bias, torch.Tensor) else float(logit_bias)
+        else:
+            t = float(logit_scale.detach().item()) if isinstance(logit_scale, torch.Tensor) else float(logit_scale)
+            bias = float(logit_bias.detach().item()) if isinstance(logit_bias, torch.Tensor) else float(logit_bias)
+        if hasattr(block, "begin_step"):
+            block.begin_step(x.device)
         loss = ring_siglip_forward(block, x_hat, y_hat, t, bias, group, rank, world)
         ctx.save_for_backward(*([x_hat, y_hat] + ([inv_x, inv_y] if normalize else [])))
         ctx.ring = (t, bias, bool(normalize), x.dtype, y.dtype, x.shape[1], group, rank, world, block, param_grad,
@@ -465,7 +506,9 @@ class RingSigLIPLossFn(torch.autograd.Function):
         go = grad_output.detach().to(device=x_hat.device, dtype=torch.float32).reshape(1).contiguous()
         want_tb = bool(need[2] or need[3])
         sums = block.new_sum(x_hat.device) if want_tb else None
-        dx, dy = ring_siglip_backward(block, x_hat, y_hat, t, bias, go, t / (b * world), group, rank, world, sums)
+        # grad_scale = t / B; with a device-resident t the kernel multiplies 1/B by t itself
+        gscale = 1.0 / (b * world) if ops.is_dev(t) else t / (b * world)
+        dx, dy = ring_siglip_backward(block, x_hat, y_hat, t, bias, go, gscale, group, rank, world, sums)
         dx = block.finish_grad(dx, x_hat, inv_x, x_dtype, d)
         dy = block.finish_grad(dy, y_hat, inv_y, y_dtype, d)
         dt = db = None
@@ -477,6 +520,8 @@ class RingSigLIPLossFn(torch.autograd.Function):
                 dt = (sums[0] / t).reshape(t_tensor[0]).to(t_tensor[1])
             if need[3] and b_tensor is not None:
                 db = (sums[1] / t).reshape(b_tensor[0]).to(b_tensor[1])
+        if hasattr(block, "end_step"):
+            block.end_step(x_hat.device)
         return dx, dy, dt, db, None, None, None, None
 
 

@@ -33,10 +33,12 @@ class MemoryEfficientSigLIPLossFn(torch.autograd.Function):
         else:
             x_hat, inv_x = ops.as_operand(x), None
             y_hat, inv_y = ops.as_operand(y), None
-        # scale and bias are read on the host once per forward (they are kernel parameters)
-        t = float(logit_scale.detach().item()) if isinstance(logit_scale, torch.Tensor) else float(logit_scale)
-        b = float(logit_bias.detach().item()) if isinstance(logit_bias, torch.Tensor) else float(logit_bias)
-        loss = ops.siglip_forward(x_hat, y_hat, t, b)
+        # tensor scale / bias stay on the device (the kernels read them there): no host synchronisation
+        t = logit_scale.detach() if isinstance(logit_scale, torch.Tensor) else float(logit_scale)
+        b = logit_bias.detach() if isinstance(logit_bias, torch.Tensor) else float(logit_bias)
+        status = ops.status_word(x.device)
+        ops.poll_status(x.device)
+        loss = ops.siglip_forward(x_hat, y_hat, t, b, status=status)
         saved = [x_hat, y_hat] + ([inv_x, inv_y] if normalize else [])
         ctx.save_for_backward(*saved)
         ctx.sig = (t, b, bool(normalize), x.dtype, y.dtype, x.shape[1],
@@ -62,7 +64,10 @@ class MemoryEfficientSigLIPLossFn(torch.autograd.Function):
         post_y = normalize or not ops.direct_grad_dtype(y_dtype, d)
         dx_t = torch.float32 if post_x else x_dtype
         dy_t = torch.float32 if post_y else y_dtype
-        dx, dy = ops.siglip_backward(x_hat, y_hat, t, b, go, t / batch, dx_t, dy_t, sums, want_dx, want_dy)
+        # grad_scale = t / B; with a device-resident t the kernel multiplies 1/B by t itself
+        gscale = 1.0 / batch if ops.is_dev(t) else t / batch
+        dx, dy = ops.siglip_backward(x_hat, y_hat, t, b, go, gscale, dx_t, dy_t, sums, want_dx, want_dy,
+                                     status=ops.status_word(x_hat.device))
         if post_x and dx is not None:
             dx = ops.normalize_bwd(dx, x_hat, inv_x, x_dtype, d)
         if post_y and dy is not None:
@@ -74,6 +79,7 @@ class MemoryEfficientSigLIPLossFn(torch.autograd.Function):
                 dt = (sums[0] / t).reshape(t_tensor[0]).to(t_tensor[1])
             if need[3] and b_tensor is not None:
                 db = (sums[1] / t).reshape(b_tensor[0]).to(b_tensor[1])
+        ops.post_status(x_hat.device)
         return (dx if need[0] else None), (dy if need[1] else None), dt, db, None
 
 
