@@ -98,7 +98,7 @@ int meclip_debug_wait_probe(uint64_t limit_ns, int* status, void* stream);
 /*
  * Test hook: override the backward's blocking (rows of the coefficient matrix formed per
  * block, a multiple of 128, and the byte limit of one panel) so that small problems run
- * the multi-panel / multi-row-block code paths; 0, 0 restores the defaults (32768 rows,
+ * the multi-panel / multi-row-block code paths; 0, 0 restores the defaults (16384 rows,
  * 512 MiB).  Affects meclip_grad_workspace_bytes too.  Has no counterpart in the reference.
  */
 int meclip_debug_set_blocking(int64_t row_block, int64_t panel_bytes);

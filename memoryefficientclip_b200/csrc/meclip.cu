@@ -755,10 +755,12 @@ static int launch_gemm(int epi, const Operand& a, const Operand& b, long long m,
     if (stages < 2) return fail(MECLIP_EINVAL, "tile does not fit shared memory");
     if (pair) p.num_m_tiles = (int)((m + PAIR_BM - 1) / PAIR_BM);
     if (epi == EPI_OUT && p.bn_last < bn && p.num_n_tiles >= 2) {
-        // Narrow tiles last (MECLIP_NARROW_LAST: 0 never, 1 when the launch has fewer than four waves of tiles,
-        // 2 always).  Few long tiles: the short ones even out the last wave.  Many tiles: the walk that keeps a
-        // row tile's column tiles together re-uses the A operand from L2 and wins.
-        static const int env_narrow = []() { const char* v = std::getenv("MECLIP_NARROW_LAST"); return v ? std::atoi(v) : 1; }();
+        // Narrow tiles last (MECLIP_NARROW_LAST: 0 never (the default), 1 when the launch has fewer than four
+        // waves of tiles, 2 always): the short tiles would even out the last wave, but they then read their
+        // rows of the A operand a second time from HBM instead of from L2 next to the wide tiles of the same
+        // rows.  Measured at B = 32768, D = 1152: dY alone 977 (off) / 971 (on) TFLOP/s, step 8.10-8.14 /
+        // 8.24-8.27 ms (fewer than four waves), 8.40 ms (always).  Kept as a switch for that A/B only.
+        static const int env_narrow = []() { const char* v = std::getenv("MECLIP_NARROW_LAST"); return v ? std::atoi(v) : 0; }();
         const long long slots = pair ? sm_count() / 2 : sm_count();
         const long long tiles_all = (long long)p.num_m_tiles * p.num_n_tiles;
         if (env_narrow == 2 || (env_narrow == 1 && tiles_all < 4 * slots)) p.narrow_last = 1;
@@ -797,7 +799,12 @@ static int launch_gemm(int epi, const Operand& a, const Operand& b, long long m,
 // ------------------------------------------------------------------------------------
 // backward blocking
 // ------------------------------------------------------------------------------------
-static constexpr long long ROW_BLOCK = 32768;                  // rows of G formed per block
+// Rows of G formed per block.  The two contractions of a block have (rows / 256) x column tiles (dX) and
+// (panel width / 256) x column tiles (dY) CTA-pair tiles, so a square block gives both the same number of
+// tiles.  Measured at B = 32768, D = 1152, kernels timed alone (TFLOP/s dX / dY) and the step (ms), one GPU,
+// one call: blocks of 32768 x 8192: 1205 / 977, 8.10-8.14; 16384 x 16384: 1141-1150 / 1136-1144, 8.03-8.13;
+// with 1 GiB panels 32768 x 16384: 1254 / 1162, 8.07 and 16384 x 32768: 1173 / 1260, 7.98.
+static constexpr long long ROW_BLOCK = 16384;
 static constexpr long long PANEL_BYTES = 512ll << 20;          // most bytes one bf16 coefficient panel may take
 
 struct GradPlan {

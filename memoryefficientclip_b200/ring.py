@@ -30,6 +30,27 @@ import torch.nn as nn
 from . import _lib, ops
 
 
+# Phase marks for a per-phase breakdown of one step (benchmarks): while TRACE is a list, the functions below
+# append (label, CUDA event) pairs recorded on the current stream; the time between two consecutive marks is
+# what the compute stream spent on the phase the LATER mark names.  None (the default) records nothing.
+TRACE = None
+
+
+def _mark(label: str) -> None:
+    if TRACE is not None:
+        ev = torch.cuda.Event(enable_timing=True)
+        ev.record()
+        TRACE.append((label, ev))
+
+
+def trace_durations(trace):
+    """{label: milliseconds} summed over the marks of a finished (synchronised) trace."""
+    out = {}
+    for (_, a), (label, b) in zip(trace[:-1], trace[1:]):
+        out[label] = out.get(label, 0.0) + a.elapsed_time(b)
+    return out
+
+
 def shard_at(rank: int, step: int, world: int) -> int:
     """Index of the text shard rank `rank` holds at ring step `step`."""
     return (rank + step) % world
@@ -153,6 +174,7 @@ def ring_forward(block, kind, x_hat, y_hat, temperature, group, rank, world):
     if world > 2:
         bufs.append(torch.empty_like(y_hat))      # never receive into the caller's own shard
     cur = 0
+    _mark("fwd_setup")
     for step in range(world):
         shard = shard_at(rank, step, world)
         reqs = []
@@ -161,8 +183,10 @@ def ring_forward(block, kind, x_hat, y_hat, temperature, group, rank, world):
             reqs = _rotate(bufs[cur], bufs[nxt], group, rank, world)
         block.sum_exp(kind, x_hat, bufs[cur], temperature, row_sum, col_part[shard] if clip else None, diag,
                       rank * b, shard * b)
+        _mark("fwd_kernels")
         for r in reqs:
             r.wait()
+        _mark("fwd_exposed_shard_wait")
         if step + 1 < world:
             cur = nxt
     col_sum = None
@@ -172,9 +196,11 @@ def ring_forward(block, kind, x_hat, y_hat, temperature, group, rank, world):
             block.reduce_scatter(col_sum, col_part, group)
         else:
             col_sum = col_part[0]
+    _mark("fwd_reduce_scatter_col_sums")
     loss = block.local_loss_sum(kind, row_sum, col_sum, diag, temperature, 1.0 / (b * world))
     if world > 1:
         dist.all_reduce(loss, op=dist.ReduceOp.SUM, group=group)
+    _mark("fwd_loss_all_reduce")
     return loss, row_sum, col_sum, diag
 
 
@@ -204,6 +230,7 @@ def _ring_backward_loop(block, x_hat, y_hat, group, rank, world, want_dy, grad_c
         bufs.append(torch.empty_like(y_hat))
     cur = 0
     pending = None          # (requests, inbox buffer) of the previous step's partial exchange
+    _mark("bwd_setup")
     for step in range(world):
         shard = shard_at(rank, step, world)
         reqs = []
@@ -214,21 +241,27 @@ def _ring_backward_loop(block, x_hat, y_hat, group, rank, world, want_dy, grad_c
         if want_dy:
             out = dy if step == 0 else part[step % 2]
         grad_call(bufs[cur], shard, dx, out, workspace)
+        _mark("bwd_kernels")
         if pending is not None:          # the exchange started one step ago ran under this step's kernels
             for r in pending[0]:
                 r.wait()
+            _mark("bwd_exposed_partial_wait")
             block.accumulate(dy, pending[1])
+            _mark("bwd_accumulate_f32")
             pending = None
         if want_dy and step > 0:
             pending = (_exchange_partial(part[step % 2], inbox[step % 2], group, rank, world, step), inbox[step % 2])
         for r in reqs:
             r.wait()
+        _mark("bwd_exposed_shard_wait")
         if step + 1 < world:
             cur = nxt
     if pending is not None:
         for r in pending[0]:
             r.wait()
+        _mark("bwd_exposed_last_partial_wait")
         block.accumulate(dy, pending[1])
+        _mark("bwd_accumulate_f32")
     return dx, dy
 
 
@@ -242,7 +275,9 @@ def ring_backward(block, kind, x_hat, y_hat, temperature, row_sum, col_sum, grad
     if clip:
         if world > 1:
             col_all = torch.empty(world, b, dtype=torch.float32, device=x_hat.device)
+            _mark("fwd_to_bwd_gap")
             block.all_gather(col_all, col_sum, group)
+            _mark("bwd_all_gather_col_sums")
         else:
             col_all = col_sum.view(1, b)
     extra = {} if sum_g_s is None else {"sum_g_s": sum_g_s}
@@ -360,8 +395,10 @@ class RingContrastiveLossFn(torch.autograd.Function):
             ctx.ring = (temperature, kind, bool(stable), bool(normalize), x.dtype, y.dtype, x.shape[1], group, rank,
                         world, block)
             return loss
+        _mark("fwd_begin")
         x_hat, inv_x = block.prepare(x, normalize)
         y_hat, inv_y = block.prepare(y, normalize)
+        _mark("fwd_normalize")
         loss, row_sum, col_sum, _diag = ring_forward(block, kind, x_hat, y_hat, temperature, group, rank, world)
         saved = [x_hat, y_hat, row_sum]
         if col_sum is not None:
@@ -405,6 +442,7 @@ class RingContrastiveLossFn(torch.autograd.Function):
         dx = block.finish_grad(dx, x_hat, inv_x, x_dtype, d)
         if dy is not None:
             dy = block.finish_grad(dy, y_hat, inv_y, y_dtype, d)
+        _mark("bwd_normalize_jacobian")
         dt = None
         if t_info is not None:
             t_param, mode = t_info

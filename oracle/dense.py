@@ -193,9 +193,11 @@ def clip_streaming(xn: torch.Tensor, yn: torch.Tensor, temperature: float, sampl
     r = torch.zeros(b, dtype=torch.float64)
     c = torch.zeros(b, dtype=torch.float64)
     for i0 in range(0, b, block):
-        e = torch.exp2((xn[i0:i0 + block] @ yn.t()) * k - k).double()
-        r[i0:i0 + block] = e.sum(dim=1)
-        c += e.sum(dim=0)
+        e = xn[i0:i0 + block] @ yn.t()              # in place from here on: one [block, B] buffer per trip
+        e.mul_(k).sub_(k)
+        torch.exp2(e, out=e)
+        r[i0:i0 + block] = e.sum(dim=1, dtype=torch.float64)
+        c += e.sum(dim=0, dtype=torch.float64)
     sv = ((xn.double() * yn.double()).sum(dim=1) * k - k) * math.log(2.0)
     if lit:
         loss = (torch.log(r) - sv).mean()
@@ -216,6 +218,56 @@ def clip_streaming(xn: torch.Tensor, yn: torch.Tensor, temperature: float, sampl
         gt = (et / r[None, :] + et / c[rows, None]) * (scale / 2)
         out["dy_rows"] = gt @ xn.double() - xn[rows].double() * scale
     return out
+
+
+def clip_blocked_step(xn: torch.Tensor, yn: torch.Tensor, temperature: float, row_block: int = 4096,
+                      rows: int | None = None, want_grads: bool = True):
+    """The reference's two-kernel algorithm on the host cores, fp32, in row blocks: a forward pass over
+    [row_block x B] strips of S = X Y^T for the row and column sums (clip_sum_exp_kernel,
+    clip_loss.py:36-64), the loss from the diagonal (clip_loss.py:206-211), then a backward pass that
+    RECOMPUTES each strip, forms G = (E/r + E/c) / (2 B T) (clip_loss.py:96-124) and contracts it:
+    dX_strip = G Y - Y_strip/(B T), dY += G^T X_strip (clip_loss.py:127-156, 235-236).  Executed FLOPs are
+    the 8 B^2 D the throughput metric counts; peak memory is three strips, never B x B.
+
+    rows: work on the first `rows` rows of X only (a bounded SAMPLE of a problem too large to time whole on
+    the host: the column sums then cover those rows only and the results are not the loss's, the work per
+    row is).  Returns (loss, dX [rows, D], dY [B, D]) - fp32 tensors."""
+    xn = xn.float()
+    yn = yn.float()
+    b, d = yn.shape
+    n = b if rows is None else min(rows, xn.shape[0])
+    k = LOG2E / temperature
+    r = torch.zeros(n, dtype=torch.float32)
+    c = torch.zeros(b, dtype=torch.float32)
+    yt = yn.t().contiguous()
+    for i0 in range(0, n, row_block):
+        i1 = min(n, i0 + row_block)
+        e = xn[i0:i1] @ yt
+        e.mul_(k).sub_(k)
+        torch.exp2(e, out=e)
+        r[i0:i1] = e.sum(dim=1)
+        c += e.sum(dim=0)
+    sv = ((xn[:n] * yn[:n]).sum(dim=1) * k - k) * math.log(2.0)
+    loss = 0.5 * (torch.log(r) + torch.log(c[:n]) - 2 * sv).mean()
+    if not want_grads:
+        return loss, None, None
+    scale = 1.0 / (temperature * b)
+    inv_r = (0.5 * scale) / r
+    inv_c = (0.5 * scale) / c
+    dx = torch.empty(n, d, dtype=torch.float32)
+    dy = torch.zeros(b, d, dtype=torch.float32)
+    for i0 in range(0, n, row_block):
+        i1 = min(n, i0 + row_block)
+        e = xn[i0:i1] @ yt
+        e.mul_(k).sub_(k)
+        torch.exp2(e, out=e)
+        g = e * inv_r[i0:i1, None]
+        g.addcmul_(e, inv_c[None, :])
+        torch.mm(g, yn, out=dx[i0:i1])
+        dx[i0:i1].sub_(yn[i0:i1] * scale)
+        dy.addmm_(g.t(), xn[i0:i1])
+    dy[:n].sub_(xn[:n] * scale)
+    return loss, dx, dy
 
 
 # --------------------------------------------------------------------------- #

@@ -29,3 +29,29 @@ def test_reference_arm_other_ranks_stay_silent():
                           "--steps", "1", "--warmup", "0"], capture_output=True, text=True, timeout=600, cwd=ROOT, env=env)
     assert out.returncode == 0
     assert not [l for l in out.stdout.splitlines() if l.startswith("{")]
+
+
+def test_reference_arm_samples_rows_only_when_the_step_is_too_large():
+    sys.path.insert(0, ROOT)
+    import bench
+    # the headline configuration is timed whole; the ring configurations as a row sample against all columns
+    assert bench.cpu_sample_rows(32768, 1152, 1.2e13) == 32768
+    rows = bench.cpu_sample_rows(262144, 1024, 1.2e13)
+    assert 512 <= rows < 262144 and rows % 512 == 0
+    assert 8.0 * rows * 262144 * 1024 <= 1.2e13
+
+
+def test_blocked_cpu_step_is_the_dense_loss():
+    """The reference arm's workload (oracle.dense.clip_blocked_step) is the same loss and the same gradients
+    as the dense formulation; a row sample does the full problem's work per row."""
+    import torch
+    import torch.nn.functional as F
+    from oracle import dense
+    g = torch.Generator().manual_seed(5)
+    x = F.normalize(torch.randn(700, 48, generator=g), dim=1)
+    y = F.normalize(torch.randn(700, 48, generator=g), dim=1)
+    loss, dx, dy = dense.clip_blocked_step(x, y, 0.07, row_block=256)
+    rl, rx, ry = dense.clip_dense(x, y, 0.07, True)
+    dense.assert_parity(float(loss), rl, (dx, dy), (rx, ry), "blocked cpu step")
+    _l, dxs, dys = dense.clip_blocked_step(x, y, 0.07, row_block=128, rows=256)
+    assert dxs.shape == (256, 48) and dys.shape == (700, 48)

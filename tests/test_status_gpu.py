@@ -84,19 +84,21 @@ def test_learnable_temperature_without_host_sync(kind, stable):
     cls = {("clip", False): m.MemoryEfficientCLIPLoss, ("clip", True): m.StableMemoryEfficientCLIPLoss,
            ("lit", False): m.MemoryEfficientLiTLoss, ("lit", True): m.StableMemoryEfficientLiTLoss}[(kind, stable)]
 
-    def run():
-        xg = x.cuda().requires_grad_(True)
-        yg = y.cuda().requires_grad_(kind == "clip")
-        t = torch.tensor(t0, device="cuda", requires_grad=True)
+    def inputs():      # made outside the checked region: a copy from pageable host memory synchronises
+        return (x.cuda().requires_grad_(True), y.cuda().requires_grad_(kind == "clip"),
+                torch.tensor(t0, device="cuda", requires_grad=True))
+
+    def run(xg, yg, t):
         loss = cls(t, normalized_inputs=False)(xg, yg)
         loss.backward()
-        return loss, xg, yg, t
+        return loss
 
-    run()                                          # warm-up: library load, pinned status buffer, side streams
+    run(*inputs())                                 # warm-up: library load, pinned status buffer, side streams
+    xg, yg, t = inputs()
     torch.cuda.synchronize()
     torch.cuda.set_sync_debug_mode("error")
     try:
-        loss, xg, yg, t = run()
+        loss = run(xg, yg, t)
     finally:
         torch.cuda.set_sync_debug_mode("default")
     torch.cuda.synchronize()
@@ -126,18 +128,18 @@ def test_siglip_scale_and_bias_without_host_sync():
     x, y = _pair(b, d, 6)
     mod = m.MemoryEfficientSigLIPLoss(10.0, -10.0, normalized_inputs=True).cuda()
 
-    def run():
-        mod.zero_grad()
-        xg, yg = x.cuda().requires_grad_(True), y.cuda().requires_grad_(True)
+    def run(xg, yg):
         loss = mod(xg, yg)
         loss.backward()
-        return loss, xg, yg
+        return loss
 
-    run()
+    run(x.cuda().requires_grad_(True), y.cuda().requires_grad_(True))
+    mod.zero_grad()
+    xg, yg = x.cuda().requires_grad_(True), y.cuda().requires_grad_(True)
     torch.cuda.synchronize()
     torch.cuda.set_sync_debug_mode("error")
     try:
-        loss, xg, yg = run()
+        loss = run(xg, yg)
     finally:
         torch.cuda.set_sync_debug_mode("default")
     torch.cuda.synchronize()
