@@ -87,6 +87,27 @@ enum meclip_grad_scale_rule {
 int meclip_bind_device_scalars(const float* temperature_or_scale, const float* logit_bias, int grad_scale_rule);
 
 /*
+ * Peer memory for the ring on one NVLink box (one process per GPU).  A rank exports a handle for a device
+ * buffer it owns; the other ranks of the node open it and fetch the visiting shard from it with
+ * meclip_copy_async, a plain device-to-device cudaMemcpyAsync that runs on the copy engines: no SM is
+ * taken from the persistent tile kernels while a shard is in flight, and no kernel of this library ever
+ * reads another GPU's memory (a shard always lands in local memory first).
+ *   meclip_ipc_export  handle_out: MECLIP_IPC_HANDLE_BYTES host bytes naming the ALLOCATION that contains ptr
+ *                      (as cudaMalloc made it), offset_out: ptr's byte offset inside it
+ *   meclip_ipc_open    maps that allocation into the calling process (current device, peer access enabled
+ *                      on demand) and returns its base; a handle can be opened once per process
+ *   meclip_ipc_close   unmaps it
+ *   meclip_copy_async  cudaMemcpyAsync(dst, src, bytes, device-to-device) on `stream`
+ * Ordering between processes (when a buffer may be read, when it may be overwritten) is the caller's:
+ * the ring host uses its collectives for that.  The reference has no counterpart (it is single-GPU).
+ */
+#define MECLIP_IPC_HANDLE_BYTES 64
+int meclip_ipc_export(const void* ptr, void* handle_out, uint64_t* offset_out);
+int meclip_ipc_open(const void* handle, void** base_out);
+int meclip_ipc_close(void* base);
+int meclip_copy_async(void* dst, const void* src, size_t bytes, void* stream);
+
+/*
  * Test hook: one tiny kernel (one CTA, no tile loads, no tensor memory) that waits on a barrier nobody
  * arrives on, with the same bounded-wait routine the tile kernels use and a limit of limit_ns nanoseconds
  * (at most 100 ms).  The wait runs out, the kernel sets *status non-zero and ends normally, so that

@@ -26,6 +26,10 @@ SIGNATURES = {
     "meclip_last_error": (c_int, [c_char_p, c_size_t]),
     "meclip_read_status": (c_int, [c_void_p, c_void_p]),
     "meclip_bind_device_scalars": (c_int, [c_void_p, c_void_p, c_int]),
+    "meclip_ipc_export": (c_int, [c_void_p, c_void_p, c_void_p]),
+    "meclip_ipc_open": (c_int, [c_void_p, c_void_p]),
+    "meclip_ipc_close": (c_int, [c_void_p]),
+    "meclip_copy_async": (c_int, [c_void_p, c_void_p, c_size_t, c_void_p]),
     "meclip_debug_wait_probe": (c_int, [ctypes.c_uint64, c_void_p, c_void_p]),
     "meclip_debug_set_blocking": (c_int, [c_int64, c_int64]),
     "meclip_debug_set_trace": (c_int, [c_void_p, c_size_t]),

@@ -1,0 +1,119 @@
+"""Shard transport of the ring over peer memory: each rank PUBLISHES its own shard in a buffer
+the other ranks of the node have mapped (CUDA IPC), and a rank that needs shard j at ring step
+s fetches it from its owner with a device-to-device cudaMemcpyAsync on a copy stream.
+
+Why not NCCL send/recv for the shards: an NCCL transfer is a kernel and needs SMs, while the
+persistent tile kernels hold every SM of the GPU (227 KiB of shared memory per CTA), so a
+send/recv queued next to them starts only when a tile kernel ends, i.e. the transfer is not
+hidden under the MMAs but runs in the gaps between kernels.  Measured on 8 GPUs at global
+B = 131072, D = 768: 1.8 ms of a 14.5 ms step were spent waiting for shards.  Copy engines need
+no SM.
+
+Ordering between the processes comes from collectives the ring issues anyway:
+  * a rank's publish is followed by a one-word all-reduce on the copy stream; a fetch is queued
+    behind it, so it starts only after EVERY rank has published (the all-reduce completes
+    nowhere before all ranks have contributed, and each contributes after its publish);
+  * there are two publish slots, used alternately by successive forwards.  A slot is
+    overwritten two forwards later; by then every rank has passed the next forward's all-reduce,
+    which it enters only after the fetches of its previous forward and backward have completed
+    (stream order).  A backward must therefore run before the second-next forward of the same
+    module and shapes (checked: RuntimeError otherwise).
+No kernel ever reads a peer's memory: a shard always lands in a local buffer first.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+import torch.distributed as dist
+
+from . import _lib
+
+
+class PeerShards:
+    """Two publish slots of `rows x cols` elements on this rank, mapped by all ranks of `group`."""
+
+    def __init__(self, group, rank: int, world: int, rows: int, cols: int, dtype, device):
+        self.group, self.rank, self.world = group, rank, world
+        self.shape = (rows, cols)
+        self.dtype = dtype
+        self.device = device
+        self.slot_bytes = rows * cols * torch.empty((), dtype=dtype).element_size()
+        # one allocation for both slots: one handle per rank, opened once per process
+        self.local = torch.empty(2, rows, cols, dtype=dtype, device=device)
+        self.comm = torch.cuda.Stream(device=device)
+        self.flag = torch.zeros(1, dtype=torch.float32, device=device)
+        self.gen = 0                     # forwards published so far
+        lib = _lib.load()
+        handle = ctypes.create_string_buffer(64)
+        offset = ctypes.c_uint64(0)
+        with torch.cuda.device(device):
+            _lib.check(lib.meclip_ipc_export(self.local.data_ptr(), handle, ctypes.byref(offset)))
+        mine = (bytes(handle.raw), int(offset.value))
+        everyone = [None] * world
+        dist.all_gather_object(everyone, mine, group=group)
+        self.peer_slot0 = [0] * world    # address of slot 0 of every rank in THIS process
+        self._bases = []
+        self.ok = True
+        try:
+            for p, (h, off) in enumerate(everyone):
+                if p == rank:
+                    self.peer_slot0[p] = self.local.data_ptr()
+                    continue
+                base = ctypes.c_void_p()
+                with torch.cuda.device(device):
+                    _lib.check(lib.meclip_ipc_open(ctypes.create_string_buffer(h, 64), ctypes.byref(base)))
+                self._bases.append(base.value)
+                self.peer_slot0[p] = base.value + off
+        except _lib.MeclipError:
+            self.ok = False              # e.g. a rank on another node: its memory cannot be mapped here
+        # all ranks must agree on the transport: one that could not map a peer sends everyone back to send/recv
+        verdicts = [None] * world
+        dist.all_gather_object(verdicts, self.ok, group=group)
+        self.ok = all(verdicts)
+
+    def publish(self, shard: torch.Tensor) -> int:
+        """Copy this rank's shard into the next slot (current stream) and start the all-reduce that tells
+        every rank that all shards are in place.  Returns the generation to fetch from."""
+        gen = self.gen
+        self.gen += 1
+        slot = self.local[gen % 2]
+        slot.copy_(shard)
+        done = torch.cuda.Event()
+        done.record()
+        with torch.cuda.stream(self.comm):
+            self.comm.wait_event(done)
+            dist.all_reduce(self.flag, group=self.group)      # fetches queued on self.comm start behind it
+        return gen
+
+    def check_live(self, gen: int) -> None:
+        if self.gen > gen + 2:
+            raise RuntimeError("ring (peer transport): this backward belongs to a forward whose published shard has "
+                               "been overwritten by two later forwards of the same shapes; run the backward earlier "
+                               "or set MECLIP_RING_TRANSPORT=nccl")
+
+    def fetch(self, gen: int, owner: int, into: torch.Tensor, after=None) -> torch.cuda.Event:
+        """Queue the copy of `owner`'s shard of generation `gen` into the local tensor `into` on the copy
+        stream, behind `after` (the event that says `into` is free again); returns the completion event."""
+        assert into.is_contiguous() and into.numel() * into.element_size() == self.slot_bytes
+        src = self.peer_slot0[owner] + (gen % 2) * self.slot_bytes
+        with torch.cuda.device(self.device):
+            if after is not None:
+                self.comm.wait_event(after)
+            _lib.check(_lib.load().meclip_copy_async(into.data_ptr(), src, self.slot_bytes, self.comm.cuda_stream))
+            ev = torch.cuda.Event()
+            ev.record(self.comm)
+        return ev
+
+
+_cache = {}
+
+
+def get(group, rank, world, rows, cols, dtype, device):
+    """The exchange for this group and shard shape, created (collectively, once) on first use; None when
+    some rank could not map a peer's buffer (the ring then falls back to send/recv on every rank)."""
+    key = (id(group) if group is not None else 0, world, rows, cols, dtype, device.index)
+    if key not in _cache:
+        ex = PeerShards(group, rank, world, rows, cols, dtype, device)
+        _cache[key] = ex if ex.ok else None
+    return _cache[key]

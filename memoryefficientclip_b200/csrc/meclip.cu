@@ -1595,6 +1595,54 @@ int meclip_grad_static(int kind, const void* x_bf16, const void* y_bf16, int64_t
                      status, (cudaStream_t)stream, false, false, nullptr, 0.f, 0.f, 0, false, ds, false);
 }
 
+// ------------------------------------------------------------------------------------
+// peer memory of another process on the same node (ring: shards fetched by the copy engines)
+// ------------------------------------------------------------------------------------
+int meclip_ipc_export(const void* ptr, void* handle_out, uint64_t* offset_out) {
+    if (ptr == nullptr || handle_out == nullptr || offset_out == nullptr) return fail(MECLIP_EINVAL, "ipc_export: null pointer");
+    static_assert(sizeof(cudaIpcMemHandle_t) == MECLIP_IPC_HANDLE_BYTES, "handle size");
+    typedef CUresult (*RangeFn)(CUdeviceptr*, size_t*, CUdeviceptr);
+    static RangeFn range_fn = []() -> RangeFn {
+        void* f = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuMemGetAddressRange", &f, cudaEnableDefault, &q) != cudaSuccess) return nullptr;
+        return q == cudaDriverEntryPointSuccess ? reinterpret_cast<RangeFn>(f) : nullptr;
+    }();
+    if (range_fn == nullptr) return fail(MECLIP_EUNSUPPORTED, "ipc_export: cuMemGetAddressRange not available");
+    CUdeviceptr base = 0;
+    size_t size = 0;
+    if (range_fn(&base, &size, (CUdeviceptr)(uintptr_t)ptr) != CUDA_SUCCESS)
+        return fail(MECLIP_ECUDA, "ipc_export: %p is not inside a device allocation", ptr);
+    cudaIpcMemHandle_t h;
+    MECLIP_CUDA(cudaIpcGetMemHandle(&h, reinterpret_cast<void*>((uintptr_t)base)));
+    std::memcpy(handle_out, &h, sizeof(h));
+    *offset_out = (uint64_t)((uintptr_t)ptr - (uintptr_t)base);
+    return MECLIP_OK;
+}
+
+int meclip_ipc_open(const void* handle, void** base_out) {
+    if (handle == nullptr || base_out == nullptr) return fail(MECLIP_EINVAL, "ipc_open: null pointer");
+    cudaIpcMemHandle_t h;
+    std::memcpy(&h, handle, sizeof(h));
+    void* base = nullptr;
+    MECLIP_CUDA(cudaIpcOpenMemHandle(&base, h, cudaIpcMemLazyEnablePeerAccess));
+    *base_out = base;
+    return MECLIP_OK;
+}
+
+int meclip_ipc_close(void* base) {
+    if (base == nullptr) return fail(MECLIP_EINVAL, "ipc_close: null pointer");
+    MECLIP_CUDA(cudaIpcCloseMemHandle(base));
+    return MECLIP_OK;
+}
+
+int meclip_copy_async(void* dst, const void* src, size_t bytes, void* stream) {
+    if (dst == nullptr || src == nullptr) return fail(MECLIP_EINVAL, "copy_async: null pointer");
+    if (bytes == 0) return MECLIP_OK;
+    MECLIP_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, (cudaStream_t)stream));
+    return MECLIP_OK;
+}
+
 int meclip_debug_wait_probe(uint64_t limit_ns, int* status, void* stream) {
     if (status == nullptr) return fail(MECLIP_EINVAL, "wait_probe: status is null");
     if (limit_ns == 0 || limit_ns > 100000000ull) return fail(MECLIP_EINVAL, "wait_probe: limit must be in (0, 100 ms]");

@@ -51,6 +51,11 @@ def trace_durations(trace):
     return out
 
 
+# how the shards of the second argument reach the ranks: "peer" (copy-engine fetches from the owner's published
+# buffer) or "nccl" (send/recv from rank to rank)
+_TRANSPORT = __import__("os").environ.get("MECLIP_RING_TRANSPORT", "peer").lower()
+
+
 def shard_at(rank: int, step: int, world: int) -> int:
     """Index of the text shard rank `rank` holds at ring step `step`."""
     return (rank + step) % world
@@ -77,6 +82,22 @@ class CudaBlockOps:
 
     def end_step(self, device):
         ops.post_status(device)
+
+    def rotation(self, y_own, group, rank, world, token=None):
+        """Shard transport: peer-memory fetches by the copy engines (the default on GPUs; see _peer.py) or,
+        with MECLIP_RING_TRANSPORT=nccl, send/recv from rank to rank (returns None: the caller's default)."""
+        if _TRANSPORT != "peer" or not y_own.is_cuda:
+            return None
+        from . import _peer
+        ex = token[0] if token is not None else _peer.get(group, rank, world, y_own.shape[0], y_own.shape[1],
+                                                          y_own.dtype, y_own.device)
+        if ex is None:
+            return None
+        if token is None:
+            token = (ex, ex.publish(y_own))       # forward: publish this rank's shard for everyone
+        else:
+            ex.check_live(token[1])               # backward: the shards of its own forward
+        return _PeerRotation(ex, token[1], y_own, rank, world), token
 
     def prepare(self, x, normalize):
         if normalize:
@@ -162,33 +183,91 @@ def _rotate(cur: torch.Tensor, nxt: torch.Tensor, group, rank: int, world: int):
     return dist.batch_isend_irecv(p2p)
 
 
+class _SendRecvRotation:
+    """The shards travel rank to rank: at step s a rank sends the shard it works on to rank-1 and receives
+    the next one from rank+1 (NCCL on GPUs, gloo in the CPU tests)."""
+
+    def __init__(self, y_own, group, rank, world):
+        self.group, self.rank, self.world = group, rank, world
+        self.bufs = [y_own, torch.empty_like(y_own)] if world > 1 else [y_own]
+        if world > 2:
+            self.bufs.append(torch.empty_like(y_own))      # never receive into the caller's own shard
+        self.cur = 0
+        self.nxt = 0
+        self.reqs = []
+
+    def begin(self, step):
+        """Called before the step's kernels are queued; returns the shard they work on."""
+        if step + 1 < self.world:
+            self.nxt = 1 + (step % 2) if self.world > 2 else 1
+            self.reqs = _rotate(self.bufs[self.cur], self.bufs[self.nxt], self.group, self.rank, self.world)
+        return self.bufs[self.cur]
+
+    def end(self, step):
+        """Called after the step's kernels were queued: wait for the transfer that ran under them."""
+        for r in self.reqs:
+            r.wait()
+        self.reqs = []
+        if step + 1 < self.world:
+            self.cur = self.nxt
+
+
+class _PeerRotation:
+    """Every rank fetches the shard of step s+1 from its owner's published buffer with the copy engines
+    while the kernels of step s run (_peer.PeerShards)."""
+
+    def __init__(self, exchange, gen, y_own, rank, world):
+        self.ex, self.gen, self.rank, self.world = exchange, gen, rank, world
+        self.y_own = y_own
+        self.recv = [torch.empty_like(y_own) for _ in range(min(2, world - 1))]
+        self.kernels_done = {}
+        self.fetched = {}
+
+    def begin(self, step):
+        if step + 1 < self.world:      # the buffer it lands in was last read by the kernels of step - 1
+            owner = shard_at(self.rank, step + 1, self.world)
+            self.fetched[step + 1] = self.ex.fetch(self.gen, owner, self.recv[(step + 1) % len(self.recv)],
+                                                   after=self.kernels_done.get(step - 1))
+        if step == 0:
+            return self.y_own
+        torch.cuda.current_stream().wait_event(self.fetched.pop(step))
+        return self.recv[step % len(self.recv)]
+
+    def end(self, step):
+        ev = torch.cuda.Event()
+        ev.record()
+        self.kernels_done[step] = ev
+
+
+def _rotation(block, y_own, group, rank, world, token=None):
+    """(rotation, token): the block implementation may bring its own shard transport; the token is what a
+    backward needs to find the same shards again."""
+    if world > 1 and hasattr(block, "rotation"):
+        made = block.rotation(y_own, group, rank, world, token)
+        if made is not None:
+            return made
+    return _SendRecvRotation(y_own, group, rank, world), None
+
+
 def ring_forward(block, kind, x_hat, y_hat, temperature, group, rank, world):
-    """Returns (loss, row_sum [b], col_sum_own [b] or None, diag [b])."""
+    """Returns (loss, row_sum [b], col_sum_own [b] or None, diag [b], transport token for the backward)."""
     b, d = x_hat.shape
     dev = x_hat.device
     clip = kind == _lib.CLIP
     row_sum = torch.zeros(b, dtype=torch.float32, device=dev)
     diag = torch.zeros(b, dtype=torch.float32, device=dev)
     col_part = torch.zeros(world, b, dtype=torch.float32, device=dev) if clip else None
-    bufs = [y_hat, torch.empty_like(y_hat)] if world > 1 else [y_hat]
-    if world > 2:
-        bufs.append(torch.empty_like(y_hat))      # never receive into the caller's own shard
-    cur = 0
+    rot, token = _rotation(block, y_hat, group, rank, world)
     _mark("fwd_setup")
     for step in range(world):
         shard = shard_at(rank, step, world)
-        reqs = []
-        if step + 1 < world:
-            nxt = 1 + (step % 2) if world > 2 else 1
-            reqs = _rotate(bufs[cur], bufs[nxt], group, rank, world)
-        block.sum_exp(kind, x_hat, bufs[cur], temperature, row_sum, col_part[shard] if clip else None, diag,
+        y_cur = rot.begin(step)
+        _mark("fwd_exposed_shard_wait")
+        block.sum_exp(kind, x_hat, y_cur, temperature, row_sum, col_part[shard] if clip else None, diag,
                       rank * b, shard * b)
         _mark("fwd_kernels")
-        for r in reqs:
-            r.wait()
+        rot.end(step)
         _mark("fwd_exposed_shard_wait")
-        if step + 1 < world:
-            cur = nxt
     col_sum = None
     if clip:
         if world > 1:
@@ -201,7 +280,7 @@ def ring_forward(block, kind, x_hat, y_hat, temperature, group, rank, world):
     if world > 1:
         dist.all_reduce(loss, op=dist.ReduceOp.SUM, group=group)
     _mark("fwd_loss_all_reduce")
-    return loss, row_sum, col_sum, diag
+    return loss, row_sum, col_sum, diag, token
 
 
 def _exchange_partial(send_buf, recv_buf, group, rank, world, step):
@@ -215,7 +294,7 @@ def _exchange_partial(send_buf, recv_buf, group, rank, world, step):
     return dist.batch_isend_irecv(p2p)
 
 
-def _ring_backward_loop(block, x_hat, y_hat, group, rank, world, want_dy, grad_call):
+def _ring_backward_loop(block, x_hat, y_hat, group, rank, world, want_dy, grad_call, token=None):
     """The backward choreography shared by the softmax and the sigmoid losses.  grad_call(y_shard, shard,
     dx_acc, dy_out, workspace) runs the block kernels: dx_acc accumulates in fp32, dy_out is stored."""
     b, d = x_hat.shape
@@ -225,22 +304,17 @@ def _ring_backward_loop(block, x_hat, y_hat, group, rank, world, want_dy, grad_c
     part = [torch.empty(b, d, dtype=torch.float32, device=dev) for _ in range(2)] if want_dy and world > 1 else []
     inbox = [torch.empty(b, d, dtype=torch.float32, device=dev) for _ in range(2)] if want_dy and world > 1 else []
     workspace = block.workspace(b, b, d, dev)
-    bufs = [y_hat, torch.empty_like(y_hat)] if world > 1 else [y_hat]
-    if world > 2:
-        bufs.append(torch.empty_like(y_hat))
-    cur = 0
+    rot, _ = _rotation(block, y_hat, group, rank, world, token)
     pending = None          # (requests, inbox buffer) of the previous step's partial exchange
     _mark("bwd_setup")
     for step in range(world):
         shard = shard_at(rank, step, world)
-        reqs = []
-        if step + 1 < world:
-            nxt = 1 + (step % 2) if world > 2 else 1
-            reqs = _rotate(bufs[cur], bufs[nxt], group, rank, world)
+        y_cur = rot.begin(step)
+        _mark("bwd_exposed_shard_wait")
         out = None
         if want_dy:
             out = dy if step == 0 else part[step % 2]
-        grad_call(bufs[cur], shard, dx, out, workspace)
+        grad_call(y_cur, shard, dx, out, workspace)
         _mark("bwd_kernels")
         if pending is not None:          # the exchange started one step ago ran under this step's kernels
             for r in pending[0]:
@@ -251,11 +325,8 @@ def _ring_backward_loop(block, x_hat, y_hat, group, rank, world, want_dy, grad_c
             pending = None
         if want_dy and step > 0:
             pending = (_exchange_partial(part[step % 2], inbox[step % 2], group, rank, world, step), inbox[step % 2])
-        for r in reqs:
-            r.wait()
+        rot.end(step)
         _mark("bwd_exposed_shard_wait")
-        if step + 1 < world:
-            cur = nxt
     if pending is not None:
         for r in pending[0]:
             r.wait()
@@ -266,7 +337,7 @@ def _ring_backward_loop(block, x_hat, y_hat, group, rank, world, want_dy, grad_c
 
 
 def ring_backward(block, kind, x_hat, y_hat, temperature, row_sum, col_sum, grad_out, grad_scale, group, rank, world,
-                  sum_g_s=None, scale_rule=0):
+                  sum_g_s=None, scale_rule=0, token=None):
     """Returns (dx fp32 [b, D], dy_own fp32 [b, D] or None) w.r.t. the normalised operands.
     sum_g_s: optional zeroed pair; element 0 receives sum_ij G_ij S_ij over this rank's rows and ALL columns."""
     b = x_hat.shape[0]
@@ -288,7 +359,7 @@ def ring_backward(block, kind, x_hat, y_hat, temperature, row_sum, col_sum, grad
         block.grad(kind, x_hat, y_shard, temperature, row_sum, col_all[shard] if clip else None, grad_out, grad_scale,
                    dx_acc, dy_out, rank * b, shard * b, workspace, **extra)
 
-    return _ring_backward_loop(block, x_hat, y_hat, group, rank, world, clip, grad_call)
+    return _ring_backward_loop(block, x_hat, y_hat, group, rank, world, clip, grad_call, token)
 
 
 def ring_lit_fused_forward(block, x_hat, y_ext, d_pad, temperature, group, rank, world):
@@ -298,21 +369,12 @@ def ring_lit_fused_forward(block, x_hat, y_ext, d_pad, temperature, group, rank,
     b = x_hat.shape[0]
     u = block.new_u(b, d_pad, x_hat.device)
     workspace = block.workspace(b, b, d_pad + 8, x_hat.device)
-    bufs = [y_ext, torch.empty_like(y_ext)] if world > 1 else [y_ext]
-    if world > 2:
-        bufs.append(torch.empty_like(y_ext))
-    cur = 0
+    rot, _ = _rotation(block, y_ext, group, rank, world)
     for step in range(world):
         shard = shard_at(rank, step, world)
-        reqs = []
-        if step + 1 < world:
-            nxt = 1 + (step % 2) if world > 2 else 1
-            reqs = _rotate(bufs[cur], bufs[nxt], group, rank, world)
-        block.lit_fused_block(x_hat, bufs[cur], d_pad, temperature, u, rank * b, shard * b, workspace)
-        for r in reqs:
-            r.wait()
-        if step + 1 < world:
-            cur = nxt
+        y_cur = rot.begin(step)
+        block.lit_fused_block(x_hat, y_cur, d_pad, temperature, u, rank * b, shard * b, workspace)
+        rot.end(step)
     row_sum, diag = block.lit_fused_stats(x_hat, y_ext, u, d_pad)        # the positives are the own shard's rows
     loss = block.local_loss_sum(_lib.LIT, row_sum, None, diag, temperature, 1.0 / (b * world))
     if world > 1:
@@ -326,29 +388,20 @@ def ring_siglip_forward(block, x_hat, y_hat, logit_scale, logit_bias, group, ran
     dev = x_hat.device
     row_sum = torch.zeros(b, dtype=torch.float32, device=dev)
     diag = torch.zeros(b, dtype=torch.float32, device=dev)
-    bufs = [y_hat, torch.empty_like(y_hat)] if world > 1 else [y_hat]
-    if world > 2:
-        bufs.append(torch.empty_like(y_hat))
-    cur = 0
+    rot, token = _rotation(block, y_hat, group, rank, world)
     for step in range(world):
         shard = shard_at(rank, step, world)
-        reqs = []
-        if step + 1 < world:
-            nxt = 1 + (step % 2) if world > 2 else 1
-            reqs = _rotate(bufs[cur], bufs[nxt], group, rank, world)
-        block.siglip_sum(x_hat, bufs[cur], logit_scale, logit_bias, row_sum, diag, rank * b, shard * b)
-        for r in reqs:
-            r.wait()
-        if step + 1 < world:
-            cur = nxt
+        y_cur = rot.begin(step)
+        block.siglip_sum(x_hat, y_cur, logit_scale, logit_bias, row_sum, diag, rank * b, shard * b)
+        rot.end(step)
     loss = block.siglip_local_loss(row_sum, diag, logit_scale, logit_bias, 1.0 / (b * world))
     if world > 1:
         dist.all_reduce(loss, op=dist.ReduceOp.SUM, group=group)
-    return loss
+    return loss, token
 
 
 def ring_siglip_backward(block, x_hat, y_hat, logit_scale, logit_bias, grad_out, grad_scale, group, rank, world,
-                         sums=None):
+                         sums=None, token=None):
     """Returns (dx, dy_own) fp32; sums (optional zeroed pair) receives {sum G S, sum G} over this rank's rows."""
     b = x_hat.shape[0]
 
@@ -356,7 +409,7 @@ def ring_siglip_backward(block, x_hat, y_hat, logit_scale, logit_bias, grad_out,
         block.siglip_grad(x_hat, y_shard, logit_scale, logit_bias, grad_out, grad_scale, dx_acc, dy_out, rank * b,
                           shard * b, workspace, sums)
 
-    return _ring_backward_loop(block, x_hat, y_hat, group, rank, world, True, grad_call)
+    return _ring_backward_loop(block, x_hat, y_hat, group, rank, world, True, grad_call, token)
 
 
 class RingContrastiveLossFn(torch.autograd.Function):
@@ -399,7 +452,8 @@ class RingContrastiveLossFn(torch.autograd.Function):
         x_hat, inv_x = block.prepare(x, normalize)
         y_hat, inv_y = block.prepare(y, normalize)
         _mark("fwd_normalize")
-        loss, row_sum, col_sum, _diag = ring_forward(block, kind, x_hat, y_hat, temperature, group, rank, world)
+        loss, row_sum, col_sum, _diag, ctx.ring_token = ring_forward(block, kind, x_hat, y_hat, temperature, group,
+                                                                     rank, world)
         saved = [x_hat, y_hat, row_sum]
         if col_sum is not None:
             saved.append(col_sum)
@@ -438,7 +492,7 @@ class RingContrastiveLossFn(torch.autograd.Function):
         t_info = getattr(ctx, "ring_t", None)
         sum_g_s = block.new_sum(x_hat.device) if t_info is not None else None
         dx, dy = ring_backward(block, kind, x_hat, y_hat, temperature, row_sum, col_sum, go, scale, group, rank, world,
-                               sum_g_s=sum_g_s, scale_rule=rule)
+                               sum_g_s=sum_g_s, scale_rule=rule, token=getattr(ctx, "ring_token", None))
         dx = block.finish_grad(dx, x_hat, inv_x, x_dtype, d)
         if dy is not None:
             dy = block.finish_grad(dy, y_hat, inv_y, y_dtype, d)
@@ -526,7 +580,7 @@ class RingSigLIPLossFn(torch.autograd.Function):
             bias = float(logit_bias.detach().item()) if isinstance(logit_bias, torch.Tensor) else float(logit_bias)
         if hasattr(block, "begin_step"):
             block.begin_step(x.device)
-        loss = ring_siglip_forward(block, x_hat, y_hat, t, bias, group, rank, world)
+        loss, ctx.ring_token = ring_siglip_forward(block, x_hat, y_hat, t, bias, group, rank, world)
         ctx.save_for_backward(*([x_hat, y_hat] + ([inv_x, inv_y] if normalize else [])))
         ctx.ring = (t, bias, bool(normalize), x.dtype, y.dtype, x.shape[1], group, rank, world, block, param_grad,
                     (logit_scale.shape, logit_scale.dtype) if isinstance(logit_scale, torch.Tensor) else None,
@@ -546,7 +600,8 @@ class RingSigLIPLossFn(torch.autograd.Function):
         sums = block.new_sum(x_hat.device) if want_tb else None
         # grad_scale = t / B; with a device-resident t the kernel multiplies 1/B by t itself
         gscale = 1.0 / (b * world) if ops.is_dev(t) else t / (b * world)
-        dx, dy = ring_siglip_backward(block, x_hat, y_hat, t, bias, go, gscale, group, rank, world, sums)
+        dx, dy = ring_siglip_backward(block, x_hat, y_hat, t, bias, go, gscale, group, rank, world, sums,
+                                      token=getattr(ctx, "ring_token", None))
         dx = block.finish_grad(dx, x_hat, inv_x, x_dtype, d)
         dy = block.finish_grad(dy, y_hat, inv_y, y_dtype, d)
         dt = db = None
