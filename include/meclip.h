@@ -70,7 +70,7 @@ int meclip_read_status(const int* status, void* stream);
  * binds device addresses for the NEXT tile-pass or loss-finalisation call made by the same host thread
  * (meclip_sum_exp, meclip_loss_finalize, meclip_loss_forward, meclip_grad, meclip_grad_t, meclip_grad_static,
  * meclip_loss_backward, meclip_lit_fused_forward, meclip_lit_fused_backward, meclip_siglip_sum,
- * meclip_siglip_grad); that call consumes the binding whether it succeeds or not and ignores its float
+ * meclip_siglip_grad, meclip_step_forward, meclip_step_backward); that call consumes the binding whether it succeeds or not and ignores its float
  * temperature / scale / bias arguments in favour of the bound values:
  *   temperature_or_scale  fp32 device scalar: T for CLIP / LiT, t for the sigmoid loss
  *   logit_bias            fp32 device scalar or NULL (sigmoid loss only; NULL keeps the float argument)
@@ -341,6 +341,33 @@ int meclip_loss_backward(int kind, const void* x_bf16, const void* y_bf16, int64
                          int64_t ldy, float temperature, const float* row_sum, const float* col_sum,
                          const float* grad_out, float grad_scale, void* dx, int dx_mode, int64_t lddx, void* dy,
                          int dy_mode, int64_t lddy, void* workspace, size_t workspace_bytes, int* status, void* stream);
+
+/*
+ * A whole training step of the module in two calls, for SMALL batches (up to a few thousand rows), where
+ * the step is bound by the host: the general entry points above cost about a dozen library calls, as many
+ * small allocations and 17 launches per step, against 0.06 ms of device work at B = 4096, D = 512.
+ *   meclip_step_forward   x, y: the module's inputs as they are (fp32 / bf16 / fp16, both the same dtype, any d
+ *                         and pitch); normalize != 0 does F.normalize(dim=1) inside (clip_loss.py:266-268).
+ *                         Four launches: both inputs -> bf16 operands (one kernel), ONE clear of
+ *                         row sums | column sums | diagonal | tile counter, the tile pass, the loss.
+ *                         `saved` (meclip_step_saved_bytes, 256-byte aligned) receives everything the backward
+ *                         needs: operands, inverse norms, sums.  Replaces clip_loss.py:160-213 + 265-271.
+ *   meclip_step_backward  coefficient panel, the two contractions (one stream, no transposed operand copies:
+ *                         at these sizes every extra launch costs more than it saves) and the Jacobian of the
+ *                         normalisation for both gradients in one kernel; dx / dy get out_dtype (either may be
+ *                         NULL).  `workspace`: meclip_step_workspace_bytes.  Replaces clip_loss.py:215-256 and the
+ *                         autograd node of F.normalize.
+ * Same arithmetic and kernels as the general path; results agree with it to the last bits of the bf16
+ * coefficient rounding.  A device-resident temperature is bound as for the other calls.
+ */
+size_t meclip_step_saved_bytes(int64_t batch, int64_t d);
+size_t meclip_step_workspace_bytes(int64_t batch, int64_t d);
+int meclip_step_forward(int kind, const void* x, const void* y, int in_dtype, int64_t batch, int64_t d, int64_t ldx,
+                        int64_t ldy, int normalize, float temperature, void* saved, size_t saved_bytes, float* loss_out,
+                        int* status, void* stream);
+int meclip_step_backward(int kind, const void* saved, size_t saved_bytes, int64_t batch, int64_t d, int normalize,
+                         float temperature, const float* grad_out, float grad_scale, void* dx, void* dy, int out_dtype,
+                         int64_t lddx, int64_t lddy, void* workspace, size_t workspace_bytes, int* status, void* stream);
 
 /*
  * Test hook: C (m x n, fp32, ldc) = A * B^T-style contraction through the same

@@ -13,6 +13,10 @@ import os
 
 from . import _lib, ops
 
+# Batches up to this many rows take the whole-step entry points (two library calls per step: the step is
+# host-bound there); MECLIP_STEP_PATH_ROWS=0 switches that path off.
+_STEP_PATH_ROWS = int(os.environ.get("MECLIP_STEP_PATH_ROWS", "8192"))
+
 # MECLIP_LIT_FUSED=0 keeps LiT on the two-pass path (sums, then recomputing backward) for A/B measurements
 _LIT_FUSED = os.environ.get("MECLIP_LIT_FUSED", "1") != "0"
 
@@ -53,6 +57,18 @@ class ContrastiveLossFn(torch.autograd.Function):
             ctx.meclip_fused = True
             return loss
         ctx.meclip_fused = False
+        ctx.meclip_step = False
+        if (kind == _lib.CLIP and not learn_t and x.shape[0] <= _STEP_PATH_ROWS and x.dtype == y.dtype
+                and x.stride(1) == 1 and y.stride(1) == 1 and x.stride(0) >= x.shape[1] and y.stride(0) >= y.shape[1]):
+            loss, saved = ops.step_forward(kind, x, y, normalize, temperature_value, status=status)
+            ctx.save_for_backward(saved)
+            ctx.meclip = (temperature_value, kind, bool(stable), bool(normalize), x.dtype, y.dtype, x.shape[1])
+            ctx.meclip_t = None
+            ctx.meclip_step = True
+            ctx.meclip_batch = x.shape[0]
+            if not any(ctx.needs_input_grad[:2]):
+                ops.post_status(x.device)
+            return loss
         if normalize:
             x_hat, inv_x = ops.normalize_fwd(x, True)
             y_hat, inv_y = ops.normalize_fwd(y, True)
@@ -90,6 +106,23 @@ class ContrastiveLossFn(torch.autograd.Function):
                 dx = ops.lit_fused_backward(u, y_ext, row_sum, go, scale, d, x_dtype, temperature, rule)
             ops.post_status(u.device)
             return dx, None
+        if getattr(ctx, "meclip_step", False):
+            buf = saved[0]
+            go = grad_output
+            if go.dtype != torch.float32 or go.device != buf.device or not go.is_contiguous():
+                go = go.detach().to(device=buf.device, dtype=torch.float32).reshape(1).contiguous()
+            batch = ctx.meclip_batch
+            scale, rule = ops.grad_scale_args(batch, temperature, stable)
+            need = tuple(ctx.needs_input_grad) + (False, False)
+            ctx.meclip_dt = None
+            if not (need[0] or need[1]):
+                return None, None
+            dx, dy = ops.step_backward(kind, buf, batch, d, normalize, temperature, go, scale, rule, x_dtype,
+                                       need_dx=bool(need[0]), need_dy=bool(need[1]),
+                                       status=ops.status_word(buf.device))
+            ctx.meclip_dt = None
+            ops.post_status(buf.device)
+            return dx, dy
         x_hat, y_hat, row_sum = saved[:3]
         rest = saved[3:]
         col_sum = rest.pop(0) if kind == _lib.CLIP else None

@@ -74,6 +74,12 @@ SIGNATURES = {
     "meclip_loss_backward": (c_int, [c_int, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_float,
                                      c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_int, c_int64, c_void_p,
                                      c_int, c_int64, c_void_p, c_size_t, c_void_p, c_void_p]),
+    "meclip_step_saved_bytes": (c_size_t, [c_int64, c_int64]),
+    "meclip_step_workspace_bytes": (c_size_t, [c_int64, c_int64]),
+    "meclip_step_forward": (c_int, [c_int, c_void_p, c_void_p, c_int, c_int64, c_int64, c_int64, c_int64, c_int, c_float,
+                                    c_void_p, c_size_t, c_void_p, c_void_p, c_void_p]),
+    "meclip_step_backward": (c_int, [c_int, c_void_p, c_size_t, c_int64, c_int64, c_int, c_float, c_void_p, c_float,
+                                     c_void_p, c_void_p, c_int, c_int64, c_int64, c_void_p, c_size_t, c_void_p, c_void_p]),
     "meclip_debug_gemm": (c_int, [c_void_p, c_int64, c_int, c_void_p, c_int64, c_int, c_int64, c_int64, c_int64,
                                   c_int, c_void_p, c_int64, c_void_p, c_void_p, c_void_p]),
 }

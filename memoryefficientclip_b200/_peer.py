@@ -30,6 +30,43 @@ import torch.distributed as dist
 from . import _lib
 
 
+_opened = {}       # (device index, handle bytes) -> base address of the mapping in this process
+
+
+def _map_everywhere(local: torch.Tensor, group, rank: int, world: int, device):
+    """Export `local` (this rank's buffer) and map every other rank's counterpart into this process.
+    Returns (addresses of the buffers of all ranks in this process, ok); collective over `group`."""
+    lib = _lib.load()
+    handle = ctypes.create_string_buffer(64)
+    offset = ctypes.c_uint64(0)
+    with torch.cuda.device(device):
+        _lib.check(lib.meclip_ipc_export(local.data_ptr(), handle, ctypes.byref(offset)))
+    everyone = [None] * world
+    dist.all_gather_object(everyone, (bytes(handle.raw), int(offset.value)), group=group)
+    addr = [0] * world
+    ok = True
+    try:
+        for p, (h, off) in enumerate(everyone):
+            if p == rank:
+                addr[p] = local.data_ptr()
+                continue
+            # An allocation can be mapped once per process; torch may carve several of our buffers out of one
+            # cudaMalloc block, which then share a handle: map it the first time, reuse the mapping afterwards.
+            key = (device.index, h)
+            if key not in _opened:
+                base = ctypes.c_void_p()
+                with torch.cuda.device(device):
+                    _lib.check(lib.meclip_ipc_open(ctypes.create_string_buffer(h, 64), ctypes.byref(base)))
+                _opened[key] = base.value
+            addr[p] = _opened[key] + off
+    except _lib.MeclipError:
+        ok = False                       # e.g. a rank on another node: its memory cannot be mapped here
+    # all ranks must agree on the transport: one that could not map a peer sends everyone back to send/recv
+    verdicts = [None] * world
+    dist.all_gather_object(verdicts, ok, group=group)
+    return addr, all(verdicts)
+
+
 class PeerShards:
     """Two publish slots of `rows x cols` elements on this rank, mapped by all ranks of `group`."""
 
@@ -44,33 +81,7 @@ class PeerShards:
         self.comm = torch.cuda.Stream(device=device)
         self.flag = torch.zeros(1, dtype=torch.float32, device=device)
         self.gen = 0                     # forwards published so far
-        lib = _lib.load()
-        handle = ctypes.create_string_buffer(64)
-        offset = ctypes.c_uint64(0)
-        with torch.cuda.device(device):
-            _lib.check(lib.meclip_ipc_export(self.local.data_ptr(), handle, ctypes.byref(offset)))
-        mine = (bytes(handle.raw), int(offset.value))
-        everyone = [None] * world
-        dist.all_gather_object(everyone, mine, group=group)
-        self.peer_slot0 = [0] * world    # address of slot 0 of every rank in THIS process
-        self._bases = []
-        self.ok = True
-        try:
-            for p, (h, off) in enumerate(everyone):
-                if p == rank:
-                    self.peer_slot0[p] = self.local.data_ptr()
-                    continue
-                base = ctypes.c_void_p()
-                with torch.cuda.device(device):
-                    _lib.check(lib.meclip_ipc_open(ctypes.create_string_buffer(h, 64), ctypes.byref(base)))
-                self._bases.append(base.value)
-                self.peer_slot0[p] = base.value + off
-        except _lib.MeclipError:
-            self.ok = False              # e.g. a rank on another node: its memory cannot be mapped here
-        # all ranks must agree on the transport: one that could not map a peer sends everyone back to send/recv
-        verdicts = [None] * world
-        dist.all_gather_object(verdicts, self.ok, group=group)
-        self.ok = all(verdicts)
+        self.peer_slot0, self.ok = _map_everywhere(self.local, group, rank, world, device)
 
     def publish(self, shard: torch.Tensor) -> int:
         """Copy this rank's shard into the next slot (current stream) and start the all-reduce that tells
@@ -106,6 +117,48 @@ class PeerShards:
         return ev
 
 
+class PeerInbox:
+    """Where the partial gradients of this rank's own shard arrive in the ring backward: world-1 fp32 buffers
+    of `rows x cols`, one per ring step, which the ranks that computed the partials fill with copy-engine
+    writes (a rank's partial for shard j goes straight into rank j's buffer of that step).
+
+    No per-transfer signal is needed.  After its last push a rank joins ONE one-word all-reduce on the copy
+    stream; when that completes on a rank, every rank's pushes - queued before its contribution - have
+    landed, and the owner adds the world-1 buffers to its gradient in a fixed order (deterministic).
+    A buffer is written again by the NEXT backward: that one starts with a collective of the ring (the
+    column-sum all-gather, or an all-reduce for the losses without one) which the owner joins only after
+    it has consumed the buffers (stream order), and pushes are queued behind kernels that wait for it."""
+
+    def __init__(self, group, rank: int, world: int, rows: int, cols: int, device):
+        self.group, self.rank, self.world, self.device = group, rank, world, device
+        self.slot_bytes = rows * cols * 4
+        self.local = torch.empty(world - 1, rows, cols, dtype=torch.float32, device=device)
+        self.comm = torch.cuda.Stream(device=device)
+        self.flag = torch.zeros(1, dtype=torch.float32, device=device)
+        self.addr, self.ok = _map_everywhere(self.local, group, rank, world, device)
+
+    def push(self, step: int, partial: torch.Tensor, after) -> torch.cuda.Event:
+        """Queue the copy of `partial` (computed at ring step `step` >= 1 for shard rank+step) into its owner's
+        buffer of that step, behind `after` (the kernels that wrote it); returns the completion event."""
+        assert 1 <= step < self.world and partial.is_contiguous() and partial.numel() * 4 == self.slot_bytes
+        owner = (self.rank + step) % self.world
+        dst = self.addr[owner] + (step - 1) * self.slot_bytes
+        with torch.cuda.device(self.device):
+            self.comm.wait_event(after)
+            _lib.check(_lib.load().meclip_copy_async(dst, partial.data_ptr(), self.slot_bytes, self.comm.cuda_stream))
+            ev = torch.cuda.Event()
+            ev.record(self.comm)
+        return ev
+
+    def arrived(self) -> torch.cuda.Event:
+        """The event after which all world-1 buffers of this rank hold this backward's partials."""
+        with torch.cuda.stream(self.comm):
+            dist.all_reduce(self.flag, group=self.group)
+            ev = torch.cuda.Event()
+            ev.record(self.comm)
+        return ev
+
+
 _cache = {}
 
 
@@ -116,4 +169,14 @@ def get(group, rank, world, rows, cols, dtype, device):
     if key not in _cache:
         ex = PeerShards(group, rank, world, rows, cols, dtype, device)
         _cache[key] = ex if ex.ok else None
+    return _cache[key]
+
+
+def get_inbox(group, rank, world, rows, cols, device):
+    """The partial-gradient inbox for this group and shape (collective on first use); None when peer memory
+    cannot be mapped on some rank."""
+    key = ("inbox", id(group) if group is not None else 0, world, rows, cols, device.index)
+    if key not in _cache:
+        box = PeerInbox(group, rank, world, rows, cols, device)
+        _cache[key] = box if box.ok else None
     return _cache[key]

@@ -319,12 +319,28 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, const CUtenso
             if (lane == 0) { atomicAdd(p.sg_acc, sg); atomicAdd(p.sg_acc + 1, sg1); }
         }
     } else {   // EPI_OUT
+        // Wide tiles (two MMAs per K step, see GemmParams::wide): the first MMA's 256 accumulator columns hold the
+        // first 128 B rows of CTA 0 and of CTA 1, the second MMA's columns (from TMEM column 256) the remaining rows
+        // of each, so accumulator chunk ch maps to tile columns through the four pieces below.  For tiles of up
+        // to 256 columns the map is the identity.
+        const int n1 = tile_bn < MAX_BN ? tile_bn : MAX_BN, n2 = tile_bn - n1, h1 = n1 >> 1, half = tile_bn >> 1;
         for (int ch = u_begin; ch < u_end; ++ch) {
+            const int c = ch * 32;
+            int tcol = c, gcol = c;
+            if (p.wide && tile_bn > MAX_BN) {
+                if (c < n1) {
+                    gcol = c < h1 ? c : half + (c - h1);
+                } else {
+                    const int c2 = c - n1;
+                    tcol = MAX_BN + c2;
+                    gcol = c2 < (n2 >> 1) ? h1 + c2 : half + h1 + (c2 - (n2 >> 1));
+                }
+            }
             uint32_t v[32];
-            tmem_ld32(taddr + ch * 32, v);
+            tmem_ld32(taddr + tcol, v);
             tmem_ld_wait();
             if (rvalid) {
-                const int col0 = n0 + ch * 32;
+                const int col0 = n0 + gcol;
                 if (p.acc_in != nullptr) {
                     const float* ap = p.acc_in + (long long)grow * p.ld_acc + col0;
 #pragma unroll

@@ -176,9 +176,9 @@ static constexpr int ROW_KERNEL_THREADS = 256;
 // The output row has dpad = round_up(d, 8) columns, the ones past d are zero, so that the tile kernels
 // always see 16-byte rows.  vec == 0 (d not a multiple of 8, or an unaligned input): element-wise reads.
 template <typename TIn>
-__global__ void __launch_bounds__(ROW_KERNEL_THREADS)
-normalize_fwd_kernel(const TIn* __restrict__ x, long long ldx, long long rows, int d, int dpad, int normalize, int vec,
-                     __nv_bfloat16* __restrict__ out, long long ldh, float* __restrict__ inv_norm) {
+__device__ __forceinline__ void normalize_fwd_row(const TIn* __restrict__ x, long long ldx, long long rows, int d, int dpad,
+                                                  int normalize, int vec, __nv_bfloat16* __restrict__ out, long long ldh,
+                                                  float* __restrict__ inv_norm) {
     const long long row = (long long)blockIdx.x * (ROW_KERNEL_THREADS / 32) + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
     if (row >= rows) return;
@@ -214,13 +214,30 @@ normalize_fwd_kernel(const TIn* __restrict__ x, long long ldx, long long rows, i
     }
 }
 
+template <typename TIn>
+__global__ void __launch_bounds__(ROW_KERNEL_THREADS)
+normalize_fwd_kernel(const TIn* __restrict__ x, long long ldx, long long rows, int d, int dpad, int normalize, int vec,
+                     __nv_bfloat16* __restrict__ out, long long ldh, float* __restrict__ inv_norm) {
+    normalize_fwd_row<TIn>(x, ldx, rows, d, dpad, normalize, vec, out, ldh, inv_norm);
+}
+
+// Both inputs of a step in one launch (blockIdx.y = 0: first matrix, 1: second matrix; same shape and dtype).
+template <typename TIn>
+__global__ void __launch_bounds__(ROW_KERNEL_THREADS)
+normalize_fwd_pair_kernel(const TIn* __restrict__ x0, long long ld0, int vec0, __nv_bfloat16* __restrict__ out0,
+                          float* __restrict__ inv0, const TIn* __restrict__ x1, long long ld1, int vec1,
+                          __nv_bfloat16* __restrict__ out1, float* __restrict__ inv1, long long rows, int d, int dpad,
+                          int normalize, long long ldh) {
+    if (blockIdx.y == 0) normalize_fwd_row<TIn>(x0, ld0, rows, d, dpad, normalize, vec0, out0, ldh, inv0);
+    else                 normalize_fwd_row<TIn>(x1, ld1, rows, d, dpad, normalize, vec1, out1, ldh, inv1);
+}
+
 // dx = (g - x_hat (x_hat . g)) * inv_norm; inv_norm == nullptr: dx = g (dtype conversion of a gradient).
 // g and x_hat are this library's own 16-byte-aligned buffers; vec_out == 0: element-wise stores of dx.
 template <typename TG, typename TOut>
-__global__ void __launch_bounds__(ROW_KERNEL_THREADS)
-normalize_bwd_kernel(const TG* __restrict__ g, long long ldg, const __nv_bfloat16* __restrict__ xh, long long ldh,
-                     const float* __restrict__ inv_norm, long long rows, int d, int vec_out, TOut* __restrict__ dx,
-                     long long lddx) {
+__device__ __forceinline__ void normalize_bwd_row(const TG* __restrict__ g, long long ldg, const __nv_bfloat16* __restrict__ xh,
+                                                  long long ldh, const float* __restrict__ inv_norm, long long rows, int d,
+                                                  int vec_out, TOut* __restrict__ dx, long long lddx) {
     const long long row = (long long)blockIdx.x * (ROW_KERNEL_THREADS / 32) + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
     if (row >= rows) return;
@@ -259,6 +276,25 @@ normalize_bwd_kernel(const TG* __restrict__ g, long long ldg, const __nv_bfloat1
             store1(orow + c, v);
         }
     }
+}
+
+template <typename TG, typename TOut>
+__global__ void __launch_bounds__(ROW_KERNEL_THREADS)
+normalize_bwd_kernel(const TG* __restrict__ g, long long ldg, const __nv_bfloat16* __restrict__ xh, long long ldh,
+                     const float* __restrict__ inv_norm, long long rows, int d, int vec_out, TOut* __restrict__ dx,
+                     long long lddx) {
+    normalize_bwd_row<TG, TOut>(g, ldg, xh, ldh, inv_norm, rows, d, vec_out, dx, lddx);
+}
+
+// Both gradients of a step in one launch (blockIdx.y selects); fp32 contraction outputs in, the inputs' dtype out.
+template <typename TOut>
+__global__ void __launch_bounds__(ROW_KERNEL_THREADS)
+normalize_bwd_pair_kernel(const float* __restrict__ g0, const __nv_bfloat16* __restrict__ xh0, const float* __restrict__ inv0,
+                          int vec0, TOut* __restrict__ dx0, long long lddx0, const float* __restrict__ g1,
+                          const __nv_bfloat16* __restrict__ xh1, const float* __restrict__ inv1, int vec1,
+                          TOut* __restrict__ dx1, long long lddx1, long long ldg, long long ldh, long long rows, int d) {
+    if (blockIdx.y == 0) normalize_bwd_row<float, TOut>(g0, ldg, xh0, ldh, inv0, rows, d, vec0, dx0, lddx0);
+    else                 normalize_bwd_row<float, TOut>(g1, ldg, xh1, ldh, inv1, rows, d, vec1, dx1, lddx1);
 }
 
 // ---- LiT in one tile pass (its coefficients separate: G_ij = g E_ij / r_i - g [i == j]) -----------------
@@ -579,17 +615,47 @@ static int pick_bn(long long n) {
 // dynamic tiles) fill each other's last wave, so there the widest tile wins; a kernel that runs alone
 // pays for a partly filled last wave, so there the width is chosen by waves x tile cost.
 static int pair_mode();
+
+// MECLIP_WIDE=1 runs the contractions on wide CTA-pair tiles (GemmParams::wide).  Off by default: measured at
+// B = 32768, D = 1152 (3 x 384 columns instead of 4 x 256 + 128), same GPU and call: dX / dY alone 960 / 963
+// against 1016 / 1018 TFLOP/s, step 8.85-8.92 against 8.87-8.88 ms.  The 17 % fewer operand bytes per FLOP do
+// not pay for the accumulator that can no longer be double-buffered and the shallower operand ring (5 stages
+// of 40 KiB); the kernels are kept, and unit-tested, as that measured alternative.
+static bool wide_allowed() {
+    static const bool on = []() { const char* v = std::getenv("MECLIP_WIDE"); return v && v[0] == '1'; }();
+    return on;
+}
+
+// Width of a wide CTA-pair tile (a multiple of 64 in (256, 512], see GemmParams::wide) for n > 256 output
+// columns: the width whose tiles cover n with the fewest computed columns (the last tile may be narrower, in
+// steps of 32 up to 256 and of 64 beyond); wider on ties.  1152 -> 3 x 384, 1024 -> 2 x 512, 768 -> 2 x 384.
+static int pick_wide_bn(long long n) {
+    int best = 256;
+    long long best_cost = -1;
+    for (int bn = 512; bn >= 320; bn -= 64) {
+        const long long tiles = (n + bn - 1) / bn;
+        const long long rest = n - (tiles - 1) * bn;
+        const long long last = rest > 256 ? (rest + 63) / 64 * 64 : (rest + 31) / 32 * 32;
+        const long long cost = (tiles - 1) * bn + last;
+        if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = bn; }
+    }
+    return best;
+}
+
 static int pick_contraction_bn(long long m, long long n, bool shares_gpu, bool b_k_major) {
     if (n < 256) return pick_bn(n);
     if (shares_gpu) return 256;
     // CTA pairs: 256-wide tiles even when alone (measured: a 192-wide pair tile loses more per column than the
     // fuller last wave gains: dX 960 vs 1127 TFLOP/s, dY 915 vs 923 at B = 32768, D = 1152)
-    if (b_k_major && pair_mode() != 0) return 256;
-    const int cand[2] = {256, 192};
-    const double cost_per_col[2] = {1.0, 1.07};      // measured: a 192-wide tile costs ~7 % more per column
+    if (b_k_major && pair_mode() != 0) return wide_allowed() ? pick_wide_bn(n) : 256;
+    // measured: a 192-wide tile costs ~7 % more per column than a 256-wide one; the narrower ones (more cost per
+    // column still: less reuse of the A tile) only pay when the wide tiles would leave most SMs without work,
+    // i.e. for the small problems of the whole-step path (4096 x 512 outputs: 64 tiles of 256 columns on 148 SMs)
+    const int cand[4] = {256, 192, 128, 64};
+    const double cost_per_col[4] = {1.0, 1.07, 1.2, 1.5};
     int best = 256;
     double best_t = 0.0;
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < 4; ++i) {
         const long long tiles = ((m + BM - 1) / BM) * ((n + cand[i] - 1) / cand[i]);
         const long long waves = (tiles + sm_count() - 1) / sm_count();
         const double t = (double)waves * cand[i] * cost_per_col[i];
@@ -681,7 +747,9 @@ static int launch_gemm(int epi, const Operand& a, const Operand& b, long long m,
                        long long panel_chunks_alloc = 0) {
     if (m < 1 || n < 1 || k < 1) return fail(MECLIP_EINVAL, "gemm extents must be >= 1 (m=%lld n=%lld k=%lld)", m, n, k);
     if (m > 0x7fffffffLL || n > 0x7fffffffLL || k > 0x7fffffffLL) return fail(MECLIP_EINVAL, "gemm extent exceeds 2^31");
-    if (bn < 32 || bn > MAX_BN || bn % 32 != 0 || ((b.mn_major || epi == EPI_COEF) && bn % 64 != 0))
+    const bool wide = bn > MAX_BN;      // two MMAs per K step, CTA-pair kernel, plain contraction only
+    if (bn < 32 || bn > 2 * MAX_BN || bn % 32 != 0 || ((b.mn_major || epi == EPI_COEF || wide) && bn % 64 != 0) ||
+        (wide && (epi != EPI_OUT || b.mn_major || g_trace_buf != nullptr || pair_mode() == 0)))
         return fail(MECLIP_EINVAL, "tile width %d not supported", bn);
     if (!aligned16(a.ptr) || !aligned16(b.ptr) || (a.blocked_rows_alloc == 0 && a.ld % 8 != 0) || b.ld % 8 != 0)
         return fail(MECLIP_EINVAL, "operands must be 16-byte aligned with pitches that are multiples of 8 elements");
@@ -698,7 +766,7 @@ static int launch_gemm(int epi, const Operand& a, const Operand& b, long long m,
     // CTA pairs (256 x bn tiles) whenever B is K-major; the single-CTA kernel keeps MN-major B
     const int pmode = pair_mode();
     const bool pair = !b.mn_major && bn % 64 == 0 && g_trace_buf == nullptr &&      // the in-kernel trace is a single-CTA hook
-                      (pmode == 1 || ((pmode == 2 || pmode < 0) && epi == EPI_OUT && bn == 256) ||
+                      (wide || pmode == 1 || ((pmode == 2 || pmode < 0) && epi == EPI_OUT && bn == 256) ||
                        (pmode < 0 && epi != EPI_OUT && bn == 256 && k >= PAIR_MIN_K));
     if (b.mn_major) rc = make_tmap(&tb, b.ptr, n, k, b.ld, 64, BK);
     else            rc = make_tmap(&tb, b.ptr, k, n, b.ld, BK, pair ? bn / 2 : bn);
@@ -737,7 +805,7 @@ static int launch_gemm(int epi, const Operand& a, const Operand& b, long long m,
     if (epi == EPI_OUT) {      // narrower last column tile: only as many 32-column chunks as hold valid columns
         const long long rest = n - (long long)(p.num_n_tiles - 1) * bn;
         int last = (int)((rest + 31) / 32 * 32);
-        if (b.mn_major) last = (int)((rest + 63) / 64 * 64);
+        if (b.mn_major || rest > MAX_BN) last = (int)((rest + 63) / 64 * 64);
         if (last < bn) {
             p.bn_last = last;
             p.idesc_last = umma_idesc_bf16(BM, last, a.mn_major ? 1 : 0, b.mn_major ? 1 : 0);
@@ -766,8 +834,12 @@ static int launch_gemm(int epi, const Operand& a, const Operand& b, long long m,
         if (env_narrow == 2 || (env_narrow == 1 && tiles_all < 4 * slots)) p.narrow_last = 1;
     }
     if (pair) {
-        p.idesc = umma_idesc_bf16(PAIR_BM, bn, a.mn_major ? 1 : 0, 0);
-        p.idesc_last = p.bn_last < bn ? umma_idesc_bf16(PAIR_BM, p.bn_last, a.mn_major ? 1 : 0, 0) : p.idesc;
+        const int amn = a.mn_major ? 1 : 0;
+        p.wide = wide ? 1 : 0;
+        p.idesc = umma_idesc_bf16(PAIR_BM, bn < MAX_BN ? bn : MAX_BN, amn, 0);
+        p.idesc2 = wide ? umma_idesc_bf16(PAIR_BM, bn - MAX_BN, amn, 0) : 0u;
+        p.idesc_last = umma_idesc_bf16(PAIR_BM, p.bn_last < MAX_BN ? p.bn_last : MAX_BN, amn, 0);
+        p.idesc2_last = p.bn_last > MAX_BN ? umma_idesc_bf16(PAIR_BM, p.bn_last - MAX_BN, amn, 0) : 0u;
         p.stage_bytes = A_STAGE_BYTES + (bn / 2) * BK * 2;
         stages = (SMEM_LIMIT - 1024 - tail_bytes(epi)) / p.stage_bytes;
         if (stages > MAX_STAGES) stages = MAX_STAGES;
@@ -1535,6 +1607,153 @@ int meclip_loss_backward(int kind, const void* x_bf16, const void* y_bf16, int64
                          int dy_mode, int64_t lddy, void* workspace, size_t workspace_bytes, int* status, void* stream) {
     return meclip_grad(kind, x_bf16, y_bf16, batch, batch, d, ldx, ldy, temperature, 0, 0, row_sum, col_sum, grad_out,
                        grad_scale, dx, dx_mode, lddx, dy, dy_mode, lddy, workspace, workspace_bytes, status, stream);
+}
+
+// ------------------------------------------------------------------------------------
+// whole-step entry points for small batches (the step is host-bound there)
+// ------------------------------------------------------------------------------------
+}  // extern "C"
+
+namespace meclip {
+struct StepLayout {
+    long long dp;
+    size_t x_hat, y_hat, inv_x, inv_y, row_sum, col_sum, diag, counter, stats_bytes, total;
+};
+static StepLayout step_layout(int64_t b, int64_t d) {
+    StepLayout l;
+    l.dp = (long long)round_up((size_t)d, 8);
+    const size_t op = round_up((size_t)b * l.dp * 2, 256), vec = round_up((size_t)b * 4, 256);
+    l.x_hat = 0;
+    l.y_hat = op;
+    l.inv_x = 2 * op;
+    l.inv_y = l.inv_x + vec;
+    l.row_sum = l.inv_y + vec;            // row_sum | col_sum | diag | counter are cleared by ONE memset
+    l.col_sum = l.row_sum + vec;
+    l.diag = l.col_sum + vec;
+    l.counter = l.diag + vec;
+    l.stats_bytes = 3 * vec + 256;
+    l.total = l.counter + 256;
+    return l;
+}
+}  // namespace meclip
+
+extern "C" {
+
+size_t meclip_step_saved_bytes(int64_t batch, int64_t d) {
+    if (batch < 1 || d < 1) return 0;
+    return step_layout(batch, d).total;
+}
+
+size_t meclip_step_workspace_bytes(int64_t batch, int64_t d) {
+    if (batch < 1 || d < 1) return 0;
+    const StepLayout l = step_layout(batch, d);
+    return 2 * round_up((size_t)batch * l.dp * 4, 256) + plan_grad(batch, batch, l.dp, false).total() + 256;
+}
+
+int meclip_step_forward(int kind, const void* x, const void* y, int in_dtype, int64_t batch, int64_t d, int64_t ldx,
+                        int64_t ldy, int normalize, float temperature, void* saved, size_t saved_bytes, float* loss_out,
+                        int* status, void* stream) {
+    const DeviceScalars ds = take_scalars();
+    NvtxRange range("meclip_step_forward");
+    if (kind != MECLIP_CLIP && kind != MECLIP_LIT) return fail(MECLIP_EINVAL, "step_forward: bad kind %d", kind);
+    if (x == nullptr || y == nullptr || saved == nullptr || loss_out == nullptr) return fail(MECLIP_EINVAL, "step_forward: null pointer");
+    if (batch < 1 || d < 1 || ldx < d || ldy < d) return fail(MECLIP_EINVAL, "step_forward: need batch, d >= 1 and ld >= d");
+    if ((reinterpret_cast<uintptr_t>(saved) & 255u) != 0) return fail(MECLIP_EINVAL, "step_forward: saved must be 256-byte aligned");
+    const StepLayout l = step_layout(batch, d);
+    if (saved_bytes < l.total) return fail(MECLIP_ENOSPC, "step_forward: saved buffer %zu < %zu bytes", saved_bytes, l.total);
+    const int elt = in_dtype == MECLIP_F32 ? 4 : 2;
+    if (in_dtype != MECLIP_F32 && in_dtype != MECLIP_BF16 && in_dtype != MECLIP_F16) return fail(MECLIP_EINVAL, "step_forward: bad dtype %d", in_dtype);
+    uint8_t* sv = reinterpret_cast<uint8_t*>(saved);
+    __nv_bfloat16* xh = reinterpret_cast<__nv_bfloat16*>(sv + l.x_hat);
+    __nv_bfloat16* yh = reinterpret_cast<__nv_bfloat16*>(sv + l.y_hat);
+    float* inv_x = reinterpret_cast<float*>(sv + l.inv_x);
+    float* inv_y = reinterpret_cast<float*>(sv + l.inv_y);
+    cudaStream_t s = (cudaStream_t)stream;
+    {   // (1) both inputs: normalise (or convert) to bf16 operands, one launch
+        const int vec0 = (d % 8 == 0) && aligned16(x) && ((ldx * elt) % 16 == 0);
+        const int vec1 = (d % 8 == 0) && aligned16(y) && ((ldy * elt) % 16 == 0);
+        const int wpb = ROW_KERNEL_THREADS / 32;
+        dim3 grid((unsigned)((batch + wpb - 1) / wpb), 2);
+        ScopedTiming timing(s, TAG_NORM_FWD, 2.0 * (double)batch * ((double)d * elt + (double)l.dp * 2 + (normalize ? 4 : 0)));
+        if (in_dtype == MECLIP_F32)
+            normalize_fwd_pair_kernel<float><<<grid, ROW_KERNEL_THREADS, 0, s>>>((const float*)x, ldx, vec0, xh, inv_x, (const float*)y, ldy, vec1, yh, inv_y, batch, (int)d, (int)l.dp, normalize, l.dp);
+        else if (in_dtype == MECLIP_BF16)
+            normalize_fwd_pair_kernel<__nv_bfloat16><<<grid, ROW_KERNEL_THREADS, 0, s>>>((const __nv_bfloat16*)x, ldx, vec0, xh, inv_x, (const __nv_bfloat16*)y, ldy, vec1, yh, inv_y, batch, (int)d, (int)l.dp, normalize, l.dp);
+        else
+            normalize_fwd_pair_kernel<__half><<<grid, ROW_KERNEL_THREADS, 0, s>>>((const __half*)x, ldx, vec0, xh, inv_x, (const __half*)y, ldy, vec1, yh, inv_y, batch, (int)d, (int)l.dp, normalize, l.dp);
+        MECLIP_CUDA(cudaGetLastError());
+    }
+    // (2) sums, diagonal and the tile counter in one clear
+    MECLIP_CUDA(cudaMemsetAsync(sv + l.row_sum, 0, l.stats_bytes, s));
+    // (3) tile pass, (4) loss
+    float* row_sum = reinterpret_cast<float*>(sv + l.row_sum);
+    float* col_sum = kind == MECLIP_CLIP ? reinterpret_cast<float*>(sv + l.col_sum) : nullptr;
+    float* diag = reinterpret_cast<float*>(sv + l.diag);
+    int rc = sum_exp_impl(kind, xh, yh, batch, batch, l.dp, l.dp, l.dp, temperature, 0, 0, row_sum, col_sum, diag,
+                          reinterpret_cast<unsigned int*>(sv + l.counter), status, stream, ds);
+    if (rc) return rc;
+    return loss_finalize_impl(kind, row_sum, col_sum, diag, batch, temperature, 1.0f / (float)batch, 0, loss_out, stream, ds);
+}
+
+int meclip_step_backward(int kind, const void* saved, size_t saved_bytes, int64_t batch, int64_t d, int normalize,
+                         float temperature, const float* grad_out, float grad_scale, void* dx, void* dy, int out_dtype,
+                         int64_t lddx, int64_t lddy, void* workspace, size_t workspace_bytes, int* status, void* stream) {
+    const DeviceScalars ds = take_scalars();
+    NvtxRange range("meclip_step_backward");
+    if (saved == nullptr || workspace == nullptr || (dx == nullptr && dy == nullptr)) return fail(MECLIP_EINVAL, "step_backward: null pointer");
+    if (batch < 1 || d < 1 || (dx != nullptr && lddx < d) || (dy != nullptr && lddy < d)) return fail(MECLIP_EINVAL, "step_backward: bad shape");
+    if (out_dtype != MECLIP_F32 && out_dtype != MECLIP_BF16 && out_dtype != MECLIP_F16) return fail(MECLIP_EINVAL, "step_backward: bad dtype %d", out_dtype);
+    if ((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0) return fail(MECLIP_EINVAL, "step_backward: workspace must be 256-byte aligned");
+    const StepLayout l = step_layout(batch, d);
+    if (saved_bytes < l.total) return fail(MECLIP_ENOSPC, "step_backward: saved buffer %zu < %zu bytes", saved_bytes, l.total);
+    if (workspace_bytes < meclip_step_workspace_bytes(batch, d)) return fail(MECLIP_ENOSPC, "step_backward: workspace too small");
+    const uint8_t* sv = reinterpret_cast<const uint8_t*>(saved);
+    const __nv_bfloat16* xh = reinterpret_cast<const __nv_bfloat16*>(sv + l.x_hat);
+    const __nv_bfloat16* yh = reinterpret_cast<const __nv_bfloat16*>(sv + l.y_hat);
+    const float* row_sum = reinterpret_cast<const float*>(sv + l.row_sum);
+    const float* col_sum = kind == MECLIP_CLIP ? reinterpret_cast<const float*>(sv + l.col_sum) : nullptr;
+    if (kind == MECLIP_LIT) dy = nullptr;
+    uint8_t* ws = reinterpret_cast<uint8_t*>(workspace);
+    const size_t g32 = round_up((size_t)batch * l.dp * 4, 256);
+    float* dx32 = reinterpret_cast<float*>(ws);
+    float* dy32 = reinterpret_cast<float*>(ws + g32);
+    uint8_t* gws = ws + 2 * g32;
+    const size_t gws_bytes = workspace_bytes - 2 * g32;
+    const int oelt = out_dtype == MECLIP_F32 ? 4 : 2;
+    // the contractions write the outputs themselves when no Jacobian follows and they can (dtype, 16-byte rows)
+    const bool direct = !normalize && out_dtype != MECLIP_F16 && d % 8 == 0 &&
+                        (dx == nullptr || (aligned16(dx) && lddx % 8 == 0)) && (dy == nullptr || (aligned16(dy) && lddy % 8 == 0));
+    const int mode = direct ? (out_dtype == MECLIP_BF16 ? MECLIP_STORE_BF16 : MECLIP_STORE_F32) : MECLIP_STORE_F32;
+    // one stream, no transposed operand copies: at these sizes every extra launch costs more than it saves
+    int rc = grad_impl(kind, xh, yh, batch, batch, l.dp, l.dp, l.dp, temperature, 0, 0, row_sum, col_sum, grad_out, grad_scale,
+                       dx == nullptr ? nullptr : (direct ? dx : (void*)dx32), mode, direct ? lddx : l.dp,
+                       dy == nullptr ? nullptr : (direct ? dy : (void*)dy32), mode, direct ? lddy : l.dp, gws, gws_bytes, status,
+                       (cudaStream_t)stream, false, false, nullptr, 0.f, 0.f, 0, false, ds);
+    if (rc || direct) return rc;
+    // Jacobian of the normalisation (or the plain conversion) for both gradients in one launch
+    cudaStream_t s = (cudaStream_t)stream;
+    const float* inv_x = normalize ? reinterpret_cast<const float*>(sv + l.inv_x) : nullptr;
+    const float* inv_y = normalize ? reinterpret_cast<const float*>(sv + l.inv_y) : nullptr;
+    const int wpb = ROW_KERNEL_THREADS / 32;
+    const bool both = dx != nullptr && dy != nullptr;
+    dim3 grid((unsigned)((batch + wpb - 1) / wpb), both ? 2 : 1);
+    // with one output only, it takes slot 0 of the pair kernel
+    const float* g0 = dx != nullptr ? dx32 : dy32;
+    const __nv_bfloat16* h0 = dx != nullptr ? xh : yh;
+    const float* i0 = dx != nullptr ? inv_x : inv_y;
+    void* o0 = dx != nullptr ? dx : dy;
+    const int64_t ld0 = dx != nullptr ? lddx : lddy;
+    const int v0 = (d % 8 == 0) && aligned16(o0) && ((ld0 * oelt) % 16 == 0);
+    const int v1 = both && (d % 8 == 0) && aligned16(dy) && ((lddy * oelt) % 16 == 0);
+    ScopedTiming timing(s, TAG_NORM_BWD, (both ? 2.0 : 1.0) * (double)batch * ((double)l.dp * 6 + (double)d * oelt + 4));
+    if (out_dtype == MECLIP_F32)
+        normalize_bwd_pair_kernel<float><<<grid, ROW_KERNEL_THREADS, 0, s>>>(g0, h0, i0, v0, (float*)o0, ld0, dy32, yh, inv_y, v1, (float*)dy, lddy, l.dp, l.dp, batch, (int)d);
+    else if (out_dtype == MECLIP_BF16)
+        normalize_bwd_pair_kernel<__nv_bfloat16><<<grid, ROW_KERNEL_THREADS, 0, s>>>(g0, h0, i0, v0, (__nv_bfloat16*)o0, ld0, dy32, yh, inv_y, v1, (__nv_bfloat16*)dy, lddy, l.dp, l.dp, batch, (int)d);
+    else
+        normalize_bwd_pair_kernel<__half><<<grid, ROW_KERNEL_THREADS, 0, s>>>(g0, h0, i0, v0, (__half*)o0, ld0, dy32, yh, inv_y, v1, (__half*)dy, lddy, l.dp, l.dp, batch, (int)d);
+    MECLIP_CUDA(cudaGetLastError());
+    return MECLIP_OK;
 }
 
 // ------------------------------------------------------------------------------------

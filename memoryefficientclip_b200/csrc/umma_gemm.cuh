@@ -63,6 +63,12 @@ struct GemmParams {
     // feeds the tensor cores better than six tiles of 192.  bn_last == bn when there is no such tile.
     int bn_last;
     uint32_t idesc_last;
+    // Wide tiles (CTA-pair kernel, EPI_OUT only): bn in (256, 512].  A tile is then computed by TWO MMAs per K
+    // step that share the A operand in shared memory (N = 256 into TMEM columns 0.., N = bn - 256 into columns
+    // 256..), and the one 512-column accumulator is not double-buffered: with K in the thousands the epilogue
+    // is ~1 % of a tile.  Operand bytes per FLOP drop by 17 % (bn = 384) / 25 % (bn = 512) against 256 x 256.
+    int wide;
+    uint32_t idesc2, idesc2_last;   // second MMA of a wide tile (0: none)
     unsigned int* tile_counter;   // zeroed by the caller; null = static round-robin
     int strip_len;            // tiles handed out together (consecutive ids share their columns), >= 1
     int a_blocked;            // A is the coefficient panel in its column-blocked layout (3-D tensor map)

@@ -170,7 +170,12 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
                 tc_fence_after();
                 int mt_, nt_;
                 tile_coords(p, tile, mt_, nt_);
-                const uint32_t idesc = (nt_ == p.num_n_tiles - 1) ? p.idesc_last : p.idesc;
+                const bool last_nt = nt_ == p.num_n_tiles - 1;
+                const uint32_t idesc = last_nt ? p.idesc_last : p.idesc;
+                const uint32_t idesc2 = last_nt ? p.idesc2_last : p.idesc2;       // second MMA of a wide tile
+                const int tile_bn_ = last_nt ? p.bn_last : p.bn;
+                // rows of this CTA's B half that the first MMA consumes; the second one starts behind them
+                const uint32_t b2_off = (uint32_t)(min(tile_bn_, MAX_BN) >> 1) * 128u;
                 const uint32_t tmem_d = tmem_base + (uint32_t)acc * MAX_BN;
                 for (int ks = 0; ks < p.k_steps; ++ks) {
                     if (!mbar_wait(smem_u32(&tail->full_bar[stage]), phase, abort_flag, true, wl)) { ok = false; break; }
@@ -182,14 +187,22 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
                         const uint64_t ad = umma_smem_desc(sa + kk * A_KSTEP, A_LBO, 1024);
                         const uint64_t bd = umma_smem_desc(sb + kk * 32, 16, 1024);
                         umma_bf16_pair(tmem_d, ad, bd, idesc, (ks | kk) != 0 ? 1u : 0u);
+                        if (idesc2 != 0u) {
+                            const uint64_t bd2 = umma_smem_desc(sb + b2_off + kk * 32, 16, 1024);
+                            umma_bf16_pair(tmem_d + MAX_BN, ad, bd2, idesc2, (ks | kk) != 0 ? 1u : 0u);
+                        }
                     }
                     umma_commit_pair(smem_u32(&tail->empty_bar[stage]), 3);     // frees the stage in both CTAs
                     if (++stage == num_stages) { stage = 0; phase ^= 1u; }
                 }
                 if (!ok) break;
                 umma_commit_pair(smem_u32(&tail->tmem_full_bar[acc]), 3);       // accumulator halves complete
-                acc ^= 1;
-                if (acc == 0) acc_phase ^= 1u;
+                if (p.wide) {
+                    acc_phase ^= 1u;             // one accumulator of up to 512 columns: every tile flips its phase
+                } else {
+                    acc ^= 1;
+                    if (acc == 0) acc_phase ^= 1u;
+                }
             }
         }
         __syncwarp();
@@ -224,8 +237,12 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
                                    __syncwarp();
                                    if (lane == 0) mbar_arrive_cluster(free_bar);
                                });
-            acc ^= 1;
-            if (acc == 0) acc_phase ^= 1u;
+            if (p.wide) {
+                acc_phase ^= 1u;
+            } else {
+                acc ^= 1;
+                if (acc == 0) acc_phase ^= 1u;
+            }
         }
         if (EPI == EPI_SUMS && !tail->abort_flag) flush_column_sums(p, tail, st, warp, lane);
         epilogue_drain<EPI>(st, lane);

@@ -457,6 +457,51 @@ def lit_fused_backward(u, y_ext, row_sum, grad_out, grad_scale_, d_out, out_dtyp
     return dx
 
 
+# ---- whole-step entry points (small batches) --------------------------------------------------------------
+_step_ws = {}
+
+
+def step_workspace(batch: int, d: int, device) -> torch.Tensor:
+    """Backward workspace of the small-batch step path, cached per (device, stream, shape): it is scratch that
+    lives only inside one library call, and calls on one stream are ordered."""
+    key = (device.index, torch.cuda.current_stream(device).cuda_stream, batch, d)
+    need = _lib.load().meclip_step_workspace_bytes(batch, d)      # depends on the blocking (a test hook can change it)
+    ws = _step_ws.get(key)
+    if ws is None or ws.numel() < need:
+        ws = _step_ws[key] = torch.empty(need, dtype=torch.uint8, device=device)
+    return ws
+
+
+def step_forward(kind, x, y, normalize, temperature, status=None):
+    """(loss, saved): the module's forward in one library call (meclip_step_forward)."""
+    b, d = x.shape
+    lib = _lib.load()
+    saved = torch.empty(lib.meclip_step_saved_bytes(b, d), dtype=torch.uint8, device=x.device)
+    loss = torch.empty((), dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        t, _b, _keep = _bind(temperature, x.device)
+        _lib.check(lib.meclip_step_forward(kind, x.data_ptr(), y.data_ptr(), _DT[x.dtype], b, d, x.stride(0), y.stride(0),
+                                           int(normalize), t, saved.data_ptr(), saved.numel(), loss.data_ptr(),
+                                           _ptr(status), _stream(x)))
+    return loss, saved
+
+
+def step_backward(kind, saved, batch, d, normalize, temperature, grad_out, grad_scale_, scale_rule, out_dtype,
+                  need_dx=True, need_dy=True, status=None):
+    """(dx, dy) in out_dtype from the buffer step_forward saved (meclip_step_backward)."""
+    dev = saved.device
+    dx = torch.empty(batch, d, dtype=out_dtype, device=dev) if need_dx else None
+    dy = torch.empty(batch, d, dtype=out_dtype, device=dev) if need_dy else None
+    ws = step_workspace(batch, d, dev)
+    with torch.cuda.device(dev):
+        t, _b, _keep = _bind(temperature, dev, scale_rule)
+        _lib.check(_lib.load().meclip_step_backward(kind, saved.data_ptr(), saved.numel(), batch, d, int(normalize), t,
+                                                    _ptr(grad_out), float(grad_scale_), _ptr(dx), _ptr(dy),
+                                                    _DT[out_dtype], d, d, ws.data_ptr(), ws.numel(), _ptr(status),
+                                                    torch.cuda.current_stream(dev).cuda_stream))
+    return dx, dy
+
+
 def grad_scale(batch: int, temperature: float, stable: bool) -> float:
     """1/(B T) (reference clip_loss.py:182, 235) or, for the Stable variants,
     sqrt(B/T)/B = 1/sqrt(B T) (clip_loss.py:299, 352)."""

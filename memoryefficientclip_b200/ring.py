@@ -99,6 +99,13 @@ class CudaBlockOps:
             ex.check_live(token[1])               # backward: the shards of its own forward
         return _PeerRotation(ex, token[1], y_own, rank, world), token
 
+    def partial_inbox(self, rows, cols, device, group, rank, world):
+        """Copy-engine transport of the partial text gradients (None: send/recv)."""
+        if _TRANSPORT != "peer" or device.type != "cuda":
+            return None
+        from . import _peer
+        return _peer.get_inbox(group, rank, world, rows, cols, device)
+
     def prepare(self, x, normalize):
         if normalize:
             return ops.normalize_fwd(x, True)
@@ -296,16 +303,22 @@ def _exchange_partial(send_buf, recv_buf, group, rank, world, step):
 
 def _ring_backward_loop(block, x_hat, y_hat, group, rank, world, want_dy, grad_call, token=None):
     """The backward choreography shared by the softmax and the sigmoid losses.  grad_call(y_shard, shard,
-    dx_acc, dy_out, workspace) runs the block kernels: dx_acc accumulates in fp32, dy_out is stored."""
+    dx_acc, dy_out, workspace) runs the block kernels: dx_acc accumulates in fp32, dy_out is stored.
+    The partial gradient a rank computes for a visiting shard goes straight to the shard's owner while the next
+    step computes: with copy-engine writes into the owner's inbox (block.partial_inbox, see _peer.PeerInbox)
+    or, without peer memory, with send/recv; the owner adds the partials in the order of the ring steps."""
     b, d = x_hat.shape
     dev = x_hat.device
     dx = torch.zeros(b, d, dtype=torch.float32, device=dev)
     dy = torch.empty(b, d, dtype=torch.float32, device=dev) if want_dy else None       # own shard: step 0 stores it
-    part = [torch.empty(b, d, dtype=torch.float32, device=dev) for _ in range(2)] if want_dy and world > 1 else []
-    inbox = [torch.empty(b, d, dtype=torch.float32, device=dev) for _ in range(2)] if want_dy and world > 1 else []
+    exchange = want_dy and world > 1
+    inbox_peer = block.partial_inbox(b, d, dev, group, rank, world) if exchange and hasattr(block, "partial_inbox") else None
+    part = [torch.empty(b, d, dtype=torch.float32, device=dev) for _ in range(2)] if exchange else []
+    inbox = [torch.empty(b, d, dtype=torch.float32, device=dev) for _ in range(2)] if exchange and inbox_peer is None else []
     workspace = block.workspace(b, b, d, dev)
     rot, _ = _rotation(block, y_hat, group, rank, world, token)
-    pending = None          # (requests, inbox buffer) of the previous step's partial exchange
+    pending = None          # send/recv: (requests, inbox buffer) of the previous step's partial exchange
+    pushed = {}             # peer inbox: step -> event after which part[step % 2] may be written again
     _mark("bwd_setup")
     for step in range(world):
         shard = shard_at(rank, step, world)
@@ -314,6 +327,8 @@ def _ring_backward_loop(block, x_hat, y_hat, group, rank, world, want_dy, grad_c
         out = None
         if want_dy:
             out = dy if step == 0 else part[step % 2]
+            if step - 2 in pushed:      # the copy out of this buffer had a whole ring step to finish
+                torch.cuda.current_stream().wait_event(pushed.pop(step - 2))
         grad_call(y_cur, shard, dx, out, workspace)
         _mark("bwd_kernels")
         if pending is not None:          # the exchange started one step ago ran under this step's kernels
@@ -323,8 +338,13 @@ def _ring_backward_loop(block, x_hat, y_hat, group, rank, world, want_dy, grad_c
             block.accumulate(dy, pending[1])
             _mark("bwd_accumulate_f32")
             pending = None
-        if want_dy and step > 0:
-            pending = (_exchange_partial(part[step % 2], inbox[step % 2], group, rank, world, step), inbox[step % 2])
+        if exchange and step > 0:
+            if inbox_peer is not None:
+                done = torch.cuda.Event()
+                done.record()
+                pushed[step] = inbox_peer.push(step, part[step % 2], done)
+            else:
+                pending = (_exchange_partial(part[step % 2], inbox[step % 2], group, rank, world, step), inbox[step % 2])
         rot.end(step)
         _mark("bwd_exposed_shard_wait")
     if pending is not None:
@@ -332,6 +352,12 @@ def _ring_backward_loop(block, x_hat, y_hat, group, rank, world, want_dy, grad_c
             r.wait()
         _mark("bwd_exposed_last_partial_wait")
         block.accumulate(dy, pending[1])
+        _mark("bwd_accumulate_f32")
+    if inbox_peer is not None:
+        torch.cuda.current_stream().wait_event(inbox_peer.arrived())     # every rank's pushes have landed
+        _mark("bwd_exposed_last_partial_wait")
+        for step in range(1, world):     # fixed order: the partial of ring step 1 first
+            block.accumulate(dy, inbox_peer.local[step - 1])
         _mark("bwd_accumulate_f32")
     return dx, dy
 
@@ -404,6 +430,13 @@ def ring_siglip_backward(block, x_hat, y_hat, logit_scale, logit_bias, grad_out,
                          sums=None, token=None):
     """Returns (dx, dy_own) fp32; sums (optional zeroed pair) receives {sum G S, sum G} over this rank's rows."""
     b = x_hat.shape[0]
+    if world > 1 and hasattr(block, "partial_inbox"):
+        # The peer inbox is reused by every backward; this loss has no collective at the start of its backward,
+        # so a one-word all-reduce takes that place: a rank joins it only after it has consumed the partials of
+        # its previous backward, and this backward's pushes are queued behind kernels that wait for it.
+        gate = torch.zeros(1, dtype=torch.float32, device=x_hat.device)
+        dist.all_reduce(gate, group=group)
+        grad_out = grad_out + 0.0 * gate
 
     def grad_call(y_shard, shard, dx_acc, dy_out, workspace):
         block.siglip_grad(x_hat, y_shard, logit_scale, logit_bias, grad_out, grad_scale, dx_acc, dy_out, rank * b,

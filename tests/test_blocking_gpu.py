@@ -9,6 +9,16 @@ from oracle import dense
 
 pytestmark = pytest.mark.gpu
 
+@pytest.fixture(autouse=True, params=["step_path", "general_path"])
+def both_module_routes(request, monkeypatch):
+    """Small CLIP batches take the whole-step entry points (two library calls per step); every case of this
+    file also runs with that route switched off, through the block-level entry points."""
+    from memoryefficientclip_b200 import _function
+    if request.param == "general_path":
+        monkeypatch.setattr(_function, "_STEP_PATH_ROWS", 0)
+    yield
+
+
 
 @pytest.fixture
 def small_blocks():

@@ -79,3 +79,20 @@ def test_in_kernel_trace_hook():
         by_tile.setdefault(tile, {})[tag] = t
     for tile, ev in by_tile.items():
         assert ev[1] <= ev[11] <= ev[12] <= ev[21] <= ev[22], (tile, ev)     # loads, data, last MMA, release, end
+
+
+@pytest.mark.parametrize("a_mn", [False, True])
+@pytest.mark.parametrize("m,n,k,tile_n", [
+    (256, 384, 128, 384),       # one wide tile: two MMAs per K step (256 + 128 columns)
+    (256, 512, 192, 512),       # 256 + 256 columns
+    (512, 1152, 640, 384),      # 3 x 384, several row tiles, wrap-around of the operand ring
+    (768, 1160, 512, 512),      # 512, 512 and a narrow last tile (136 -> 160 columns, one MMA)
+    (304, 1000, 200, 384),      # ragged rows and a last tile of 232 -> 256 columns
+    (1280, 840, 1024, 448),     # 840 = 448 + 392: the last tile is wide too (392 -> 448 columns)
+    (2048, 704, 2304, 384),     # last tile 320 wide (two MMAs: 256 + 64)
+])
+def test_wide_pair_tiles(m, n, k, tile_n, a_mn):
+    """Tiles wider than 256 columns on the CTA-pair kernel: the accumulator columns of the two MMAs are
+    interleaved halves of the tile (see the epilogue's column map), single-buffered accumulator."""
+    _run(m, n, k, a_mn, False, tile_n)
+    _run(m, n, k, a_mn, False, tile_n, accumulate=True, seed=3)

@@ -6,6 +6,8 @@ call reuses the same built-in scratch array and finds the previous call's data i
 Collected last on purpose (file name), so a run that stops at the first failure has already
 run everything else; it also passes when run alone in a fresh process.
 """
+import gc
+
 import pytest
 import torch
 import torch.nn.functional as F
@@ -36,6 +38,7 @@ def _case(b, d, kind, seed, strict_free=False, bit_identical=True):
     dx_st, dy_st = outputs()
     # the call itself must not take device memory from anyone: neither from the driver (free bytes of the
     # device unchanged) nor from torch's allocator (bytes handed out unchanged)
+    gc.collect()            # garbage of earlier tests must not be freed (or its blocks reused) in between
     torch.cuda.synchronize()
     free0, _total = torch.cuda.mem_get_info()
     alloc0, reserved0 = torch.cuda.memory_allocated(), torch.cuda.memory_reserved()
