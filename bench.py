@@ -619,8 +619,10 @@ def run_ours(args):
 
 
 # DRAM bytes (read + written) per FLOP of one contraction launch, from the ncu capture under profiles/
-TRAFFIC_BYTES_PER_FLOP = {"dx_contraction": 0.827e9 / 6.18e11, "dy_contraction": 0.827e9 / 6.18e11}
-TRAFFIC_SOURCE = "ncu capture of the contraction kernel at B=16384, D=1152 (0.83 GB per 537 MB panel), scaled by FLOPs"
+TRAFFIC_BYTES_PER_FLOP = {"dx_contraction": 817.4e6 / 6.18475e11, "dy_contraction": 817.9e6 / 6.18475e11}
+TRAFFIC_SOURCE = ("ncu capture of one dY and one dX launch at the step's own block shape (M=16384, N=1152, K=16384: "
+                  "818 MB per launch, profiles/umma_gemm_pair_kernel_contractions_block16384_d1152_ncu_full.md); "
+                  "other shapes: scaled by FLOPs")
 
 
 def main():

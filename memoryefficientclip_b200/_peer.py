@@ -84,18 +84,22 @@ class PeerShards:
         self.peer_slot0, self.ok = _map_everywhere(self.local, group, rank, world, device)
 
     def publish(self, shard: torch.Tensor) -> int:
-        """Copy this rank's shard into the next slot (current stream) and start the all-reduce that tells
-        every rank that all shards are in place.  Returns the generation to fetch from."""
+        """Copy this rank's shard into the next slot (current stream).  Returns the generation to fetch from;
+        call announce() before the first fetch of that generation."""
         gen = self.gen
         self.gen += 1
-        slot = self.local[gen % 2]
-        slot.copy_(shard)
-        done = torch.cuda.Event()
-        done.record()
-        with torch.cuda.stream(self.comm):
-            self.comm.wait_event(done)
-            dist.all_reduce(self.flag, group=self.group)      # fetches queued on self.comm start behind it
+        self.local[gen % 2].copy_(shard)
+        self._published = torch.cuda.Event()
+        self._published.record()
         return gen
+
+    def announce(self) -> None:
+        """The all-reduce that tells every rank that all shards are in place, on the copy stream: fetches queued
+        after this call start behind it.  Issuing a collective costs the host ~0.1 ms, so the ring calls this
+        after it has queued the kernels of its first step (which work on the rank's own shard)."""
+        with torch.cuda.stream(self.comm):
+            self.comm.wait_event(self._published)
+            dist.all_reduce(self.flag, group=self.group)
 
     def check_live(self, gen: int) -> None:
         if self.gen > gen + 2:

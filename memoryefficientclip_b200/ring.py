@@ -95,8 +95,8 @@ class CudaBlockOps:
             return None
         if token is None:
             token = (ex, ex.publish(y_own))       # forward: publish this rank's shard for everyone
-        else:
-            ex.check_live(token[1])               # backward: the shards of its own forward
+            return _PeerRotation(ex, token[1], y_own, rank, world, announce=True), token
+        ex.check_live(token[1])                   # backward: the shards of its own forward
         return _PeerRotation(ex, token[1], y_own, rank, world), token
 
     def partial_inbox(self, rows, cols, device, group, rank, world):
@@ -223,18 +223,24 @@ class _PeerRotation:
     """Every rank fetches the shard of step s+1 from its owner's published buffer with the copy engines
     while the kernels of step s run (_peer.PeerShards)."""
 
-    def __init__(self, exchange, gen, y_own, rank, world):
+    def __init__(self, exchange, gen, y_own, rank, world, announce=False):
         self.ex, self.gen, self.rank, self.world = exchange, gen, rank, world
         self.y_own = y_own
+        self.announce = announce          # forward: the shards were just published, the ranks have to be told
         self.recv = [torch.empty_like(y_own) for _ in range(min(2, world - 1))]
         self.kernels_done = {}
         self.fetched = {}
 
+    def _prefetch(self, step):
+        """Queue the fetch of the shard of `step`; the buffer it lands in was last read by the kernels of step - 2."""
+        if step < self.world:
+            owner = shard_at(self.rank, step, self.world)
+            self.fetched[step] = self.ex.fetch(self.gen, owner, self.recv[step % len(self.recv)],
+                                               after=self.kernels_done.get(step - 2))
+
     def begin(self, step):
-        if step + 1 < self.world:      # the buffer it lands in was last read by the kernels of step - 1
-            owner = shard_at(self.rank, step + 1, self.world)
-            self.fetched[step + 1] = self.ex.fetch(self.gen, owner, self.recv[(step + 1) % len(self.recv)],
-                                                   after=self.kernels_done.get(step - 1))
+        if not (step == 0 and self.announce):
+            self._prefetch(step + 1)
         if step == 0:
             return self.y_own
         torch.cuda.current_stream().wait_event(self.fetched.pop(step))
@@ -244,6 +250,9 @@ class _PeerRotation:
         ev = torch.cuda.Event()
         ev.record()
         self.kernels_done[step] = ev
+        if step == 0 and self.announce:       # the own shard's kernels are queued: now the collective, then the fetch
+            self.ex.announce()
+            self._prefetch(1)
 
 
 def _rotation(block, y_own, group, rank, world, token=None):

@@ -279,3 +279,59 @@ def test_shard_schedule():
         for s in range(world):
             assert sorted(ring.shard_at(r, s, world) for r in range(world)) == list(range(world))
     assert ring.ring_neighbours(0, 4) == (3, 1)
+
+
+def _worker_lost_send(rank, world, port, out):
+    """Rank 1 never sends its shard (the message is dropped on the host): rank 0's receive must end with an
+    error after the process group's time limit instead of blocking forever."""
+    import datetime
+    import time
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=4))
+    t0 = time.monotonic()
+    try:
+        from memoryefficientclip_b200 import ring
+        if rank == 1:
+            real_rotate = ring._rotate
+
+            def rotate_without_send(cur, nxt, group, rank_, world_):
+                # the receive is posted, the send is skipped
+                src = ring.ring_neighbours(rank_, world_)[1]
+                return [dist.irecv(nxt, src, group)]
+
+            ring._rotate = rotate_without_send
+        b, d = 16, 8
+        g = torch.Generator().manual_seed(rank)
+        xl = torch.nn.functional.normalize(torch.randn(b, d, generator=g, dtype=torch.float64), dim=1).requires_grad_(True)
+        yl = torch.nn.functional.normalize(torch.randn(b, d, generator=g, dtype=torch.float64), dim=1).requires_grad_(True)
+        mod = ring.RingMemoryEfficientCLIPLoss(0.1, True, None, OracleBlockOps())
+        try:
+            mod(xl, yl)
+            out[rank] = ("finished", time.monotonic() - t0)
+        except Exception as e:      # noqa: BLE001 - whatever the backend raises when its wait runs out
+            out[rank] = ("error: " + type(e).__name__, time.monotonic() - t0)
+    finally:
+        try:
+            dist.destroy_process_group()
+        except Exception:           # noqa: BLE001 - the group is broken by design at this point
+            pass
+
+
+def test_lost_shard_send_surfaces_as_an_error_not_a_hang():
+    port = _free_port()
+    with mp.Manager() as mgr:
+        out = mgr.dict()
+        ctx = mp.spawn(_worker_lost_send, args=(2, port, out), nprocs=2, join=False)
+        deadline = 60.0
+        import time
+        t0 = time.monotonic()
+        while not ctx.join(timeout=1.0):
+            if time.monotonic() - t0 > deadline:
+                for p in ctx.processes:
+                    p.kill()
+                pytest.fail("a rank was still blocked after %.0f s" % deadline)
+        res = dict(out)
+    # rank 0 waited for a shard that was never sent: an error within the group's limit (4 s) plus slack
+    assert res[0][0].startswith("error"), res
+    assert res[0][1] < 30.0, res
