@@ -438,8 +438,9 @@ def run_ours(args):
         loss_val = float(last["loss"].detach())
         if world == 1:
             if rank == 0:
+                rows = PARITY_ROWS + ([b_global // 2, b_global - 1] if b_global > 32768 else [])
                 parity = parity_against_oracle(name, loss_val, a_dev.grad, t_dev.grad, b_global, temperature,
-                                               normalized_inputs, host_a, host_b, PARITY_ROWS)
+                                               normalized_inputs, host_a, host_b, rows)
         else:
             # every rank runs the single-GPU kernels on the all-gathered global batch and compares its own slice
             ga = torch.empty(b_global, d, dtype=a_dev.dtype, device=dev)
