@@ -15,7 +15,7 @@ from . import _lib, ops
 
 # Batches up to this many rows take the whole-step entry points (two library calls per step: the step is
 # host-bound there); MECLIP_STEP_PATH_ROWS=0 switches that path off.
-_STEP_PATH_ROWS = int(os.environ.get("MECLIP_STEP_PATH_ROWS", "8192"))
+_STEP_PATH_ROWS = int(os.environ.get("MECLIP_STEP_PATH_ROWS", "4096"))
 
 # MECLIP_LIT_FUSED=0 keeps LiT on the two-pass path (sums, then recomputing backward) for A/B measurements
 _LIT_FUSED = os.environ.get("MECLIP_LIT_FUSED", "1") != "0"
