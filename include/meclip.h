@@ -158,6 +158,12 @@ int meclip_profile_end(double* ms_by_tag, long long* launches_by_tag, double* fl
  * send it.  Has no counterpart in the reference (which is single-GPU).
  */
 int meclip_accumulate_f32(float* dst, const float* src, int64_t n, void* stream);
+/*
+ * dst[i] += src[i] + src[src_stride + i] + ... + src[(n_src - 1) * src_stride + i], added in that order: the
+ * n_src partial gradients that arrived in one backward (one buffer per ring step, src_stride floats apart), in one
+ * pass over dst.  Same alignment rules; src_stride a multiple of 4 and >= n.  No counterpart in the reference.
+ */
+int meclip_accumulate_many_f32(float* dst, const float* src, int n_src, int64_t src_stride, int64_t n, void* stream);
 
 /*
  * x_hat = x / max(||x||_2, 1e-12) per row, written as bf16, plus inv_norm[i] =

@@ -37,6 +37,7 @@ SIGNATURES = {
     "meclip_profile_begin": (c_int, []),
     "meclip_profile_end": (c_int, [c_void_p, c_void_p, c_void_p, c_int]),
     "meclip_accumulate_f32": (c_int, [c_void_p, c_void_p, c_int64, c_void_p]),
+    "meclip_accumulate_many_f32": (c_int, [c_void_p, c_void_p, c_int, c_int64, c_int64, c_void_p]),
     "meclip_normalize_fwd": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_int, c_void_p, c_int64, c_void_p,
                                      c_void_p]),
     "meclip_normalize_bwd": (c_int, [c_void_p, c_int, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int64,

@@ -16,8 +16,10 @@ Ordering between the processes comes from collectives the ring issues anyway:
   * there are two publish slots, used alternately by successive forwards.  A slot is
     overwritten two forwards later; by then every rank has passed the next forward's all-reduce,
     which it enters only after the fetches of its previous forward and backward have completed
-    (stream order).  A backward must therefore run before the second-next forward of the same
-    module and shapes (checked: RuntimeError otherwise).
+    (stream order), and every backward ends with a collective behind its fetches (the all-reduce
+    that closes the partial-gradient exchange, or one of its own), so a backward that runs directly
+    before the overwriting forward is ordered too.  A backward must run before the second-next
+    forward of the same module and shapes (checked: RuntimeError otherwise).
 No kernel ever reads a peer's memory: a shard always lands in a local buffer first.
 """
 from __future__ import annotations
@@ -100,6 +102,14 @@ class PeerShards:
         with torch.cuda.stream(self.comm):
             self.comm.wait_event(self._published)
             dist.all_reduce(self.flag, group=self.group)
+
+    def fetches_done_everywhere(self) -> torch.cuda.Event:
+        """The event after which every rank's fetches queued so far have completed (an all-reduce behind them)."""
+        with torch.cuda.stream(self.comm):
+            dist.all_reduce(self.flag, group=self.group)
+            ev = torch.cuda.Event()
+            ev.record(self.comm)
+        return ev
 
     def check_live(self, gen: int) -> None:
         if self.gen > gen + 2:

@@ -422,6 +422,22 @@ accumulate_f32_kernel(float* __restrict__ dst, const float* __restrict__ src, lo
     }
 }
 
+// dst[i] += src_0[i] + src_1[i] + ... (added in that order), the sources `stride4` float4 apart: the owner of a
+// text shard adds the world-1 partial gradients of one backward in one pass over its gradient.
+__global__ void __launch_bounds__(256)
+accumulate_many_f32_kernel(float* __restrict__ dst, const float* __restrict__ src, int n_src, long long stride4,
+                           long long n4) {
+    const long long step = (long long)gridDim.x * blockDim.x;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += step) {
+        float4 a = reinterpret_cast<float4*>(dst)[i];
+        for (int s = 0; s < n_src; ++s) {
+            const float4 b = reinterpret_cast<const float4*>(src)[(long long)s * stride4 + i];
+            a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
+        }
+        reinterpret_cast<float4*>(dst)[i] = a;
+    }
+}
+
 // loss (+)= scale * sum_i [ w (log r_i + log c_i) - (s_ii - 1)/T ]: one block, fixed order.
 __global__ void __launch_bounds__(1024)
 loss_finalize_kernel(const float* __restrict__ r, const float* __restrict__ c, const float* __restrict__ diag,
@@ -1084,6 +1100,20 @@ int meclip_accumulate_f32(float* dst, const float* src, int64_t n, void* stream)
     if (blocks > 8LL * sm_count()) blocks = 8LL * sm_count();
     ScopedTiming timing((cudaStream_t)stream, TAG_ACCUM, 12.0 * (double)n);
     accumulate_f32_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(dst, src, n4);
+    MECLIP_CUDA(cudaGetLastError());
+    return MECLIP_OK;
+}
+
+int meclip_accumulate_many_f32(float* dst, const float* src, int n_src, int64_t src_stride, int64_t n, void* stream) {
+    if (dst == nullptr || src == nullptr || n_src < 1 || n < 0 || n % 4 != 0 || src_stride % 4 != 0 || src_stride < n ||
+        !aligned16(dst) || !aligned16(src))
+        return fail(MECLIP_EINVAL, "accumulate_many_f32: need 16-byte aligned pointers, n and stride multiples of 4, stride >= n");
+    if (n == 0) return MECLIP_OK;
+    const long long n4 = n / 4;
+    long long blocks = (n4 + 255) / 256;
+    if (blocks > 8LL * sm_count()) blocks = 8LL * sm_count();
+    ScopedTiming timing((cudaStream_t)stream, TAG_ACCUM, 4.0 * (double)n * (n_src + 2));
+    accumulate_many_f32_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(dst, src, n_src, src_stride / 4, n4);
     MECLIP_CUDA(cudaGetLastError());
     return MECLIP_OK;
 }

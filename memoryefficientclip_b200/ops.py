@@ -191,6 +191,15 @@ def accumulate_f32(dst: torch.Tensor, src: torch.Tensor) -> None:
         _lib.check(_lib.load().meclip_accumulate_f32(dst.data_ptr(), src.data_ptr(), dst.numel(), _stream(dst)))
 
 
+def accumulate_many_f32(dst: torch.Tensor, srcs: torch.Tensor) -> None:
+    """dst += srcs[0] + srcs[1] + ... in that order; srcs is one contiguous fp32 tensor [n_src, *dst.shape]."""
+    assert dst.dtype == torch.float32 and srcs.dtype == torch.float32 and srcs.is_contiguous() and dst.is_contiguous()
+    assert srcs.shape[1:] == dst.shape
+    with torch.cuda.device(dst.device):
+        _lib.check(_lib.load().meclip_accumulate_many_f32(dst.data_ptr(), srcs.data_ptr(), srcs.shape[0], dst.numel(),
+                                                          dst.numel(), _stream(dst)))
+
+
 def as_operand(x: torch.Tensor) -> torch.Tensor:
     """bf16, unit-stride rows of padded(d) columns, 16-byte aligned: what the tile kernels read."""
     _check_matrix(x, "operand")

@@ -43,6 +43,17 @@ def _mark(label: str) -> None:
         TRACE.append((label, ev))
 
 
+def _nvtx_push(name: str, t) -> None:
+    """NVTX range around one ring step (visible in a profiler's timeline; a no-op on CPU tensors)."""
+    if t.is_cuda:
+        torch.cuda.nvtx.range_push(name)
+
+
+def _nvtx_pop(t) -> None:
+    if t.is_cuda:
+        torch.cuda.nvtx.range_pop()
+
+
 def trace_durations(trace):
     """{label: milliseconds} summed over the marks of a finished (synchronised) trace."""
     out = {}
@@ -169,6 +180,9 @@ class CudaBlockOps:
     def accumulate(self, dst, src):
         ops.accumulate_f32(dst, src)
 
+    def accumulate_many(self, dst, srcs):
+        ops.accumulate_many_f32(dst, srcs)
+
     def reduce_scatter(self, out, table, group):
         dist.reduce_scatter_tensor(out.view(-1), table.view(-1), op=dist.ReduceOp.SUM, group=group)
 
@@ -218,6 +232,9 @@ class _SendRecvRotation:
         if step + 1 < self.world:
             self.cur = self.nxt
 
+    def finish(self):
+        pass
+
 
 class _PeerRotation:
     """Every rank fetches the shard of step s+1 from its owner's published buffer with the copy engines
@@ -254,6 +271,12 @@ class _PeerRotation:
             self.ex.announce()
             self._prefetch(1)
 
+    def finish(self):
+        """End of a backward that has no other collective behind its fetches: a one-word all-reduce on the copy
+        stream, which the compute stream waits for, so that this rank's next publish (which overwrites a slot)
+        cannot overtake another rank that is still fetching from it."""
+        torch.cuda.current_stream().wait_event(self.ex.fetches_done_everywhere())
+
 
 def _rotation(block, y_own, group, rank, world, token=None):
     """(rotation, token): the block implementation may bring its own shard transport; the token is what a
@@ -277,12 +300,14 @@ def ring_forward(block, kind, x_hat, y_hat, temperature, group, rank, world):
     _mark("fwd_setup")
     for step in range(world):
         shard = shard_at(rank, step, world)
+        _nvtx_push(f"ring_fwd_step{step}", x_hat)
         y_cur = rot.begin(step)
         _mark("fwd_exposed_shard_wait")
         block.sum_exp(kind, x_hat, y_cur, temperature, row_sum, col_part[shard] if clip else None, diag,
                       rank * b, shard * b)
         _mark("fwd_kernels")
         rot.end(step)
+        _nvtx_pop(x_hat)
         _mark("fwd_exposed_shard_wait")
     col_sum = None
     if clip:
@@ -331,6 +356,7 @@ def _ring_backward_loop(block, x_hat, y_hat, group, rank, world, want_dy, grad_c
     _mark("bwd_setup")
     for step in range(world):
         shard = shard_at(rank, step, world)
+        _nvtx_push(f"ring_bwd_step{step}", x_hat)
         y_cur = rot.begin(step)
         _mark("bwd_exposed_shard_wait")
         out = None
@@ -355,6 +381,7 @@ def _ring_backward_loop(block, x_hat, y_hat, group, rank, world, want_dy, grad_c
             else:
                 pending = (_exchange_partial(part[step % 2], inbox[step % 2], group, rank, world, step), inbox[step % 2])
         rot.end(step)
+        _nvtx_pop(x_hat)
         _mark("bwd_exposed_shard_wait")
     if pending is not None:
         for r in pending[0]:
@@ -365,9 +392,14 @@ def _ring_backward_loop(block, x_hat, y_hat, group, rank, world, want_dy, grad_c
     if inbox_peer is not None:
         torch.cuda.current_stream().wait_event(inbox_peer.arrived())     # every rank's pushes have landed
         _mark("bwd_exposed_last_partial_wait")
-        for step in range(1, world):     # fixed order: the partial of ring step 1 first
-            block.accumulate(dy, inbox_peer.local[step - 1])
+        if hasattr(block, "accumulate_many") and dy.numel() % 4 == 0:
+            block.accumulate_many(dy, inbox_peer.local)      # one pass, the partial of ring step 1 first
+        else:
+            for step in range(1, world):
+                block.accumulate(dy, inbox_peer.local[step - 1])
         _mark("bwd_accumulate_f32")
+    elif world > 1:
+        rot.finish()
     return dx, dy
 
 

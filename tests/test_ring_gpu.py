@@ -19,10 +19,11 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _worker(rank, world, port, kind, b_global, d, dtype_name, normalize, outdir):
+def _worker(rank, world, port, kind, b_global, d, dtype_name, normalize, outdir, transport="peer"):
     import torch.distributed as dist
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
+    os.environ["MECLIP_RING_TRANSPORT"] = transport      # read when the ring module is imported (below)
     torch.cuda.set_device(rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
     try:
@@ -47,12 +48,12 @@ def _worker(rank, world, port, kind, b_global, d, dtype_name, normalize, outdir)
         dist.destroy_process_group()
 
 
-def _run(world, kind, b_global, d, dtype_name, normalize):
+def _run(world, kind, b_global, d, dtype_name, normalize, transport="peer"):
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
     with tempfile.TemporaryDirectory() as outdir:
-        mp.spawn(_worker, args=(world, _free_port(), kind, b_global, d, dtype_name, normalize, outdir), nprocs=world,
-                 join=True)
+        mp.spawn(_worker, args=(world, _free_port(), kind, b_global, d, dtype_name, normalize, outdir, transport),
+                 nprocs=world, join=True)
         res = [torch.load(os.path.join(outdir, f"r{r}.pt")) for r in range(world)]
     dtype = getattr(torch, dtype_name)
     g = torch.Generator().manual_seed(0)
@@ -84,6 +85,60 @@ def _run(world, kind, b_global, d, dtype_name, normalize):
                                                       ("clip", 640, 52, "float32", False)])
 def test_ring_two_gpus(kind, b, d, dtype, normalize):
     _run(2, kind, b, d, dtype, normalize)
+
+
+def test_ring_two_gpus_send_recv_transport():
+    """The fallback transport (NCCL send/recv from rank to rank instead of copy-engine fetches from peer memory)."""
+    _run(2, "clip", 1024, 128, "bfloat16", False, transport="nccl")
+
+
+def _interleaved_worker(rank, world, port, outdir):
+    """Two forwards, then their backwards in reverse order: the second forward publishes into the other slot,
+    the first backward to run fetches the newer shards, the second one the older ones; the partial-gradient
+    inbox is used by two backwards in a row."""
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        from memoryefficientclip_b200 import ring
+        b_global, d = 768, 96
+        b = b_global // world
+        out = {}
+        mod = ring.RingMemoryEfficientCLIPLoss(0.07, False)
+        batches, losses = [], []
+        for seed in (1, 2):
+            g = torch.Generator().manual_seed(seed)
+            x = torch.randn(b_global, d, generator=g)[rank * b:(rank + 1) * b].cuda().requires_grad_(True)
+            y = torch.randn(b_global, d, generator=g)[rank * b:(rank + 1) * b].cuda().requires_grad_(True)
+            batches.append((x, y))
+            losses.append(mod(x, y))
+        losses[1].backward()
+        losses[0].backward()
+        torch.cuda.synchronize()
+        for i, (x, y) in enumerate(batches):
+            out[i] = {"loss": losses[i].item(), "dx": x.grad.float().cpu(), "dy": y.grad.float().cpu()}
+        torch.save(out, os.path.join(outdir, f"r{rank}.pt"))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_ring_two_forwards_then_two_backwards():
+    world = 2
+    if torch.cuda.device_count() < world:
+        pytest.skip("needs 2 GPUs")
+    with tempfile.TemporaryDirectory() as outdir:
+        mp.spawn(_interleaved_worker, args=(world, _free_port(), outdir), nprocs=world, join=True)
+        res = [torch.load(os.path.join(outdir, f"r{r}.pt")) for r in range(world)]
+    for i, seed in enumerate((1, 2)):
+        g = torch.Generator().manual_seed(seed)
+        x = torch.randn(768, 96, generator=g)
+        y = torch.randn(768, 96, generator=g)
+        loss, gx, gy = dense.clip_dense(x, y, 0.07, False)
+        dx = torch.cat([r[i]["dx"] for r in res])
+        dy = torch.cat([r[i]["dy"] for r in res])
+        dense.assert_parity(res[0][i]["loss"], loss, (dx, dy), (gx, gy), f"interleaved step {i}")
 
 
 def _large_worker(rank, world, port, outdir):
