@@ -207,6 +207,22 @@ int meclip_sum_exp(int kind, const void* x_bf16, const void* y_bf16, int64_t row
                    float* col_sum, float* diag_s, unsigned int* tile_counter, int* status, void* stream);
 
 /*
+ * meclip_sum_exp with sums that are bit-identical from run to run.  The plain entry point adds its per-tile
+ * partial sums with fp32 atomics (as the reference does, clip_loss.py:63-64), so the last bits of row_sum, col_sum,
+ * the loss and - through the bf16 rounding of single coefficients - the gradients depend on the order in which
+ * tiles finish.  Here every partial is stored in a slot of its own (two per column tile for the rows, one per 128
+ * rows for the columns) and a second kernel adds the slots in a fixed order onto row_sum / col_sum; together with
+ * the backward, which has no atomics, a whole step is then reproducible bit for bit.  Costs the per-tile hand-in
+ * of the column partials and one pass over the slots (33.5 MB each at 32768 x 32768).
+ * workspace: meclip_sum_exp_det_workspace_bytes(rows, cols) bytes, 256-byte aligned; cleared by the call.
+ */
+size_t meclip_sum_exp_det_workspace_bytes(int64_t rows, int64_t cols);
+int meclip_sum_exp_det(int kind, const void* x_bf16, const void* y_bf16, int64_t rows, int64_t cols, int64_t d,
+                       int64_t ldx, int64_t ldy, float temperature, int64_t row_off, int64_t col_off, float* row_sum,
+                       float* col_sum, float* diag_s, unsigned int* tile_counter, void* workspace,
+                       size_t workspace_bytes, int* status, void* stream);
+
+/*
  * loss_out (+)= scale * sum_i [ w*(log row_sum[i] + log col_sum[i]) - (diag_s[i] - 1)/T ],
  * w = 1/2 and both logs for CLIP; w = 1 and only the row log for LiT.
  * scale = 1/B gives the mean.  Deterministic single-block reduction.

@@ -59,6 +59,7 @@ class ContrastiveLossFn(torch.autograd.Function):
         ctx.meclip_fused = False
         ctx.meclip_step = False
         if (kind == _lib.CLIP and not learn_t and x.shape[0] <= _STEP_PATH_ROWS and x.dtype == y.dtype
+                and not ops.DETERMINISTIC
                 and x.stride(1) == 1 and y.stride(1) == 1 and x.stride(0) >= x.shape[1] and y.stride(0) >= y.shape[1]):
             loss, saved = ops.step_forward(kind, x, y, normalize, temperature_value, status=status)
             ctx.save_for_backward(saved)

@@ -44,6 +44,10 @@ SIGNATURES = {
                                      c_void_p, c_int, c_int64, c_void_p]),
     "meclip_sum_exp": (c_int, [c_int, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64, c_float,
                                c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "meclip_sum_exp_det_workspace_bytes": (c_size_t, [c_int64, c_int64]),
+    "meclip_sum_exp_det": (c_int, [c_int, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64, c_float,
+                                   c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p,
+                                   c_void_p]),
     "meclip_loss_finalize": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_int64, c_float, c_float, c_int,
                                      c_void_p, c_void_p]),
     "meclip_grad_workspace_bytes": (c_size_t, [c_int64, c_int64, c_int64]),

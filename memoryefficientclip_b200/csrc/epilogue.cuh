@@ -90,6 +90,7 @@ struct EpiState {        // per-thread state that lives across tiles
     // their columns; reduced across rows (shuffles, shared memory, atomics) once per strip
     float cacc[COL_SLOTS][32] = {};
     int strip_n0 = -1;          // first column of the tiles accumulated so far, -1 = nothing pending
+    int strip_m0 = 0;           // first row of the last tile accumulated (the slot of a deterministic flush)
 };
 
 // Per-thread set-up of the epilogue state: the affine part of the elementwise function and the
@@ -136,8 +137,11 @@ __device__ __forceinline__ void flush_column_sums(const GemmParams& p, SharedTai
     }
     named_bar_sync(1, EPI_THREADS);
     for (int j = et; j < p.bn; j += EPI_THREADS)
-        if (st.strip_n0 + j < p.n)
-            atomicAdd(p.col_sum + st.strip_n0 + j, (colpart[0][j] + colpart[1][j]) + (colpart[2][j] + colpart[3][j]));
+        if (st.strip_n0 + j < p.n) {
+            const float v = (colpart[0][j] + colpart[1][j]) + (colpart[2][j] + colpart[3][j]);
+            if (p.col_part != nullptr) p.col_part[(long long)(st.strip_m0 >> 7) * p.part_ld_cols + st.strip_n0 + j] = v;
+            else atomicAdd(p.col_sum + st.strip_n0 + j, v);
+        }
     named_bar_sync(1, EPI_THREADS);
     st.strip_n0 = -1;
 }
@@ -208,6 +212,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, const CUtenso
             flush_column_sums(p, tail, st, warp, lane);
             st.strip_n0 = n0;
         }
+        st.strip_m0 = m0;
         float ra0 = 0.f, ra1 = 0.f, ra2 = 0.f, ra3 = 0.f;
         float sdiag = 0.f;
         const bool diag_here = __any_sync(0xffffffffu, jd >= 0);   // warp-uniform: most tiles miss the diagonal
@@ -230,8 +235,14 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, const CUtenso
         }
         tc_fence_before();
         release();
-        if (rvalid && u_end > u_begin) atomicAdd(p.row_sum + grow, (ra0 + ra1) + (ra2 + ra3));
+        if (rvalid && u_end > u_begin) {
+            const float rs = (ra0 + ra1) + (ra2 + ra3);
+            if (p.row_part != nullptr) p.row_part[(long long)(2 * (n0 / p.bn) + wg) * p.part_ld_rows + grow] = rs;
+            else atomicAdd(p.row_sum + grow, rs);
+        }
         if (jd >= 0 && (jd >> 5) >= u_begin && (jd >> 5) < u_end) p.diag[grow] = sdiag;
+        // deterministic mode: one slot per tile, so the column partials are handed in after every tile
+        if (want_cols && p.col_part != nullptr) flush_column_sums(p, tail, st, warp, lane);
     } else if (EPI == EPI_COEF) {
         // g / c_j for the tile's columns, staged once per tile for all eight warps
         named_bar_sync(1, EPI_THREADS);            // previous tile's readers of icol are done

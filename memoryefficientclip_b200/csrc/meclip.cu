@@ -438,6 +438,16 @@ accumulate_many_f32_kernel(float* __restrict__ dst, const float* __restrict__ sr
     }
 }
 
+// out[i] += parts[0][i] + parts[1][i] + ... in that order (deterministic forward: the slots of the partial sums).
+__global__ void __launch_bounds__(256)
+reduce_parts_kernel(const float* __restrict__ parts, int n_slots, long long ld, long long n, float* __restrict__ out) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    float acc = 0.f;
+    for (int k = 0; k < n_slots; ++k) acc += parts[(long long)k * ld + i];
+    out[i] += acc;
+}
+
 // loss (+)= scale * sum_i [ w (log r_i + log c_i) - (s_ii - 1)/T ]: one block, fixed order.
 __global__ void __launch_bounds__(1024)
 loss_finalize_kernel(const float* __restrict__ r, const float* __restrict__ c, const float* __restrict__ diag,
@@ -1195,10 +1205,23 @@ int meclip_normalize_bwd(const void* g, int g_dtype, int64_t ldg, const void* x_
 }  // extern "C"
 
 namespace meclip {
+struct DetLayout { int row_slots, col_slots; long long ld_rows, ld_cols; size_t col_off, total; };
+static DetLayout det_layout(int64_t rows, int64_t cols) {
+    DetLayout l;
+    const int bn = pick_bn(cols);
+    l.row_slots = 2 * (int)((cols + bn - 1) / bn);
+    l.col_slots = (int)((rows + 127) / 128);
+    l.ld_rows = (long long)round_up((size_t)rows, 64);
+    l.ld_cols = (long long)round_up((size_t)cols, 64);
+    l.col_off = round_up((size_t)l.row_slots * l.ld_rows * 4, 256);
+    l.total = l.col_off + round_up((size_t)l.col_slots * l.ld_cols * 4, 256);
+    return l;
+}
+
 static int sum_exp_impl(int kind, const void* x_bf16, const void* y_bf16, int64_t rows, int64_t cols, int64_t d,
                         int64_t ldx, int64_t ldy, float temperature, int64_t row_off, int64_t col_off, float* row_sum,
                         float* col_sum, float* diag_s, unsigned int* tile_counter, int* status, void* stream,
-                        const DeviceScalars& ds) {
+                        const DeviceScalars& ds, void* det_ws = nullptr, size_t det_ws_bytes = 0) {
     if (kind != MECLIP_CLIP && kind != MECLIP_LIT) return fail(MECLIP_EINVAL, "sum_exp: bad kind %d", kind);
     if (x_bf16 == nullptr || y_bf16 == nullptr || row_sum == nullptr || diag_s == nullptr)
         return fail(MECLIP_EINVAL, "sum_exp: null pointer");
@@ -1221,7 +1244,32 @@ static int sum_exp_impl(int kind, const void* x_bf16, const void* y_bf16, int64_
     p.status = status;
     Operand a{x_bf16, ldx, false}, b{y_bf16, ldy, false};
     t_tag = TAG_SUMS;
-    return launch_gemm(EPI_SUMS, a, b, rows, cols, d, pick_bn(cols), p, (cudaStream_t)stream);
+    const int bn = pick_bn(cols);
+    if (det_ws == nullptr) return launch_gemm(EPI_SUMS, a, b, rows, cols, d, bn, p, (cudaStream_t)stream);
+    // Deterministic sums: every partial goes to its own slot (plain stores), a second kernel adds the slots in a
+    // fixed order.  Slots: 2 per column tile for the rows, 1 per 128 rows for the columns.
+    if (!MECLIP_STRIPS) return fail(MECLIP_EUNSUPPORTED, "deterministic sums need the default epilogue build");
+    const DetLayout l = det_layout(rows, cols);
+    if ((reinterpret_cast<uintptr_t>(det_ws) & 255u) != 0 || det_ws_bytes < l.total)
+        return fail(MECLIP_ENOSPC, "sum_exp_det: workspace %zu < %zu bytes or not 256-byte aligned", det_ws_bytes, l.total);
+    cudaStream_t s = (cudaStream_t)stream;
+    MECLIP_CUDA(cudaMemsetAsync(det_ws, 0, l.total, s));      // slots no tile writes (ragged edges) count as zero
+    p.row_part = reinterpret_cast<float*>(det_ws);
+    p.part_ld_rows = l.ld_rows;
+    p.col_part = kind == MECLIP_CLIP ? reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(det_ws) + l.col_off) : nullptr;
+    p.part_ld_cols = l.ld_cols;
+    rc = launch_gemm(EPI_SUMS, a, b, rows, cols, d, bn, p, s);
+    if (rc) return rc;
+    {
+        ScopedTiming timing(s, TAG_ROW, 4.0 * (double)rows * (l.row_slots + 2));
+        reduce_parts_kernel<<<(unsigned)((rows + 255) / 256), 256, 0, s>>>(p.row_part, l.row_slots, l.ld_rows, rows, row_sum);
+    }
+    if (p.col_part != nullptr) {
+        ScopedTiming timing(s, TAG_ROW, 4.0 * (double)cols * (l.col_slots + 2));
+        reduce_parts_kernel<<<(unsigned)((cols + 255) / 256), 256, 0, s>>>(p.col_part, l.col_slots, l.ld_cols, cols, col_sum);
+    }
+    MECLIP_CUDA(cudaGetLastError());
+    return MECLIP_OK;
 }
 
 static int loss_finalize_impl(int kind, const float* row_sum, const float* col_sum, const float* diag_s, int64_t n,
@@ -1256,6 +1304,22 @@ int meclip_sum_exp(int kind, const void* x_bf16, const void* y_bf16, int64_t row
     NvtxRange range("meclip_sum_exp");
     return sum_exp_impl(kind, x_bf16, y_bf16, rows, cols, d, ldx, ldy, temperature, row_off, col_off, row_sum, col_sum,
                         diag_s, tile_counter, status, stream, ds);
+}
+
+size_t meclip_sum_exp_det_workspace_bytes(int64_t rows, int64_t cols) {
+    if (rows < 1 || cols < 1) return 0;
+    return det_layout(rows, cols).total;
+}
+
+int meclip_sum_exp_det(int kind, const void* x_bf16, const void* y_bf16, int64_t rows, int64_t cols, int64_t d,
+                       int64_t ldx, int64_t ldy, float temperature, int64_t row_off, int64_t col_off, float* row_sum,
+                       float* col_sum, float* diag_s, unsigned int* tile_counter, void* workspace,
+                       size_t workspace_bytes, int* status, void* stream) {
+    const DeviceScalars ds = take_scalars();
+    if (workspace == nullptr) return fail(MECLIP_EINVAL, "sum_exp_det: workspace is null");
+    NvtxRange range("meclip_sum_exp_det");
+    return sum_exp_impl(kind, x_bf16, y_bf16, rows, cols, d, ldx, ldy, temperature, row_off, col_off, row_sum, col_sum,
+                        diag_s, tile_counter, status, stream, ds, workspace, workspace_bytes);
 }
 
 int meclip_loss_finalize(int kind, const float* row_sum, const float* col_sum, const float* diag_s, int64_t n,

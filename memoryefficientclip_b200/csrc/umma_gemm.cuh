@@ -83,6 +83,12 @@ struct GemmParams {
     float* row_sum;           // SUMS: accumulated with atomics
     float* col_sum;           // SUMS: may be null (LiT)
     float* diag;              // SUMS: S_ii per row, written where the diagonal crosses the block
+    // SUMS, deterministic mode: instead of atomics every partial sum is STORED in its own slot and a second kernel
+    // adds the slots in a fixed order.  row_part[(2 * column tile + warp group) * part_ld_rows + row],
+    // col_part[(row / 128) * part_ld_cols + column]; both null = atomics.
+    float* row_part;
+    float* col_part;
+    long long part_ld_rows, part_ld_cols;
     const float* r;           // COEF: saved row sums
     const float* c;           // COEF: saved column sums or null (LiT)
     const float* grad_out;    // COEF: device scalar

@@ -215,10 +215,26 @@ def direct_grad_dtype(dtype, d: int) -> bool:
     return d % 8 == 0 and dtype in (torch.float32, torch.bfloat16)
 
 
-def sum_exp(kind, x_hat, y_hat, temperature, row_sum, col_sum, diag_s, row_off=0, col_off=0, status=None):
+# MECLIP_DETERMINISTIC=1: forward sums without atomics (meclip_sum_exp_det), so that a whole step is reproducible
+# bit for bit; the modules then also stay off the small-batch step path, whose forward uses the atomics.
+DETERMINISTIC = __import__("os").environ.get("MECLIP_DETERMINISTIC", "0") not in ("", "0")
+
+
+def sum_exp(kind, x_hat, y_hat, temperature, row_sum, col_sum, diag_s, row_off=0, col_off=0, status=None,
+            deterministic=None):
     rows, d = x_hat.shape
     cols = y_hat.shape[0]
     counter = torch.zeros(1, dtype=torch.int32, device=x_hat.device)     # dynamic tile hand-out
+    if DETERMINISTIC if deterministic is None else deterministic:
+        lib = _lib.load()
+        ws = torch.empty(lib.meclip_sum_exp_det_workspace_bytes(rows, cols), dtype=torch.uint8, device=x_hat.device)
+        with torch.cuda.device(x_hat.device):
+            t, _b, _keep = _bind(temperature, x_hat.device)
+            _lib.check(lib.meclip_sum_exp_det(kind, x_hat.data_ptr(), y_hat.data_ptr(), rows, cols, d, x_hat.stride(0),
+                                              y_hat.stride(0), t, row_off, col_off, row_sum.data_ptr(), _ptr(col_sum),
+                                              diag_s.data_ptr(), counter.data_ptr(), ws.data_ptr(), ws.numel(),
+                                              _ptr(status), _stream(x_hat)))
+        return
     with torch.cuda.device(x_hat.device):
         t, _b, _keep = _bind(temperature, x_hat.device)
         _lib.check(_lib.load().meclip_sum_exp(kind, x_hat.data_ptr(), y_hat.data_ptr(), rows, cols, d, x_hat.stride(0),
@@ -235,11 +251,19 @@ def loss_finalize(kind, row_sum, col_sum, diag_s, temperature, scale, loss_out, 
                                                     loss_out.data_ptr(), _stream(row_sum)))
 
 
-def loss_forward(kind, x_hat, y_hat, temperature, status=None):
+def loss_forward(kind, x_hat, y_hat, temperature, status=None, deterministic=None):
     """Returns (loss 0-dim fp32, row_sum, col_sum or None, diag_s)."""
     b, d = x_hat.shape
     assert y_hat.shape == x_hat.shape
     dev = x_hat.device
+    if DETERMINISTIC if deterministic is None else deterministic:
+        row_sum = torch.zeros(b, dtype=torch.float32, device=dev)
+        col_sum = torch.zeros(b, dtype=torch.float32, device=dev) if kind == _lib.CLIP else None
+        diag_s = torch.zeros(b, dtype=torch.float32, device=dev)
+        loss = torch.empty((), dtype=torch.float32, device=dev)
+        sum_exp(kind, x_hat, y_hat, temperature, row_sum, col_sum, diag_s, 0, 0, status, deterministic=True)
+        loss_finalize(kind, row_sum, col_sum, diag_s, temperature, 1.0 / b, loss)
+        return loss, row_sum, col_sum, diag_s
     row_sum = torch.empty(b, dtype=torch.float32, device=dev)
     col_sum = torch.empty(b, dtype=torch.float32, device=dev) if kind == _lib.CLIP else None
     diag_s = torch.empty(b, dtype=torch.float32, device=dev)

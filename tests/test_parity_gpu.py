@@ -300,3 +300,33 @@ def test_lit_one_pass_and_two_pass_routes_agree_with_the_oracle(b, d, dtype, nor
     with torch.no_grad():
         l2 = m.MemoryEfficientLiTLoss(0.07, normalized)(txt.cuda(), img.cuda()).item()
     assert dense.loss_rel_err(l2, rl) <= dense.LOSS_RTOL
+
+
+@pytest.mark.parametrize("b,d,dtype,normalized", [(1000, 96, torch.float32, False), (2304, 256, torch.bfloat16, True),
+                                                  (200, 40, torch.float32, True)])
+def test_deterministic_forward_makes_the_whole_step_bit_identical(b, d, dtype, normalized, monkeypatch):
+    """With the deterministic sums (no atomics in the forward) loss, sums and both gradients of two runs are
+    bit-identical, and they are still the dense formulation's; the block-level sums agree with the atomic ones."""
+    from memoryefficientclip_b200 import _lib, ops
+    m = _mods()
+    monkeypatch.setattr(ops, "DETERMINISTIC", True)
+    x, y = _inputs(b, d, 31, normalized, dtype)
+    runs = []
+    for _ in range(2):
+        xg, yg = x.cuda().requires_grad_(True), y.cuda().requires_grad_(True)
+        loss = m.MemoryEfficientCLIPLoss(0.07, normalized)(xg, yg)
+        loss.backward()
+        runs.append((loss.detach().clone(), xg.grad.clone(), yg.grad.clone()))
+    torch.cuda.synchronize()
+    for a, c in zip(*runs):
+        assert torch.equal(a, c)
+    rl, rx, ry = dense.clip_dense(x, y, 0.07, normalized)
+    dense.assert_parity(runs[0][0].item(), rl, (runs[0][1].float().cpu(), runs[0][2].float().cpu()), (rx, ry), "deterministic")
+    # the sums themselves: deterministic against atomic, same kernels otherwise
+    xh = ops.normalize_fwd(x.cuda(), not normalized)[0]
+    yh = ops.normalize_fwd(y.cuda(), not normalized)[0]
+    _l0, r0, c0, d0 = ops.loss_forward(_lib.CLIP, xh, yh, 0.07, deterministic=False)
+    _l1, r1, c1, d1 = ops.loss_forward(_lib.CLIP, xh, yh, 0.07, deterministic=True)
+    _l2, r2, c2, _d2 = ops.loss_forward(_lib.CLIP, xh, yh, 0.07, deterministic=True)
+    assert torch.equal(r1, r2) and torch.equal(c1, c2)
+    assert torch.allclose(r0, r1, rtol=1e-5) and torch.allclose(c0, c1, rtol=1e-5) and torch.equal(d0, d1)
