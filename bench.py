@@ -128,12 +128,12 @@ def cpu_inputs(name: str, batch=None):
     return kind, b, d, temperature, xn, yn
 
 
-def cpu_sample_rows(b: int, d: int, budget_flops: float) -> int:
+def cpu_sample_rows(b: int, d: int, flop_limit: float) -> int:
     """Rows of the first matrix one timed CPU step works on: all of them when the whole step fits the
-    budget, else a multiple of 512 rows against ALL columns (the work per row is the full problem's)."""
-    if 8.0 * b * b * d <= budget_flops:
+    limit, else a multiple of 512 rows against ALL columns (the work per row is the full problem's)."""
+    if 8.0 * b * b * d <= flop_limit:
         return b
-    return max(512, int(budget_flops / (8.0 * b * d)) // 512 * 512)
+    return max(512, int(flop_limit / (8.0 * b * d)) // 512 * 512)
 
 
 def cpu_blocked_step_seconds(xn, yn, temperature, rows):
