@@ -41,13 +41,20 @@ def _map_everywhere(local: torch.Tensor, group, rank: int, world: int, device):
     lib = _lib.load()
     handle = ctypes.create_string_buffer(64)
     offset = ctypes.c_uint64(0)
-    with torch.cuda.device(device):
-        _lib.check(lib.meclip_ipc_export(local.data_ptr(), handle, ctypes.byref(offset)))
-    everyone = [None] * world
-    dist.all_gather_object(everyone, (bytes(handle.raw), int(offset.value)), group=group)
-    addr = [0] * world
-    ok = True
+    mine = None
     try:
+        with torch.cuda.device(device):
+            _lib.check(lib.meclip_ipc_export(local.data_ptr(), handle, ctypes.byref(offset)))
+        mine = (bytes(handle.raw), int(offset.value))
+    except _lib.MeclipError:
+        pass                             # e.g. an allocator whose memory cannot be exported (virtual-memory segments)
+    everyone = [None] * world
+    dist.all_gather_object(everyone, mine, group=group)
+    addr = [0] * world
+    ok = all(e is not None for e in everyone)
+    try:
+        if not ok:
+            raise _lib.MeclipError(_lib.EUNSUPPORTED, "a rank could not export its buffer")
         for p, (h, off) in enumerate(everyone):
             if p == rank:
                 addr[p] = local.data_ptr()

@@ -42,7 +42,10 @@ static int fail(int code, const char* fmt, ...) {
 #define MECLIP_CUDA(expr)                                                                         \
     do {                                                                                          \
         cudaError_t e__ = (expr);                                                                 \
-        if (e__ != cudaSuccess) return fail(MECLIP_ECUDA, "%s: %s", #expr, cudaGetErrorString(e__)); \
+        if (e__ != cudaSuccess) {                                                                 \
+            cudaGetLastError(); /* reported here: do not leave it for the next launch's check */  \
+            return fail(MECLIP_ECUDA, "%s: %s", #expr, cudaGetErrorString(e__));                  \
+        }                                                                                         \
     } while (0)
 
 // ------------------------------------------------------------------------------------

@@ -23,6 +23,11 @@ def _worker(rank, world, port, kind, b_global, d, dtype_name, normalize, outdir,
     import torch.distributed as dist
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
+    if transport == "peer_unexportable":
+        # memory from virtual-memory segments has no IPC handle: the peer transport must notice and every rank must
+        # fall back to send/recv together
+        transport = "peer"
+        torch.cuda.memory._set_allocator_settings("expandable_segments:True")
     os.environ["MECLIP_RING_TRANSPORT"] = transport      # read when the ring module is imported (below)
     torch.cuda.set_device(rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
@@ -90,6 +95,10 @@ def test_ring_two_gpus(kind, b, d, dtype, normalize):
 def test_ring_two_gpus_send_recv_transport():
     """The fallback transport (NCCL send/recv from rank to rank instead of copy-engine fetches from peer memory)."""
     _run(2, "clip", 1024, 128, "bfloat16", False, transport="nccl")
+
+
+def test_ring_two_gpus_falls_back_when_memory_cannot_be_exported():
+    _run(2, "clip", 768, 64, "float32", True, transport="peer_unexportable")
 
 
 def _interleaved_worker(rank, world, port, outdir):
