@@ -224,7 +224,7 @@ def errors_vs(got: torch.Tensor, ref: torch.Tensor):
     return max_rel, cos
 
 
-def parity_against_oracle(name, loss, gx, gy, b, temperature, normalized_inputs, first, second, rows):
+def parity_against_oracle(name, loss, gx, gy, b, temperature, normalized_inputs, first, second, rows, lit=False):
     """Loss and sampled gradient rows against the row-blocked CPU oracle (fp32 matmuls, fp64 sums).  `first`,
     `second` are the host copies of the inputs exactly as the GPU saw them (bf16 values upcast)."""
     from oracle import dense
@@ -235,17 +235,19 @@ def parity_against_oracle(name, loss, gx, gy, b, temperature, normalized_inputs,
     else:
         xn, yn = torch.nn.functional.normalize(xf, dim=1), torch.nn.functional.normalize(yf, dim=1)
     rows = sorted({r for r in rows if r < b})
-    ref = dense.clip_streaming(xn, yn, temperature, rows)
-    want_x, want_y = ref["dx_rows"], ref["dy_rows"]
+    ref = dense.clip_streaming(xn, yn, temperature, rows, lit=lit)
+    want_x, want_y = ref["dx_rows"], ref.get("dy_rows")
     if not normalized_inputs:        # chain the normalise Jacobian onto the oracle's rows
         inv_x = 1.0 / xf.norm(dim=1).clamp_min(1e-12)
         inv_y = 1.0 / yf.norm(dim=1).clamp_min(1e-12)
         want_x = torch.from_numpy(dense.normalize_jacobian_np(xn[rows].double().numpy(), inv_x[rows].double().numpy(),
                                                               want_x.numpy()))
-        want_y = torch.from_numpy(dense.normalize_jacobian_np(yn[rows].double().numpy(), inv_y[rows].double().numpy(),
-                                                              want_y.numpy()))
+        if want_y is not None:
+            want_y = torch.from_numpy(dense.normalize_jacobian_np(yn[rows].double().numpy(),
+                                                                  inv_y[rows].double().numpy(), want_y.numpy()))
     dx_rel, dx_cos = dense.grad_errors(gx[rows].float().cpu(), want_x)
-    dy_rel, dy_cos = dense.grad_errors(gy[rows].float().cpu(), want_y)
+    # LiT: the second argument is frozen, there is no second gradient to compare
+    dy_rel, dy_cos = dense.grad_errors(gy[rows].float().cpu(), want_y) if want_y is not None else (0.0, 1.0)
     out = {"against": "row_blocked_cpu_oracle", "workload": name, "rows_sampled": len(rows),
            "loss_rel": dense.loss_rel_err(loss, ref["loss"]), "dx_max_rel": dx_rel, "dx_cos": dx_cos,
            "dy_max_rel": dy_rel, "dy_cos": dy_cos, "oracle_seconds": round(time.perf_counter() - t0, 1)}
@@ -434,13 +436,13 @@ def run_ours(args):
 
     # ---- parity of what was timed, outside every timed region --------------------------------
     parity = None
-    if not lit and not args.no_parity:
+    if not args.no_parity and (world == 1 or not lit):
         loss_val = float(last["loss"].detach())
         if world == 1:
             if rank == 0:
                 rows = PARITY_ROWS + ([b_global // 2, b_global - 1] if b_global > 32768 else [])
                 parity = parity_against_oracle(name, loss_val, a_dev.grad, t_dev.grad, b_global, temperature,
-                                               normalized_inputs, host_a, host_b, rows)
+                                               normalized_inputs, host_a, host_b, rows, lit=lit)
         else:
             # every rank runs the single-GPU kernels on the all-gathered global batch and compares its own slice
             ga = torch.empty(b_global, d, dtype=a_dev.dtype, device=dev)
