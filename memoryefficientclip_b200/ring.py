@@ -1,20 +1,23 @@
 """Ring-distributed CLIP / LiT loss for one NVLink box: one process per GPU.
 
-Rank r keeps its B/N image rows (first argument) for the whole step.  The N text
-shards (second argument) rotate around the ring: at step s rank r works on shard
-(r + s) mod N while it already sends that shard to rank r-1 and receives the next
-one from rank r+1 (NCCL send/recv on the process group's stream, waited on only
-after the tile kernels of the step have been queued, so the transfer runs under the
-MMAs).  A shard always lands in local HBM before a kernel reads it.
+Rank r keeps its B/N image rows (first argument) for the whole step.  At ring step s it works
+on text shard (r + s) mod N, which is in local HBM before any kernel reads it.  How a shard
+gets there is the transport's business:
+  peer (default on GPUs)  every rank publishes its shard in a buffer the other ranks have mapped
+          (CUDA IPC) and fetches the shard of step s+1 from its owner with a copy-engine copy while
+          the kernels of step s run (_peer.PeerShards): no SM is taken from the tile kernels;
+  send/recv  the shards travel rank to rank (NCCL on GPUs without peer mapping, gloo in the CPU
+          tests): rank r sends the shard it works on to r-1 and receives the next one from r+1.
 
 forward   row sums finish locally; per-shard column partial sums [N, b] are
           reduce-scattered so that each rank ends with the column sums of its own
           shard; the loss is the all-reduced sum of the local terms.
 backward  column sums are all-gathered (B floats); d(first) accumulates locally in
           fp32 over the N steps; the d(second) partial a rank computes for a visiting
-          shard is sent straight to the shard's owner while the next step computes
-          (a reduce-scatter spread over the steps: only the last partial's transfer is
-          exposed, and no [N, b, D] table exists); the owner adds what it receives.
+          shard goes straight to the shard's owner while the next step computes
+          (copy-engine writes into the owner's inbox, or send/recv), and the owner adds the
+          N-1 partials in the order of the ring steps: a reduce-scatter spread over the steps,
+          no [N, b, D] table.
 
 The reference has no distributed code; the result is defined as the single-process
 loss on the concatenated global batch (rank-major row order).
