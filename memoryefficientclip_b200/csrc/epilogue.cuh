@@ -149,15 +149,15 @@ __device__ __forceinline__ void flush_column_sums(const GemmParams& p, SharedTai
 // `release()` is called by every thread once its last tcgen05.ld of the tile has completed; it must
 // tell the MMA issuer that this thread is done with the accumulator.
 template <int EPI, class Release>
-__device__ __forceinline__ void epilogue_tile(const GemmParams& p, const CUtensorMap* tmap_c, SharedTail* tail,
-                                              EpiState& st, uint32_t taddr, int m0, int n0, int tile_bn, int warp,
-                                              int lane, Release release) {
+__device__ __forceinline__ void epilogue_tile(const GemmParams& p, const OutDesc od, const CUtensorMap* tmap_c,
+                                              SharedTail* tail, EpiState& st, uint32_t taddr, int m0, int n0,
+                                              int tile_bn, int warp, int lane, Release release) {
     const int q = warp & 3;
     const int wg = EPI_WARPS == 8 ? (warp - 2) >> 2 : 0;
     const int et = (int)threadIdx.x - 64;                 // index within the epilogue group
     const int grow = m0 + q * 32 + lane;
-    const bool rvalid = grow < p.m;
-    const bool full_tile = (m0 + BM <= p.m) && (n0 + p.bn <= p.n);
+    const bool rvalid = grow < od.m;          // od.m == p.m except for the second problem of a dual launch
+    const bool full_tile = (m0 + BM <= od.m) && (n0 + p.bn <= p.n);
     // column (tile-local) on which this row meets the diagonal, -1 if outside the tile
     const long long jd_ll = (long long)grow + p.diag_shift - n0;
     const int jd = (jd_ll >= 0 && jd_ll < p.bn && n0 + jd_ll < p.n && rvalid) ? (int)jd_ll : -1;
@@ -352,8 +352,8 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, const CUtenso
             tmem_ld_wait();
             if (rvalid) {
                 const int col0 = n0 + gcol;
-                if (p.acc_in != nullptr) {
-                    const float* ap = p.acc_in + (long long)grow * p.ld_acc + col0;
+                if (od.acc_in != nullptr) {
+                    const float* ap = od.acc_in + (long long)grow * od.ld_acc + col0;
 #pragma unroll
                     for (int c = 0; c < 32; c += 4) {
                         if (col0 + c < p.n) {
@@ -365,8 +365,8 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, const CUtenso
                         }
                     }
                 }
-                if (p.out_bf16) {
-                    __nv_bfloat16* op = reinterpret_cast<__nv_bfloat16*>(p.out) + (long long)grow * p.ld_out + col0;
+                if (od.out_bf16) {
+                    __nv_bfloat16* op = reinterpret_cast<__nv_bfloat16*>(od.out) + (long long)grow * od.ld_out + col0;
 #pragma unroll
                     for (int c = 0; c < 32; c += 8) {
                         if (col0 + c < p.n) {
@@ -379,7 +379,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, const CUtenso
                         }
                     }
                 } else {
-                    float* op = reinterpret_cast<float*>(p.out) + (long long)grow * p.ld_out + col0;
+                    float* op = reinterpret_cast<float*>(od.out) + (long long)grow * od.ld_out + col0;
 #pragma unroll
                     for (int c = 0; c < 32; c += 4) {
                         if (col0 + c < p.n) {

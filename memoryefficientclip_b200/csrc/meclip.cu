@@ -719,10 +719,11 @@ static int launch_gemm_t(const CUtensorMap& ta, const CUtensorMap& tb, const CUt
     return MECLIP_OK;
 }
 
-template <int EPI, bool A_MN>
+template <int EPI, int A_MODE>
 static int launch_pair_t(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmParams& p,
-                         size_t smem_bytes, cudaStream_t stream) {
-    auto kern = umma_gemm_pair_kernel<EPI, A_MN>;
+                         size_t smem_bytes, cudaStream_t stream, const CUtensorMap* td_opt = nullptr, double flops = -1.0) {
+    auto kern = umma_gemm_pair_kernel<EPI, A_MODE>;
+    const CUtensorMap& td = td_opt != nullptr ? *td_opt : tb;
     MECLIP_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_LIMIT));
     // how many CTA pairs the device can hold at once (an SM without a free neighbour cannot host one)
     static int max_clusters[64] = {0};
@@ -743,11 +744,11 @@ static int launch_pair_t(const CUtensorMap& ta, const CUtensorMap& tb, const CUt
         max_clusters[dev] = n;
     }
     const int cap = (dev >= 0 && dev < 64) ? max_clusters[dev] : sm_count() / 2;
-    const int tiles = p.num_m_tiles * p.num_n_tiles;
+    const int tiles = p.dual ? p.tiles0 + p.num_m_tiles2 * p.num_n_tiles : p.num_m_tiles * p.num_n_tiles;
     const int units = (tiles + p.strip_len - 1) / p.strip_len;
     const int clusters = units < cap ? units : cap;
-    ScopedTiming timing(stream, t_tag, 2.0 * p.m * p.n * p.k);
-    kern<<<2 * clusters, GEMM_THREADS, smem_bytes, stream>>>(ta, tb, tc, p);
+    ScopedTiming timing(stream, t_tag, flops >= 0.0 ? flops : 2.0 * p.m * p.n * p.k);
+    kern<<<2 * clusters, GEMM_THREADS, smem_bytes, stream>>>(ta, tb, tc, td, p);
     MECLIP_CUDA(cudaGetLastError());
     return MECLIP_OK;
 }
@@ -875,10 +876,10 @@ static int launch_gemm(int epi, const Operand& a, const Operand& b, long long m,
         if (env_max_stages >= 2 && stages > env_max_stages) stages = env_max_stages;
         p.num_stages = stages;
         const size_t pair_smem = 1024 + (size_t)stages * p.stage_bytes + tail_bytes(epi);
-        if (epi == EPI_SUMS) return launch_pair_t<EPI_SUMS, false>(ta, tb, tc, p, pair_smem, stream);
-        if (epi == EPI_COEF) return launch_pair_t<EPI_COEF, false>(ta, tb, tc, p, pair_smem, stream);
-        if (epi == EPI_OUT) return a.mn_major ? launch_pair_t<EPI_OUT, true>(ta, tb, tc, p, pair_smem, stream)
-                                              : launch_pair_t<EPI_OUT, false>(ta, tb, tc, p, pair_smem, stream);
+        if (epi == EPI_SUMS) return launch_pair_t<EPI_SUMS, 0>(ta, tb, tc, p, pair_smem, stream);
+        if (epi == EPI_COEF) return launch_pair_t<EPI_COEF, 0>(ta, tb, tc, p, pair_smem, stream);
+        if (epi == EPI_OUT) return a.mn_major ? launch_pair_t<EPI_OUT, 1>(ta, tb, tc, p, pair_smem, stream)
+                                              : launch_pair_t<EPI_OUT, 0>(ta, tb, tc, p, pair_smem, stream);
         return fail(MECLIP_EINVAL, "unknown epilogue %d", epi);
     }
     p.num_stages = stages;
@@ -895,6 +896,70 @@ static int launch_gemm(int epi, const Operand& a, const Operand& b, long long m,
     MECLIP_DISPATCH(EPI_OUT)
 #undef MECLIP_DISPATCH
     return fail(MECLIP_EINVAL, "unknown epilogue %d", epi);
+}
+
+// MECLIP_DUAL=0 launches the two contractions of a block separately (A/B switch).
+static bool dual_allowed() {
+    static const bool on = []() { const char* v = std::getenv("MECLIP_DUAL"); return !(v && v[0] == '0'); }();
+    return on;
+}
+
+// Both contractions of one block of the backward in ONE launch of the CTA-pair kernel:
+//   problem 0  dY [cols x n] (+)= G^T X   A = the panel read MN-major (M = cols, K = rows), B = X^T (K-major)
+//   problem 1  dX [rows x n] (+)= G Y     A = the panel read K-major  (M = rows, K = cols), B = Y^T (K-major)
+// Twice the tiles per launch means a fuller last wave (640 tiles instead of 2 x 320 on 74 CTA pairs) and one
+// launch less per block.  py / px carry the outputs (out, ld_out, out_bf16, acc_in, ld_acc, tile_counter, status).
+static int launch_contractions_dual(const void* panel, long long panel_rows_alloc, long long panel_chunks_alloc,
+                                    const void* xt, long long ld_xt, const void* yt, long long ld_yt, long long rows,
+                                    long long cols, long long n, const GemmParams& py, const GemmParams& px,
+                                    cudaStream_t stream) {
+    if (rows < 1 || cols < 1 || n < 1 || rows > 0x7fffffffLL || cols > 0x7fffffffLL) return fail(MECLIP_EINVAL, "dual contraction: bad extents");
+    const int bn = 256;
+    CUtensorMap tay, tby, tax, tbx;
+    int rc = make_tmap_blocked(&tay, panel, rows, (cols + 63) / 64, panel_rows_alloc, BK, panel_chunks_alloc);   // G^T: K = rows
+    if (rc) return rc;
+    rc = make_tmap_blocked(&tax, panel, rows, (cols + 63) / 64, panel_rows_alloc, BM, panel_chunks_alloc);        // G: M = rows
+    if (rc) return rc;
+    rc = make_tmap(&tby, xt, rows, n, ld_xt, BK, bn / 2);     // X^T [n][K = rows]
+    if (rc) return rc;
+    rc = make_tmap(&tbx, yt, cols, n, ld_yt, BK, bn / 2);     // Y^T [n][K = cols]
+    if (rc) return rc;
+    GemmParams p = py;
+    p.a_blocked = 1;
+    p.m = (int)cols; p.n = (int)n; p.k = (int)rows; p.bn = bn;
+    p.num_m_tiles = (int)((cols + PAIR_BM - 1) / PAIR_BM);
+    p.num_n_tiles = (int)((n + bn - 1) / bn);
+    p.k_steps = (int)((rows + BK - 1) / BK);
+    p.m2 = (int)rows;
+    p.num_m_tiles2 = (int)((rows + PAIR_BM - 1) / PAIR_BM);
+    p.k_steps2 = (int)((cols + BK - 1) / BK);
+    p.out2 = px.out; p.ld_out2 = px.ld_out; p.out_bf16_2 = px.out_bf16; p.acc_in2 = px.acc_in; p.ld_acc2 = px.ld_acc;
+    p.dual = 1;
+    p.tiles0 = p.num_m_tiles * p.num_n_tiles;
+    if ((long long)p.tiles0 + (long long)p.num_m_tiles2 * p.num_n_tiles > 0x7fffffffLL) return fail(MECLIP_EINVAL, "too many tiles");
+    p.trace = nullptr; p.trace_capacity = 0;
+    p.wait_limit_ns = wait_limit_ns();
+    p.group_m = 2;
+    static const int env_group_m = []() { const char* v = std::getenv("MECLIP_GROUP_M"); return v ? std::atoi(v) : 0; }();
+    if (env_group_m > 0) p.group_m = env_group_m;
+    p.strip_len = 1;
+    const long long rest = n - (long long)(p.num_n_tiles - 1) * bn;
+    p.bn_last = (int)((rest + 31) / 32 * 32);
+    p.idesc = umma_idesc_bf16(PAIR_BM, bn, 1, 0);
+    p.idesc_last = umma_idesc_bf16(PAIR_BM, p.bn_last, 1, 0);
+    p.idesc_p2 = umma_idesc_bf16(PAIR_BM, bn, 0, 0);
+    p.idesc_last_p2 = umma_idesc_bf16(PAIR_BM, p.bn_last, 0, 0);
+    p.wide = 0; p.idesc2 = 0; p.idesc2_last = 0; p.narrow_last = 0;
+    static const bool env_static = []() { const char* v = std::getenv("MECLIP_STATIC_SCHED"); return v && v[0] == '1'; }();
+    if (env_static) p.tile_counter = nullptr;
+    p.stage_bytes = A_STAGE_BYTES + (bn / 2) * BK * 2;
+    int stages = (SMEM_LIMIT - 1024 - tail_bytes(EPI_OUT)) / p.stage_bytes;
+    if (stages > MAX_STAGES) stages = MAX_STAGES;
+    static const int env_max_stages = []() { const char* v = std::getenv("MECLIP_MAX_STAGES"); return v ? std::atoi(v) : 0; }();
+    if (env_max_stages >= 2 && stages > env_max_stages) stages = env_max_stages;
+    p.num_stages = stages;
+    const size_t smem = 1024 + (size_t)stages * p.stage_bytes + tail_bytes(EPI_OUT);
+    return launch_pair_t<EPI_OUT, 2>(tay, tby, tax, p, smem, stream, &tbx, 4.0 * (double)rows * (double)cols * (double)n);
 }
 
 // ------------------------------------------------------------------------------------
@@ -1402,6 +1467,11 @@ static int grad_impl(int kind, const void* x_bf16, const void* y_bf16, int64_t r
         sx = side->sx;
         sy = side->sy;
     }
+    // both contractions of a block in one launch: needs both outputs, K-major B operands (the transposed copies)
+    // and the 256-column CTA-pair tiles
+    const bool use_dual = want_dx && want_dy && transposed_copies && dual_allowed() && pair_mode() != 0 && !wide_allowed() &&
+                          dn == d && d >= 256 && g_trace_buf == nullptr;
+    if (use_dual) sy = sx;      // one side stream carries the transposes and the contractions
     // the tile counters are the only part of the workspace that has to start at zero
     MECLIP_CUDA(cudaMemsetAsync(counters, 0, plan.counter_bytes, s0));
     if (transposed_copies) {
@@ -1473,9 +1543,10 @@ static int grad_impl(int kind, const void* x_bf16, const void* y_bf16, int64_t r
             }
             // (3) dY[c0:] (+)= G^T X[r0:]        M = nc, N = d, K = nr; A = G^T (M contiguous), B = X (N contiguous)
             //     issued before dX: its tiles are the long ones (K = nr)
+            GemmParams py;
+            std::memset(&py, 0, sizeof(py));
             if (want_dy) {
-                GemmParams p;
-                std::memset(&p, 0, sizeof(p));
+                GemmParams& p = py;
                 p.status = status;
                 p.tile_counter = counters + 3 * t + 2;
                 uint8_t* user = reinterpret_cast<uint8_t*>(dy) + (size_t)c0 * lddy * dy_elt;
@@ -1490,12 +1561,14 @@ static int grad_impl(int kind, const void* x_bf16, const void* y_bf16, int64_t r
                     if (rb == plan.n_row_blocks - 1) { p.out = user; p.ld_out = lddy; p.out_bf16 = (dy_mode == MECLIP_STORE_BF16); }
                     else { p.out = scratch; p.ld_out = d; p.out_bf16 = 0; }
                 }
-                Operand a{gpanel[gb], plan.ldg / 64, true, plan.row_block}, b{X + r0 * ldx, ldx, true};
-                if (transposed_copies) b = Operand{xt + r0, plan.ld_xt, false};   // [d][K = rows] K-major
-                t_tag = TAG_DY;
-                rc = launch_gemm(EPI_OUT, a, b, nc, d, nr, pick_contraction_bn(nc, d, overlap, transposed_copies), p, sy);
-                if (rc) return rc;
-                if (overlap) MECLIP_CUDA(cudaEventRecord(side->dy[gb], sy));
+                if (!use_dual) {
+                    Operand a{gpanel[gb], plan.ldg / 64, true, plan.row_block}, b{X + r0 * ldx, ldx, true};
+                    if (transposed_copies) b = Operand{xt + r0, plan.ld_xt, false};   // [d][K = rows] K-major
+                    t_tag = TAG_DY;
+                    rc = launch_gemm(EPI_OUT, a, b, nc, d, nr, pick_contraction_bn(nc, d, overlap, transposed_copies), p, sy);
+                    if (rc) return rc;
+                    if (overlap) MECLIP_CUDA(cudaEventRecord(side->dy[gb], sy));
+                }
             }
             // (2) dX[r0:] (+)= G Y[c0:]          M = nr, N = d, K = nc; A = G (K contiguous), B = Y (N contiguous)
             if (want_dx) {
@@ -1514,12 +1587,23 @@ static int grad_impl(int kind, const void* x_bf16, const void* y_bf16, int64_t r
                     if (cp == plan.n_panels - 1) { p.out = user; p.ld_out = lddx; p.out_bf16 = (dx_mode == MECLIP_STORE_BF16); }
                     else { p.out = dx_scratch; p.ld_out = dn; p.out_bf16 = 0; }
                 }
-                Operand a{gpanel[gb], plan.ldg / 64, false, plan.row_block}, b{Y + c0 * ldy, ldy, true};
-                if (transposed_copies) b = Operand{yt + c0, plan.ld_yt, false};   // [d][K = cols] K-major
-                t_tag = TAG_DX;
-                rc = launch_gemm(EPI_OUT, a, b, nr, dn, nc, pick_contraction_bn(nr, dn, overlap, transposed_copies), p, sx);
-                if (rc) return rc;
-                if (overlap) MECLIP_CUDA(cudaEventRecord(side->dx[gb], sx));
+                if (use_dual) {
+                    t_tag = TAG_DX;         // one launch: its time and FLOPs are booked under the dX tag
+                    rc = launch_contractions_dual(gpanel[gb], plan.row_block, plan.ldg / 64, xt + r0, plan.ld_xt, yt + c0,
+                                                  plan.ld_yt, nr, nc, d, py, p, sx);
+                    if (rc) return rc;
+                    if (overlap) {
+                        MECLIP_CUDA(cudaEventRecord(side->dx[gb], sx));
+                        MECLIP_CUDA(cudaEventRecord(side->dy[gb], sx));
+                    }
+                } else {
+                    Operand a{gpanel[gb], plan.ldg / 64, false, plan.row_block}, b{Y + c0 * ldy, ldy, true};
+                    if (transposed_copies) b = Operand{yt + c0, plan.ld_yt, false};   // [d][K = cols] K-major
+                    t_tag = TAG_DX;
+                    rc = launch_gemm(EPI_OUT, a, b, nr, dn, nc, pick_contraction_bn(nr, dn, overlap, transposed_copies), p, sx);
+                    if (rc) return rc;
+                    if (overlap) MECLIP_CUDA(cudaEventRecord(side->dx[gb], sx));
+                }
             }
         }
     }

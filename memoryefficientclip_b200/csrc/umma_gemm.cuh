@@ -101,6 +101,19 @@ struct GemmParams {
     int out_bf16;
     const float* acc_in;      // optional fp32 partial added before the store
     long long ld_acc;
+    // Two contractions in ONE launch (CTA-pair kernel, EPI_OUT, A_MODE = 2): tile ids below tiles0 belong to the first
+    // problem (the fields above; its A is read MN-major: dY = G^T X), the others to the second one (dX = G Y, A read
+    // K-major).  Both share n, bn and the tile width of the last column tile; rows, K, outputs and the instruction
+    // descriptors (they carry A's majorness) are per problem.  One launch of 640 tiles ends in a fuller last wave
+    // than two launches of 320 (74 CTA pairs).
+    int dual, tiles0;
+    int m2, k_steps2, num_m_tiles2;
+    uint32_t idesc_p2, idesc_last_p2;
+    void* out2;
+    long long ld_out2;
+    int out_bf16_2;
+    const float* acc_in2;
+    long long ld_acc2;
     int* status;
     unsigned long long wait_limit_ns;   // bound of every barrier wait inside the kernel
     // Scalars that live on the device (a learnable temperature / logit scale / bias): when t_dev is set the
@@ -179,19 +192,40 @@ __device__ __forceinline__ float warp_transpose_reduce32(float (&v)[32], int lan
     return v[0];
 }
 
-__device__ __forceinline__ void tile_coords(const GemmParams& p, int tile, int& mt, int& nt) {
+// What the plain-contraction epilogue needs to know about the problem a tile belongs to.
+struct OutDesc {
+    int m;                    // valid rows
+    void* out;
+    long long ld_out;
+    int out_bf16;
+    const float* acc_in;
+    long long ld_acc;
+};
+
+// Problem of a tile id in a dual launch (0 or 1); the id is made relative to its problem.
+__device__ __forceinline__ int tile_problem(const GemmParams& p, int& tile) {
+    if (p.dual && tile >= p.tiles0) { tile -= p.tiles0; return 1; }
+    return 0;
+}
+__device__ __forceinline__ OutDesc out_desc(const GemmParams& p, int problem) {
+    if (problem == 0) return OutDesc{p.m, p.out, p.ld_out, p.out_bf16, p.acc_in, p.ld_acc};
+    return OutDesc{p.m2, p.out2, p.ld_out2, p.out_bf16_2, p.acc_in2, p.ld_acc2};
+}
+
+__device__ __forceinline__ void tile_coords(const GemmParams& p, int tile, int& mt, int& nt, int problem = 0) {
+    const int num_m_tiles = problem == 0 ? p.num_m_tiles : p.num_m_tiles2;
     int n_tiles = p.num_n_tiles;
     if (p.narrow_last) {
         // ids [0, m_tiles * (n_tiles - 1)) walk the full-width column tiles in groups as below,
         // the remaining m_tiles ids are the narrow last column tile of every row tile
         n_tiles = p.num_n_tiles - 1;
-        const int full = p.num_m_tiles * n_tiles;
+        const int full = num_m_tiles * n_tiles;
         if (tile >= full) { mt = tile - full; nt = n_tiles; return; }
     }
     const int per_group = p.group_m * n_tiles;
     const int grp = tile / per_group;
     const int first_m = grp * p.group_m;
-    const int rows_in_group = min(p.group_m, p.num_m_tiles - first_m);
+    const int rows_in_group = min(p.group_m, num_m_tiles - first_m);
     const int local = tile - grp * per_group;
     mt = first_m + local % rows_in_group;
     nt = local / rows_in_group;
@@ -407,8 +441,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)acc * MAX_BN;
             const uint32_t free_bar = smem_u32(&tail->tmem_empty_bar[acc]);
             if (threadIdx.x == 64) trace_event(p, 2, ntrace, TR_EPI_BEGIN, tile);
-            epilogue_tile<EPI>(p, &tmap_c, tail, st, taddr, mt * BM, nt * p.bn, (nt == p.num_n_tiles - 1) ? p.bn_last : p.bn,
-                               warp, lane,
+            epilogue_tile<EPI>(p, out_desc(p, 0), &tmap_c, tail, st, taddr, mt * BM, nt * p.bn,
+                               (nt == p.num_n_tiles - 1) ? p.bn_last : p.bn, warp, lane,
                                [free_bar, &p, &ntrace, tile]() {
                                    mbar_arrive(free_bar);
                                    if (threadIdx.x == 64) trace_event(p, 2, ntrace, TR_EPI_RELEASED, tile);

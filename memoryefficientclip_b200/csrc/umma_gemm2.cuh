@@ -18,16 +18,22 @@
 // consumers of both CTAs have arrived on the leader's `sched_empty` barrier (one arrive per warp).
 // The last column tile of an output kernel may be narrower (bn_last), as in the single-CTA kernel.
 #pragma once
+#include <type_traits>
+
 #include "umma_gemm.cuh"
 
 namespace meclip {
 
 static constexpr int PAIR_BM = 256;
 
-template <int EPI, bool A_MN>
+// A_MODE: 0 = A is K-major, 1 = A is MN-major, 2 = two contractions in one launch (GemmParams::dual): the first
+// problem reads A MN-major through tmap_a / tmap_b, the second one K-major through tmap_c (its A) / tmap_d (its B).
+template <int EPI, int A_MODE>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
 umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                      const __grid_constant__ CUtensorMap tmap_c, const __grid_constant__ GemmParams p) {
+                      const __grid_constant__ CUtensorMap tmap_c, const __grid_constant__ CUtensorMap tmap_d,
+                      const __grid_constant__ GemmParams p) {
+    constexpr bool DUAL = A_MODE == 2;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw_addr = smem_u32(smem_raw);
     const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
@@ -40,7 +46,7 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const uint32_t rank = cluster_ctarank();          // 0 = leader of the pair
-    const int num_tiles = p.num_m_tiles * p.num_n_tiles;
+    const int num_tiles = DUAL ? p.tiles0 + p.num_m_tiles2 * p.num_n_tiles : p.num_m_tiles * p.num_n_tiles;
     const int num_clusters = (int)(gridDim.x >> 1);
     const int cluster_id = blockIdx.x >> 1;
     const int num_stages = p.num_stages;
@@ -66,7 +72,8 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
         fence_barrier_init();
         tma_prefetch_desc(&tmap_a);
         tma_prefetch_desc(&tmap_b);
-        if (EPI == EPI_COEF) tma_prefetch_desc(&tmap_c);
+        if (EPI == EPI_COEF || DUAL) tma_prefetch_desc(&tmap_c);
+        if (DUAL) tma_prefetch_desc(&tmap_d);
     }
     if (warp == 1) {
         tmem_alloc_pair(smem_u32(&tail->tmem_base), TMEM_COLS);
@@ -109,12 +116,17 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
                 }
                 if (++slot == SCHED_DEPTH) { slot = 0; sphase ^= 1u; }
                 if (tile < 0) break;
-                int mt, nt;
-                tile_coords(p, tile, mt, nt);
+                int mt, nt, t_rel = tile;
+                const int prob = DUAL ? tile_problem(p, t_rel) : 0;
+                tile_coords(p, t_rel, mt, nt, prob);
+                const bool a_mn = DUAL ? prob == 0 : A_MODE == 1;
+                const CUtensorMap* ta = (DUAL && prob == 1) ? &tmap_c : &tmap_a;
+                const CUtensorMap* tb = (DUAL && prob == 1) ? &tmap_d : &tmap_b;
+                const int k_steps = (DUAL && prob == 1) ? p.k_steps2 : p.k_steps;
                 const int tile_bn = (nt == p.num_n_tiles - 1) ? p.bn_last : p.bn;
                 const int m0 = mt * PAIR_BM + (int)rank * BM;              // this CTA's rows
                 const int n0 = nt * p.bn + (int)rank * (tile_bn >> 1);      // this CTA's share of the B rows
-                for (int ks = 0; ks < p.k_steps; ++ks) {
+                for (int ks = 0; ks < k_steps; ++ks) {
                     if (!mbar_wait(smem_u32(&tail->empty_bar[stage]), phase ^ 1u, abort_flag, true, wl)) { ok = false; break; }
                     const uint32_t full_local = smem_u32(&tail->full_bar[stage]);
                     const uint32_t full = mapa_u32(full_local, 0);    // the leader's barrier counts both CTAs' bytes
@@ -123,20 +135,20 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
                     const uint32_t sb = sa + A_STAGE_BYTES;
                     const int k0 = ks * BK;
                     if (p.a_blocked) {
-                        if (A_MN) {
-                            tma_load_3d_pair(sa, &tmap_a, full, 0, k0, m0 >> 6);
-                            tma_load_3d_pair(sa + BK * 128, &tmap_a, full, 0, k0, (m0 >> 6) + 1);
+                        if (a_mn) {
+                            tma_load_3d_pair(sa, ta, full, 0, k0, m0 >> 6);
+                            tma_load_3d_pair(sa + BK * 128, ta, full, 0, k0, (m0 >> 6) + 1);
                         } else {
-                            tma_load_3d_pair(sa, &tmap_a, full, 0, m0, ks);
+                            tma_load_3d_pair(sa, ta, full, 0, m0, ks);
                         }
-                    } else if (A_MN) {
-                        tma_load_2d_pair(sa, &tmap_a, full, m0, k0);
-                        tma_load_2d_pair(sa + BK * 128, &tmap_a, full, m0 + 64, k0);
+                    } else if (a_mn) {
+                        tma_load_2d_pair(sa, ta, full, m0, k0);
+                        tma_load_2d_pair(sa + BK * 128, ta, full, m0 + 64, k0);
                     } else {
-                        tma_load_2d_pair(sa, &tmap_a, full, k0, m0);
+                        tma_load_2d_pair(sa, ta, full, k0, m0);
                     }
                     // the box always has half_bn rows; a narrower last tile uses the first tile_bn / 2 of them
-                    tma_load_2d_pair(sb, &tmap_b, full, k0, n0);
+                    tma_load_2d_pair(sb, tb, full, k0, n0);
                     if (++stage == num_stages) { stage = 0; phase ^= 1u; }
                 }
                 if (rank == 0) {
@@ -159,7 +171,6 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
             int acc = 0;
             uint32_t acc_phase = 0;
             bool ok = true;
-            constexpr uint32_t A_LBO = A_MN ? BK * 128 : 16, A_KSTEP = A_MN ? 2048 : 32;
             while (ok) {
                 if (!mbar_wait(smem_u32(&tail->sched_full_bar[slot]), sphase, abort_flag, true, wl)) break;
                 const int tile = tail->sched_tile[slot];
@@ -168,33 +179,47 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
                 if (tile < 0) break;
                 if (!mbar_wait_cluster(smem_u32(&tail->tmem_empty_bar[acc]), acc_phase ^ 1u, abort_flag, true, wl)) break;
                 tc_fence_after();
-                int mt_, nt_;
-                tile_coords(p, tile, mt_, nt_);
+                int mt_, nt_, t_rel = tile;
+                const int prob = DUAL ? tile_problem(p, t_rel) : 0;
+                tile_coords(p, t_rel, mt_, nt_, prob);
+                const bool a_mn = DUAL ? prob == 0 : A_MODE == 1;
+                const int k_steps = (DUAL && prob == 1) ? p.k_steps2 : p.k_steps;
                 const bool last_nt = nt_ == p.num_n_tiles - 1;
-                const uint32_t idesc = last_nt ? p.idesc_last : p.idesc;
+                const uint32_t idesc = (DUAL && prob == 1) ? (last_nt ? p.idesc_last_p2 : p.idesc_p2)
+                                                           : (last_nt ? p.idesc_last : p.idesc);
                 const uint32_t idesc2 = last_nt ? p.idesc2_last : p.idesc2;       // second MMA of a wide tile
                 const int tile_bn_ = last_nt ? p.bn_last : p.bn;
                 // rows of this CTA's B half that the first MMA consumes; the second one starts behind them
                 const uint32_t b2_off = (uint32_t)(min(tile_bn_, MAX_BN) >> 1) * 128u;
                 const uint32_t tmem_d = tmem_base + (uint32_t)acc * MAX_BN;
-                for (int ks = 0; ks < p.k_steps; ++ks) {
-                    if (!mbar_wait(smem_u32(&tail->full_bar[stage]), phase, abort_flag, true, wl)) { ok = false; break; }
-                    tc_fence_after();
-                    const uint32_t sa = smem_base + (uint32_t)stage * (uint32_t)p.stage_bytes;
-                    const uint32_t sb = sa + A_STAGE_BYTES;
+                // The K loop with A's majorness as a compile-time constant: the issuing thread's instruction stream
+                // per K step decides how well the tensor pipe is fed, so the dual launch gets one copy of the loop per
+                // majorness instead of run-time descriptor strides.
+                auto k_loop = [&](auto amn_tag) -> bool {
+                    constexpr bool AMN = decltype(amn_tag)::value;
+                    constexpr uint32_t A_LBO = AMN ? BK * 128 : 16, A_KSTEP = AMN ? 2048 : 32;
+                    for (int ks = 0; ks < k_steps; ++ks) {
+                        if (!mbar_wait(smem_u32(&tail->full_bar[stage]), phase, abort_flag, true, wl)) return false;
+                        tc_fence_after();
+                        const uint32_t sa = smem_base + (uint32_t)stage * (uint32_t)p.stage_bytes;
+                        const uint32_t sb = sa + A_STAGE_BYTES;
 #pragma unroll
-                    for (int kk = 0; kk < BK / 16; ++kk) {
-                        const uint64_t ad = umma_smem_desc(sa + kk * A_KSTEP, A_LBO, 1024);
-                        const uint64_t bd = umma_smem_desc(sb + kk * 32, 16, 1024);
-                        umma_bf16_pair(tmem_d, ad, bd, idesc, (ks | kk) != 0 ? 1u : 0u);
-                        if (idesc2 != 0u) {
-                            const uint64_t bd2 = umma_smem_desc(sb + b2_off + kk * 32, 16, 1024);
-                            umma_bf16_pair(tmem_d + MAX_BN, ad, bd2, idesc2, (ks | kk) != 0 ? 1u : 0u);
+                        for (int kk = 0; kk < BK / 16; ++kk) {
+                            const uint64_t ad = umma_smem_desc(sa + kk * A_KSTEP, A_LBO, 1024);
+                            const uint64_t bd = umma_smem_desc(sb + kk * 32, 16, 1024);
+                            umma_bf16_pair(tmem_d, ad, bd, idesc, (ks | kk) != 0 ? 1u : 0u);
+                            if (idesc2 != 0u) {
+                                const uint64_t bd2 = umma_smem_desc(sb + b2_off + kk * 32, 16, 1024);
+                                umma_bf16_pair(tmem_d + MAX_BN, ad, bd2, idesc2, (ks | kk) != 0 ? 1u : 0u);
+                            }
                         }
+                        umma_commit_pair(smem_u32(&tail->empty_bar[stage]), 3);     // frees the stage in both CTAs
+                        if (++stage == num_stages) { stage = 0; phase ^= 1u; }
                     }
-                    umma_commit_pair(smem_u32(&tail->empty_bar[stage]), 3);     // frees the stage in both CTAs
-                    if (++stage == num_stages) { stage = 0; phase ^= 1u; }
-                }
+                    return true;
+                };
+                if (DUAL) ok = a_mn ? k_loop(std::true_type{}) : k_loop(std::false_type{});
+                else      ok = k_loop(std::integral_constant<bool, A_MODE == 1>{});
                 if (!ok) break;
                 umma_commit_pair(smem_u32(&tail->tmem_full_bar[acc]), 3);       // accumulator halves complete
                 if (p.wide) {
@@ -223,15 +248,16 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
             if (++slot == SCHED_DEPTH) { slot = 0; sphase ^= 1u; }
             ok = named_bar_and(2, EPI_THREADS, ok);
             if (!ok || tile < 0) break;
-            int mt, nt;
-            tile_coords(p, tile, mt, nt);
+            int mt, nt, t_rel = tile;
+            const int prob = DUAL ? tile_problem(p, t_rel) : 0;
+            tile_coords(p, t_rel, mt, nt, prob);
             ok = mbar_wait(smem_u32(&tail->tmem_full_bar[acc]), acc_phase, abort_flag, false, wl);
             ok = named_bar_and(2, EPI_THREADS, ok);
             if (!ok) break;
             tc_fence_after();
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)acc * MAX_BN;
             const uint32_t free_bar = mapa_u32(smem_u32(&tail->tmem_empty_bar[acc]), 0);   // the leader's barrier
-            epilogue_tile<EPI>(p, &tmap_c, tail, st, taddr, mt * PAIR_BM + (int)rank * BM, nt * p.bn,
+            epilogue_tile<EPI>(p, out_desc(p, prob), &tmap_c, tail, st, taddr, mt * PAIR_BM + (int)rank * BM, nt * p.bn,
                                (nt == p.num_n_tiles - 1) ? p.bn_last : p.bn, warp, lane,
                                [free_bar, lane]() {
                                    __syncwarp();
