@@ -18,7 +18,27 @@ def _ptr(t):
 
 
 def _stream(t: torch.Tensor):
-    return torch.cuda.current_stream(t.device).cuda_stream
+    """Raw handle of the current stream of t's device (the C getter: no Stream object is built)."""
+    return torch._C._cuda_getCurrentRawStream(t.device.index if t.device.index is not None
+                                              else torch.cuda.current_device())
+
+
+class _on_device:
+    """`with _on_device(dev):` like torch.cuda.device, but free when dev is already the current device."""
+    __slots__ = ("guard",)
+
+    def __init__(self, device):
+        idx = device.index
+        self.guard = None if idx is None or idx == torch.cuda.current_device() else torch.cuda.device(idx)
+
+    def __enter__(self):
+        if self.guard is not None:
+            self.guard.__enter__()
+
+    def __exit__(self, *exc):
+        if self.guard is not None:
+            self.guard.__exit__(*exc)
+        return False
 
 
 def _check_matrix(t: torch.Tensor, name: str):
@@ -39,7 +59,7 @@ def new_status(device) -> torch.Tensor:
 
 def read_status(status: torch.Tensor) -> None:
     """Synchronise and raise if a kernel recorded an expired wait."""
-    with torch.cuda.device(status.device):
+    with _on_device(status.device):
         _lib.check(_lib.load().meclip_read_status(status.data_ptr(), _stream(status)))
 
 
@@ -88,9 +108,11 @@ class _DeviceStatus:
         self.host = torch.zeros(1, dtype=torch.int32).pin_memory()
         self.event = torch.cuda.Event()
         self.pending = False
+        self.posted_at = 0.0
 
 
 _status_by_device = {}
+_monotonic = __import__("time").monotonic
 _SYNC_CHECK = __import__("os").environ.get("MECLIP_CHECK_STATUS", "0") not in ("", "0")
 
 
@@ -126,16 +148,25 @@ def poll_status(device) -> None:
             _raise_timeout(st)
 
 
-def post_status(device) -> None:
-    """Queue a copy of the status word to pinned host memory on the current stream (no synchronisation)."""
+def post_status(device, force: bool = False) -> None:
+    """Queue a copy of the status word to pinned host memory on the current stream (no synchronisation).
+    At most one copy per 2 ms unless `force`."""
     st = _dev_status(device)
-    if torch.cuda.is_current_stream_capturing():
-        return
     if _SYNC_CHECK:
-        check_status(device)
+        if not torch.cuda.is_current_stream_capturing():
+            check_status(device)
         return
+    # A wait gives up after seconds, so a copy every couple of milliseconds loses nothing; steps of small batches
+    # (a fifth of a millisecond) do not pay for one each.
+    now = _monotonic()
+    if (now - st.posted_at < 0.002 and not force) or torch.cuda.is_current_stream_capturing():
+        return
+    st.posted_at = now
     st.host.copy_(st.word, non_blocking=True)
-    st.event.record(torch.cuda.current_stream(st.word.device))
+    if st.word.device.index == torch.cuda.current_device():
+        st.event.record()
+    else:
+        st.event.record(torch.cuda.current_stream(st.word.device))
     st.pending = True
 
 
@@ -163,7 +194,7 @@ def normalize_fwd(x: torch.Tensor, normalize: bool = True, extra_cols: int = 0):
     dp = padded(d)
     out = torch.empty(rows, dp + extra_cols, dtype=torch.bfloat16, device=x.device)
     inv = torch.empty(rows, dtype=torch.float32, device=x.device) if normalize else None
-    with torch.cuda.device(x.device):
+    with _on_device(x.device):
         _lib.check(_lib.load().meclip_normalize_fwd(x.data_ptr(), _DT[x.dtype], rows, d, max(x.stride(0), d),
                                                     int(normalize), out.data_ptr(), dp + extra_cols, _ptr(inv),
                                                     _stream(x)))
@@ -177,7 +208,7 @@ def normalize_bwd(g: torch.Tensor, x_hat, inv_norm, out_dtype, d: int | None = N
     d = g.shape[1] if d is None else d
     assert g.shape[1] == padded(d) and g.stride(1) == 1
     dx = torch.empty(rows, d, dtype=out_dtype, device=g.device)
-    with torch.cuda.device(g.device):
+    with _on_device(g.device):
         _lib.check(_lib.load().meclip_normalize_bwd(g.data_ptr(), _DT[g.dtype], g.stride(0), _ptr(x_hat),
                                                     x_hat.stride(0) if x_hat is not None else 0, _ptr(inv_norm),
                                                     rows, d, dx.data_ptr(), _DT[out_dtype], d, _stream(g)))
@@ -187,7 +218,7 @@ def normalize_bwd(g: torch.Tensor, x_hat, inv_norm, out_dtype, d: int | None = N
 def accumulate_f32(dst: torch.Tensor, src: torch.Tensor) -> None:
     """dst += src (fp32, contiguous, same shape) on the current stream."""
     assert dst.dtype == torch.float32 and src.dtype == torch.float32 and dst.numel() == src.numel()
-    with torch.cuda.device(dst.device):
+    with _on_device(dst.device):
         _lib.check(_lib.load().meclip_accumulate_f32(dst.data_ptr(), src.data_ptr(), dst.numel(), _stream(dst)))
 
 
@@ -195,7 +226,7 @@ def accumulate_many_f32(dst: torch.Tensor, srcs: torch.Tensor) -> None:
     """dst += srcs[0] + srcs[1] + ... in that order; srcs is one contiguous fp32 tensor [n_src, *dst.shape]."""
     assert dst.dtype == torch.float32 and srcs.dtype == torch.float32 and srcs.is_contiguous() and dst.is_contiguous()
     assert srcs.shape[1:] == dst.shape
-    with torch.cuda.device(dst.device):
+    with _on_device(dst.device):
         _lib.check(_lib.load().meclip_accumulate_many_f32(dst.data_ptr(), srcs.data_ptr(), srcs.shape[0], dst.numel(),
                                                           dst.numel(), _stream(dst)))
 
@@ -228,14 +259,14 @@ def sum_exp(kind, x_hat, y_hat, temperature, row_sum, col_sum, diag_s, row_off=0
     if DETERMINISTIC if deterministic is None else deterministic:
         lib = _lib.load()
         ws = torch.empty(lib.meclip_sum_exp_det_workspace_bytes(rows, cols), dtype=torch.uint8, device=x_hat.device)
-        with torch.cuda.device(x_hat.device):
+        with _on_device(x_hat.device):
             t, _b, _keep = _bind(temperature, x_hat.device)
             _lib.check(lib.meclip_sum_exp_det(kind, x_hat.data_ptr(), y_hat.data_ptr(), rows, cols, d, x_hat.stride(0),
                                               y_hat.stride(0), t, row_off, col_off, row_sum.data_ptr(), _ptr(col_sum),
                                               diag_s.data_ptr(), counter.data_ptr(), ws.data_ptr(), ws.numel(),
                                               _ptr(status), _stream(x_hat)))
         return
-    with torch.cuda.device(x_hat.device):
+    with _on_device(x_hat.device):
         t, _b, _keep = _bind(temperature, x_hat.device)
         _lib.check(_lib.load().meclip_sum_exp(kind, x_hat.data_ptr(), y_hat.data_ptr(), rows, cols, d, x_hat.stride(0),
                                               y_hat.stride(0), t, row_off, col_off, row_sum.data_ptr(),
@@ -244,7 +275,7 @@ def sum_exp(kind, x_hat, y_hat, temperature, row_sum, col_sum, diag_s, row_off=0
 
 
 def loss_finalize(kind, row_sum, col_sum, diag_s, temperature, scale, loss_out, accumulate=False):
-    with torch.cuda.device(row_sum.device):
+    with _on_device(row_sum.device):
         t, _b, _keep = _bind(temperature, row_sum.device)
         _lib.check(_lib.load().meclip_loss_finalize(kind, row_sum.data_ptr(), _ptr(col_sum), diag_s.data_ptr(),
                                                     row_sum.numel(), t, float(scale), int(accumulate),
@@ -269,7 +300,7 @@ def loss_forward(kind, x_hat, y_hat, temperature, status=None, deterministic=Non
     diag_s = torch.empty(b, dtype=torch.float32, device=dev)
     loss = torch.empty((), dtype=torch.float32, device=dev)
     counter = torch.empty(1, dtype=torch.int32, device=dev)              # cleared by the call
-    with torch.cuda.device(dev):
+    with _on_device(dev):
         t, _b, _keep = _bind(temperature, dev)
         _lib.check(_lib.load().meclip_loss_forward(kind, x_hat.data_ptr(), y_hat.data_ptr(), b, d, x_hat.stride(0),
                                                    y_hat.stride(0), t, row_sum.data_ptr(),
@@ -296,7 +327,7 @@ def grad_block(kind, x_hat, y_hat, temperature, row_sum, col_sum, grad_out, grad
     cols = y_hat.shape[0]
     if workspace is None:
         workspace = grad_workspace(rows, cols, d, x_hat.device)
-    with torch.cuda.device(x_hat.device):
+    with _on_device(x_hat.device):
         t, _b, _keep = _bind(temperature, x_hat.device, scale_rule)
         head = (kind, x_hat.data_ptr(), y_hat.data_ptr(), rows, cols, d, x_hat.stride(0), y_hat.stride(0), t,
                 row_off, col_off, row_sum.data_ptr(), _ptr(col_sum), _ptr(grad_out), float(grad_scale), dx.data_ptr(), dx_mode,
@@ -315,7 +346,7 @@ def grad_block_static(kind, x_hat, y_hat, temperature, row_sum, col_sum, grad_ou
     the scratch, so keep them on one stream."""
     rows, d = x_hat.shape
     cols = y_hat.shape[0]
-    with torch.cuda.device(x_hat.device):
+    with _on_device(x_hat.device):
         _lib.check(_lib.load().meclip_grad_static(kind, x_hat.data_ptr(), y_hat.data_ptr(), rows, cols, d,
                                                   x_hat.stride(0), y_hat.stride(0), float(temperature), row_off,
                                                   col_off, row_sum.data_ptr(), _ptr(col_sum), _ptr(grad_out),
@@ -338,7 +369,7 @@ def loss_backward(kind, x_hat, y_hat, temperature, row_sum, col_sum, grad_out, g
     dy = torch.empty(b, d, dtype=dy_dtype, device=dev) if need_dy else None
     ws = grad_workspace(b, b, d, dev)
     if sum_g_s is not None:
-        with torch.cuda.device(dev):
+        with _on_device(dev):
             t, _b, _keep = _bind(temperature, dev, scale_rule)
             _lib.check(_lib.load().meclip_grad_t(kind, x_hat.data_ptr(), y_hat.data_ptr(), b, b, d, x_hat.stride(0),
                                                  y_hat.stride(0), t, 0, 0, row_sum.data_ptr(),
@@ -347,7 +378,7 @@ def loss_backward(kind, x_hat, y_hat, temperature, row_sum, col_sum, grad_out, g
                                                  _MODE[dy_dtype] if dy is not None else 0, d, sum_g_s.data_ptr(),
                                                  ws.data_ptr(), ws.numel(), _ptr(status), _stream(x_hat)))
         return dx, dy
-    with torch.cuda.device(dev):
+    with _on_device(dev):
         t, _b, _keep = _bind(temperature, dev, scale_rule)
         _lib.check(_lib.load().meclip_loss_backward(kind, x_hat.data_ptr(), y_hat.data_ptr(), b, d, x_hat.stride(0),
                                                     y_hat.stride(0), t, row_sum.data_ptr(),
@@ -363,7 +394,7 @@ def siglip_sum(x_hat, y_hat, logit_scale, logit_bias, row_sum, diag_s, row_off=0
     rows, d = x_hat.shape
     cols = y_hat.shape[0]
     counter = torch.zeros(1, dtype=torch.int32, device=x_hat.device)
-    with torch.cuda.device(x_hat.device):
+    with _on_device(x_hat.device):
         t, b, _keep = _bind(logit_scale, x_hat.device, GSCALE_FIXED, logit_bias)
         _lib.check(_lib.load().meclip_siglip_sum(x_hat.data_ptr(), y_hat.data_ptr(), rows, cols, d, x_hat.stride(0),
                                                  y_hat.stride(0), t, b, row_off, col_off,
@@ -372,7 +403,7 @@ def siglip_sum(x_hat, y_hat, logit_scale, logit_bias, row_sum, diag_s, row_off=0
 
 
 def siglip_loss_finalize(row_sum, diag_s, logit_scale, logit_bias, scale, loss_out, accumulate=False):
-    with torch.cuda.device(row_sum.device):
+    with _on_device(row_sum.device):
         _lib.check(_lib.load().meclip_siglip_loss_finalize(row_sum.data_ptr(), diag_s.data_ptr(), row_sum.numel(),
                                                            0.0, 0.0, float(scale),
                                                            int(accumulate), loss_out.data_ptr(), _stream(row_sum)))
@@ -397,7 +428,7 @@ def siglip_grad_block(x_hat, y_hat, logit_scale, logit_bias, grad_out, grad_scal
     cols = y_hat.shape[0]
     if workspace is None:
         workspace = grad_workspace(rows, cols, d, x_hat.device)
-    with torch.cuda.device(x_hat.device):
+    with _on_device(x_hat.device):
         t, b, _keep = _bind(logit_scale, x_hat.device, GSCALE_TIMES_T if is_dev(logit_scale) else GSCALE_FIXED,
                             logit_bias)
         _lib.check(_lib.load().meclip_siglip_grad(x_hat.data_ptr(), y_hat.data_ptr(), rows, cols, d, x_hat.stride(0),
@@ -420,7 +451,7 @@ def siglip_backward(x_hat, y_hat, logit_scale, logit_bias, grad_out, grad_scale_
     dx = torch.empty(b, d, dtype=dx_dtype, device=dev) if need_dx else None
     dy = torch.empty(b, d, dtype=dy_dtype, device=dev) if need_dy else None
     ws = grad_workspace(b, b, d, dev)
-    with torch.cuda.device(dev):
+    with _on_device(dev):
         t, bias, _keep = _bind(logit_scale, dev, GSCALE_TIMES_T if is_dev(logit_scale) else GSCALE_FIXED, logit_bias)
         _lib.check(_lib.load().meclip_siglip_grad(x_hat.data_ptr(), y_hat.data_ptr(), b, b, d, x_hat.stride(0),
                                                   y_hat.stride(0), t, bias, 0, 0,
@@ -432,7 +463,7 @@ def siglip_backward(x_hat, y_hat, logit_scale, logit_bias, grad_out, grad_scale_
 
 def lit_extend(y_ext, d_pad):
     """Writes the ones column (and seven zeros) at column d_pad of y_ext [rows, d_pad + 8]."""
-    with torch.cuda.device(y_ext.device):
+    with _on_device(y_ext.device):
         _lib.check(_lib.load().meclip_lit_extend(y_ext.data_ptr(), y_ext.shape[0], d_pad, y_ext.stride(0), _stream(y_ext)))
 
 
@@ -441,7 +472,7 @@ def lit_fused_block(x_hat, y_ext, d_pad, temperature, u, u_mode, row_off=0, col_
     rows, cols = x_hat.shape[0], y_ext.shape[0]
     if workspace is None:
         workspace = grad_workspace(rows, cols, d_pad + 8, x_hat.device)
-    with torch.cuda.device(x_hat.device):
+    with _on_device(x_hat.device):
         t, _b, _keep = _bind(temperature, x_hat.device)
         _lib.check(_lib.load().meclip_lit_fused_forward(x_hat.data_ptr(), y_ext.data_ptr(), rows, cols, d_pad,
                                                         x_hat.stride(0), y_ext.stride(0), t, row_off,
@@ -454,7 +485,7 @@ def lit_fused_stats(x_hat, y_ext, u, d_pad):
     b = x_hat.shape[0]
     row_sum = torch.empty(b, dtype=torch.float32, device=u.device)
     diag_s = torch.empty(b, dtype=torch.float32, device=u.device)
-    with torch.cuda.device(u.device):
+    with _on_device(u.device):
         _lib.check(_lib.load().meclip_lit_fused_stats(x_hat.data_ptr(), x_hat.stride(0), y_ext.data_ptr(), y_ext.stride(0),
                                                       u.data_ptr(), u.stride(0), b, d_pad, row_sum.data_ptr(),
                                                       diag_s.data_ptr(), _stream(u)))
@@ -481,7 +512,7 @@ def lit_fused_backward(u, y_ext, row_sum, grad_out, grad_scale_, d_out, out_dtyp
     when it is a tensor (grad_scale_ is then the scale for T = 1, completed on the device by scale_rule)."""
     b = u.shape[0]
     dx = torch.empty(b, d_out, dtype=out_dtype, device=u.device)
-    with torch.cuda.device(u.device):
+    with _on_device(u.device):
         if is_dev(temperature):
             _t, _b, _keep = _bind(temperature, u.device, scale_rule)
         _lib.check(_lib.load().meclip_lit_fused_backward(u.data_ptr(), u.stride(0), y_ext.data_ptr(), y_ext.stride(0),
@@ -492,12 +523,13 @@ def lit_fused_backward(u, y_ext, row_sum, grad_out, grad_scale_, d_out, out_dtyp
 
 # ---- whole-step entry points (small batches) --------------------------------------------------------------
 _step_ws = {}
+_step_saved_bytes = {}
 
 
 def step_workspace(batch: int, d: int, device) -> torch.Tensor:
     """Backward workspace of the small-batch step path, cached per (device, stream, shape): it is scratch that
     lives only inside one library call, and calls on one stream are ordered."""
-    key = (device.index, torch.cuda.current_stream(device).cuda_stream, batch, d)
+    key = (device.index, torch._C._cuda_getCurrentRawStream(device.index), batch, d)
     need = _lib.load().meclip_step_workspace_bytes(batch, d)      # depends on the blocking (a test hook can change it)
     ws = _step_ws.get(key)
     if ws is None or ws.numel() < need:
@@ -509,9 +541,12 @@ def step_forward(kind, x, y, normalize, temperature, status=None):
     """(loss, saved): the module's forward in one library call (meclip_step_forward)."""
     b, d = x.shape
     lib = _lib.load()
-    saved = torch.empty(lib.meclip_step_saved_bytes(b, d), dtype=torch.uint8, device=x.device)
+    n_saved = _step_saved_bytes.get((b, d))
+    if n_saved is None:
+        n_saved = _step_saved_bytes[(b, d)] = lib.meclip_step_saved_bytes(b, d)
+    saved = torch.empty(n_saved, dtype=torch.uint8, device=x.device)
     loss = torch.empty((), dtype=torch.float32, device=x.device)
-    with torch.cuda.device(x.device):
+    with _on_device(x.device):
         t, _b, _keep = _bind(temperature, x.device)
         _lib.check(lib.meclip_step_forward(kind, x.data_ptr(), y.data_ptr(), _DT[x.dtype], b, d, x.stride(0), y.stride(0),
                                            int(normalize), t, saved.data_ptr(), saved.numel(), loss.data_ptr(),
@@ -526,12 +561,12 @@ def step_backward(kind, saved, batch, d, normalize, temperature, grad_out, grad_
     dx = torch.empty(batch, d, dtype=out_dtype, device=dev) if need_dx else None
     dy = torch.empty(batch, d, dtype=out_dtype, device=dev) if need_dy else None
     ws = step_workspace(batch, d, dev)
-    with torch.cuda.device(dev):
+    with _on_device(dev):
         t, _b, _keep = _bind(temperature, dev, scale_rule)
         _lib.check(_lib.load().meclip_step_backward(kind, saved.data_ptr(), saved.numel(), batch, d, int(normalize), t,
                                                     _ptr(grad_out), float(grad_scale_), _ptr(dx), _ptr(dy),
                                                     _DT[out_dtype], d, d, ws.data_ptr(), ws.numel(), _ptr(status),
-                                                    torch.cuda.current_stream(dev).cuda_stream))
+                                                    torch._C._cuda_getCurrentRawStream(dev.index)))
     return dx, dy
 
 
@@ -552,13 +587,13 @@ def grad_scale_args(batch: int, temperature, stable: bool):
 
 def debug_wait_probe(status: torch.Tensor, limit_ns: int = 1_000_000) -> None:
     """Test hook: one tiny kernel whose bounded wait is meant to run out (it sets the status word)."""
-    with torch.cuda.device(status.device):
+    with _on_device(status.device):
         _lib.check(_lib.load().meclip_debug_wait_probe(int(limit_ns), status.data_ptr(), _stream(status)))
 
 
 def debug_gemm(a, b, a_mn_major, b_mn_major, m, n, k, tile_n=0, c_in=None, status=None) -> torch.Tensor:
     c = torch.empty(m, n, dtype=torch.float32, device=a.device) if c_in is None else c_in.clone()
-    with torch.cuda.device(a.device):
+    with _on_device(a.device):
         _lib.check(_lib.load().meclip_debug_gemm(a.data_ptr(), a.stride(0), int(a_mn_major), b.data_ptr(), b.stride(0),
                                                  int(b_mn_major), m, n, k, tile_n, c.data_ptr(), c.stride(0),
                                                  _ptr(c_in) and c.data_ptr(), _ptr(status), _stream(a)))

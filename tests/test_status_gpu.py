@@ -50,7 +50,7 @@ def test_module_path_raises_on_the_next_forward():
     mod(xg, yg).backward()                        # the poll at its start sees the clear word
     # a kernel of "this step" gives up a wait: the probe sets the module path's own status word
     ops.debug_wait_probe(ops.status_word(dev), limit_ns=1_000_000)
-    ops.post_status(dev)
+    ops.post_status(dev, force=True)
     torch.cuda.synchronize()
     with pytest.raises(_lib.MeclipError) as e:
         mod(xg, yg)
