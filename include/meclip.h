@@ -392,6 +392,59 @@ int meclip_step_backward(int kind, const void* saved, size_t saved_bytes, int64_
                          int64_t lddx, int64_t lddy, void* workspace, size_t workspace_bytes, int* status, void* stream);
 
 /*
+ * The ring over peer memory for a C caller: one process per GPU of one NVLink box, rank p keeps rows
+ * [p*rows, (p+1)*rows) of both arguments.  These two calls queue the whole choreography of one rank (what
+ * memoryefficientclip_b200/ring.py does from Python): at ring step s the tile kernels work on shard
+ * (rank + s) mod nranks of the second argument while the copy engines fetch the shard of step s + 1 from its
+ * owner into one of two local receive buffers (cudaMemcpyAsync on copy_stream, ordered against the kernels on
+ * compute_stream with events; no kernel reads a peer's memory and no NCCL kernel is involved, since the
+ * persistent tile kernels hold every SM).  The reference has no counterpart (it is single-GPU); a planned
+ * signature over an NCCL communicator was dropped for that reason.
+ *
+ *   meclip_ring_desc   rank, nranks (>= 1); rows per rank; d (multiple of 8), ldx, ldy as for meclip_sum_exp;
+ *                      shards[p]: rank p's bf16 shard of the second argument (rows x ldy, contiguous), readable
+ *                      from this device: the own one local, the others mapped with meclip_ipc_open;
+ *                      recv[0..1]: two local buffers of rows*ldy bf16 (recv[0] may be NULL when nranks <= 2,
+ *                      both when nranks == 1); compute_stream, copy_stream: two different streams.
+ *   meclip_ring_sum_exp  the forward sums.  Clears and fills row_sum [rows] (complete: all columns), diag_s
+ *                      [rows] and, for MECLIP_CLIP, col_part [nranks*rows]: this rank's partial column sums of
+ *                      every shard, to be reduce-scattered by the caller (sum over ranks of col_part[p*rows..] =
+ *                      rank p's column sums).  tile_counters: nranks device words (cleared by the call).
+ *                      Then meclip_loss_finalize(kind, row_sum, col_sum, diag_s, rows, T, 1/(rows*nranks), ...)
+ *                      gives this rank's share of the global loss (sum the shares over the ranks).
+ *   meclip_ring_grad   the backward.  col_sum_all [nranks*rows]: all column sums (all-gathered by the caller;
+ *                      NULL for MECLIP_LIT).  dx_acc [rows x lddx] fp32: cleared, then the complete gradient of
+ *                      the first argument's rows.  MECLIP_CLIP only: dy_own [rows x d] fp32 contiguous receives
+ *                      the own-shard part of the second argument's gradient; the part computed at step s >= 1
+ *                      belongs to rank (rank+s) mod nranks and is copied (copy engines) to
+ *                      inbox[that rank] + (s-1)*rows*d floats, from part[s & 1] (two local fp32 buffers of
+ *                      rows*d).  inbox[p]: rank p's inbox of (nranks-1)*rows*d floats as seen from this device.
+ *                      When EVERY rank's copy_stream has drained (the caller's barrier or collective), the
+ *                      owner finishes with meclip_accumulate_many_f32(dy_own, own inbox, nranks-1, rows*d,
+ *                      rows*d, stream): partials added in ring-step order, deterministic.
+ *                      workspace: meclip_grad_workspace_bytes(rows, rows, d).
+ * Ordering between the processes is the caller's: every shard must be in place before the first copy of a
+ * call can run (make copy_stream wait for your barrier or collective), a shard or inbox may be overwritten
+ * only when all ranks' copies of the previous call have drained.  One ring call at a time per device is
+ * queued (the events are shared); a device-resident temperature is bound as for the other calls and
+ * applies to every step of the call.
+ */
+typedef struct meclip_ring_desc {
+    int rank, nranks;
+    int64_t rows, d, ldx, ldy;
+    const void* const* shards;
+    void* recv[2];
+    void* compute_stream;
+    void* copy_stream;
+} meclip_ring_desc;
+int meclip_ring_sum_exp(const meclip_ring_desc* ring, int kind, const void* x_bf16, float temperature, float* row_sum,
+                        float* col_part, float* diag_s, unsigned int* tile_counters, int* status);
+int meclip_ring_grad(const meclip_ring_desc* ring, int kind, const void* x_bf16, float temperature, const float* row_sum,
+                     const float* col_sum_all, const float* grad_out, float grad_scale, float* dx_acc, int64_t lddx,
+                     float* dy_own, float* part0, float* part1, void* const* inbox, void* workspace,
+                     size_t workspace_bytes, int* status);
+
+/*
  * Test hook: C (m x n, fp32, ldc) = A * B^T-style contraction through the same
  * tcgen05 mainloop the loss kernels use.  a_mn_major == 0: A is m x k row-major
  * (K contiguous); 1: A is stored k x m row-major (M contiguous).  Same for B

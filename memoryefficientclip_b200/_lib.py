@@ -19,6 +19,15 @@ CLIP, LIT, SIGLIP = 0, 1, 2
 BF16, F32, F16 = 0, 1, 2
 STORE_BF16, STORE_F32, ACCUM_F32 = 0, 1, 2
 
+
+
+class RingDesc(ctypes.Structure):
+    """meclip_ring_desc of include/meclip.h."""
+    _fields_ = [("rank", c_int), ("nranks", c_int), ("rows", c_int64), ("d", c_int64), ("ldx", c_int64),
+                ("ldy", c_int64), ("shards", ctypes.POINTER(c_void_p)), ("recv", c_void_p * 2),
+                ("compute_stream", c_void_p), ("copy_stream", c_void_p)]
+
+
 # name -> (restype, argtypes); mirrors include/meclip.h declaration by declaration
 SIGNATURES = {
     "meclip_version": (c_int, []),
@@ -30,6 +39,10 @@ SIGNATURES = {
     "meclip_ipc_open": (c_int, [c_void_p, c_void_p]),
     "meclip_ipc_close": (c_int, [c_void_p]),
     "meclip_copy_async": (c_int, [c_void_p, c_void_p, c_size_t, c_void_p]),
+    "meclip_ring_sum_exp": (c_int, [c_void_p, c_int, c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_void_p,
+                                    c_void_p]),
+    "meclip_ring_grad": (c_int, [c_void_p, c_int, c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_float, c_void_p,
+                                 c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p]),
     "meclip_debug_wait_probe": (c_int, [ctypes.c_uint64, c_void_p, c_void_p]),
     "meclip_debug_set_blocking": (c_int, [c_int64, c_int64]),
     "meclip_debug_set_trace": (c_int, [c_void_p, c_size_t]),

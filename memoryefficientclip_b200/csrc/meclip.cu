@@ -2043,6 +2043,166 @@ int meclip_copy_async(void* dst, const void* src, size_t bytes, void* stream) {
     return MECLIP_OK;
 }
 
+}  // extern "C"
+
+// ------------------------------------------------------------------------------------
+// the ring of one rank, queued in one call: tile kernels on the compute stream, shard
+// fetches and partial-gradient pushes on the copy stream (copy engines, peer memory)
+// ------------------------------------------------------------------------------------
+struct RingEvents {
+    bool ready = false;
+    cudaEvent_t fetched[2] = {nullptr, nullptr};     // shard of step s landed in recv[s & 1]
+    cudaEvent_t kernels[2] = {nullptr, nullptr};     // kernels of step s are done (recv[s & 1], part[s & 1] free)
+    cudaEvent_t pushed[2] = {nullptr, nullptr};      // partial of step s left part[s & 1]
+    std::mutex mutex;
+};
+static RingEvents g_ring[64];
+static std::mutex g_ring_init_mutex;
+
+static int get_ring_events(RingEvents** out) {
+    int dev = 0;
+    MECLIP_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return fail(MECLIP_EUNSUPPORTED, "device index %d out of range", dev);
+    RingEvents& re = g_ring[dev];
+    std::lock_guard<std::mutex> lock(g_ring_init_mutex);
+    if (!re.ready) {
+        cudaEvent_t* evs[6] = {&re.fetched[0], &re.fetched[1], &re.kernels[0], &re.kernels[1], &re.pushed[0], &re.pushed[1]};
+        for (auto e : evs) MECLIP_CUDA(cudaEventCreateWithFlags(e, cudaEventDisableTiming));
+        re.ready = true;
+    }
+    *out = &re;
+    return MECLIP_OK;
+}
+
+static int ring_check(const meclip_ring_desc* r, const char* who) {
+    if (r == nullptr) return fail(MECLIP_EINVAL, "%s: ring descriptor is null", who);
+    if (r->nranks < 1 || r->rank < 0 || r->rank >= r->nranks)
+        return fail(MECLIP_EINVAL, "%s: rank %d of %d", who, r->rank, r->nranks);
+    if (r->rows < 1 || r->d < 8 || r->d % 8 != 0 || r->ldx < r->d || r->ldy < r->d)
+        return fail(MECLIP_EINVAL, "%s: rows=%lld d=%lld ldx=%lld ldy=%lld", who, (long long)r->rows, (long long)r->d,
+                    (long long)r->ldx, (long long)r->ldy);
+    if (r->shards == nullptr) return fail(MECLIP_EINVAL, "%s: shards is null", who);
+    for (int p = 0; p < r->nranks; ++p)
+        if (r->shards[p] == nullptr || !aligned16(r->shards[p])) return fail(MECLIP_EINVAL, "%s: shards[%d] is null or not 16-byte aligned", who, p);
+    if (r->nranks > 1) {
+        if (r->recv[1] == nullptr || (r->nranks > 2 && r->recv[0] == nullptr)) return fail(MECLIP_EINVAL, "%s: receive buffer is null", who);
+        if (r->compute_stream == r->copy_stream) return fail(MECLIP_EINVAL, "%s: compute and copy stream must differ", who);
+    }
+    return MECLIP_OK;
+}
+
+// The operand of ring step `step`: the own shard at step 0, else the receive buffer the fetch of that step went to.
+// Queues the fetch of step + 1 first, so that it runs under this step's kernels.
+static int ring_operand(const meclip_ring_desc* r, RingEvents* re, int step, const void** y_out) {
+    cudaStream_t compute = (cudaStream_t)r->compute_stream, copy = (cudaStream_t)r->copy_stream;
+    const size_t shard_bytes = (size_t)r->rows * (size_t)r->ldy * 2;
+    if (step + 1 < r->nranks) {
+        const int slot = (step + 1) & 1;
+        if (step >= 1) MECLIP_CUDA(cudaStreamWaitEvent(copy, re->kernels[slot], 0));   // step - 1 read this buffer
+        MECLIP_CUDA(cudaMemcpyAsync(r->recv[slot], r->shards[(r->rank + step + 1) % r->nranks], shard_bytes,
+                                    cudaMemcpyDeviceToDevice, copy));
+        MECLIP_CUDA(cudaEventRecord(re->fetched[slot], copy));
+    }
+    if (step == 0) {
+        *y_out = r->shards[r->rank];
+    } else {
+        MECLIP_CUDA(cudaStreamWaitEvent(compute, re->fetched[step & 1], 0));
+        *y_out = r->recv[step & 1];
+    }
+    return MECLIP_OK;
+}
+
+extern "C" {
+
+int meclip_ring_sum_exp(const meclip_ring_desc* r, int kind, const void* x_bf16, float temperature, float* row_sum,
+                        float* col_part, float* diag_s, unsigned int* tile_counters, int* status) {
+    const DeviceScalars ds = take_scalars();
+    int rc = ring_check(r, "ring_sum_exp");
+    if (rc != MECLIP_OK) return rc;
+    if (kind != MECLIP_CLIP && kind != MECLIP_LIT) return fail(MECLIP_EINVAL, "ring_sum_exp: kind %d", kind);
+    if (x_bf16 == nullptr || row_sum == nullptr || diag_s == nullptr || tile_counters == nullptr ||
+        (kind == MECLIP_CLIP && col_part == nullptr))
+        return fail(MECLIP_EINVAL, "ring_sum_exp: null pointer");
+    RingEvents* re = nullptr;
+    rc = get_ring_events(&re);
+    if (rc != MECLIP_OK) return rc;
+    std::lock_guard<std::mutex> lock(re->mutex);
+    NvtxRange range("meclip_ring_sum_exp");
+    cudaStream_t compute = (cudaStream_t)r->compute_stream;
+    const int64_t b = r->rows;
+    MECLIP_CUDA(cudaMemsetAsync(row_sum, 0, (size_t)b * 4, compute));
+    MECLIP_CUDA(cudaMemsetAsync(diag_s, 0, (size_t)b * 4, compute));
+    MECLIP_CUDA(cudaMemsetAsync(tile_counters, 0, (size_t)r->nranks * 4, compute));
+    if (kind == MECLIP_CLIP) MECLIP_CUDA(cudaMemsetAsync(col_part, 0, (size_t)r->nranks * (size_t)b * 4, compute));
+    for (int step = 0; step < r->nranks; ++step) {
+        const int shard = (r->rank + step) % r->nranks;
+        const void* y = nullptr;
+        rc = ring_operand(r, re, step, &y);
+        if (rc != MECLIP_OK) return rc;
+        rc = sum_exp_impl(kind, x_bf16, y, b, b, r->d, r->ldx, r->ldy, temperature, (int64_t)r->rank * b, (int64_t)shard * b,
+                          row_sum, kind == MECLIP_CLIP ? col_part + (size_t)shard * b : nullptr, diag_s,
+                          tile_counters + step, status, r->compute_stream, ds);
+        if (rc != MECLIP_OK) return rc;
+        MECLIP_CUDA(cudaEventRecord(re->kernels[step & 1], compute));
+    }
+    return MECLIP_OK;
+}
+
+int meclip_ring_grad(const meclip_ring_desc* r, int kind, const void* x_bf16, float temperature, const float* row_sum,
+                     const float* col_sum_all, const float* grad_out, float grad_scale, float* dx_acc, int64_t lddx,
+                     float* dy_own, float* part0, float* part1, void* const* inbox, void* workspace,
+                     size_t workspace_bytes, int* status) {
+    const DeviceScalars ds = take_scalars();
+    int rc = ring_check(r, "ring_grad");
+    if (rc != MECLIP_OK) return rc;
+    if (kind != MECLIP_CLIP && kind != MECLIP_LIT) return fail(MECLIP_EINVAL, "ring_grad: kind %d", kind);
+    const bool want_dy = kind == MECLIP_CLIP;
+    const bool exchange = want_dy && r->nranks > 1;
+    if (x_bf16 == nullptr || row_sum == nullptr || dx_acc == nullptr || workspace == nullptr || lddx < r->d ||
+        (want_dy && (col_sum_all == nullptr || dy_own == nullptr)))
+        return fail(MECLIP_EINVAL, "ring_grad: null pointer or lddx < d");
+    if (exchange) {
+        if (part1 == nullptr || (r->nranks > 2 && part0 == nullptr) || inbox == nullptr)
+            return fail(MECLIP_EINVAL, "ring_grad: partial buffers or inbox table are null");
+        for (int p = 0; p < r->nranks; ++p)
+            if (p != r->rank && inbox[p] == nullptr) return fail(MECLIP_EINVAL, "ring_grad: inbox[%d] is null", p);
+    }
+    RingEvents* re = nullptr;
+    rc = get_ring_events(&re);
+    if (rc != MECLIP_OK) return rc;
+    std::lock_guard<std::mutex> lock(re->mutex);
+    NvtxRange range("meclip_ring_grad");
+    cudaStream_t compute = (cudaStream_t)r->compute_stream, copy = (cudaStream_t)r->copy_stream;
+    const int64_t b = r->rows;
+    const size_t slot_bytes = (size_t)b * (size_t)r->d * 4;
+    float* part[2] = {part0, part1};
+    MECLIP_CUDA(cudaMemsetAsync(dx_acc, 0, (size_t)b * (size_t)lddx * 4, compute));
+    for (int step = 0; step < r->nranks; ++step) {
+        const int shard = (r->rank + step) % r->nranks;
+        const void* y = nullptr;
+        rc = ring_operand(r, re, step, &y);
+        if (rc != MECLIP_OK) return rc;
+        float* out = nullptr;
+        if (want_dy) {
+            out = step == 0 ? dy_own : part[step & 1];
+            if (step >= 3) MECLIP_CUDA(cudaStreamWaitEvent(compute, re->pushed[step & 1], 0));   // push of step - 2
+        }
+        rc = grad_impl(kind, x_bf16, y, b, b, r->d, r->ldx, r->ldy, temperature, (int64_t)r->rank * b, (int64_t)shard * b,
+                       row_sum, want_dy ? col_sum_all + (size_t)shard * b : nullptr, grad_out, grad_scale, dx_acc,
+                       MECLIP_ACCUM_F32, lddx, out, MECLIP_STORE_F32, r->d, workspace, workspace_bytes, status, compute,
+                       overlap_allowed(), transposes_allowed(), nullptr, 0.f, 0.f, 0, false, ds);
+        if (rc != MECLIP_OK) return rc;
+        MECLIP_CUDA(cudaEventRecord(re->kernels[step & 1], compute));
+        if (exchange && step >= 1) {
+            char* dst = static_cast<char*>(inbox[shard]) + (size_t)(step - 1) * slot_bytes;
+            MECLIP_CUDA(cudaStreamWaitEvent(copy, re->kernels[step & 1], 0));
+            MECLIP_CUDA(cudaMemcpyAsync(dst, out, slot_bytes, cudaMemcpyDeviceToDevice, copy));
+            MECLIP_CUDA(cudaEventRecord(re->pushed[step & 1], copy));
+        }
+    }
+    return MECLIP_OK;
+}
+
 int meclip_debug_wait_probe(uint64_t limit_ns, int* status, void* stream) {
     if (status == nullptr) return fail(MECLIP_EINVAL, "wait_probe: status is null");
     if (limit_ns == 0 || limit_ns > 100000000ull) return fail(MECLIP_EINVAL, "wait_probe: limit must be in (0, 100 ms]");

@@ -598,3 +598,73 @@ def debug_gemm(a, b, a_mn_major, b_mn_major, m, n, k, tile_n=0, c_in=None, statu
                                                  int(b_mn_major), m, n, k, tile_n, c.data_ptr(), c.stride(0),
                                                  _ptr(c_in) and c.data_ptr(), _ptr(status), _stream(a)))
     return c
+
+
+class RingCall:
+    """One rank's view of the ring for meclip_ring_sum_exp / meclip_ring_grad (include/meclip.h): the addresses
+    of every rank's shard of the second argument as this device sees them, two local receive buffers and the
+    copy stream.  The compute stream is the current stream at call time."""
+
+    def __init__(self, rank: int, world: int, x_hat: torch.Tensor, shard_addresses, y_own: torch.Tensor, copy_stream):
+        import ctypes
+        assert len(shard_addresses) == world and x_hat.shape == y_own.shape
+        self.rank, self.world, self.x_hat, self.y_own = rank, world, x_hat, y_own
+        self.copy_stream = copy_stream
+        self.recv = [torch.empty_like(y_own) for _ in range(2)] if world > 1 else [None, None]
+        self._shards = (ctypes.c_void_p * world)(*[int(a) for a in shard_addresses])
+        self.desc = _lib.RingDesc(rank, world, x_hat.shape[0], x_hat.shape[1], x_hat.stride(0), y_own.stride(0),
+                                  ctypes.cast(self._shards, ctypes.POINTER(ctypes.c_void_p)),
+                                  (ctypes.c_void_p * 2)(_ptr(self.recv[0]), _ptr(self.recv[1])), None,
+                                  copy_stream.cuda_stream)
+
+    def _ref(self):
+        import ctypes
+        self.desc.compute_stream = _stream(self.x_hat)
+        return ctypes.byref(self.desc)
+
+
+def ring_sum_exp(call: RingCall, kind, temperature, status=None):
+    """Forward sums of one rank over the whole ring in one library call.  Returns (row_sum [b], col_part
+    [world, b] or None, diag [b]); the caller reduce-scatters col_part over the ranks."""
+    x = call.x_hat
+    b, dev = x.shape[0], x.device
+    row_sum = torch.empty(b, dtype=torch.float32, device=dev)
+    diag = torch.empty(b, dtype=torch.float32, device=dev)
+    col_part = torch.empty(call.world, b, dtype=torch.float32, device=dev) if kind == _lib.CLIP else None
+    counters = torch.empty(call.world, dtype=torch.int32, device=dev)
+    with _on_device(dev):
+        t, _b, _keep = _bind(temperature, dev)
+        _lib.check(_lib.load().meclip_ring_sum_exp(call._ref(), kind, x.data_ptr(), t, row_sum.data_ptr(),
+                                                   _ptr(col_part), diag.data_ptr(), counters.data_ptr(), _ptr(status)))
+    return row_sum, col_part, diag
+
+
+def ring_grad(call: RingCall, kind, temperature, row_sum, col_sum_all, grad_out, grad_scale, inbox_addresses,
+              status=None, scale_rule=GSCALE_FIXED):
+    """Backward of one rank over the whole ring in one library call.  Returns (dx fp32 [b, d], dy_own fp32
+    [b, d] or None); for CLIP the partial gradients of the other ranks' shards are on their way into the
+    owners' inboxes (inbox_addresses[p]: rank p's inbox as this device sees it) on the copy stream."""
+    import ctypes
+    x = call.x_hat
+    b, d = x.shape
+    dev = x.device
+    clip = kind == _lib.CLIP
+    dx = torch.empty(b, d, dtype=torch.float32, device=dev)
+    dy = torch.empty(b, d, dtype=torch.float32, device=dev) if clip else None
+    part = [torch.empty(b, d, dtype=torch.float32, device=dev) for _ in range(2)] if clip and call.world > 1 else [None, None]
+    inbox = None
+    if clip and call.world > 1:
+        inbox = (ctypes.c_void_p * call.world)(*[int(a) if a else None for a in inbox_addresses])
+    ws = grad_workspace(b, b, d, dev)
+    with _on_device(dev):
+        t, _b, _keep = _bind(temperature, dev, scale_rule)
+        _lib.check(_lib.load().meclip_ring_grad(call._ref(), kind, x.data_ptr(), t, row_sum.data_ptr(),
+                                                _ptr(col_sum_all), _ptr(grad_out), float(grad_scale), dx.data_ptr(),
+                                                dx.stride(0), _ptr(dy), _ptr(part[0]), _ptr(part[1]), inbox,
+                                                ws.data_ptr(), ws.numel(), _ptr(status)))
+    # part, ws and the receive buffers are in use on the copy / compute streams: the caching allocator must not
+    # hand them out to another stream's tensors before this work has run
+    for t_ in part:
+        if t_ is not None:
+            t_.record_stream(call.copy_stream)
+    return dx, dy

@@ -67,6 +67,25 @@ def test_bad_arguments_return_error_codes(lib):
     # so here only the argument validation is exercised
     assert lib.meclip_grad(0, fake, fake, 8, 8, 8, 8, 8, 0.07, 0, 0, fake, None, None, 1.0, fake, 0, 8, None, 0, 8,
                            fake, 0, None, None) == _lib.EINVAL
+    # ring calls: the descriptor is checked before anything touches a device
+    assert lib.meclip_ring_sum_exp(None, 0, fake, 0.07, fake, fake, fake, fake, None) == _lib.EINVAL
+    shards = (ctypes.c_void_p * 2)(0x1000, 0x2000)
+    recv = (ctypes.c_void_p * 2)(0x3000, 0x4000)
+
+    def desc(rank=0, nranks=2, d=8, compute=0x10, copy=0x20):
+        return _lib.RingDesc(rank, nranks, 8, d, 8, 8, ctypes.cast(shards, ctypes.POINTER(ctypes.c_void_p)), recv,
+                             compute, copy)
+
+    for bad in (desc(rank=2), desc(nranks=0), desc(d=12), desc(compute=0x20)):
+        assert lib.meclip_ring_sum_exp(ctypes.byref(bad), 0, fake, 0.07, fake, fake, fake, fake, None) == _lib.EINVAL
+        assert lib.meclip_ring_grad(ctypes.byref(bad), 0, fake, 0.07, fake, fake, None, 1.0, fake, 8, fake, fake, fake,
+                                    None, fake, 0, None) == _lib.EINVAL
+    shards[1] = None                                     # a peer's shard is not mapped
+    assert lib.meclip_ring_sum_exp(ctypes.byref(desc()), 0, fake, 0.07, fake, fake, fake, fake, None) == _lib.EINVAL
+    shards[1] = 0x2000
+    assert lib.meclip_ring_sum_exp(ctypes.byref(desc()), 5, fake, 0.07, fake, fake, fake, fake, None) == _lib.EINVAL
+    assert lib.meclip_ring_grad(ctypes.byref(desc()), 0, fake, 0.07, fake, fake, None, 1.0, fake, 8, fake, fake, fake,
+                                None, fake, 0, None) == _lib.EINVAL            # CLIP over 2 ranks without an inbox table
 
 
 def test_missing_library_fails_loudly(monkeypatch, tmp_path):
