@@ -44,9 +44,13 @@ class ContrastiveLossFn(torch.autograd.Function):
         learn_t = t_is_tensor and temperature.requires_grad
         status = ops.status_word(x.device)
         ops.poll_status(x.device)           # raises if a kernel of an earlier step gave up a bounded wait
+        # small batches are host-bound: the whole step in two library calls (LiT too: fewer calls beat fewer FLOPs there)
+        step_path = (not learn_t and x.shape[0] <= _STEP_PATH_ROWS and x.dtype == y.dtype and not ops.DETERMINISTIC
+                     and x.stride(1) == 1 and y.stride(1) == 1 and x.stride(0) >= x.shape[1]
+                     and y.stride(0) >= y.shape[1])
         # LiT's coefficients separate (G_ij = g E_ij / r_i - g [i == j]), so when the first input needs a gradient the
         # forward also contracts E with [Y | 1] and the backward is a row kernel: 4 B^2 D FLOPs instead of 6 B^2 D
-        if kind == _lib.LIT and _LIT_FUSED and ctx.needs_input_grad[0] and not learn_t:
+        if kind == _lib.LIT and _LIT_FUSED and ctx.needs_input_grad[0] and not learn_t and not step_path:
             x_hat, inv_x = ops.normalize_fwd(x, True) if normalize else (ops.as_operand(x), None)
             y_ext, _inv_y = ops.normalize_fwd(y, normalize, extra_cols=8)
             d_pad = x_hat.shape[1]
@@ -58,9 +62,7 @@ class ContrastiveLossFn(torch.autograd.Function):
             return loss
         ctx.meclip_fused = False
         ctx.meclip_step = False
-        if (kind == _lib.CLIP and not learn_t and x.shape[0] <= _STEP_PATH_ROWS and x.dtype == y.dtype
-                and not ops.DETERMINISTIC
-                and x.stride(1) == 1 and y.stride(1) == 1 and x.stride(0) >= x.shape[1] and y.stride(0) >= y.shape[1]):
+        if step_path:
             loss, saved = ops.step_forward(kind, x, y, normalize, temperature_value, status=status)
             ctx.save_for_backward(saved)
             ctx.meclip = (temperature_value, kind, bool(stable), bool(normalize), x.dtype, y.dtype, x.shape[1])
@@ -116,10 +118,11 @@ class ContrastiveLossFn(torch.autograd.Function):
             scale, rule = ops.grad_scale_args(batch, temperature, stable)
             need = tuple(ctx.needs_input_grad) + (False, False)
             ctx.meclip_dt = None
-            if not (need[0] or need[1]):
+            need_dy = bool(need[1]) and kind == _lib.CLIP       # LiT: the second input gets none (lit_loss.py:247)
+            if not (need[0] or need_dy):
                 return None, None
             dx, dy = ops.step_backward(kind, buf, batch, d, normalize, temperature, go, scale, rule, x_dtype,
-                                       need_dx=bool(need[0]), need_dy=bool(need[1]),
+                                       need_dx=bool(need[0]), need_dy=need_dy,
                                        status=ops.status_word(buf.device))
             ctx.meclip_dt = None
             ops.post_status(buf.device)

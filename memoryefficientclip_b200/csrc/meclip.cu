@@ -1881,6 +1881,7 @@ int meclip_step_backward(int kind, const void* saved, size_t saved_bytes, int64_
                          int64_t lddx, int64_t lddy, void* workspace, size_t workspace_bytes, int* status, void* stream) {
     const DeviceScalars ds = take_scalars();
     NvtxRange range("meclip_step_backward");
+    if (kind == MECLIP_LIT) dy = nullptr;       // the second argument of LiT gets no gradient (lit_loss.py:247)
     if (saved == nullptr || workspace == nullptr || (dx == nullptr && dy == nullptr)) return fail(MECLIP_EINVAL, "step_backward: null pointer");
     if (batch < 1 || d < 1 || (dx != nullptr && lddx < d) || (dy != nullptr && lddy < d)) return fail(MECLIP_EINVAL, "step_backward: bad shape");
     if (out_dtype != MECLIP_F32 && out_dtype != MECLIP_BF16 && out_dtype != MECLIP_F16) return fail(MECLIP_EINVAL, "step_backward: bad dtype %d", out_dtype);
@@ -1893,7 +1894,6 @@ int meclip_step_backward(int kind, const void* saved, size_t saved_bytes, int64_
     const __nv_bfloat16* yh = reinterpret_cast<const __nv_bfloat16*>(sv + l.y_hat);
     const float* row_sum = reinterpret_cast<const float*>(sv + l.row_sum);
     const float* col_sum = kind == MECLIP_CLIP ? reinterpret_cast<const float*>(sv + l.col_sum) : nullptr;
-    if (kind == MECLIP_LIT) dy = nullptr;
     uint8_t* ws = reinterpret_cast<uint8_t*>(workspace);
     const size_t g32 = round_up((size_t)batch * l.dp * 4, 256);
     float* dx32 = reinterpret_cast<float*>(ws);
