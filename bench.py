@@ -552,7 +552,7 @@ def run_ours(args):
         "step_frac_of_sustained": median_tflops * per_gpu / peaks["bf16_tflops_sustained"],
         "per_kernel": [dict(t, ms_per_step=t["ms"] / prof_steps,
                             tflops=(t["flops"] / (t["ms"] / 1e3) / 1e12 if t["ms"] > 0 else 0.0))
-                       for t in tags[:N_TENSOR_TAGS]],
+                       for t in tags[:N_TENSOR_TAGS] if t["launches"] > 0],
         # the HBM-bound passes (normalise, transposes, accumulation): algorithmic bytes / CUDA-event time against
         # the measured copy bandwidth
         "hbm_passes": [dict(t, ms_per_step=t["ms"] / prof_steps, gbs=t["bytes"] / (t["ms"] / 1e3) / 1e9,
