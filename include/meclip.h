@@ -255,6 +255,32 @@ int meclip_grad(int kind, const void* x_bf16, const void* y_bf16, int64_t rows, 
                 void* stream);
 
 /*
+ * fp32 operands multiplied as tf32 (tcgen05 kind::tf32), for callers whose inputs are fp32 and who want the
+ * similarities S = X Y^T formed the way the reference's tl.dot forms them on fp32 inputs (clip_loss.py:53, :113)
+ * instead of from bf16-rounded operands: 10 mantissa bits per operand instead of 8, at half the tensor rate and
+ * twice the operand bytes for the two passes that form S (forward sums, coefficient pass).  The two gradient
+ * contractions keep bf16 operands (G is a bf16 panel either way).
+ *   meclip_operand_f32   out[r, :] = x[r, :] * inv_norm[r] (inv_norm NULL: x itself), rounded to nearest tf32 and
+ *                        stored as fp32 with round_up(d, 8) columns, zeros in the pad: the fp32 operand next to
+ *                        the bf16 one of meclip_normalize_fwd.  The tensor cores drop the low 13 mantissa bits of
+ *                        what they read, so operands that are not pre-rounded like this are truncated.
+ *   meclip_sum_exp_tf32  meclip_sum_exp on fp32 operands (d % 8 == 0, 16-byte aligned, pitches multiples of 4)
+ *   meclip_grad_tf32     meclip_grad whose coefficient pass reads x_f32 / y_f32 (pitches ldxf / ldyf); the
+ *                        contractions read x_bf16 / y_bf16 as before.  Same workspace.
+ * Always the CTA-pair kernel (cta_group::2), 32 elements per K step.
+ */
+int meclip_operand_f32(const float* x, int64_t rows, int64_t d, int64_t ldx, const float* inv_norm, float* out,
+                       int64_t ldo, void* stream);
+int meclip_sum_exp_tf32(int kind, const float* x_f32, const float* y_f32, int64_t rows, int64_t cols, int64_t d,
+                        int64_t ldx, int64_t ldy, float temperature, int64_t row_off, int64_t col_off, float* row_sum,
+                        float* col_sum, float* diag_s, unsigned int* tile_counter, int* status, void* stream);
+int meclip_grad_tf32(int kind, const void* x_bf16, const void* y_bf16, const float* x_f32, int64_t ldxf,
+                     const float* y_f32, int64_t ldyf, int64_t rows, int64_t cols, int64_t d, int64_t ldx, int64_t ldy,
+                     float temperature, int64_t row_off, int64_t col_off, const float* row_sum, const float* col_sum,
+                     const float* grad_out, float grad_scale, void* dx, int dx_mode, int64_t lddx, void* dy, int dy_mode,
+                     int64_t lddy, void* workspace, size_t workspace_bytes, int* status, void* stream);
+
+/*
  * meclip_grad that also accumulates sum_g_s[0] += sum_ij G_ij S_ij and sum_g_s[1] += sum_ij G_ij
  * over the block (fp32 device
  * two-element array {sum G S, sum G}, zeroed by the caller, fp32 atomics).  With g = grad_scale * (*grad_out) the matrix G

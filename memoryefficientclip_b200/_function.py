@@ -45,12 +45,15 @@ class ContrastiveLossFn(torch.autograd.Function):
         status = ops.status_word(x.device)
         ops.poll_status(x.device)           # raises if a kernel of an earlier step gave up a bounded wait
         # small batches are host-bound: the whole step in two library calls (LiT too: fewer calls beat fewer FLOPs there)
-        step_path = (not learn_t and x.shape[0] <= _STEP_PATH_ROWS and x.dtype == y.dtype and not ops.DETERMINISTIC
+        # fp32 inputs, on request: S from fp32 operands with tf32 MMAs, as the reference's tl.dot (clip_loss.py:53)
+        tf32 = (ops.TF32_OPERANDS and x.dtype == torch.float32 and y.dtype == torch.float32 and not learn_t
+                and not ops.DETERMINISTIC and x.stride(1) == 1 and y.stride(1) == 1)
+        step_path = (not tf32 and not learn_t and x.shape[0] <= _STEP_PATH_ROWS and x.dtype == y.dtype and not ops.DETERMINISTIC
                      and x.stride(1) == 1 and y.stride(1) == 1 and x.stride(0) >= x.shape[1]
                      and y.stride(0) >= y.shape[1])
         # LiT's coefficients separate (G_ij = g E_ij / r_i - g [i == j]), so when the first input needs a gradient the
         # forward also contracts E with [Y | 1] and the backward is a row kernel: 4 B^2 D FLOPs instead of 6 B^2 D
-        if kind == _lib.LIT and _LIT_FUSED and ctx.needs_input_grad[0] and not learn_t and not step_path:
+        if kind == _lib.LIT and _LIT_FUSED and ctx.needs_input_grad[0] and not learn_t and not step_path and not tf32:
             x_hat, inv_x = ops.normalize_fwd(x, True) if normalize else (ops.as_operand(x), None)
             y_ext, _inv_y = ops.normalize_fwd(y, normalize, extra_cols=8)
             d_pad = x_hat.shape[1]
@@ -78,7 +81,9 @@ class ContrastiveLossFn(torch.autograd.Function):
         else:
             x_hat, inv_x = ops.as_operand(x), None
             y_hat, inv_y = ops.as_operand(y), None
-        loss, row_sum, col_sum, _diag = ops.loss_forward(kind, x_hat, y_hat, temperature_value, status=status)
+        f32_ops = (ops.operand_f32(x, inv_x), ops.operand_f32(y, inv_y)) if tf32 else None
+        loss, row_sum, col_sum, _diag = ops.loss_forward(kind, x_hat, y_hat, temperature_value, status=status,
+                                                         f32_operands=f32_ops)
         if not any(ctx.needs_input_grad[:3]):
             ops.post_status(x.device)       # no backward will follow this forward
         saved = [x_hat, y_hat, row_sum]
@@ -86,6 +91,9 @@ class ContrastiveLossFn(torch.autograd.Function):
             saved.append(col_sum)
         if normalize:
             saved += [inv_x, inv_y]
+        ctx.meclip_tf32 = tf32
+        if tf32:
+            saved += list(f32_ops)
         ctx.save_for_backward(*saved)
         ctx.meclip = (temperature_value, kind, bool(stable), bool(normalize), x.dtype, y.dtype, x.shape[1])
         ctx.meclip_t = temperature if t_is_tensor and temperature.requires_grad else None
@@ -129,6 +137,10 @@ class ContrastiveLossFn(torch.autograd.Function):
             return dx, dy
         x_hat, y_hat, row_sum = saved[:3]
         rest = saved[3:]
+        f32_ops = None
+        if getattr(ctx, "meclip_tf32", False):
+            f32_ops = (rest[-2], rest[-1])
+            rest = rest[:-2]
         col_sum = rest.pop(0) if kind == _lib.CLIP else None
         inv_x, inv_y = (rest if normalize else (None, None))
         batch = x_hat.shape[0]
@@ -150,7 +162,8 @@ class ContrastiveLossFn(torch.autograd.Function):
         if sum_g_s is not None and not (want_dx or want_dy):
             want_dx = True       # the temperature sum is produced by the coefficient pass of the backward
         dx, dy = ops.loss_backward(kind, x_hat, y_hat, temperature, row_sum, col_sum, go, scale, dx_t, dy_t,
-                                   status=status, sum_g_s=sum_g_s, need_dx=want_dx, need_dy=want_dy, scale_rule=rule)
+                                   status=status, sum_g_s=sum_g_s, need_dx=want_dx, need_dy=want_dy, scale_rule=rule,
+                                   f32_operands=f32_ops)
         ctx.meclip_dt = None
         if sum_g_s is not None:
             # sum_ij G_ij S_ij = g B dL/d(1/T) with g = go * scale, so go * dL/dT = -(sum / (scale B)) / T^2.

@@ -70,6 +70,13 @@ SIGNATURES = {
     "meclip_grad_t": (c_int, [c_int, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64, c_float, c_int64,
                               c_int64, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_int, c_int64, c_void_p,
                               c_int, c_int64, c_void_p, c_void_p, c_size_t, c_void_p, c_void_p]),
+    "meclip_operand_f32": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_int64, c_void_p]),
+    "meclip_sum_exp_tf32": (c_int, [c_int, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64, c_float,
+                                    c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "meclip_grad_tf32": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_int64, c_int64,
+                                 c_int64, c_int64, c_int64, c_float, c_int64, c_int64, c_void_p, c_void_p, c_void_p,
+                                 c_float, c_void_p, c_int, c_int64, c_void_p, c_int, c_int64, c_void_p, c_size_t,
+                                 c_void_p, c_void_p]),
     "meclip_lit_extend": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_void_p]),
     "meclip_lit_fused_forward": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64, c_float, c_int64,
                                          c_int64, c_void_p, c_int, c_int64, c_void_p, c_size_t, c_void_p, c_void_p]),

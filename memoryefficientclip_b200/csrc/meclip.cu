@@ -560,15 +560,16 @@ static EncodeTiledFn get_encode_fn() {
 
 // bf16 matrix, row-major: `outer` rows of `inner` contiguous elements, pitch ld elements.
 // Box = box_inner (64 elements = 128 bytes, swizzled) x box_outer rows.
+// f32: the elements are fp32 (box_inner then counts 4-byte elements: 32 of them are the 128 swizzled bytes).
 static int make_tmap(CUtensorMap* tm, const void* base, long long inner, long long outer, long long ld, int box_inner,
-                     int box_outer) {
+                     int box_outer, bool f32 = false) {
     EncodeTiledFn enc = get_encode_fn();
     if (enc == nullptr) return fail(MECLIP_EUNSUPPORTED, "cuTensorMapEncodeTiled not available from this driver");
     cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)outer};
-    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * (f32 ? 4 : 2)};
     cuuint32_t box[2] = {(cuuint32_t)box_inner, (cuuint32_t)box_outer};
     cuuint32_t estr[2] = {1, 1};
-    CUresult r = enc(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+    CUresult r = enc(tm, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS)
@@ -703,6 +704,8 @@ struct Operand {
     // > 0: the operand is a coefficient panel in column-blocked layout with this many allocated rows
     // per 64-column chunk (ld then holds the allocated chunk count); only for the A operand
     long long blocked_rows_alloc = 0;
+    // fp32 elements, multiplied as tf32 (K-major, sums and coefficient passes only; A and B together)
+    bool f32 = false;
 };
 
 template <int EPI, bool A_MN, bool B_MN>
@@ -719,10 +722,10 @@ static int launch_gemm_t(const CUtensorMap& ta, const CUtensorMap& tb, const CUt
     return MECLIP_OK;
 }
 
-template <int EPI, int A_MODE>
+template <int EPI, int A_MODE, bool TF32 = false>
 static int launch_pair_t(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmParams& p,
                          size_t smem_bytes, cudaStream_t stream, const CUtensorMap* td_opt = nullptr, double flops = -1.0) {
-    auto kern = umma_gemm_pair_kernel<EPI, A_MODE>;
+    auto kern = umma_gemm_pair_kernel<EPI, A_MODE, TF32>;
     const CUtensorMap& td = td_opt != nullptr ? *td_opt : tb;
     MECLIP_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_LIMIT));
     // how many CTA pairs the device can hold at once (an SM without a free neighbour cannot host one)
@@ -781,8 +784,20 @@ static int launch_gemm(int epi, const Operand& a, const Operand& b, long long m,
     if (bn < 32 || bn > 2 * MAX_BN || bn % 32 != 0 || ((b.mn_major || epi == EPI_COEF || wide) && bn % 64 != 0) ||
         (wide && (epi != EPI_OUT || b.mn_major || g_trace_buf != nullptr || pair_mode() == 0)))
         return fail(MECLIP_EINVAL, "tile width %d not supported", bn);
+    const bool f32 = a.f32;
+    if (f32) {
+        // fp32 operands read as tf32: the CTA-pair kernel with K-major A and B, 32 elements per K step
+        if (!b.f32 || a.mn_major || b.mn_major || a.blocked_rows_alloc > 0 || epi == EPI_OUT || wide || bn % 64 != 0 ||
+            g_trace_buf != nullptr)
+            return fail(MECLIP_EINVAL, "fp32 operands: sums and coefficient passes with K-major A and B only");
+        if (!aligned16(a.ptr) || !aligned16(b.ptr) || a.ld % 4 != 0 || b.ld % 4 != 0)
+            return fail(MECLIP_EINVAL, "fp32 operands must be 16-byte aligned with pitches that are multiples of 4 elements");
+    } else if (b.f32) {
+        return fail(MECLIP_EINVAL, "fp32 operands: A and B together");
+    } else
     if (!aligned16(a.ptr) || !aligned16(b.ptr) || (a.blocked_rows_alloc == 0 && a.ld % 8 != 0) || b.ld % 8 != 0)
         return fail(MECLIP_EINVAL, "operands must be 16-byte aligned with pitches that are multiples of 8 elements");
+    const int bk = f32 ? BK / 2 : BK;         // elements per K step: 128 bytes per row either way
     CUtensorMap ta, tb, tc;
     int rc;
     if (a.blocked_rows_alloc > 0) {
@@ -791,15 +806,15 @@ static int launch_gemm(int epi, const Operand& a, const Operand& b, long long m,
         else            rc = make_tmap_blocked(&ta, a.ptr, m, (k + 63) / 64, a.blocked_rows_alloc, BM, a.ld);
         p.a_blocked = 1;
     } else if (a.mn_major) rc = make_tmap(&ta, a.ptr, m, k, a.ld, 64, BK);
-    else                   rc = make_tmap(&ta, a.ptr, k, m, a.ld, BK, BM);
+    else                   rc = make_tmap(&ta, a.ptr, k, m, a.ld, bk, BM, f32);
     if (rc) return rc;
     // CTA pairs (256 x bn tiles) whenever B is K-major; the single-CTA kernel keeps MN-major B
     const int pmode = pair_mode();
     const bool pair = !b.mn_major && bn % 64 == 0 && g_trace_buf == nullptr &&      // the in-kernel trace is a single-CTA hook
-                      (wide || pmode == 1 || ((pmode == 2 || pmode < 0) && epi == EPI_OUT && bn == 256) ||
+                      (f32 || wide || pmode == 1 || ((pmode == 2 || pmode < 0) && epi == EPI_OUT && bn == 256) ||
                        (pmode < 0 && epi != EPI_OUT && bn == 256 && k >= PAIR_MIN_K));
     if (b.mn_major) rc = make_tmap(&tb, b.ptr, n, k, b.ld, 64, BK);
-    else            rc = make_tmap(&tb, b.ptr, k, n, b.ld, BK, pair ? bn / 2 : bn);
+    else            rc = make_tmap(&tb, b.ptr, k, n, b.ld, bk, pair ? bn / 2 : bn, f32);
     if (rc) return rc;
     if (epi == EPI_COEF) {
         if (panel == nullptr || !aligned16(panel) || panel_rows_alloc < m) return fail(MECLIP_EINVAL, "coefficient panel misaligned");
@@ -811,7 +826,7 @@ static int launch_gemm(int epi, const Operand& a, const Operand& b, long long m,
     p.m = (int)m; p.n = (int)n; p.k = (int)k; p.bn = bn;
     p.num_m_tiles = (int)((m + BM - 1) / BM);
     p.num_n_tiles = (int)((n + bn - 1) / bn);
-    p.k_steps = (int)((k + BK - 1) / BK);
+    p.k_steps = (int)((k + bk - 1) / bk);
     p.trace = g_trace_buf;
     p.trace_capacity = g_trace_capacity;
     p.wait_limit_ns = wait_limit_ns();
@@ -876,6 +891,11 @@ static int launch_gemm(int epi, const Operand& a, const Operand& b, long long m,
         if (env_max_stages >= 2 && stages > env_max_stages) stages = env_max_stages;
         p.num_stages = stages;
         const size_t pair_smem = 1024 + (size_t)stages * p.stage_bytes + tail_bytes(epi);
+        if (f32) {
+            p.idesc = p.idesc_last = umma_idesc_tf32(PAIR_BM, bn);
+            if (epi == EPI_SUMS) return launch_pair_t<EPI_SUMS, 0, true>(ta, tb, tc, p, pair_smem, stream);
+            return launch_pair_t<EPI_COEF, 0, true>(ta, tb, tc, p, pair_smem, stream);
+        }
         if (epi == EPI_SUMS) return launch_pair_t<EPI_SUMS, 0>(ta, tb, tc, p, pair_smem, stream);
         if (epi == EPI_COEF) return launch_pair_t<EPI_COEF, 0>(ta, tb, tc, p, pair_smem, stream);
         if (epi == EPI_OUT) return a.mn_major ? launch_pair_t<EPI_OUT, 1>(ta, tb, tc, p, pair_smem, stream)
@@ -1077,6 +1097,28 @@ static bool overlap_allowed() {
 }
 
 static int check_out_mode(int mode) { return mode == MECLIP_STORE_BF16 || mode == MECLIP_STORE_F32 || mode == MECLIP_ACCUM_F32; }
+
+// fp32 operand for the tf32 passes: out[r, c] = tf32(x[r, c] * inv[r]) (inv == nullptr: x itself), zeros in the pad
+// columns.  Rounded to nearest here (cvt.rna.tf32), because the tensor cores just drop the 13 low mantissa bits
+// of what they read: with pre-rounded operands that truncation changes nothing and the products are unbiased.
+__global__ void __launch_bounds__(ROW_KERNEL_THREADS)
+operand_f32_kernel(const float* __restrict__ x, long long ldx, long long rows, int d, int dpad,
+                   const float* __restrict__ inv, float* __restrict__ out, long long ldo) {
+    const long long row = (long long)blockIdx.x * (ROW_KERNEL_THREADS / 32) + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    const int lane = threadIdx.x & 31;
+    const float f = inv != nullptr ? inv[row] : 1.f;
+    const float* xr = x + row * ldx;
+    float* o = out + row * ldo;
+    for (int c = lane; c < dpad; c += 32) {
+        uint32_t bits = 0u;
+        if (c < d) {
+            const float v = xr[c] * f;
+            asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(bits) : "f"(v));
+        }
+        o[c] = __uint_as_float(bits);
+    }
+}
 
 }  // namespace meclip
 
@@ -1289,7 +1331,8 @@ static DetLayout det_layout(int64_t rows, int64_t cols) {
 static int sum_exp_impl(int kind, const void* x_bf16, const void* y_bf16, int64_t rows, int64_t cols, int64_t d,
                         int64_t ldx, int64_t ldy, float temperature, int64_t row_off, int64_t col_off, float* row_sum,
                         float* col_sum, float* diag_s, unsigned int* tile_counter, int* status, void* stream,
-                        const DeviceScalars& ds, void* det_ws = nullptr, size_t det_ws_bytes = 0) {
+                        const DeviceScalars& ds, void* det_ws = nullptr, size_t det_ws_bytes = 0, bool f32 = false) {
+    // f32: x and y are fp32 matrices (same shape rules), multiplied as tf32
     if (kind != MECLIP_CLIP && kind != MECLIP_LIT) return fail(MECLIP_EINVAL, "sum_exp: bad kind %d", kind);
     if (x_bf16 == nullptr || y_bf16 == nullptr || row_sum == nullptr || diag_s == nullptr)
         return fail(MECLIP_EINVAL, "sum_exp: null pointer");
@@ -1310,7 +1353,7 @@ static int sum_exp_impl(int kind, const void* x_bf16, const void* y_bf16, int64_
     p.diag = diag_s;
     p.tile_counter = tile_counter;
     p.status = status;
-    Operand a{x_bf16, ldx, false}, b{y_bf16, ldy, false};
+    Operand a{x_bf16, ldx, false, 0, f32}, b{y_bf16, ldy, false, 0, f32};
     t_tag = TAG_SUMS;
     const int bn = pick_bn(cols);
     if (det_ws == nullptr) return launch_gemm(EPI_SUMS, a, b, rows, cols, d, bn, p, (cudaStream_t)stream);
@@ -1374,6 +1417,29 @@ int meclip_sum_exp(int kind, const void* x_bf16, const void* y_bf16, int64_t row
                         diag_s, tile_counter, status, stream, ds);
 }
 
+int meclip_operand_f32(const float* x, int64_t rows, int64_t d, int64_t ldx, const float* inv_norm, float* out,
+                       int64_t ldo, void* stream) {
+    if (x == nullptr || out == nullptr) return fail(MECLIP_EINVAL, "operand_f32: null pointer");
+    const int64_t dpad = (d + 7) / 8 * 8;
+    if (rows < 1 || d < 1 || ldx < d || ldo < dpad || ldo % 4 != 0 || !aligned16(out))
+        return fail(MECLIP_EINVAL, "operand_f32: need rows, d >= 1, ldx >= d, ldo >= round_up(d, 8), out 16-byte aligned");
+    const int wpb = ROW_KERNEL_THREADS / 32;
+    ScopedTiming timing((cudaStream_t)stream, TAG_NORM_FWD, (double)rows * ((double)d * 4 + (double)dpad * 4));
+    operand_f32_kernel<<<(unsigned)((rows + wpb - 1) / wpb), ROW_KERNEL_THREADS, 0, (cudaStream_t)stream>>>(
+        x, ldx, rows, (int)d, (int)dpad, inv_norm, out, ldo);
+    MECLIP_CUDA(cudaGetLastError());
+    return MECLIP_OK;
+}
+
+int meclip_sum_exp_tf32(int kind, const float* x_f32, const float* y_f32, int64_t rows, int64_t cols, int64_t d,
+                        int64_t ldx, int64_t ldy, float temperature, int64_t row_off, int64_t col_off, float* row_sum,
+                        float* col_sum, float* diag_s, unsigned int* tile_counter, int* status, void* stream) {
+    const DeviceScalars ds = take_scalars();
+    NvtxRange range("meclip_sum_exp_tf32");
+    return sum_exp_impl(kind, x_f32, y_f32, rows, cols, d, ldx, ldy, temperature, row_off, col_off, row_sum, col_sum,
+                        diag_s, tile_counter, status, stream, ds, nullptr, 0, true);
+}
+
 size_t meclip_sum_exp_det_workspace_bytes(int64_t rows, int64_t cols) {
     if (rows < 1 || cols < 1) return 0;
     return det_layout(rows, cols).total;
@@ -1413,8 +1479,13 @@ static int grad_impl(int kind, const void* x_bf16, const void* y_bf16, int64_t r
                      void* dy, int dy_mode, int64_t lddy, void* workspace, size_t workspace_bytes, int* status,
                      cudaStream_t s0, bool overlap, bool transposed_copies, float* sg_acc = nullptr,
                      float logit_scale = 0.f, float logit_bias = 0.f, int64_t n_extra = 0, bool plain_e = false,
-                     const DeviceScalars& ds = DeviceScalars(), bool honour_overrides = true) {
+                     const DeviceScalars& ds = DeviceScalars(), bool honour_overrides = true,
+                     const float* x_f32 = nullptr, int64_t ldxf = 0, const float* y_f32 = nullptr, int64_t ldyf = 0) {
+    // x_f32 / y_f32: optional fp32 copies of the operands; the coefficient pass then forms S from them with tf32
+    // MMAs (the contractions keep the bf16 operands)
     NvtxRange range("meclip_grad");
+    if ((x_f32 == nullptr) != (y_f32 == nullptr) || (x_f32 != nullptr && (ldxf < d || ldyf < d)))
+        return fail(MECLIP_EINVAL, "grad: fp32 operands come as a pair with pitches >= d");
     // kind MECLIP_SIGLIP: `temperature` is unused, the element function is sigmoid(logit_scale * s + logit_bias),
     // there are no row / column sums and both inputs get a gradient
     // plain_e (LiT only): the panel holds E itself (no 1/r, no diagonal term) and the contraction runs over
@@ -1532,6 +1603,10 @@ static int grad_impl(int kind, const void* x_bf16, const void* y_bf16, int64_t r
                 p.tile_counter = counters + 3 * t;
                 p.status = status;
                 Operand a{X + r0 * ldx, ldx, false}, b{Y + c0 * ldy, ldy, false};
+                if (x_f32 != nullptr) {
+                    a = Operand{x_f32 + r0 * ldxf, ldxf, false, 0, true};
+                    b = Operand{y_f32 + c0 * ldyf, ldyf, false, 0, true};
+                }
                 t_tag = TAG_COEF;
                 rc = launch_gemm(EPI_COEF, a, b, nr, nc, d, pick_bn(nc), p, s0, gpanel[gb], plan.row_block, plan.ldg / 64);
                 if (rc) return rc;
@@ -1645,6 +1720,19 @@ int meclip_grad_t(int kind, const void* x_bf16, const void* y_bf16, int64_t rows
     return grad_impl(kind, x_bf16, y_bf16, rows, cols, d, ldx, ldy, temperature, row_off, col_off, row_sum, col_sum,
                      grad_out, grad_scale, dx, dx_mode, lddx, dy, dy_mode, lddy, workspace, workspace_bytes, status,
                      (cudaStream_t)stream, overlap_allowed(), transposes_allowed(), sum_g_s, 0.f, 0.f, 0, false, ds);
+}
+
+int meclip_grad_tf32(int kind, const void* x_bf16, const void* y_bf16, const float* x_f32, int64_t ldxf,
+                     const float* y_f32, int64_t ldyf, int64_t rows, int64_t cols, int64_t d, int64_t ldx, int64_t ldy,
+                     float temperature, int64_t row_off, int64_t col_off, const float* row_sum, const float* col_sum,
+                     const float* grad_out, float grad_scale, void* dx, int dx_mode, int64_t lddx, void* dy, int dy_mode,
+                     int64_t lddy, void* workspace, size_t workspace_bytes, int* status, void* stream) {
+    const DeviceScalars ds = take_scalars();
+    if (x_f32 == nullptr || y_f32 == nullptr) return fail(MECLIP_EINVAL, "grad_tf32: fp32 operands are null");
+    return grad_impl(kind, x_bf16, y_bf16, rows, cols, d, ldx, ldy, temperature, row_off, col_off, row_sum, col_sum,
+                     grad_out, grad_scale, dx, dx_mode, lddx, dy, dy_mode, lddy, workspace, workspace_bytes, status,
+                     (cudaStream_t)stream, overlap_allowed(), transposes_allowed(), nullptr, 0.f, 0.f, 0, false, ds, true,
+                     x_f32, ldxf, y_f32, ldyf);
 }
 
 // ---- LiT forward that already holds the gradient's contraction ------------------------------------

@@ -28,7 +28,9 @@ static constexpr int PAIR_BM = 256;
 
 // A_MODE: 0 = A is K-major, 1 = A is MN-major, 2 = two contractions in one launch (GemmParams::dual): the first
 // problem reads A MN-major through tmap_a / tmap_b, the second one K-major through tmap_c (its A) / tmap_d (its B).
-template <int EPI, int A_MODE>
+// TF32: A and B are fp32 matrices (both K-major) whose elements the tensor cores read as tf32; a K step is still
+// 128 bytes per row (32 elements instead of 64), so stages, descriptors and barriers are those of the bf16 kernel.
+template <int EPI, int A_MODE, bool TF32 = false>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
 umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                       const __grid_constant__ CUtensorMap tmap_c, const __grid_constant__ CUtensorMap tmap_d,
@@ -133,7 +135,7 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
                     if (rank == 0) mbar_expect_tx(full_local, 2u * tx_per_cta);
                     const uint32_t sa = smem_base + (uint32_t)stage * (uint32_t)p.stage_bytes;
                     const uint32_t sb = sa + A_STAGE_BYTES;
-                    const int k0 = ks * BK;
+                    const int k0 = ks * (TF32 ? BK / 2 : BK);       // in elements
                     if (p.a_blocked) {
                         if (a_mn) {
                             tma_load_3d_pair(sa, ta, full, 0, k0, m0 >> 6);
@@ -207,7 +209,8 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
                         for (int kk = 0; kk < BK / 16; ++kk) {
                             const uint64_t ad = umma_smem_desc(sa + kk * A_KSTEP, A_LBO, 1024);
                             const uint64_t bd = umma_smem_desc(sb + kk * 32, 16, 1024);
-                            umma_bf16_pair(tmem_d, ad, bd, idesc, (ks | kk) != 0 ? 1u : 0u);
+                            if (TF32) umma_tf32_pair(tmem_d, ad, bd, idesc, (ks | kk) != 0 ? 1u : 0u);
+                            else      umma_bf16_pair(tmem_d, ad, bd, idesc, (ks | kk) != 0 ? 1u : 0u);
                             if (idesc2 != 0u) {
                                 const uint64_t bd2 = umma_smem_desc(sb + b2_off + kk * 32, 16, 1024);
                                 umma_bf16_pair(tmem_d + MAX_BN, ad, bd2, idesc2, (ks | kk) != 0 ? 1u : 0u);

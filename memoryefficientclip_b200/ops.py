@@ -5,12 +5,18 @@ device memory and streams only; no arithmetic of the loss path happens in torch.
 from __future__ import annotations
 
 import math
+import os
 
 import torch
 
 from . import _lib
 
 _DT = {torch.bfloat16: _lib.BF16, torch.float32: _lib.F32, torch.float16: _lib.F16}
+
+
+# MECLIP_TF32=1 (or ops.TF32_OPERANDS = True): fp32 module inputs keep fp32 operands for the two passes that form
+# S = X Y^T, multiplied as tf32 like the reference's tl.dot (clip_loss.py:53); default: bf16 operands
+TF32_OPERANDS = os.environ.get("MECLIP_TF32", "0") == "1"
 
 
 def _ptr(t):
@@ -282,11 +288,40 @@ def loss_finalize(kind, row_sum, col_sum, diag_s, temperature, scale, loss_out, 
                                                     loss_out.data_ptr(), _stream(row_sum)))
 
 
-def loss_forward(kind, x_hat, y_hat, temperature, status=None, deterministic=None):
-    """Returns (loss 0-dim fp32, row_sum, col_sum or None, diag_s)."""
+def operand_f32(x: torch.Tensor, inv_norm=None) -> torch.Tensor:
+    """The fp32 operand of the tf32 passes: x * inv_norm (or x itself) with round_up(d, 8) columns, zero padded."""
+    assert x.dtype == torch.float32 and x.dim() == 2 and x.stride(1) == 1
+    rows, d = x.shape
+    dpad = (d + 7) // 8 * 8
+    out = torch.empty(rows, dpad, dtype=torch.float32, device=x.device)
+    with _on_device(x.device):
+        _lib.check(_lib.load().meclip_operand_f32(x.data_ptr(), rows, d, x.stride(0), _ptr(inv_norm), out.data_ptr(),
+                                                  dpad, _stream(x)))
+    return out
+
+
+def loss_forward(kind, x_hat, y_hat, temperature, status=None, deterministic=None, f32_operands=None):
+    """Returns (loss 0-dim fp32, row_sum, col_sum or None, diag_s).
+    f32_operands: optional (x fp32, y fp32) of the same padded shape; S is then formed with tf32 MMAs."""
     b, d = x_hat.shape
     assert y_hat.shape == x_hat.shape
     dev = x_hat.device
+    if f32_operands is not None:
+        x32, y32 = f32_operands
+        assert x32.shape == x_hat.shape and y32.shape == y_hat.shape and x32.dtype == y32.dtype == torch.float32
+        row_sum = torch.zeros(b, dtype=torch.float32, device=dev)
+        col_sum = torch.zeros(b, dtype=torch.float32, device=dev) if kind == _lib.CLIP else None
+        diag_s = torch.zeros(b, dtype=torch.float32, device=dev)
+        loss = torch.empty((), dtype=torch.float32, device=dev)
+        counter = torch.zeros(1, dtype=torch.int32, device=dev)
+        with _on_device(dev):
+            t, _b, _keep = _bind(temperature, dev)
+            _lib.check(_lib.load().meclip_sum_exp_tf32(kind, x32.data_ptr(), y32.data_ptr(), b, b, d, x32.stride(0),
+                                                       y32.stride(0), t, 0, 0, row_sum.data_ptr(), _ptr(col_sum),
+                                                       diag_s.data_ptr(), counter.data_ptr(), _ptr(status),
+                                                       _stream(x_hat)))
+        loss_finalize(kind, row_sum, col_sum, diag_s, temperature, 1.0 / b, loss)
+        return loss, row_sum, col_sum, diag_s
     if DETERMINISTIC if deterministic is None else deterministic:
         row_sum = torch.zeros(b, dtype=torch.float32, device=dev)
         col_sum = torch.zeros(b, dtype=torch.float32, device=dev) if kind == _lib.CLIP else None
@@ -356,7 +391,7 @@ def grad_block_static(kind, x_hat, y_hat, temperature, row_sum, col_sum, grad_ou
 
 
 def loss_backward(kind, x_hat, y_hat, temperature, row_sum, col_sum, grad_out, grad_scale, dx_dtype, dy_dtype,
-                  status=None, sum_g_s=None, need_dx=True, need_dy=True, scale_rule=GSCALE_FIXED):
+                  status=None, sum_g_s=None, need_dx=True, need_dy=True, scale_rule=GSCALE_FIXED, f32_operands=None):
     """Whole-batch backward on one GPU.  Returns (dx, dy) w.r.t. the normalised operands; an output
     that is not needed (frozen tower, or the second argument of LiT) is None and its contraction is skipped.
     sum_g_s: optional zeroed fp32 scalar that receives sum_ij G_ij S_ij (temperature gradient)."""
@@ -368,6 +403,19 @@ def loss_backward(kind, x_hat, y_hat, temperature, row_sum, col_sum, grad_out, g
     dx = torch.empty(b, d, dtype=dx_dtype, device=dev) if need_dx else None
     dy = torch.empty(b, d, dtype=dy_dtype, device=dev) if need_dy else None
     ws = grad_workspace(b, b, d, dev)
+    if f32_operands is not None:
+        assert sum_g_s is None, "the tf32 route has no temperature gradient"
+        x32, y32 = f32_operands
+        with _on_device(dev):
+            t, _b, _keep = _bind(temperature, dev, scale_rule)
+            _lib.check(_lib.load().meclip_grad_tf32(kind, x_hat.data_ptr(), y_hat.data_ptr(), x32.data_ptr(),
+                                                    x32.stride(0), y32.data_ptr(), y32.stride(0), b, b, d,
+                                                    x_hat.stride(0), y_hat.stride(0), t, 0, 0, row_sum.data_ptr(),
+                                                    _ptr(col_sum), _ptr(grad_out), float(grad_scale), _ptr(dx),
+                                                    _MODE[dx_dtype], d, _ptr(dy),
+                                                    _MODE[dy_dtype] if dy is not None else 0, d, ws.data_ptr(),
+                                                    ws.numel(), _ptr(status), _stream(x_hat)))
+        return dx, dy
     if sum_g_s is not None:
         with _on_device(dev):
             t, _b, _keep = _bind(temperature, dev, scale_rule)
