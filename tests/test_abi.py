@@ -80,6 +80,11 @@ def test_bad_arguments_return_error_codes(lib):
         assert lib.meclip_ring_sum_exp(ctypes.byref(bad), 0, fake, 0.07, fake, fake, fake, fake, None) == _lib.EINVAL
         assert lib.meclip_ring_grad(ctypes.byref(bad), 0, fake, 0.07, fake, fake, None, 1.0, fake, 8, fake, fake, fake,
                                     None, fake, 0, None) == _lib.EINVAL
+    import torch
+    if not torch.cuda.is_available():
+        # a well-formed descriptor passes the argument checks (every field is read where the C struct has it) and
+        # fails only at the first CUDA call; never tried where a GPU could run the fake pointers
+        assert lib.meclip_ring_sum_exp(ctypes.byref(desc()), 0, fake, 0.07, fake, fake, fake, fake, None) == _lib.ECUDA
     shards[1] = None                                     # a peer's shard is not mapped
     assert lib.meclip_ring_sum_exp(ctypes.byref(desc()), 0, fake, 0.07, fake, fake, fake, fake, None) == _lib.EINVAL
     shards[1] = 0x2000
