@@ -164,6 +164,19 @@ def lit_closed_form(xn, yn, temperature=0.07, stable=False, grad_output=1.0):
     return {"loss": loss, "row_sum": r, "dx": dx}
 
 
+def round_tf32(x):
+    """fp32 values rounded to the nearest tf32 (10 explicit mantissa bits, ties away from zero: what the PTX
+    conversion cvt.rna.tf32.f32 does), returned as fp32 whose 13 low mantissa bits are zero.  This is the operand
+    precision of tl.dot on fp32 inputs in the reference (clip_loss.py:53, :113; Triton's default tf32 input
+    precision).  Accepts a numpy array or a torch tensor; finite values only."""
+    is_torch = isinstance(x, torch.Tensor)
+    a = (x.detach().cpu().float().numpy() if is_torch else np.asarray(x, dtype=np.float32)).copy()
+    bits = a.view(np.uint32)
+    bits += np.uint32(0x1000)              # half a tf32 unit in the last place, added to the magnitude
+    bits &= np.uint32(0xFFFFE000)
+    return torch.from_numpy(a) if is_torch else a
+
+
 def normalize_np(x: np.ndarray, eps: float = 1e-12):
     """F.normalize(dim=1): x / max(||x||, eps).  Returns (x_hat, 1/max(||x||, eps))."""
     x = np.asarray(x, dtype=np.float64)

@@ -109,3 +109,18 @@ def test_streaming_matches_dense():
     loss, gx = dense.lit_dense(x, y, 0.07, True)
     assert dense.loss_rel_err(s["loss"], loss) < 1e-6
     assert dense.grad_errors(s["dx_rows"], gx[rows])[0] < 1e-5
+
+
+def test_round_tf32_is_nearest_with_ten_mantissa_bits():
+    rng = np.random.default_rng(5)
+    x = (rng.standard_normal(20000) * np.exp(rng.uniform(-20, 20, 20000))).astype(np.float32)
+    r = dense.round_tf32(x)
+    assert r.dtype == np.float32 and np.all((r.view(np.uint32) & 0x1FFF) == 0)          # low 13 bits clear
+    assert np.array_equal(dense.round_tf32(r), r)                                       # idempotent
+    rel = np.abs(r.astype(np.float64) - x.astype(np.float64)) / np.abs(x.astype(np.float64))
+    assert rel.max() <= 2.0 ** -11 * (1 + 1e-6)                                         # at most half a unit
+    # known values: 1 + 2^-11 is a tie and goes away from zero; just below it rounds down
+    one = np.array([1.0 + 2.0 ** -11, 1.0 + 2.0 ** -11 - 2.0 ** -23, -(1.0 + 2.0 ** -11)], dtype=np.float32)
+    assert np.array_equal(dense.round_tf32(one), np.array([1.0 + 2.0 ** -10, 1.0, -(1.0 + 2.0 ** -10)], dtype=np.float32))
+    t = torch.from_numpy(x)
+    assert torch.equal(dense.round_tf32(t), torch.from_numpy(r))

@@ -85,3 +85,39 @@ def test_tf32_entry_points_reject_bad_operands():
     assert lib.meclip_sum_exp_tf32(*args(x.data_ptr() + 4, 72)) == _lib.EINVAL      # not 16-byte aligned
     assert lib.meclip_sum_exp_tf32(*args(None, 72)) == _lib.EINVAL
     assert lib.meclip_sum_exp_tf32(*args(x.data_ptr(), 70)) == _lib.EINVAL          # pitch below d
+
+
+def test_operand_f32_is_the_oracles_tf32_rounding_bit_for_bit():
+    from memoryefficientclip_b200 import ops
+    g = torch.Generator().manual_seed(21)
+    x = torch.randn(300, 200, generator=g) * torch.exp(4 * torch.randn(300, 1, generator=g))
+    xg = x.cuda()
+    plain = ops.operand_f32(xg).cpu()
+    assert plain.shape == (300, 200) and torch.equal(plain, dense.round_tf32(x))
+    _x16, inv = ops.normalize_fwd(xg, True)
+    scaled = ops.operand_f32(xg, inv).cpu()
+    assert torch.equal(scaled, dense.round_tf32(x * inv.cpu()[:, None]))
+    odd = torch.randn(64, 13, generator=g)                     # pad columns are zero
+    out = ops.operand_f32(odd.cuda()).cpu()
+    assert out.shape == (64, 16) and torch.equal(out[:, :13], dense.round_tf32(odd)) and not out[:, 13:].any()
+
+
+def test_tf32_sums_equal_fp64_sums_of_the_rounded_operands():
+    """With operands already in tf32 the products are exact and the accumulation is fp32: the row sums, the column
+    sums and the diagonal agree with fp64 arithmetic on the SAME rounded values to fp32 accuracy, far inside what
+    any coarser operand format could reach (bf16 operands are off by 1e-2 here)."""
+    from memoryefficientclip_b200 import _lib, ops
+    b, d, t = 1536, 640, 0.03
+    x, y = _inputs(b, d, 17, True)
+    xg, yg = x.cuda(), y.cuda()
+    x32, y32 = ops.operand_f32(xg), ops.operand_f32(yg)
+    x16, _ = ops.normalize_fwd(xg, False)
+    y16, _ = ops.normalize_fwd(yg, False)
+    _l, r, c, diag = ops.loss_forward(_lib.CLIP, x16, y16, t, f32_operands=(x32, y32))
+    torch.cuda.synchronize()
+    xr, yr = dense.round_tf32(x).double(), dense.round_tf32(y).double()
+    s = xr @ yr.t()
+    e = torch.exp((s - 1.0) / t)
+    torch.testing.assert_close(diag.cpu().double(), s.diagonal(), rtol=0, atol=2e-6)
+    torch.testing.assert_close(r.cpu().double(), e.sum(1), rtol=2e-4, atol=0)
+    torch.testing.assert_close(c.cpu().double(), e.sum(0), rtol=2e-4, atol=0)
