@@ -103,9 +103,9 @@ def test_operand_f32_is_the_oracles_tf32_rounding_bit_for_bit():
 
 
 def test_tf32_sums_equal_fp64_sums_of_the_rounded_operands():
-    """With operands already in tf32 the products are exact and the accumulation is fp32: the row sums, the column
-    sums and the diagonal agree with fp64 arithmetic on the SAME rounded values to fp32 accuracy, far inside what
-    any coarser operand format could reach (bf16 operands are off by 1e-2 here)."""
+    """With operands already in tf32 the products are exact and only the tensor cores' fp32 accumulation (which
+    truncates: a few 1e-6 on s over 640 terms, i.e. 1e-4 on E at T = 0.03) separates the result from fp64
+    arithmetic on the SAME rounded values: far inside what operand rounding itself costs (1e-3 on s for tf32)."""
     from memoryefficientclip_b200 import _lib, ops
     b, d, t = 1536, 640, 0.03
     x, y = _inputs(b, d, 17, True)
@@ -118,6 +118,6 @@ def test_tf32_sums_equal_fp64_sums_of_the_rounded_operands():
     xr, yr = dense.round_tf32(x).double(), dense.round_tf32(y).double()
     s = xr @ yr.t()
     e = torch.exp((s - 1.0) / t)
-    torch.testing.assert_close(diag.cpu().double(), s.diagonal(), rtol=0, atol=2e-6)
-    torch.testing.assert_close(r.cpu().double(), e.sum(1), rtol=2e-4, atol=0)
-    torch.testing.assert_close(c.cpu().double(), e.sum(0), rtol=2e-4, atol=0)
+    torch.testing.assert_close(diag.cpu().double(), s.diagonal(), rtol=0, atol=1e-5)
+    torch.testing.assert_close(r.cpu().double(), e.sum(1), rtol=1e-3, atol=0)
+    torch.testing.assert_close(c.cpu().double(), e.sum(0), rtol=1e-3, atol=0)
