@@ -71,9 +71,9 @@ def _map_everywhere(local: torch.Tensor, group, rank: int, world: int, device):
     except _lib.MeclipError:
         ok = False                       # e.g. a rank on another node: its memory cannot be mapped here
     # all ranks must agree on the transport: one that could not map a peer sends everyone back to send/recv
-    verdicts = [None] * world
-    dist.all_gather_object(verdicts, ok, group=group)
-    return addr, all(verdicts)
+    answers = [None] * world
+    dist.all_gather_object(answers, ok, group=group)
+    return addr, all(answers)
 
 
 class PeerShards:

@@ -614,17 +614,17 @@ static int sm_count() {
 // driver-API entry point and fails with "invalid context" on a thread that has made no runtime
 // call yet (PyTorch's autograd thread on its first backward).
 static int check_device() {
-    static int verdict[64] = {0};   // 0 unknown, 1 ok, -1 unsupported
+    static int supported[64] = {0};   // 0 unknown, 1 ok, -1 unsupported
     int dev = 0;
     MECLIP_CUDA(cudaGetDevice(&dev));
     MECLIP_CUDA(cudaSetDevice(dev));
     if (dev < 0 || dev >= 64) return fail(MECLIP_EUNSUPPORTED, "device index %d out of range", dev);
-    if (verdict[dev] == 0) {
+    if (supported[dev] == 0) {
         int major = 0;
         MECLIP_CUDA(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev));
-        verdict[dev] = (major == 10) ? 1 : -1;
+        supported[dev] = (major == 10) ? 1 : -1;
     }
-    if (verdict[dev] < 0) return fail(MECLIP_EUNSUPPORTED, "device %d is not sm_100: these kernels are sm_100a only", dev);
+    if (supported[dev] < 0) return fail(MECLIP_EUNSUPPORTED, "device %d is not sm_100: these kernels are sm_100a only", dev);
     return MECLIP_OK;
 }
 

@@ -50,7 +50,7 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
 // Bounded wait.  Returns false when the limit ran out or another role of this
 // CTA already raised the abort flag; the caller then leaves its loop.
 // With watch_flag == false only the caller's own time limit ends the wait (used where
-// several warps must reach the same verdict about the same barrier phase).
+// several warps must reach the same decision about the same barrier phase).
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
                                           bool watch_flag = true, unsigned long long limit_ns = WAIT_LIMIT_NS) {
     if (mbar_try_wait(bar, parity)) return true;

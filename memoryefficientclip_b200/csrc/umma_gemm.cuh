@@ -421,7 +421,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         unsigned int ntrace = 0;
         epilogue_init<EPI>(p, st);
         while (true) {
-            // The eight warps wait on the same barrier phase and then agree on the verdict, so that
+            // The eight warps wait on the same barrier phase and then agree on the outcome, so that
             // they always leave the tile loop (and its named barriers) together.
             bool ok = mbar_wait(smem_u32(&tail->sched_full_bar[slot]), sphase, abort_flag, false, wl);
             int tile = -1;

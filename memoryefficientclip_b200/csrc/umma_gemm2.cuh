@@ -243,7 +243,7 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
         epilogue_init<EPI>(p, st);
         const uint32_t sched_free0 = mapa_u32(smem_u32(&tail->sched_empty_bar[0]), 0);     // the leader's ring
         while (true) {
-            // as in the single-CTA kernel the eight warps reach one verdict per wait and leave together
+            // as in the single-CTA kernel the eight warps reach one decision per wait and leave together
             bool ok = mbar_wait_cluster(smem_u32(&tail->sched_full_bar[slot]), sphase, abort_flag, false, wl);
             const int tile = ok ? tail->sched_tile[slot] : -1;
             __syncwarp();
